@@ -1,0 +1,87 @@
+// Shared helpers for the sm_100a kernels of this library.
+//
+// Every exported entry point is `extern "C"`, takes raw device pointers, sizes and a
+// CUDA stream, launches on that stream without synchronising, and returns 0 or an
+// error code from the table below.  Nothing here allocates.  The reference launches
+// its kernels the same stream-ordered way (src/compute/ComputeOps.hpp:39-41) and
+// range-checks kernel arguments on the host before launch
+// (src/compute/cuda/GpuOps.cpp:40-47).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MM_OK 0
+#define MM_ERR_BAD_ARG 1       // a size or combination the kernel refuses
+#define MM_ERR_UNSUPPORTED 2   // valid in principle, not built for this shape/dtype
+#define MM_ERR_LAUNCH 3        // cudaGetLastError() after the launch was not success
+#define MM_ERR_DRIVER 4        // a driver entry point (tensor map encode) failed
+
+// dtype codes shared with the Python binding
+#define MM_F32 0
+#define MM_BF16 1
+
+#define MM_EXPORT extern "C" __attribute__((visibility("default")))
+
+#define MM_CHECK_LAUNCH()                                  \
+    do {                                                   \
+        cudaError_t e__ = cudaGetLastError();              \
+        if (e__ != cudaSuccess) {                          \
+            mm_set_last_error(cudaGetErrorString(e__));    \
+            return MM_ERR_LAUNCH;                          \
+        }                                                  \
+    } while (0)
+
+#define MM_REQUIRE(cond, msg)          \
+    do {                               \
+        if (!(cond)) {                 \
+            mm_set_last_error(msg);    \
+            return MM_ERR_BAD_ARG;     \
+        }                              \
+    } while (0)
+
+void mm_set_last_error(const char* msg);
+
+// ---- element conversion ------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// ---- reductions --------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum in a fixed order (lane tree, then warp 0 over the warp partials), so a
+// row's result never depends on what else is in the batch.  `scratch` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarps) ? scratch[lane] : 0.0f;
+    t = warp_sum(t);
+    return t;
+}
+
+static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }

@@ -1,0 +1,341 @@
+// Memory-bound parts of a step: embedding gather, residual-add + RMSNorm, SiLU·up,
+// and bias + rotary position encoding + paged K/V write.  All arithmetic is fp32;
+// the template type is only what is stored.
+//
+// Formulas (reference, file:line):
+//   embedding   x[t,:] = E[id_t,:], an id outside [0,V) gives a zero row
+//               (src/compute/Embedding.cpp:46-67)
+//   RMSNorm     y = x * w * (1 / sqrt(mean(x^2) + eps))      (src/compute/Norm.cpp:21-37)
+//   add+norm    x += delta, then RMSNorm of the sum          (kernels/cuda/common/add_rmsnorm.cu:32-81)
+//   SiLU·up     a = g / (1 + exp(-g)) * u                     (src/compute/Activations.cpp:25-36,
+//                                                             kernels/cuda/common/silu_mul.cu:37-41)
+//   rotary      pairs (i, i+half): theta = pos * base^(-2i/dim)
+//               x'_i = x_i cos - x_{i+half} sin, x'_{i+half} = x_i sin + x_{i+half} cos
+//               (src/compute/Rope.cpp:23-41), applied to q and k after the bias
+//               (src/runtime/arch/Qwen2Backend.cpp:316-325, 369-375)
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// embedding
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ out, int vocab, int d, float scale) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * d;
+    if (id < 0 || id >= vocab) {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = 0.0f;
+        return;
+    }
+    const T* row = table + (size_t)id * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32<T>(row[i]) * scale;
+}
+
+MM_EXPORT int mm_embedding(const void* ids, const void* table, int table_dtype, void* out, int n_tokens,
+                           int vocab, int d, float scale, void* stream) {
+    MM_REQUIRE(n_tokens >= 0 && vocab > 0 && d > 0, "embedding: bad sizes");
+    if (n_tokens == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = d >= 1024 ? 256 : 128;
+    if (table_dtype == MM_F32)
+        embedding_kernel<float><<<n_tokens, threads, 0, s>>>((const int32_t*)ids, (const float*)table, (float*)out, vocab, d, scale);
+    else if (table_dtype == MM_BF16)
+        embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>((const int32_t*)ids, (const __nv_bfloat16*)table, (float*)out, vocab, d, scale);
+    else
+        MM_REQUIRE(false, "embedding: table dtype must be float32 or bfloat16");
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// ---------------------------------------------------------------------------
+// residual add + RMSNorm
+//   residual: fp32 [*, d]; delta: T [*, d] or null; rows: int32 [n_rows] or null.
+//   Output row i is made from source row r = rows ? rows[i] : i.
+//   Without `rows` the sum is written back to the residual (it stays the running
+//   residual stream); with `rows` (a gather for the output head) it is not.
+// ---------------------------------------------------------------------------
+template <typename T, typename WT>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                   const int32_t* __restrict__ rows, const WT* __restrict__ weight,
+                                   T* __restrict__ out, int d, float eps) {
+    extern __shared__ float row_cache[];
+    __shared__ float red[32];
+    const int i = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    float* res = residual + r * d;
+    const T* dl = delta ? delta + r * d : nullptr;
+    float ss = 0.0f;
+    for (int k = threadIdx.x; k < d; k += blockDim.x) {
+        float v = res[k];
+        if (dl) v += to_f32<T>(dl[k]);
+        row_cache[k] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float total = block_sum(ss, red);
+    const float inv_rms = 1.0f / sqrtf(total / (float)d + eps);
+    T* o = out + (size_t)i * d;
+    const bool write_back = (rows == nullptr) && (dl != nullptr);
+    for (int k = threadIdx.x; k < d; k += blockDim.x) {
+        const float v = row_cache[k];
+        if (write_back) res[k] = v;
+        o[k] = from_f32<T>(v * to_f32<WT>(weight[k]) * inv_rms);
+    }
+}
+
+template <typename T, typename WT>
+static int launch_add_rmsnorm(float* residual, const void* delta, const int32_t* rows, const void* weight, void* out,
+                              int n_rows, int d, float eps, cudaStream_t s) {
+    const size_t smem = (size_t)d * sizeof(float);
+    if (smem > 48 * 1024) {
+        if (smem > 200 * 1024) {
+            mm_set_last_error("rmsnorm: width above 51200 is not supported");
+            return MM_ERR_UNSUPPORTED;
+        }
+        cudaFuncSetAttribute(add_rmsnorm_kernel<T, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+    add_rmsnorm_kernel<T, WT><<<n_rows, threads, smem, s>>>(residual, (const T*)delta, rows, (const WT*)weight, (T*)out, d, eps);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+MM_EXPORT int mm_add_rmsnorm(void* residual, const void* delta, const void* rows, const void* weight, int weight_dtype,
+                             void* out, int act_dtype, int n_rows, int d, float eps, void* stream) {
+    MM_REQUIRE(n_rows >= 0 && d > 0 && eps > 0.0f, "rmsnorm: bad sizes");
+    if (n_rows == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    float* res = (float*)residual;
+    const int32_t* rw = (const int32_t*)rows;
+    if (act_dtype == MM_F32 && weight_dtype == MM_F32) return launch_add_rmsnorm<float, float>(res, delta, rw, weight, out, n_rows, d, eps, s);
+    if (act_dtype == MM_F32 && weight_dtype == MM_BF16) return launch_add_rmsnorm<float, __nv_bfloat16>(res, delta, rw, weight, out, n_rows, d, eps, s);
+    if (act_dtype == MM_BF16 && weight_dtype == MM_F32) return launch_add_rmsnorm<__nv_bfloat16, float>(res, delta, rw, weight, out, n_rows, d, eps, s);
+    if (act_dtype == MM_BF16 && weight_dtype == MM_BF16) return launch_add_rmsnorm<__nv_bfloat16, __nv_bfloat16>(res, delta, rw, weight, out, n_rows, d, eps, s);
+    MM_REQUIRE(false, "rmsnorm: dtypes must be float32 or bfloat16");
+}
+
+// residual += delta only (the last layer's pending sum when no norm follows it)
+template <typename T>
+__global__ void add_residual_kernel(float* __restrict__ residual, const T* __restrict__ delta, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) residual[i] += to_f32<T>(delta[i]);
+}
+
+MM_EXPORT int mm_add_residual(void* residual, const void* delta, int act_dtype, long long n, void* stream) {
+    MM_REQUIRE(n >= 0, "add_residual: bad size");
+    if (n == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (act_dtype == MM_F32) add_residual_kernel<float><<<blocks, 256, 0, s>>>((float*)residual, (const float*)delta, (size_t)n);
+    else if (act_dtype == MM_BF16) add_residual_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((float*)residual, (const __nv_bfloat16*)delta, (size_t)n);
+    else MM_REQUIRE(false, "add_residual: dtype must be float32 or bfloat16");
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// ---------------------------------------------------------------------------
+// SiLU(gate) * up over a [n, 2F] buffer holding gate in columns [0,F) and up in [F,2F)
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int F) {
+    const size_t total = (size_t)n * F;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const size_t row = i / F, col = i - row * F;
+        const float g = to_f32<T>(gu[row * 2 * F + col]);
+        const float u = to_f32<T>(gu[row * 2 * F + F + col]);
+        out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+// 8 bf16 values per thread when F is a multiple of 8
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int n, int F) {
+    const int F8 = F / 8;
+    const size_t total = (size_t)n * F8;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const size_t row = i / F8, c8 = i - row * F8;
+        const uint4 gv = *reinterpret_cast<const uint4*>(gu + row * 2 * F + c8 * 8);
+        const uint4 uv = *reinterpret_cast<const uint4*>(gu + row * 2 * F + F + c8 * 8);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+        const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+        uint4 ov;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 g = __bfloat1622float2(g2[k]);
+            const float2 u = __bfloat1622float2(u2[k]);
+            float2 r;
+            r.x = g.x / (1.0f + expf(-g.x)) * u.x;
+            r.y = g.y / (1.0f + expf(-g.y)) * u.y;
+            o2[k] = __float22bfloat162_rn(r);
+        }
+        *reinterpret_cast<uint4*>(out + row * F + c8 * 8) = ov;
+    }
+}
+
+MM_EXPORT int mm_silu_mul(const void* gu, void* out, int act_dtype, int n, int F, void* stream) {
+    MM_REQUIRE(n >= 0 && F > 0, "silu_mul: bad sizes");
+    if (n == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)n * F;
+    if (act_dtype == MM_BF16 && F % 8 == 0) {
+        const size_t work = total / 8;
+        const int blocks = (int)((work + 255) / 256 < 148 * 32 ? (work + 255) / 256 : 148 * 32);
+        silu_mul_bf16x8_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F);
+    } else {
+        const int blocks = (int)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
+        if (act_dtype == MM_F32) silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, n, F);
+        else if (act_dtype == MM_BF16) silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F);
+        else MM_REQUIRE(false, "silu_mul: dtype must be float32 or bfloat16");
+    }
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// ---------------------------------------------------------------------------
+// bias + rotary + paged K/V write
+//   qkv      T [n, (H + 2G) * hd]  : q heads, then k heads, then v heads of each token
+//   bias     WT [(H + 2G) * hd] or null
+//   q_out    T [n, H * hd]
+//   k_pages, v_pages  T [num_pages, G, page_size, hd] of this layer (null: nothing cached)
+//   positions int32 [n], token_req int32 [n], block_table int32 [n_req, table_width]
+//   rotary_dim: leading dims of each head that are rotated (0: no position encoding)
+// ---------------------------------------------------------------------------
+template <typename T, typename WT>
+__global__ void qkv_rope_kvwrite_kernel(const T* __restrict__ qkv, const WT* __restrict__ bias, T* __restrict__ q_out,
+                                        T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                        const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req,
+                                        const int32_t* __restrict__ block_table, int table_width, int page_size,
+                                        int H, int G, int hd, int rotary_dim, float theta_base) {
+    extern __shared__ float cs[];  // cos[half], sin[half]
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = rotary_dim / 2;
+    float* cosv = cs;
+    float* sinv = cs + half;
+    if (half > 0) {
+        const float inv_dim = 1.0f / (float)rotary_dim;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float freq = powf(theta_base, -(float)(2 * i) * inv_dim);
+            const float ang = (float)pos * freq;
+            cosv[i] = cosf(ang);
+            sinv[i] = sinf(ang);
+        }
+    }
+    __syncthreads();
+
+    const int row_width = (H + 2 * G) * hd;
+    const T* src = qkv + (size_t)t * row_width;
+    // destination of this token's K/V rows
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (k_pages != nullptr) {
+        const int req = token_req[t];
+        const int page = block_table[(size_t)req * table_width + pos / page_size];
+        if (page >= 0) {
+            const size_t base = ((size_t)page * G * page_size + (size_t)(pos % page_size)) * hd;
+            kdst = k_pages + base;
+            vdst = v_pages + base;
+        }
+    }
+    const size_t head_stride_in_page = (size_t)page_size * hd;
+
+    // rotated part of q and k heads: one thread per (head, pair)
+    const int rot_heads = H + G;
+    for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
+        const int h = idx / half, i = idx - h * half;
+        const int c0 = h * hd + i, c1 = c0 + half;
+        float a = to_f32<T>(src[c0]), b = to_f32<T>(src[c1]);
+        if (bias) {
+            a += to_f32<WT>(bias[c0]);
+            b += to_f32<WT>(bias[c1]);
+        }
+        const float c = cosv[i], s = sinv[i];
+        const float ra = a * c - b * s;
+        const float rb = a * s + b * c;
+        if (h < H) {
+            T* q = q_out + (size_t)t * H * hd + (size_t)h * hd;
+            q[i] = from_f32<T>(ra);
+            q[i + half] = from_f32<T>(rb);
+        } else if (kdst) {
+            T* k = kdst + (size_t)(h - H) * head_stride_in_page;
+            k[i] = from_f32<T>(ra);
+            k[i + half] = from_f32<T>(rb);
+        }
+    }
+    // unrotated tail of q and k heads
+    const int tail = hd - rotary_dim;
+    if (tail > 0) {
+        for (int idx = threadIdx.x; idx < rot_heads * tail; idx += blockDim.x) {
+            const int h = idx / tail, i = rotary_dim + (idx - h * tail);
+            const int c0 = h * hd + i;
+            float a = to_f32<T>(src[c0]);
+            if (bias) a += to_f32<WT>(bias[c0]);
+            if (h < H) q_out[(size_t)t * H * hd + (size_t)h * hd + i] = from_f32<T>(a);
+            else if (kdst) kdst[(size_t)(h - H) * head_stride_in_page + i] = from_f32<T>(a);
+        }
+    }
+    // v heads
+    if (vdst) {
+        for (int idx = threadIdx.x; idx < G * hd; idx += blockDim.x) {
+            const int g = idx / hd, i = idx - g * hd;
+            const int c0 = (H + G) * hd + idx;
+            float a = to_f32<T>(src[c0]);
+            if (bias) a += to_f32<WT>(bias[c0]);
+            vdst[(size_t)g * head_stride_in_page + i] = from_f32<T>(a);
+        }
+    }
+}
+
+MM_EXPORT int mm_qkv_rope_kvwrite(const void* qkv, const void* bias, int bias_dtype, void* q_out, void* k_pages,
+                                  void* v_pages, int act_dtype, const void* positions, const void* token_req,
+                                  const void* block_table, int table_width, int page_size, int n_tokens, int H, int G,
+                                  int hd, int rotary_dim, float theta_base, void* stream) {
+    MM_REQUIRE(n_tokens >= 0 && H > 0 && G > 0 && hd > 0, "qkv_rope_kvwrite: bad sizes");
+    MM_REQUIRE(rotary_dim >= 0 && rotary_dim <= hd && rotary_dim % 2 == 0, "qkv_rope_kvwrite: rotary_dim must be even and at most head_dim");
+    MM_REQUIRE(page_size > 0 && table_width > 0, "qkv_rope_kvwrite: bad page geometry");
+    MM_REQUIRE((k_pages == nullptr) == (v_pages == nullptr), "qkv_rope_kvwrite: k and v pools must both be given or both be null");
+    if (n_tokens == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)rotary_dim * sizeof(float);
+    const int threads = 256;
+#define MM_LAUNCH_QKV(T, WT)                                                                                       \
+    qkv_rope_kvwrite_kernel<T, WT><<<n_tokens, threads, smem, s>>>(                                                \
+        (const T*)qkv, (const WT*)bias, (T*)q_out, (T*)k_pages, (T*)v_pages, (const int32_t*)positions,            \
+        (const int32_t*)token_req, (const int32_t*)block_table, table_width, page_size, H, G, hd, rotary_dim,      \
+        theta_base)
+    if (bias == nullptr) bias_dtype = MM_F32;
+    if (act_dtype == MM_F32 && bias_dtype == MM_F32) MM_LAUNCH_QKV(float, float);
+    else if (act_dtype == MM_F32 && bias_dtype == MM_BF16) MM_LAUNCH_QKV(float, __nv_bfloat16);
+    else if (act_dtype == MM_BF16 && bias_dtype == MM_F32) MM_LAUNCH_QKV(__nv_bfloat16, float);
+    else if (act_dtype == MM_BF16 && bias_dtype == MM_BF16) MM_LAUNCH_QKV(__nv_bfloat16, __nv_bfloat16);
+    else MM_REQUIRE(false, "qkv_rope_kvwrite: dtypes must be float32 or bfloat16");
+#undef MM_LAUNCH_QKV
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// ---------------------------------------------------------------------------
+// gather rows of a T [*, d] matrix: out[i,:] = src[rows[i],:]
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, const int32_t* __restrict__ rows, T* __restrict__ out, int d) {
+    const T* s = src + (size_t)rows[blockIdx.x] * d;
+    T* o = out + (size_t)blockIdx.x * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = s[i];
+}
+
+MM_EXPORT int mm_gather_rows(const void* src, const void* rows, void* out, int dtype, int n_rows, int d, void* stream) {
+    MM_REQUIRE(n_rows >= 0 && d > 0, "gather_rows: bad sizes");
+    if (n_rows == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == MM_F32) gather_rows_kernel<float><<<n_rows, 256, 0, s>>>((const float*)src, (const int32_t*)rows, (float*)out, d);
+    else if (dtype == MM_BF16) gather_rows_kernel<__nv_bfloat16><<<n_rows, 256, 0, s>>>((const __nv_bfloat16*)src, (const int32_t*)rows, (__nv_bfloat16*)out, d);
+    else MM_REQUIRE(false, "gather_rows: dtype must be float32 or bfloat16");
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}

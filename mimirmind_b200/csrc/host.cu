@@ -1,0 +1,11 @@
+// Host-side state of the kernel library: the last error message.
+#include <string.h>
+
+static thread_local char g_last_error[512] = "";
+
+void mm_set_last_error(const char* msg) {
+    strncpy(g_last_error, msg ? msg : "", sizeof(g_last_error) - 1);
+    g_last_error[sizeof(g_last_error) - 1] = 0;
+}
+
+extern "C" __attribute__((visibility("default"))) const char* mm_last_error() { return g_last_error; }

@@ -1,0 +1,240 @@
+"""Tensor-level wrappers of the kernel library.
+
+Each function checks devices, dtypes, shapes and contiguity on the host, then launches
+on the current CUDA stream.  torch is used for allocation and streams only; every
+operation here runs a kernel of this library.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import lib as _lib
+from .lib import KernelError, check
+
+F32, BF16 = 0, 1
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dt} is not supported by the kernels (float32 or bfloat16)")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, what: str, dtype: Optional[torch.dtype] = None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{what}: expected a CUDA tensor")
+    if not t.is_contiguous():
+        raise KernelError(f"{what}: tensor must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what}: expected {dtype}, got {t.dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[t,:] = table[ids[t],:] * scale as fp32; ids outside the table give zero rows."""
+    _need(ids, "embedding ids", torch.int32)
+    _need(table, "embedding table")
+    _need(out, "embedding out", torch.float32)
+    n, (v, d) = ids.numel(), table.shape
+    if out.shape != (n, d):
+        raise KernelError(f"embedding: out is {tuple(out.shape)}, expected {(n, d)}")
+    check(_lib.load().mm_embedding(ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), out.data_ptr(), n, v, d,
+                                   float(scale), _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual (fp32) += delta, out = rmsnorm(residual) * weight.  With ``rows`` output row i comes
+    from source row rows[i] and the residual is left untouched."""
+    _need(residual, "rmsnorm residual", torch.float32)
+    _need(weight, "rmsnorm weight")
+    _need(out, "rmsnorm out")
+    d = residual.shape[-1]
+    n_out = out.shape[0]
+    if weight.shape != (d,) or out.shape[-1] != d:
+        raise KernelError("rmsnorm: width mismatch")
+    if delta is not None:
+        _need(delta, "rmsnorm delta", out.dtype)
+        if delta.shape != residual.shape:
+            raise KernelError("rmsnorm: delta and residual differ in shape")
+    if rows is not None:
+        _need(rows, "rmsnorm rows", torch.int32)
+        if rows.numel() != n_out:
+            raise KernelError("rmsnorm: rows and out differ in length")
+    elif n_out != residual.shape[0]:
+        raise KernelError("rmsnorm: out and residual differ in rows")
+    check(_lib.load().mm_add_rmsnorm(residual.data_ptr(), _ptr(delta), _ptr(rows), weight.data_ptr(),
+                                     dtype_code(weight.dtype), out.data_ptr(), dtype_code(out.dtype), n_out, d,
+                                     float(eps), _stream()), "rmsnorm")
+    return out
+
+
+def add_residual(residual: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    _need(residual, "add_residual residual", torch.float32)
+    _need(delta, "add_residual delta")
+    if delta.shape != residual.shape:
+        raise KernelError("add_residual: shapes differ")
+    check(_lib.load().mm_add_residual(residual.data_ptr(), delta.data_ptr(), dtype_code(delta.dtype), residual.numel(),
+                                      _stream()), "add_residual")
+    return residual
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[n,f] = silu(gate_up[n,f]) * gate_up[n,F+f]."""
+    _need(gate_up, "silu_mul input")
+    _need(out, "silu_mul out", gate_up.dtype)
+    n, two_f = gate_up.shape
+    if two_f % 2 or out.shape != (n, two_f // 2):
+        raise KernelError("silu_mul: shapes do not match [n,2F] -> [n,F]")
+    check(_lib.load().mm_silu_mul(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n, two_f // 2, _stream()),
+          "silu_mul")
+    return out
+
+
+def qkv_rope_kvwrite(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                     k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], positions: torch.Tensor,
+                     token_req: torch.Tensor, block_table: torch.Tensor, page_size: int, num_heads: int,
+                     num_kv_heads: int, head_dim: int, rotary_dim: int, theta: float) -> None:
+    """Adds the bias, rotates q and k by position, writes q to ``q_out`` and k, v into their pages."""
+    _need(qkv, "qkv")
+    n = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape != (n, width):
+        raise KernelError(f"qkv: shape {tuple(qkv.shape)} is not [n, {width}]")
+    _need(q_out, "q_out", qkv.dtype)
+    if q_out.shape != (n, num_heads * head_dim):
+        raise KernelError("q_out: wrong shape")
+    if bias is not None:
+        _need(bias, "qkv bias")
+        if bias.shape != (width,):
+            raise KernelError("qkv bias: wrong shape")
+    if k_pages is not None:
+        for name, pool in (("k_pages", k_pages), ("v_pages", v_pages)):
+            _need(pool, name, qkv.dtype)
+            if pool.dim() != 4 or pool.shape[1:] != (num_kv_heads, page_size, head_dim):
+                raise KernelError(f"{name}: shape {tuple(pool.shape)} is not [pages, {num_kv_heads}, {page_size}, {head_dim}]")
+    _need(positions, "positions", torch.int32)
+    _need(token_req, "token_req", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    if block_table.dim() != 2:
+        raise KernelError("block_table: expected [requests, width]")
+    check(_lib.load().mm_qkv_rope_kvwrite(
+        qkv.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, q_out.data_ptr(),
+        _ptr(k_pages), _ptr(v_pages), dtype_code(qkv.dtype), positions.data_ptr(), token_req.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], page_size, n, num_heads, num_kv_heads, head_dim, rotary_dim,
+        float(theta), _stream()), "qkv_rope_kvwrite")
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    _need(src, "gather src")
+    _need(rows, "gather rows", torch.int32)
+    _need(out, "gather out", src.dtype)
+    check(_lib.load().mm_gather_rows(src.data_ptr(), rows.data_ptr(), out.data_ptr(), dtype_code(src.dtype),
+                                     rows.numel(), src.shape[-1], _stream()), "gather_rows")
+    return out
+
+
+def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor,
+                      positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                      num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float) -> torch.Tensor:
+    """Causal attention of every token over its request's pages (fp32 arithmetic, any head size)."""
+    _need(q, "attention q")
+    n = q.shape[0]
+    _need(out, "attention out", q.dtype)
+    _need(k_pages, "attention k_pages", q.dtype)
+    _need(v_pages, "attention v_pages", q.dtype)
+    if q.shape != (n, num_heads * head_dim) or out.shape != q.shape:
+        raise KernelError("attention: q/out shape mismatch")
+    if k_pages.shape[1:] != (num_kv_heads, page_size, head_dim) or v_pages.shape != k_pages.shape:
+        raise KernelError("attention: page pool shape mismatch")
+    _need(positions, "positions", torch.int32)
+    _need(token_req, "token_req", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    check(_lib.load().mm_attention_generic(
+        q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), out.data_ptr(), dtype_code(q.dtype), positions.data_ptr(),
+        token_req.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, n, num_heads, num_kv_heads,
+        head_dim, window, float(scale), _stream()), "attention_generic")
+    return out
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    """out[M,N] = a[M,K] @ w[N,K]^T (+ bias) on the fp32 FMA units, k summed in ascending order."""
+    _need(a, "gemm a")
+    _need(w, "gemm w")
+    _need(out, "gemm out")
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape != (n, k) or out.shape != (m, n):
+        raise KernelError(f"gemm: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not match")
+    if bias is not None:
+        _need(bias, "gemm bias")
+        if bias.shape != (n,):
+            raise KernelError("gemm: bias shape mismatch")
+    check(_lib.load().mm_gemm_simt(a.data_ptr(), dtype_code(a.dtype), w.data_ptr(), dtype_code(w.dtype), _ptr(bias),
+                                   dtype_code(bias.dtype) if bias is not None else F32, out.data_ptr(),
+                                   dtype_code(out.dtype), m, n, k, k, n, _stream()), "gemm_simt")
+    return out
+
+
+def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(logits, "argmax logits", torch.float32)
+    r, v = logits.shape
+    if out is None:
+        out = torch.empty(r, dtype=torch.int32, device=logits.device)
+    _need(out, "argmax out", torch.int32)
+    check(_lib.load().mm_argmax_rows(logits.data_ptr(), out.data_ptr(), r, v, _stream()), "argmax_rows")
+    return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+                seeds: torch.Tensor, counters: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need(logits, "sample logits", torch.float32)
+    r, v = logits.shape
+    _need(temperature, "temperature", torch.float32)
+    _need(top_k, "top_k", torch.int32)
+    _need(top_p, "top_p", torch.float32)
+    _need(seeds, "seeds", torch.int64)
+    _need(counters, "counters", torch.int64)
+    for t in (temperature, top_k, top_p, seeds, counters):
+        if t.numel() != r:
+            raise KernelError("sample: per-row parameter length mismatch")
+    if out is None:
+        out = torch.empty(r, dtype=torch.int32, device=logits.device)
+    check(_lib.load().mm_sample_rows(logits.data_ptr(), out.data_ptr(), r, v, temperature.data_ptr(), top_k.data_ptr(),
+                                     top_p.data_ptr(), seeds.data_ptr(), counters.data_ptr(), _stream()), "sample_rows")
+    return out
+
+
+def apply_penalties(logits: torch.Tensor, recent: Optional[torch.Tensor], repetition: torch.Tensor,
+                    frequency: torch.Tensor, presence: torch.Tensor, softcap: Optional[torch.Tensor]) -> torch.Tensor:
+    _need(logits, "penalties logits", torch.float32)
+    r, v = logits.shape
+    w = 0
+    if recent is not None:
+        _need(recent, "recent tokens", torch.int32)
+        w = recent.shape[1]
+    for t in (repetition, frequency, presence):
+        _need(t, "penalty parameter", torch.float32)
+    if softcap is not None:
+        _need(softcap, "softcap", torch.float32)
+    check(_lib.load().mm_apply_penalties(logits.data_ptr(), r, v, _ptr(recent), w, repetition.data_ptr(),
+                                         frequency.data_ptr(), presence.data_ptr(), _ptr(softcap), _stream()),
+          "apply_penalties")
+    return logits
+
+
+def uniform_from(seed: int, counter: int) -> float:
+    """The uniform number in [0,1) the device sampler draws for (seed, counter)."""
+    return float(_lib.load().mm_uniform_from(seed & 0xFFFFFFFFFFFFFFFF, counter & 0xFFFFFFFFFFFFFFFF))

@@ -1,0 +1,98 @@
+"""Causal self-attention with grouped KV heads over a paged cache.
+
+Per layer (src/runtime/arch/Qwen2Backend.cpp:203-430): ``q,k,v = n·Wᵀ + b`` (bias on
+q/k/v only, none on the output projection), position encoding on q and k, k and v
+appended to the cache *before* attention, ``s = (q·k)·scale`` with ``scale = 1/sqrt(hd)``
+(:415-416), softmax over the keys a query may see, ``o = P·v``, then the output
+projection.  Query head h reads KV head ``(h·G)/H`` (src/compute/Attention.cpp:43); a
+query at absolute position a sees keys ``[max(0, a+1−W), a]`` (:46-50, W = 0: all).
+
+Head counts, head size, window, scale, biases and the position encoding are parameters of
+the part; the three projections are concatenated at load so one product feeds the fused
+bias + rotary + cache-write kernel.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from ..config.spec import PartSpec, TensorSpec
+from ..kernels import ops
+from ..registry import MIXERS, POSITION_ENCODINGS
+from .base import KVCacheSpec, LayerCache, Mixer, Runtime, StepContext, WeightView
+from .linear import linear
+
+
+@MIXERS.register("gqa_attention")
+class GQAAttention(Mixer):
+    """spec params: hidden, num_heads, num_kv_heads, head_dim, window, scale (None: 1/sqrt(head_dim)),
+    qkv_bias, position (PartSpec), q, k, v, o (projection name stems under the prefix)."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
+        d, hd = spec["hidden"], spec["head_dim"]
+        qs, kvs = spec["num_heads"] * hd, spec["num_kv_heads"] * hd
+        out = [
+            TensorSpec(prefix + spec["q"] + ".weight", (qs, d)),
+            TensorSpec(prefix + spec["k"] + ".weight", (kvs, d)),
+            TensorSpec(prefix + spec["v"] + ".weight", (kvs, d)),
+            TensorSpec(prefix + spec["o"] + ".weight", (d, qs)),
+        ]
+        if spec.get("qkv_bias", False):
+            out += [
+                TensorSpec(prefix + spec["q"] + ".bias", (qs,), role="bias"),
+                TensorSpec(prefix + spec["k"] + ".bias", (kvs,), role="bias"),
+                TensorSpec(prefix + spec["v"] + ".bias", (kvs,), role="bias"),
+            ]
+        return out
+
+    def __init__(self, spec: PartSpec, weights: WeightView, rt: Runtime):
+        super().__init__(spec, weights, rt)
+        self.hidden = int(spec["hidden"])
+        self.num_heads = int(spec["num_heads"])
+        self.num_kv_heads = int(spec["num_kv_heads"])
+        self.head_dim = int(spec["head_dim"])
+        self.window = int(spec.get("window", 0) or 0)
+        scale = spec.get("scale")
+        # computed in fp32 like the reference (src/runtime/arch/Qwen2Backend.cpp:415-416)
+        self.scale = float(scale) if scale is not None else float(
+            torch.tensor(1.0, dtype=torch.float32) / torch.sqrt(torch.tensor(float(self.head_dim), dtype=torch.float32)))
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        pos_spec: PartSpec = spec["position"]
+        self.position = POSITION_ENCODINGS.get(pos_spec.kind)(pos_spec, weights, rt)
+
+        ws = [weights.take(spec[n] + ".weight") for n in ("q", "k", "v")]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.float() for w in ws]
+        self.w_qkv = torch.cat(ws, dim=0).contiguous()
+        del ws
+        self.b_qkv: Optional[torch.Tensor] = None
+        if spec.get("qkv_bias", False):
+            bs = [weights.take(spec[n] + ".bias") for n in ("q", "k", "v")]
+            if len({b.dtype for b in bs}) > 1:
+                bs = [b.float() for b in bs]
+            self.b_qkv = torch.cat(bs, dim=0).contiguous()
+        self.w_o = weights.take(spec["o"] + ".weight").contiguous()
+
+    def kv_cache_spec(self) -> Optional[KVCacheSpec]:
+        return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        n = x.shape[0]
+        H, G, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        qkv = linear(x, self.w_qkv, None, self.rt)
+        q = torch.empty((n, H * hd), dtype=x.dtype, device=x.device)
+        fused = self.position.fused_rotary()
+        if fused is None:
+            raise NotImplementedError("position encodings without a fused form are applied by their own apply()")
+        rotary_dim, theta = fused
+        ops.qkv_rope_kvwrite(qkv, self.b_qkv, q, cache.k_pages if cache.writes else None,
+                             cache.v_pages if cache.writes else None, ctx.positions, ctx.token_req, cache.block_table,
+                             cache.page_size, H, G, hd, rotary_dim, theta)
+        out = torch.empty_like(q)
+        from ..kernels import attention as attn_kernels
+        attn_kernels.paged_attention(q, cache, out, ctx, H, G, hd, self.window, self.scale)
+        return linear(out, self.w_o, None, self.rt)

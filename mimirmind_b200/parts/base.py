@@ -1,0 +1,179 @@
+"""Interfaces of the parts a layer is made of, and what a step hands to them.
+
+A part is built from its :class:`PartSpec` (all sizes and constants are parameters
+there), a :class:`WeightView` that resolves tensor names under the layer's prefix, and a
+:class:`Runtime` (activation dtype, device).  No part knows which model it is in.
+
+The reference's backend interface carries the same per-layer facts as virtuals on the
+architecture object (``kvDimPerLayer``, ``maxQKVDims``, ``scalesEmbedding``,
+src/runtime/arch/ArchBackend.hpp:60-223); here each part answers for itself.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config.spec import PartSpec, TensorSpec
+
+
+@dataclass(frozen=True)
+class Runtime:
+    """Where and in which precision a model runs."""
+
+    dtype: torch.dtype               # activation / cache dtype: torch.float32 or torch.bfloat16
+    device: torch.device
+    matmul: str = "auto"             # "auto": tensor-core kernels for bf16; "simt": fp32-FMA kernel everywhere
+
+
+class WeightView:
+    """Name → tensor lookup under a prefix; parts take what they need and may drop it after fusing."""
+
+    def __init__(self, tensors: Dict[str, torch.Tensor], prefix: str = ""):
+        self._tensors = tensors
+        self.prefix = prefix
+
+    def sub(self, prefix: str) -> "WeightView":
+        return WeightView(self._tensors, self.prefix + prefix)
+
+    def has(self, name: str) -> bool:
+        return (self.prefix + name) in self._tensors
+
+    def get(self, name: str) -> torch.Tensor:
+        full = self.prefix + name
+        try:
+            return self._tensors[full]
+        except KeyError:
+            raise KeyError(f"tensor '{full}' not in model") from None
+
+    def take(self, name: str) -> torch.Tensor:
+        """Like get, but removes the tensor from the store (the part keeps a fused copy)."""
+        full = self.prefix + name
+        try:
+            return self._tensors.pop(full)
+        except KeyError:
+            raise KeyError(f"tensor '{full}' not in model") from None
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """A mixer that keeps keys and values per token: head geometry and how far back it looks."""
+
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0  # 0: every earlier token; W: the last W tokens (the current one included)
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """A mixer that keeps a fixed-size state per request."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class LayerCache:
+    """What one schedule entry sees of the cache during a step."""
+
+    k_pages: Optional[torch.Tensor] = None   # [pages, kv_heads, page_size, head_dim]
+    v_pages: Optional[torch.Tensor] = None
+    block_table: Optional[torch.Tensor] = None  # int32 [requests, width] of the entry's cache group
+    page_size: int = 0
+    writes: bool = True                      # False: the entry reads another entry's cache
+    state: Optional[torch.Tensor] = None     # [slots, *StateSpec.shape]
+
+
+@dataclass
+class StepContext:
+    """One batch: tokens of several requests, portions of prompts beside single decoded tokens.
+
+    Tokens of a request are consecutive; request r owns tokens
+    [q_start[r], q_start[r] + q_len[r]) and, after the step, holds kv_len[r] tokens.
+    """
+
+    n_tokens: int
+    n_requests: int
+    token_ids: torch.Tensor            # int32 [n_tokens]
+    positions: torch.Tensor            # int32 [n_tokens] absolute position of each token
+    token_req: torch.Tensor            # int32 [n_tokens] index of the token's request in this batch
+    q_start: Sequence[int]             # host copies, per request
+    q_len: Sequence[int]
+    kv_len: Sequence[int]
+    req_meta: torch.Tensor             # int32 [n_requests, 4]: q_start, q_len, kv_len, state slot
+    state_slots: torch.Tensor          # int32 [n_requests]
+    block_tables: Dict[str, torch.Tensor]  # cache group → int32 [n_requests, width]
+    logit_rows: torch.Tensor           # int32 [n_wanted] token rows whose logits are returned
+    n_logit_rows: int
+    page_size: int
+    runtime: Runtime
+    plans: Dict[Any, Any] = field(default_factory=dict)  # per-step launch plans, shared between layers
+    max_kv_len: int = 0
+    max_q_len: int = 0
+
+
+class Part:
+    """Base of every part: declares its tensors, builds from weights."""
+
+    @classmethod
+    def tensor_specs(cls, spec: PartSpec, prefix: str) -> List[TensorSpec]:
+        return []
+
+    def __init__(self, spec: PartSpec, weights: WeightView, rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+
+
+class Norm(Part):
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
+                n_rows: Optional[int] = None) -> torch.Tensor:
+        """residual (fp32, [n, width]) += delta; returns the normalised rows in the activation dtype.
+        With ``rows`` only those rows are produced and the residual is not written."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def fused_rotary(self) -> Optional[Tuple[int, float]]:
+        """(rotary_dim, theta) if the encoding is a split-half rotation the fused kernel can apply."""
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        """Encode positions into q [n, H, hd] and k [n, G, hd] in place (unfused path)."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def kv_cache_spec(self) -> Optional[KVCacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        """x: normalised activations [n_tokens, hidden] → the mixer's output [n_tokens, hidden]."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of norms, mixer and feed-forward around the residual stream."""
+
+    def __init__(self, spec: PartSpec, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, feed_forward: FeedForward,
+                 rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+        self.mixer_norm = mixer_norm
+        self.mixer = mixer
+        self.ffn_norm = ffn_norm
+        self.feed_forward = feed_forward
+
+    def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
+                cache: LayerCache) -> Optional[torch.Tensor]:
+        """Runs the layer.  ``pending`` is a branch output not yet added to ``residual`` (so the add
+        fuses into the next norm); returns the new pending output."""
+        raise NotImplementedError
