@@ -1,0 +1,149 @@
+"""The Python entry point: load a model, generate tokens for a list of prompts.
+
+``Engine.generate`` is the counterpart of the reference's
+``InferenceEngine::generate(promptIds, GenerateParams, onToken, stats)``
+(src/runtime/InferenceEngine.hpp:207-380; .cpp:1304-2131), for many prompts at once under
+the continuous-batching scheduler: token ids in, token ids out, ``max_new`` counts the first
+token, a stop token is part of the output, statistics give prompt and generated token
+counts, prefill and decode time and whether a stop id was hit.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from ..sampling import Sampler, SamplingParams
+from .loader import load_model, random_model
+from .model import Model
+from .runner import ModelRunner, StepEntry
+from .scheduler import PlannedEntry, Request, Scheduler, SchedulerConfig
+
+
+@dataclass
+class GenerateStats:
+    """After the reference's GenerateStats (src/runtime/InferenceEngine.hpp:104-133)."""
+
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    prefill_ms: float = 0.0       # time to the request's first token
+    decode_ms: float = 0.0        # time from the first to the last token
+    hit_stop: bool = False
+    finish_reason: str = ""
+    preemptions: int = 0
+
+
+@dataclass
+class GenerateResult:
+    tokens: List[int]
+    stats: GenerateStats
+
+
+class Engine:
+    def __init__(self, model: Model, *, page_size: int = 16, cache_tokens: int = 0, max_context: int = 8192,
+                 token_budget: int = 512, max_active: int = 32, prefill_chunk: int = 0):
+        self.model = model
+        max_context = min(max_context, model.spec.max_positions)
+        if cache_tokens <= 0:
+            cache_tokens = max_context * min(max_active, 4)
+        num_pages = (cache_tokens + page_size - 1) // page_size
+        self.runner = ModelRunner(model, page_size=page_size, num_pages=num_pages, max_requests=max_active,
+                                  max_seq_len=max_context)
+        self.sched_cfg = SchedulerConfig(token_budget=token_budget, max_active=max_active,
+                                         prefill_chunk=prefill_chunk, max_seq_len=max_context)
+        self.sampler = Sampler(model.rt.device)
+        self.eos_ids = tuple(model.spec.eos_token_ids)
+        self.last_metrics = None
+
+    # ---- construction ----------------------------------------------------------------
+    @classmethod
+    def from_folder(cls, model_dir: str, dtype: str = "bfloat16", **kw) -> "Engine":
+        model, _ = load_model(model_dir, dtype)
+        return cls(model, **kw)
+
+    @classmethod
+    def from_config(cls, cfg, model_id: Optional[str] = None) -> "Engine":
+        """From an :class:`EngineConfig` (the JSON file of the command line)."""
+        from ..registry import get_architecture
+        entry = cfg.model(model_id)
+        if entry.random:
+            arch = get_architecture(entry.random["config"]["architectures"][0])
+            spec = arch.build_spec(arch.parse_config(entry.random["config"], f"models[{entry.id}].random.config"))
+            model = random_model(spec, int(entry.random.get("seed", 0)), cfg.runtime.dtype)
+        else:
+            model, _ = load_model(entry.path, cfg.runtime.dtype)
+        return cls(model, page_size=cfg.serving.blockSize, cache_tokens=cfg.runtime.cacheTokens,
+                   max_context=cfg.runtime.maxContextTokens, token_budget=cfg.serving.tokenBudget,
+                   max_active=cfg.serving.maxActiveRequests, prefill_chunk=cfg.serving.prefillChunk)
+
+    # ---- generation --------------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 256,
+                 sampling=None, stop_ids: Sequence[int] = (), use_eos: bool = True,
+                 on_token: Optional[Callable[[int, int], bool]] = None) -> List[GenerateResult]:
+        """Generates for every prompt (lists of token ids).  ``sampling`` is one SamplingParams for all
+        or one per prompt; ``on_token(prompt index, token)`` may return False to stop that request."""
+        n = len(prompts)
+        if sampling is None:
+            sampling = SamplingParams()
+        params = list(sampling) if isinstance(sampling, (list, tuple)) else [sampling] * n
+        if len(params) != n:
+            raise ValueError("one SamplingParams per prompt")
+        stops = tuple(stop_ids) + (self.eos_ids if use_eos else ())
+        sched = Scheduler(self.sched_cfg, self.runner.manager)
+        reqs = [Request(id=("gen", i), prompt=list(p), max_new=max_new_tokens, sampling=params[i].resolved(),
+                        stop_ids=stops) for i, p in enumerate(prompts)]
+        t0 = time.perf_counter()
+        first_at: Dict[Hashable, float] = {}
+        last_at: Dict[Hashable, float] = {}
+        for r in reqs:
+            sched.add(r)
+        while sched.has_work():
+            plan = sched.schedule()
+            if not plan:
+                if sched.has_work():
+                    raise RuntimeError("scheduler made no progress")   # cannot happen: a lone request fails instead
+                break
+            sampled = self._run_plan(plan)
+            now = time.perf_counter()
+            for p in plan:
+                if p.samples:
+                    first_at.setdefault(p.request.id, now)
+                    last_at[p.request.id] = now
+            sched.commit(plan, sampled)
+            if on_token is not None:
+                for p in plan:
+                    if p.samples and p.request.state != "finished":
+                        if on_token(p.request.id[1], sampled[p.request.id]) is False:
+                            sched.cancel(p.request.id)
+                    elif p.samples:
+                        on_token(p.request.id[1], sampled[p.request.id])
+        self.last_metrics = sched.metrics
+        out = []
+        for r in reqs:
+            st = GenerateStats(prompt_tokens=len(r.prompt), generated_tokens=len(r.generated),
+                               hit_stop=r.hit_stop, finish_reason=r.finish_reason or "", preemptions=r.preemptions)
+            if r.id in first_at:
+                st.prefill_ms = (first_at[r.id] - t0) * 1e3
+                st.decode_ms = (last_at[r.id] - first_at[r.id]) * 1e3
+            out.append(GenerateResult(list(r.generated), st))
+        return out
+
+    def _run_plan(self, plan: Sequence[PlannedEntry]) -> Dict[Hashable, int]:
+        entries = [StepEntry(p.request.id, p.tokens, [p.count - 1] if p.samples else []) for p in plan]
+        ctx = self.runner._build_context(entries)
+        for p in plan:
+            if self.runner.manager.mark_started(p.request.id):
+                self.runner.storage.zero_slot(self.runner.manager.slot(p.request.id))
+        logits = self.runner.forward(ctx)
+        sampled: Dict[Hashable, int] = {}
+        rows = [p for p in plan if p.samples]
+        if rows:
+            toks = self.sampler.sample(logits, [p.request.sampling for p in rows],
+                                       [len(p.request.generated) for p in rows],
+                                       [p.request.tokens for p in rows])
+            host = toks.cpu().tolist()
+            for p, t in zip(rows, host):
+                sampled[p.request.id] = t
+        return sampled
