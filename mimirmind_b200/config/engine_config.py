@@ -24,7 +24,7 @@ class EngineConfigError(ValueError):
 
 @dataclass
 class ModelEntry:
-    id: str
+    id: str = ""
     path: str = ""
     title: str = ""
     random: Optional[Dict[str, Any]] = None   # {"config": {...config.json...}, "seed": int}
@@ -78,6 +78,8 @@ def _fill(section: str, cls, obj: Any):
         if k not in known:
             raise EngineConfigError(f"unknown key '{section}.{k}' (known: {', '.join(known)})")
         want = type(getattr(inst, k)) if getattr(inst, k) is not None else None
+        if want is None and v is not None and not isinstance(v, dict):
+            raise EngineConfigError(f"'{section}.{k}' must be an object")
         if want is bool and not isinstance(v, bool):
             raise EngineConfigError(f"'{section}.{k}' must be true or false")
         if want is int and (isinstance(v, bool) or not isinstance(v, int)):
