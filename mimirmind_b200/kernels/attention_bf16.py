@@ -1,10 +1,110 @@
-"""Tensor-core attention kernels for bfloat16 (bound when built)."""
+"""Launch plans for the tensor-core attention kernels (bfloat16, head size 64 or 128).
+
+Per step the batch is sorted once, on the host, into *prefill tiles* (64 query tokens of one
+request) for portions of at least ``PREFILL_MIN`` tokens and *decode items* (single tokens)
+for the rest; every layer of the step reuses the plan.  The decode kernel cuts each token's
+key range into splits by absolute position; the split length is chosen so that the grid
+fills the GPU, and its partial results go through scratch memory that the plan owns.
+"""
 from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import lib as _lib
+from .lib import check
+
+PREFILL_MIN = 16       # shorter portions go token by token through the decode kernel
+TILE_ROWS = 64
+MIN_SPLIT = 128
+TARGET_CTAS = 2 * 148
+
+_declared = False
+
+
+def _declare():
+    global _declared
+    if _declared:
+        return
+    P, I, F = c_void_p, c_int, c_float
+    _lib.declare("mm_attention_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, F, P])
+    _lib.declare("mm_attention_decode_bf16", [P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P])
+    _declared = True
 
 
 def supports(head_dim: int, num_heads: int, num_kv_heads: int) -> bool:
-    return False
+    return head_dim in (64, 128) and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 16
 
 
-def run(*args, **kwargs):
-    raise NotImplementedError
+@dataclass
+class AttentionPlan:
+    tiles: Optional[torch.Tensor]      # int32 [n_tiles, 4] or None
+    n_tiles: int
+    items: Optional[torch.Tensor]      # int32 [n_items]; None with n_items > 0 means "every token"
+    n_items: int
+    split_len: int
+    max_splits: int
+    part_o: Optional[torch.Tensor] = None
+    part_ml: Optional[torch.Tensor] = None
+
+
+def choose_split(n_items: int, num_kv_heads: int, max_kv_len: int):
+    """Split length (a multiple of 64) and the number of splits that cover ``max_kv_len`` keys."""
+    wanted = max(1, -(-TARGET_CTAS // max(1, n_items * num_kv_heads)))
+    per = -(-max_kv_len // wanted)
+    split_len = max(MIN_SPLIT, -(-per // 64) * 64)
+    return split_len, max(1, -(-max_kv_len // split_len))
+
+
+def make_plan(ctx, num_heads: int, num_kv_heads: int, head_dim: int) -> AttentionPlan:
+    device = ctx.positions.device
+    tiles, items = [], []
+    for r in range(ctx.n_requests):
+        s, n, kv = ctx.q_start[r], ctx.q_len[r], ctx.kv_len[r]
+        if n >= PREFILL_MIN:
+            for off in range(0, n, TILE_ROWS):
+                tiles.append((r, s + off, min(TILE_ROWS, n - off), kv - n + off))
+        else:
+            items.extend(range(s, s + n))
+    d_tiles = torch.tensor(tiles, dtype=torch.int32, device=device) if tiles else None
+    if len(items) == ctx.n_tokens:
+        d_items = None
+    else:
+        d_items = torch.tensor(items, dtype=torch.int32, device=device) if items else None
+    split_len, max_splits = choose_split(len(items), num_kv_heads, ctx.max_kv_len) if items else (MIN_SPLIT, 1)
+    plan = AttentionPlan(d_tiles, len(tiles), d_items, len(items), split_len, max_splits)
+    if items and max_splits > 1:
+        plan.part_o = torch.empty((len(items), num_heads, max_splits, head_dim), dtype=torch.float32, device=device)
+        plan.part_ml = torch.empty((len(items), num_heads, max_splits, 2), dtype=torch.float32, device=device)
+    return plan
+
+
+def run(q, cache, out, ctx, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float):
+    _declare()
+    key = ("attention_bf16", num_heads, num_kv_heads, head_dim)
+    plan: AttentionPlan = ctx.plans.get(key)
+    if plan is None:
+        plan = make_plan(ctx, num_heads, num_kv_heads, head_dim)
+        ctx.plans[key] = plan
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    table = cache.block_table
+    if plan.n_tiles:
+        check(lib.mm_attention_prefill_bf16(q.data_ptr(), cache.k_pages.data_ptr(), cache.v_pages.data_ptr(),
+                                            out.data_ptr(), plan.tiles.data_ptr(), plan.n_tiles, table.data_ptr(),
+                                            table.shape[1], cache.page_size, num_heads, num_kv_heads, head_dim, window,
+                                            float(scale), stream), "attention_prefill_bf16")
+    if plan.n_items:
+        check(lib.mm_attention_decode_bf16(
+            q.data_ptr(), cache.k_pages.data_ptr(), cache.v_pages.data_ptr(), out.data_ptr(),
+            plan.part_o.data_ptr() if plan.part_o is not None else None,
+            plan.part_ml.data_ptr() if plan.part_ml is not None else None,
+            plan.items.data_ptr() if plan.items is not None else None, plan.n_items, ctx.positions.data_ptr(),
+            ctx.token_req.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size, num_heads, num_kv_heads,
+            head_dim, window, float(scale), plan.split_len, plan.max_splits, stream), "attention_decode_bf16")
+    return out

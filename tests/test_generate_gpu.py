@@ -1,0 +1,122 @@
+"""Generation through the Python entry point and the command line: greedy tokens equal the plain
+implementation's, sampling is seeded per request, running out of pages changes no output."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_qwen2 as plain
+from conftest import ROOT, TINY, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def check_greedy(pm, prompt, tokens, margin):
+    """Every generated token is the plain implementation's argmax given the same history, or lies within
+    ``margin`` of it (a near-tie may legitimately flip in reduced precision).  Returns exact matches."""
+    toks, exact = list(prompt), 0
+    for i, tok in enumerate(tokens):
+        row = pm.logits(toks)[-1]
+        best = int(plain.greedy(row.astype(np.float32)))
+        assert row[tok] >= row[best] - margin, f"token {i}: engine chose {tok} ({row[tok]:.4f}), plain {best} ({row[best]:.4f})"
+        exact += tok == best
+        toks.append(tok)
+    return exact
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("D", "bfloat16"), ("E", "bfloat16")])
+def test_greedy_generation_equals_plain(name, dtype, model_folders, plain_models):
+    from mimirmind_b200 import Engine
+    pm = plain_models(name, dtype)
+    prompts = [random_tokens(pm.V, n, 40 + n) for n in (5, 17, 33, 64)]
+    eng = Engine.from_folder(model_folders(name, dtype), dtype=dtype, page_size=16, cache_tokens=1024, max_context=512,
+                             token_budget=48, max_active=4)
+    res = eng.generate(prompts, max_new_tokens=16)
+    margin = 1e-4 if dtype == "float32" else 0.08
+    exact = 0
+    for p, r in zip(prompts, res):
+        assert r.stats.generated_tokens == 16 and r.stats.finish_reason == "length"
+        exact += check_greedy(pm, p, r.tokens, margin)
+    assert exact >= (64 if dtype == "float32" else 56)
+    assert eng.runner.manager.free_pages() == eng.runner.manager.total_pages()
+
+
+def test_chunked_mixed_temperature_run_is_seeded_and_batch_independent(model_folders, plain_models):
+    """Six requests, prompt portions of 32 mixed with decoding, temperature 0.8 with fixed seeds."""
+    from mimirmind_b200 import Engine, SamplingParams
+    pm = plain_models("B", "float32")
+    prompts = [random_tokens(pm.V, n, n) for n in (1, 9, 40, 77, 128, 200)]
+    sp = [SamplingParams(temperature=0.8, seed=1000 + i) for i in range(6)]
+    kw = dict(dtype="float32", page_size=16, max_context=512)
+    eng = Engine.from_folder(model_folders("B", "float32"), cache_tokens=4096, token_budget=64, max_active=6, prefill_chunk=32, **kw)
+    a = eng.generate(prompts, max_new_tokens=24, sampling=sp)
+    b = eng.generate(prompts, max_new_tokens=24, sampling=sp)
+    assert [r.tokens for r in a] == [r.tokens for r in b]
+    assert len({tuple(r.tokens) for r in a}) == 6
+    # one request alone gives the same stream as in the batch
+    solo = Engine.from_folder(model_folders("B", "float32"), cache_tokens=1024, token_budget=512, max_active=1, **kw)
+    for i in (0, 3, 5):
+        assert solo.generate([prompts[i]], max_new_tokens=24, sampling=sp[i])[0].tokens == a[i].tokens
+    # every sampled token is what the plain sampler draws from the plain logits (when not a near-tie)
+    toks = list(prompts[2])
+    for step, tok in enumerate(a[2].tokens[:6]):
+        row = pm.logits(toks)[-1]
+        assert tok == plain.sample(row, 0.8, 0, 1.0, plain.uniform_from(1002, step))
+        toks.append(tok)
+
+
+def test_running_out_of_pages_changes_no_output(model_folders):
+    from mimirmind_b200 import Engine
+    folder = model_folders("A", "float32")
+    prompts = [random_tokens(256, n, n) for n in (30, 45, 20, 50)]
+    roomy = Engine.from_folder(folder, dtype="float32", cache_tokens=2048, max_context=256, token_budget=64, max_active=4)
+    tight = Engine.from_folder(folder, dtype="float32", cache_tokens=160, max_context=256, token_budget=64, max_active=4)
+    a = roomy.generate(prompts, max_new_tokens=40)
+    b = tight.generate(prompts, max_new_tokens=40)
+    assert tight.last_metrics.preempted > 0 and roomy.last_metrics.preempted == 0
+    assert [r.tokens for r in a] == [r.tokens for r in b]
+    assert sum(r.stats.preemptions for r in b) == tight.last_metrics.preempted
+    # a request that can never fit is reported, not hung
+    lone = Engine.from_folder(folder, dtype="float32", cache_tokens=64, max_context=256, token_budget=64, max_active=2)
+    r = lone.generate([random_tokens(256, 60, 1)], max_new_tokens=40)[0]
+    assert r.stats.finish_reason == "out_of_pages" and 1 <= len(r.tokens) < 40
+    r = lone.generate([random_tokens(256, 100, 1)], max_new_tokens=4)[0]
+    assert r.stats.finish_reason.startswith("rejected")
+
+
+def test_stop_ids_and_callback(model_folders):
+    from mimirmind_b200 import Engine
+    eng = Engine.from_folder(model_folders("A", "float32"), dtype="float32", cache_tokens=512, max_context=256)
+    p = random_tokens(256, 12, 3)
+    free = eng.generate([p], max_new_tokens=10)[0].tokens
+    stopped = eng.generate([p], max_new_tokens=10, stop_ids=[free[3]])[0]
+    first = free.index(free[3])
+    assert stopped.tokens == free[:first + 1] and stopped.stats.hit_stop      # the stop token is part of the output
+    seen = []
+    eng.generate([p], max_new_tokens=10, on_token=lambda i, t: (seen.append(t), len(seen) < 4)[1])
+    assert seen == free[:4]
+
+
+def test_command_line_smoke(model_folders, tmp_path):
+    cfg = {"defaultModel": "m", "models": [{"id": "m", "path": model_folders("A", "float32")}],
+           "runtime": {"dtype": "float32", "maxContextTokens": 256, "cacheTokens": 512}}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "mimirmind"), "smoke", "--config", str(tmp_path / "config.json"),
+           "--prompt", "5 17 3 200", "--max-new", "6"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    lines = out.stdout.strip().splitlines()
+    assert len(lines[0].split()) == 6 and lines[1] == "generated 6"
+    assert lines[2].startswith("prefill ") and "(4 tokens, 2 blocks)" in lines[2] and lines[3].startswith("decode ")
+    missing = subprocess.run(cmd[:3] + ["--config", str(tmp_path / "nope.json")] + cmd[5:], capture_output=True, text=True, timeout=300)
+    assert missing.returncode == 2 and "not found" in missing.stderr
+    # random-weights mode writes a folder the engine loads
+    (tmp_path / "mc.json").write_text(json.dumps(TINY["C"]))
+    rw = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "mimirmind"), "random-weights", "--model-config",
+                         str(tmp_path / "mc.json"), "--seed", "9", "--out", str(tmp_path / "rw"), "--dtype", "bfloat16"],
+                        capture_output=True, text=True, timeout=300)
+    assert rw.returncode == 0, rw.stderr
+    assert os.path.isfile(tmp_path / "rw" / "model.safetensors") and json.load(open(tmp_path / "rw" / "config.json"))["torch_dtype"] == "bfloat16"

@@ -1,0 +1,372 @@
+"""Each kernel alone against a plain fp32/float64 reference of the same operation, at sizes other than
+the engine's tiny models (widths and vocabularies that are no power of two, head sizes in steps of
+16, odd head and group counts), with inputs made so that an addressing fault shows."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def ops():
+    from mimirmind_b200.kernels import ops as o
+    return o
+
+
+def t(a, dtype=torch.float32):
+    return torch.as_tensor(np.asarray(a)).to(DEV).to(dtype).contiguous()
+
+
+def bf16_round(a):
+    return torch.as_tensor(np.asarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64)
+
+
+# ---- embedding -------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding(dtype):
+    rng = np.random.RandomState(0)
+    V, d = 1003, 136
+    table = t(rng.randn(V, d), dtype)
+    ids = torch.tensor([0, V - 1, 17, V, -3, 500], dtype=torch.int32, device=DEV)
+    out = torch.empty((6, d), dtype=torch.float32, device=DEV)
+    ops().embedding(ids, table, out, 1.0)
+    ref = plain.embedding(table.float().cpu().numpy().astype(np.float64), ids.cpu().tolist())
+    assert np.array_equal(out.cpu().numpy(), ref.astype(np.float32))
+    assert not out[3].any() and not out[4].any()          # ids outside the table give zero rows
+
+
+# ---- residual add + RMSNorm -----------------------------------------------------------------
+@pytest.mark.parametrize("d", [80, 3584 + 16, 13000])
+@pytest.mark.parametrize("act,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32)])
+def test_add_rmsnorm(d, act, wdt):
+    rng = np.random.RandomState(d)
+    n, eps = 7, 3e-5
+    res = t(rng.randn(n, d) * 3)
+    delta = t(rng.randn(n, d), act)
+    w = t(1 + 0.1 * rng.randn(d), wdt)
+    x = res.double().cpu().numpy() + delta.double().cpu().numpy()
+    ref = plain.rms_norm(x, w.double().cpu().numpy(), eps)
+    out = torch.empty((n, d), dtype=act, device=DEV)
+    res2 = res.clone()
+    ops().add_rmsnorm(res2, delta, w, eps, out)
+    assert np.abs(res2.cpu().numpy() - x).max() < 1e-6                      # the sum stays in fp32
+    tol = 2e-6 if act == torch.float32 else 2 ** -8
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= tol * np.abs(ref).max()
+    # gather form: chosen rows only, residual untouched
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    out3 = torch.empty((3, d), dtype=act, device=DEV)
+    res3 = res.clone()
+    ops().add_rmsnorm(res3, delta, w, eps, out3, rows)
+    assert torch.equal(res3, res)
+    assert torch.equal(out3, out[[5, 0, 5]])
+    # no delta
+    out4 = torch.empty((n, d), dtype=act, device=DEV)
+    ops().add_rmsnorm(res.clone(), None, w, eps, out4)
+    ref4 = plain.rms_norm(res.double().cpu().numpy(), w.double().cpu().numpy(), eps)
+    assert np.abs(out4.float().cpu().numpy() - ref4).max() <= tol * np.abs(ref4).max()
+
+
+def test_rmsnorm_row_does_not_depend_on_the_batch():
+    rng = np.random.RandomState(1)
+    d = 1000
+    res = t(rng.randn(9, d))
+    w = t(rng.randn(d))
+    a = torch.empty((9, d), device=DEV)
+    b = torch.empty((1, d), device=DEV)
+    ops().add_rmsnorm(res.clone(), None, w, 1e-6, a)
+    ops().add_rmsnorm(res[4:5].clone(), None, w, 1e-6, b)
+    assert torch.equal(a[4], b[0])
+
+
+# ---- SiLU * up ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("F,dtype", [(176, torch.float32), (352, torch.bfloat16), (75, torch.bfloat16), (18944, torch.bfloat16)])
+def test_silu_mul(F, dtype):
+    rng = np.random.RandomState(F)
+    n = 5
+    gu = t(rng.randn(n, 2 * F) * 4, dtype)
+    out = torch.empty((n, F), dtype=dtype, device=DEV)
+    ops().silu_mul(gu, out)
+    g, u = gu[:, :F].double().cpu().numpy(), gu[:, F:].double().cpu().numpy()
+    ref = g / (1 + np.exp(-g)) * u
+    tol = 1e-6 if dtype == torch.float32 else 2 ** -8
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= tol * max(np.abs(ref).max(), 1)
+
+
+# ---- fp32 matrix product ------------------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(1, 7, 5), (3, 130, 67), (65, 64, 16), (2, 1003, 352), (130, 200, 129)])
+def test_gemm_simt_fp32(M, N, K):
+    rng = np.random.RandomState(M * N + K)
+    a, w, b = t(rng.randn(M, K)), t(rng.randn(N, K)), t(rng.randn(N))
+    out = torch.empty((M, N), device=DEV)
+    ops().gemm_simt(a, w, b, out)
+    ref = a.double().cpu().numpy() @ w.double().cpu().numpy().T + b.double().cpu().numpy()
+    assert np.abs(out.cpu().numpy() - ref).max() <= 2e-6 * np.abs(ref).max() * np.sqrt(K)
+    # a row's result does not depend on M or on its place in the batch
+    one = torch.empty((1, N), device=DEV)
+    ops().gemm_simt(a[M - 1:M].contiguous(), w, b, one)
+    assert torch.equal(one[0], out[M - 1])
+
+
+def test_gemm_simt_mixed_dtypes():
+    rng = np.random.RandomState(3)
+    a, w = t(rng.randn(5, 96), torch.bfloat16), t(rng.randn(40, 96))
+    out = torch.empty((5, 40), dtype=torch.bfloat16, device=DEV)
+    ops().gemm_simt(a, w, None, out)
+    ref = a.double().cpu().numpy() @ w.double().cpu().numpy().T
+    assert np.abs(out.float().cpu().numpy() - ref).max() <= 2 ** -8 * np.abs(ref).max()
+
+
+# ---- bias + rotary + paged K/V write ---------------------------------------------------------------
+def paged_layout(rng, lens, page_size, extra_pages=3):
+    """Shuffled page tables for requests of the given lengths."""
+    need = [(n + page_size - 1) // page_size for n in lens]
+    total = sum(need) + extra_pages
+    perm = rng.permutation(total)
+    width = max(need)
+    table = np.full((len(lens), width), -1, dtype=np.int32)
+    k = 0
+    for r, c in enumerate(need):
+        table[r, :c] = perm[k:k + c]
+        k += c
+    return table, total
+
+
+@pytest.mark.parametrize("dtype,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("H,G,hd,rot,ps", [(4, 2, 16, 16, 16), (6, 3, 48, 48, 8), (7, 1, 128, 128, 16), (3, 1, 32, 16, 32)])
+def test_qkv_rope_kvwrite(dtype, wdt, H, G, hd, rot, ps):
+    rng = np.random.RandomState(H * hd)
+    theta = 1e6
+    lens_before, q_lens = [0, 37, 130], [5, 1, 19]
+    table, pages = paged_layout(rng, [a + b for a, b in zip(lens_before, q_lens)], ps)
+    n = sum(q_lens)
+    pos = np.concatenate([np.arange(a, a + b) for a, b in zip(lens_before, q_lens)]).astype(np.int32)
+    req = np.concatenate([np.full(b, r) for r, b in enumerate(q_lens)]).astype(np.int32)
+    width = (H + 2 * G) * hd
+    qkv = t(rng.randn(n, width), dtype)
+    bias = t(rng.randn(width) * 0.5, wdt)
+    kp = torch.full((pages, G, ps, hd), 768.0, dtype=dtype, device=DEV)
+    vp = torch.full((pages, G, ps, hd), 768.0, dtype=dtype, device=DEV)
+    q_out = torch.empty((n, H * hd), dtype=dtype, device=DEV)
+    ops().qkv_rope_kvwrite(qkv, bias, q_out, kp, vp, t(pos, torch.int32), t(req, torch.int32), t(table, torch.int32),
+                           ps, H, G, hd, rot, theta)
+    x = qkv.double().cpu().numpy() + bias.double().cpu().numpy()
+    q = x[:, :H * hd].reshape(n, H, hd)
+    k = x[:, H * hd:(H + G) * hd].reshape(n, G, hd)
+    v = x[:, (H + G) * hd:].reshape(n, G, hd)
+
+    def rot_part(a):
+        out = a.copy()
+        out[..., :rot] = plain.rope(a[..., :rot], pos, theta)
+        return out
+    q_ref, k_ref = rot_part(q), rot_part(k)
+    tol = 3e-6 * max(1.0, pos.max() / 50) if dtype == torch.float32 else 2 ** -8
+    assert np.abs(q_out.float().cpu().numpy().reshape(n, H, hd) - q_ref).max() <= tol * np.abs(q_ref).max()
+    kp_h, vp_h = kp.float().cpu().numpy(), vp.float().cpu().numpy()
+    written = np.zeros((pages, ps), dtype=bool)
+    for i in range(n):
+        page, slot = table[req[i], pos[i] // ps], pos[i] % ps
+        written[page, slot] = True
+        assert np.abs(kp_h[page, :, slot] - k_ref[i]).max() <= tol * np.abs(k_ref).max()
+        assert np.abs(vp_h[page, :, slot] - v[i]).max() <= tol * np.abs(v).max()
+    # nothing else in the pool was touched
+    untouched = ~written[:, None, :].repeat(G, axis=1)
+    assert (kp_h[untouched] == 768.0).all() and (vp_h[untouched] == 768.0).all()
+
+
+# ---- attention -------------------------------------------------------------------------------------
+def make_attention_case(rng, H, G, hd, ps, ctx_lens, q_lens, dtype, spike=None):
+    """Requests with ``ctx_lens[r]`` cached tokens of which the last ``q_lens[r]`` are this step's queries.
+    ``spike = (request, query offset, key position, head)`` makes one far key dominate one query."""
+    table, pages = paged_layout(rng, ctx_lens, ps)
+    K = [rng.randn(n, G, hd) for n in ctx_lens]
+    V = [rng.randn(n, G, hd) for n in ctx_lens]
+    Q = [rng.randn(qn, H, hd) for qn in q_lens]
+    if spike is not None:
+        r, qo, kpos, h = spike
+        u = rng.randn(hd)
+        u /= np.linalg.norm(u)
+        Q[r][qo, h] = 12.0 * np.sqrt(np.sqrt(hd)) * u
+        K[r][kpos, (h * G) // H] = 12.0 * np.sqrt(np.sqrt(hd)) * u
+        V[r][kpos, (h * G) // H] = 50.0 + np.arange(hd)             # a value no other position has
+    rnd = bf16_round if dtype == torch.bfloat16 else (lambda a: np.asarray(a, dtype=np.float32).astype(np.float64))
+    K, V, Q = [rnd(a) for a in K], [rnd(a) for a in V], [rnd(a) for a in Q]
+    kp = np.zeros((pages, G, ps, hd)); vp = np.zeros((pages, G, ps, hd))
+    for r, n in enumerate(ctx_lens):
+        for p in range(n):
+            kp[table[r, p // ps], :, p % ps] = K[r][p]
+            vp[table[r, p // ps], :, p % ps] = V[r][p]
+    pos = np.concatenate([np.arange(n - qn, n) for n, qn in zip(ctx_lens, q_lens)]).astype(np.int32)
+    req = np.concatenate([np.full(qn, r) for r, qn in enumerate(q_lens)]).astype(np.int32)
+    return dict(Q=Q, K=K, V=V, q=t(np.concatenate(Q).reshape(len(pos), H * hd), dtype), kp=t(kp, dtype), vp=t(vp, dtype),
+                pos=t(pos, torch.int32), req=t(req, torch.int32), table=t(table, torch.int32), ctx_lens=ctx_lens,
+                q_lens=q_lens)
+
+
+def attention_reference(case, window):
+    outs = []
+    for r, (n, qn) in enumerate(zip(case["ctx_lens"], case["q_lens"])):
+        H, hd = case["Q"][r].shape[1:]
+        qfull = np.zeros((n, H, hd))
+        qfull[n - qn:] = case["Q"][r]
+        outs.append(plain.attention(qfull, case["K"][r], case["V"][r], window)[n - qn:])
+    return np.concatenate(outs)
+
+
+ATT_SHAPES = [(4, 2, 16, 16), (6, 1, 32, 8), (6, 3, 48, 16), (5, 5, 80, 16), (7, 1, 128, 16), (8, 2, 64, 32), (3, 1, 256, 16)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,hd,ps", ATT_SHAPES)
+@pytest.mark.parametrize("window", [0, 50])
+def test_attention_generic(dtype, H, G, hd, ps, window):
+    rng = np.random.RandomState(H + hd + window)
+    case = make_attention_case(rng, H, G, hd, ps, [300, 1, 77, 129], [40, 1, 77, 2], dtype, spike=(0, 39, 3 if not window else 255, H - 1))
+    out = torch.empty_like(case["q"])
+    ops().attention_generic(case["q"], case["kp"], case["vp"], out, case["pos"], case["req"], case["table"], ps, H, G, hd,
+                            window, 1.0 / np.sqrt(hd))
+    ref = attention_reference(case, window)
+    tol = 3e-6 if dtype == torch.float32 else 2 ** -8
+    got = out.float().cpu().numpy().reshape(ref.shape)
+    assert np.abs(got - ref).max() <= tol * np.abs(ref).max()
+    # the spiked query really found its far key
+    assert abs(ref[39, H - 1, 0] - 50.0) < 1.0
+
+
+def run_bf16_attention(case, H, G, hd, ps, window, prefill_min=None, split=None):
+    """Through the engine's own plan builder, with a hand-made step context."""
+    from mimirmind_b200.kernels import attention_bf16 as ab
+    from mimirmind_b200.parts.base import LayerCache, Runtime, StepContext
+    q_lens, ctx_lens = case["q_lens"], case["ctx_lens"]
+    q_start = list(np.cumsum([0] + q_lens[:-1]))
+    n = sum(q_lens)
+    ctx = StepContext(n_tokens=n, n_requests=len(q_lens), token_ids=case["pos"], positions=case["pos"], token_req=case["req"],
+                      q_start=q_start, q_len=q_lens, kv_len=ctx_lens, req_meta=None, state_slots=None, block_tables={},
+                      logit_rows=None, n_logit_rows=0, page_size=ps, runtime=Runtime(torch.bfloat16, torch.device(DEV)),
+                      max_kv_len=max(ctx_lens), max_q_len=max(q_lens))
+    cache = LayerCache(k_pages=case["kp"], v_pages=case["vp"], block_table=case["table"], page_size=ps)
+    old = (ab.PREFILL_MIN, ab.MIN_SPLIT, ab.TARGET_CTAS)
+    try:
+        if prefill_min is not None:
+            ab.PREFILL_MIN = prefill_min
+        if split is not None:
+            ab.MIN_SPLIT, ab.TARGET_CTAS = split, 10 ** 6      # forces the smallest split: many splits per token
+        out = torch.zeros_like(case["q"])
+        ab.run(case["q"], cache, out, ctx, H, G, hd, window, 1.0 / np.sqrt(hd))
+        plan = ctx.plans[("attention_bf16", H, G, hd)]
+    finally:
+        ab.PREFILL_MIN, ab.MIN_SPLIT, ab.TARGET_CTAS = old
+    return out, plan
+
+
+@pytest.mark.parametrize("H,G,hd,ps", [(7, 1, 128, 16), (8, 2, 64, 32), (28, 4, 128, 16), (16, 1, 64, 8), (3, 3, 128, 64)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_attention_tensor_core_kernels(H, G, hd, ps, window):
+    rng = np.random.RandomState(H * 3 + hd + window)
+    ctx_lens, q_lens = [700, 64, 333, 1, 130, 900], [200, 64, 1, 1, 2, 17]
+    # the dominant key sits far back (or at the window's far edge) and at a page's last slot
+    far = 15 if not window else 700 - 1 - 99
+    case = make_attention_case(rng, H, G, hd, ps, ctx_lens, q_lens, torch.bfloat16, spike=(0, 199, far, H - 1))
+    ref = attention_reference(case, window)
+    assert abs(ref[199, H - 1, 0] - 50.0) < 1.0
+    for kwargs in (dict(), dict(prefill_min=10 ** 6, split=128), dict(prefill_min=1)):
+        out, plan = run_bf16_attention(case, H, G, hd, ps, window, **kwargs)
+        got = out.float().cpu().numpy().reshape(ref.shape)
+        err = np.abs(got - ref)
+        assert err.max() <= 2.5 * 2 ** -8 * np.abs(ref).max(), (kwargs, np.unravel_index(err.argmax(), err.shape))
+    assert plan.n_tiles > 0 and plan.n_items == 0                  # the last run was all tiles
+
+
+def test_attention_window_edge_is_exact():
+    """A dominant key exactly one place outside the window must not be seen; one place inside must."""
+    H, G, hd, ps, W = 4, 2, 64, 16, 48
+    for inside in (True, False):
+        rng = np.random.RandomState(7)
+        n = 200
+        kpos = n - W if inside else n - W - 1
+        case = make_attention_case(rng, H, G, hd, ps, [n], [1], torch.bfloat16, spike=(0, 0, kpos, 1))
+        ref = attention_reference(case, W)
+        assert (abs(ref[0, 1, 0] - 50.0) < 1.0) == inside
+        for kwargs in (dict(), dict(prefill_min=1)):
+            out, _ = run_bf16_attention(case, H, G, hd, ps, W, **kwargs)
+            assert np.abs(out.float().cpu().numpy().reshape(ref.shape) - ref).max() <= 2.5 * 2 ** -8 * np.abs(ref).max()
+        out = torch.empty_like(case["q"])
+        ops().attention_generic(case["q"], case["kp"], case["vp"], out, case["pos"], case["req"], case["table"], ps, H, G,
+                                hd, W, 1.0 / np.sqrt(hd))
+        assert np.abs(out.float().cpu().numpy().reshape(ref.shape) - ref).max() <= 2 ** -8 * np.abs(ref).max()
+
+
+def test_attention_kernels_refuse_what_they_are_not_built_for():
+    from mimirmind_b200.kernels import attention_bf16 as ab
+    from mimirmind_b200.kernels.lib import KernelError
+    assert not ab.supports(48, 6, 3) and not ab.supports(128, 34, 2) and ab.supports(128, 28, 4)
+    q = torch.zeros((1, 3 * 528), device=DEV)
+    kp = torch.zeros((1, 3, 16, 528), device=DEV)
+    i32 = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(KernelError, match="512"):
+        ops().attention_generic(q, kp, kp, torch.empty_like(q), i32, i32, i32.view(1, 1), 16, 3, 3, 528, 0, 1.0)
+
+
+# ---- sampling ----------------------------------------------------------------------------------------
+def test_argmax_lowest_index_on_ties():
+    V = 152064 + 3
+    logits = torch.randn((5, V), device=DEV)
+    logits[0, 777] = logits[0, 99999] = 50.0
+    logits[1, V - 1] = 60.0
+    logits[2, 0] = 60.0
+    got = ops().argmax_rows(logits).cpu().tolist()
+    assert got[:3] == [777, V - 1, 0]
+    assert got[3:] == logits[3:].argmax(-1).cpu().tolist()
+
+
+def test_sample_matches_the_plain_sampler():
+    rng = np.random.RandomState(0)
+    V, R = 1003, 64
+    logits = (rng.randn(R, V) * 3).astype(np.float32)
+    logits[5, 10] = logits[5, 20] = logits[5].max() + 1        # a tie at the top
+    temps = rng.choice([0.0, 0.7, 1.0, 1.5], size=R).astype(np.float32)
+    ks = rng.choice([0, 1, 5, 50], size=R).astype(np.int32)
+    ps_ = rng.choice([1.0, 0.9, 0.5, 0.1], size=R).astype(np.float32)
+    seeds = rng.randint(1, 2 ** 31, size=R).astype(np.int64)
+    counters = rng.randint(0, 1000, size=R).astype(np.int64)
+    got = ops().sample_rows(t(logits), t(temps), t(ks, torch.int32), t(ps_), t(seeds, torch.int64), t(counters, torch.int64)).cpu().tolist()
+    for r in range(R):
+        u = plain.uniform_from(int(seeds[r]), int(counters[r]))
+        assert abs(u - ops().uniform_from(int(seeds[r]), int(counters[r]))) == 0
+        want = plain.sample(logits[r].astype(np.float64), float(temps[r]), int(ks[r]), float(ps_[r]), u)
+        assert got[r] == want, (r, temps[r], ks[r], ps_[r])
+
+
+def test_sample_distribution_and_batch_independence():
+    V = 37
+    logits = np.linspace(-2, 2, V).astype(np.float32)
+    R = 4096
+    rows = t(np.tile(logits, (R, 1)))
+    one = lambda v, dt: torch.full((R,), v, dtype=dt, device=DEV)
+    cnt = torch.arange(R, dtype=torch.int64, device=DEV)
+    got = ops().sample_rows(rows, one(1.0, torch.float32), one(0, torch.int32), one(1.0, torch.float32), one(99, torch.int64), cnt).cpu().numpy()
+    p = np.exp(logits - logits.max()); p /= p.sum()
+    freq = np.bincount(got, minlength=V) / R
+    assert np.abs(freq - p).max() < 0.02
+    # the same (seed, counter) gives the same token whatever else is in the batch
+    alone = ops().sample_rows(rows[100:101].contiguous(), one(1.0, torch.float32)[:1], one(0, torch.int32)[:1],
+                              one(1.0, torch.float32)[:1], one(99, torch.int64)[:1], cnt[100:101].contiguous()).item()
+    assert alone == got[100]
+
+
+def test_penalties_and_softcap():
+    V = 50
+    base = np.linspace(-3, 3, V).astype(np.float32)
+    logits = t(np.tile(base, (2, 1)))
+    recent = torch.tensor([[49, 49, 3, -1], [-1, -1, -1, -1]], dtype=torch.int32, device=DEV)
+    f = lambda a: torch.tensor(a, dtype=torch.float32, device=DEV)
+    ops().apply_penalties(logits, recent, f([2.0, 1.0]), f([0.5, 0.0]), f([0.25, 0.0]), f([0.0, 2.0]))
+    got = logits.cpu().numpy()
+    want0 = base.copy()
+    want0[49] = base[49] / 2.0 - 0.5 * 2 - 0.25            # positive logit: divided
+    want0[3] = base[3] * 2.0 - 0.5 * 1 - 0.25              # negative logit: multiplied
+    assert np.allclose(got[0], want0, atol=1e-6)
+    assert np.allclose(got[1], 2.0 * np.tanh(base / 2.0), atol=1e-6)

@@ -1,0 +1,210 @@
+"""Each part alone against the plain function of the same part, and a toy mixer with state of its own
+that is registered, built and stepped without a change to the package's files."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+import replay_util as ru
+from conftest import TINY, random_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rt(dtype=torch.float32):
+    from mimirmind_b200.engine.loader import make_runtime
+    return make_runtime(dtype)
+
+
+def t(a, dtype=torch.float32):
+    return torch.as_tensor(np.asarray(a)).to(DEV).to(dtype).contiguous()
+
+
+def test_norm_part():
+    from mimirmind_b200.config.spec import PartSpec
+    from mimirmind_b200.parts.base import WeightView
+    from mimirmind_b200.parts.norm import RMSNorm
+    rng = np.random.RandomState(0)
+    w = rng.randn(100)
+    spec = PartSpec("rmsnorm", {"width": 100, "eps": 1e-3, "weight": "n.weight"})
+    assert [s.name for s in RMSNorm.tensor_specs(spec, "p.")] == ["p.n.weight"]
+    part = RMSNorm(spec, WeightView({"p.n.weight": t(w)}, "p."), rt())
+    x, d = rng.randn(4, 100), rng.randn(4, 100)
+    res = t(x)
+    y = part.forward(res, t(d))
+    assert np.abs(y.cpu().numpy() - plain.rms_norm(x + d, w, 1e-3)).max() < 1e-5
+    assert np.abs(res.cpu().numpy() - (x + d)).max() < 1e-6
+
+
+def test_feed_forward_part():
+    from mimirmind_b200.config.spec import PartSpec
+    from mimirmind_b200.parts.base import WeightView
+    from mimirmind_b200.parts.mlp import SwiGLU
+    rng = np.random.RandomState(1)
+    d, F = 72, 200
+    Wg, Wu, Wd = rng.randn(F, d) * 0.1, rng.randn(F, d) * 0.1, rng.randn(d, F) * 0.1
+    spec = PartSpec("swiglu", {"hidden": d, "intermediate": F, "gate": "g", "up": "u", "down": "d"})
+    part = SwiGLU(spec, WeightView({"g": t(Wg), "u": t(Wu), "d": t(Wd)}), rt())
+    x = rng.randn(9, d)
+    y = part.forward(t(x), None)
+    ref = plain.swiglu(x, Wg, Wu, Wd)
+    assert np.abs(y.cpu().numpy() - ref).max() < 1e-5 * max(1, np.abs(ref).max())
+
+
+def test_embedding_and_head_parts():
+    from mimirmind_b200.config.spec import PartSpec
+    from mimirmind_b200.parts.base import WeightView
+    from mimirmind_b200.parts.embedding import LMHead, TokenEmbedding
+    rng = np.random.RandomState(2)
+    E = rng.randn(50, 24)
+    weights = {"emb": t(E)}
+    emb = TokenEmbedding(PartSpec("token_embedding", {"vocab": 50, "width": 24, "scale": 2.0, "weight": "emb"}), WeightView(weights), rt())
+    ids = torch.tensor([3, 49, 0], dtype=torch.int32, device=DEV)
+    assert np.allclose(emb.forward(ids).cpu().numpy(), 2.0 * E[[3, 49, 0]], atol=1e-6)
+    tied = LMHead(PartSpec("lm_head", {"vocab": 50, "width": 24, "weight": "head", "tied_to": "emb"}), WeightView(weights), rt())
+    x = rng.randn(2, 24)
+    assert np.abs(tied.forward(t(x)).cpu().numpy() - x @ E.T).max() < 1e-4
+    with pytest.raises(KeyError, match="head"):
+        LMHead(PartSpec("lm_head", {"vocab": 50, "width": 24, "weight": "head", "tied_to": None}), WeightView(weights), rt())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_part_alone(dtype):
+    """The mixer with its own cache view: two portions of one sequence against plain attention."""
+    from mimirmind_b200.config.spec import PartSpec
+    from mimirmind_b200.parts.attention import GQAAttention
+    from mimirmind_b200.parts.base import LayerCache, StepContext, WeightView
+    rng = np.random.RandomState(3)
+    d, H, G, hd, ps, theta, W = 96, 6, 2, 64, 16, 5000.0, 40
+    names = {"q": "q", "k": "k", "v": "v", "o": "o"}
+    spec = PartSpec("gqa_attention", dict(hidden=d, num_heads=H, num_kv_heads=G, head_dim=hd, window=W, scale=None,
+                                          qkv_bias=True, position=PartSpec("rotary_half", {"theta": theta, "rotary_dim": hd}), **names))
+    w = {"q.weight": rng.randn(H * hd, d) * 0.1, "k.weight": rng.randn(G * hd, d) * 0.1, "v.weight": rng.randn(G * hd, d) * 0.1,
+         "o.weight": rng.randn(d, H * hd) * 0.1, "q.bias": rng.randn(H * hd) * 0.1, "k.bias": rng.randn(G * hd) * 0.1,
+         "v.bias": rng.randn(G * hd) * 0.1}
+    if dtype == torch.bfloat16:
+        w = {k: torch.as_tensor(v, dtype=torch.float32).to(torch.bfloat16).double().numpy() for k, v in w.items()}
+    part = GQAAttention(spec, WeightView({k: t(v, dtype) for k, v in w.items()}), rt(dtype))
+    assert part.kv_cache_spec().window == W and part.state_spec() is None
+    T = 150
+    x = rng.randn(T, d)
+    if dtype == torch.bfloat16:
+        x = torch.as_tensor(x, dtype=torch.float32).to(torch.bfloat16).double().numpy()
+    pos = np.arange(T)
+    q = plain.rope(plain.linear(x, w["q.weight"], w["q.bias"]).reshape(T, H, hd), pos, theta)
+    k = plain.rope(plain.linear(x, w["k.weight"], w["k.bias"]).reshape(T, G, hd), pos, theta)
+    v = plain.linear(x, w["v.weight"], w["v.bias"]).reshape(T, G, hd)
+    ref = plain.linear(plain.attention(q, k, v, W).reshape(T, H * hd), w["o.weight"])
+    pages = 12
+    kp = torch.zeros((pages, G, ps, hd), dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    table = torch.tensor([[7, 2, 9, 0, 11, 4, 1, 8, 3, 10]], dtype=torch.int32, device=DEV)
+    outs = []
+    for lo, hi in ((0, 100), (100, 103), (103, 150)):
+        n = hi - lo
+        ctx = StepContext(n_tokens=n, n_requests=1, token_ids=None, positions=t(np.arange(lo, hi), torch.int32),
+                          token_req=torch.zeros(n, dtype=torch.int32, device=DEV), q_start=[0], q_len=[n], kv_len=[hi],
+                          req_meta=None, state_slots=None, block_tables={}, logit_rows=None, n_logit_rows=0, page_size=ps,
+                          runtime=part.rt, max_kv_len=hi, max_q_len=n)
+        cache = LayerCache(k_pages=kp, v_pages=vp, block_table=table, page_size=ps)
+        outs.append(part.forward(t(x[lo:hi], dtype), ctx, cache).float().cpu().numpy())
+    got = np.concatenate(outs)
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    assert np.abs(got - ref).max() <= tol * np.abs(ref).max()
+
+
+# ---- a toy mixer with state of its own ---------------------------------------------------------------
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    """A running-mean mixer: out_t = W · mean(x_0..x_t).  Its per-request state (sum, count) lives in the
+    cache manager's state slots.  Only registry calls are used; no file of the package changes."""
+    from mimirmind_b200 import registry
+    from mimirmind_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+    from mimirmind_b200.engine.loader import make_runtime
+    from mimirmind_b200.engine.model import Model
+    from mimirmind_b200.engine.runner import ModelRunner, StepEntry
+    from mimirmind_b200.parts.base import Mixer, StateSpec
+    from mimirmind_b200.weights.store import expected_tensors, random_tensors
+    registry._ensure_builtin()
+
+    @registry.MIXERS.register("toy_running_mean", replace=True)
+    class RunningMean(Mixer):
+        @classmethod
+        def tensor_specs(cls, spec, prefix):
+            return [TensorSpec(prefix + "mix.weight", (spec["hidden"], spec["hidden"]))]
+
+        def __init__(self, spec, weights, rt):
+            super().__init__(spec, weights, rt)
+            self.d = spec["hidden"]
+            self.w = weights.get("mix.weight")
+
+        def state_spec(self):
+            return StateSpec((self.d + 1,), torch.float32)          # running sum and count
+
+        def forward(self, x, ctx, cache):
+            out = torch.empty_like(x)
+            for r in range(ctx.n_requests):                         # a request's tokens in order
+                s, n = ctx.q_start[r], ctx.q_len[r]
+                slot = int(ctx.state_slots[r])
+                st = cache.state[slot]
+                xs = x[s:s + n].float()
+                csum = st[:self.d] + torch.cumsum(xs, dim=0)
+                cnt = st[self.d] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                out[s:s + n] = ((csum / cnt[:, None]) @ self.w.float().t()).to(x.dtype)
+                st[:self.d] = csum[-1]
+                st[self.d] = cnt[-1]
+            return out
+
+    def toy_spec(cfg):
+        d = cfg["hidden_size"]
+        norm = lambda name: PartSpec("rmsnorm", {"width": d, "eps": 1e-5, "weight": name})
+        attn = PartSpec("gqa_attention", dict(hidden=d, num_heads=2, num_kv_heads=1, head_dim=16, window=0, scale=None, qkv_bias=False,
+                                              position=PartSpec("rotary_half", {"theta": 100.0, "rotary_dim": 8}),
+                                              q="q", k="k", v="v", o="o"))
+        ffn = PartSpec("swiglu", {"hidden": d, "intermediate": 40, "gate": "g.weight", "up": "u.weight", "down": "d.weight"})
+        layers = (
+            LayerSpec("l0.", PartSpec("pre_norm"), PartSpec("toy_running_mean", {"hidden": d}), ffn, norm("n1"), norm("n2")),
+            LayerSpec("l1.", PartSpec("pre_norm"), attn, ffn, norm("n1"), norm("n2")),
+        )
+        # layer 0 runs twice (second time with state of its own), layer 1 once
+        return ModelSpec("ToyForTest", d, cfg["vocab_size"], 512, PartSpec("token_embedding", {"vocab": cfg["vocab_size"], "width": d, "scale": 1.0, "weight": "emb"}),
+                         layers, (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0)), norm("nf"),
+                         PartSpec("lm_head", {"vocab": cfg["vocab_size"], "width": d, "weight": "head", "tied_to": "emb"}))
+
+    registry.register_architecture("ToyForTest", lambda obj, where="": obj, toy_spec, replace=True)
+    try:
+        entry = registry.get_architecture("ToyForTest")
+        spec = entry.build_spec(entry.parse_config({"hidden_size": 32, "vocab_size": 90}))
+        assert "l0.mix.weight" in expected_tensors(spec)
+        rt_ = make_runtime("float32")
+        model = Model(spec, random_tensors(spec, 5, torch.float32, rt_.device), rt_)
+        assert sorted(model.state_specs()) == [0, 2] and len(model.cache_groups()) == 1
+        assert model.cache_groups()[0].entries == (1,)
+
+        def run(cuts, rid, runner):
+            runner.add_request(rid)
+            outs, p = [], 0
+            for c in cuts:
+                outs.append(runner.step([StepEntry(rid, toks[p:p + c], list(range(c)))]).cpu().numpy())
+                p += c
+            return np.concatenate(outs)
+
+        toks = random_tokens(90, 60, 1)
+        runner = ModelRunner(model, 16, 16, 4)
+        whole = run([60], "a", runner)
+        parts = run([7, 1, 1, 30, 2, 19], "b", runner)             # state carries over between portions
+        assert np.abs(whole - parts).max() < 1e-5
+        runner.release("a")
+        again = run([60], "c", runner)                              # takes a's slot: it must start from zero
+        assert runner.manager.slot("c") == 0
+        assert np.abs(whole - again).max() < 1e-6
+        # two requests in one batch keep separate state
+        runner.add_request("d"); runner.add_request("e")
+        other = random_tokens(90, 60, 2)
+        both = runner.step([StepEntry("d", toks, [59]), StepEntry("e", other, [59])]).cpu().numpy()
+        assert np.abs(both[0] - whole[59]).max() < 1e-5
+        assert np.abs(both[1] - whole[59]).max() > 1e-3
+    finally:
+        registry.MIXERS.unregister("toy_running_mean")
+        registry.ARCHITECTURES.unregister("ToyForTest")
