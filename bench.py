@@ -1,0 +1,262 @@
+#!/usr/bin/env python3
+"""Benchmark: decode and prefill throughput of the Qwen2.5-7B-shaped model on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 (device-timed over K
+graph replays of the decode step, 2,048-token prompts, context 4,096, page size 16, random
+bfloat16 weights, seeded uniform-random token ids); ``e2e`` is the same through
+``Engine.generate`` with host token lists in and out; ``prefill`` is one 2,048-token prompt in
+one step; ``roofline`` relates the decode step to the measured HBM bandwidth; ``points`` adds
+batch 1 and 64.  A "step" is one decode step.  This engine runs on one GPU: for N > 1 it says
+so and exits with 2.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the Qwen2.5-7B-shaped benchmark model and workload.
+MODEL_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=28, hidden_size=3584,
+                num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944, vocab_size=152064,
+                rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096,
+                use_sliding_window=False, torch_dtype="bfloat16")
+PROMPT_LEN = 2048
+CONTEXT = 4096
+PAGE_SIZE = 16
+BATCH = 8
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]),
+                    bf16_tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, since: int = 0):
+        rows = self.samples[since:]
+        sm = sorted(float(r[0]) for r in rows if r[0].replace(".", "").isdigit())
+        reasons = []
+        for i, name in enumerate(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")):
+            if any(r[3 + i].lower().startswith("active") for r in rows):
+                reasons.append(name)
+        mx = max((float(r[1]) for r in rows if r[1].replace(".", "").isdigit()), default=0.0)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": reasons, "samples": len(rows)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+                    help="run one phase only and print its timing (for profiling small cases)")
+    ap.add_argument("--batch", type=int, default=BATCH, help="decode batch size of --only decode")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a C++/CMake program without a Python package: pip cannot install it offline "
+                          "(no setup.py/pyproject), and its engine for this architecture reads 4-bit GGUF files only"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+
+    import torch
+    from mimirmind_b200.engine.decode_graph import DecodeSession
+    from mimirmind_b200.engine.engine import Engine
+    from mimirmind_b200.engine.loader import random_model
+    from mimirmind_b200.engine.runner import StepEntry
+    from mimirmind_b200.kernels import lib as kernel_lib
+    from mimirmind_b200.registry import get_architecture
+    import numpy as np
+
+    torch.cuda.set_device(0)
+    peaks = load_peaks()
+    cfg_json = dict(MODEL_7B)
+    full_layers = cfg_json["num_hidden_layers"]
+    if args.layers:
+        cfg_json["num_hidden_layers"] = args.layers
+    arch = get_architecture(cfg_json["architectures"][0])
+    mcfg = arch.parse_config(cfg_json, "bench")
+    spec = arch.build_spec(mcfg)
+    kernel_lib.load(verbose=True)
+    model = random_model(spec, seed=0, dtype="bfloat16")
+    L, d, F, V = mcfg.num_hidden_layers, mcfg.hidden_size, mcfg.intermediate_size, mcfg.vocab_size
+    qs, kvs = mcfg.q_size, mcfg.kv_size
+    layer_params = d * (qs + 2 * kvs) + (qs + 2 * kvs) + qs * d + 3 * d * F + 2 * d
+    weight_bytes = 2 * (L * layer_params + d + V * d)               # every weight a decode step uses, once
+    kv_bytes_per_token = 2 * L * kvs * 2
+
+    max_batch = 64
+    # token budget: all prompts of the batch are prefilled in one step, so that the end-to-end run is
+    # pure decoding after the first token, like the device-timed run
+    engine = Engine(model, page_size=PAGE_SIZE, cache_tokens=max_batch * CONTEXT, max_context=CONTEXT,
+                    token_budget=BATCH * PROMPT_LEN, max_active=max_batch)
+    runner = engine.runner
+    rng = np.random.RandomState(0)
+    prompts = [rng.randint(0, V, size=PROMPT_LEN).tolist() for _ in range(max_batch)]
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    clocks = ClockSampler()
+    clocks.start()
+
+    # ---- prefill: one 2,048-token prompt in one step ---------------------------------------
+    def prefill_once(rid, toks):
+        runner.add_request(rid)
+        return runner.step([StepEntry(rid, toks, [len(toks) - 1])])
+
+    for i in range(0 if args.only == "decode" else 3):
+        prefill_once(("warm", i), prompts[i])
+        runner.release(("warm", i))
+    torch.cuda.synchronize()
+    times = []
+    for i in range(1 if args.only else 5):
+        a, b = ev(), ev()
+        torch.cuda.synchronize()
+        a.record()
+        prefill_once(("pf", i), prompts[i])
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+        runner.release(("pf", i))
+    pf_ms = sorted(times)[len(times) // 2]
+    T = PROMPT_LEN
+    pf_flops = 2.0 * T * L * (d * (qs + 2 * kvs) + qs * d + 3 * d * F) + 2.0 * d * V \
+        + L * 2.0 * 2.0 * qs * (T * (T + 1) / 2)                     # causal attention: QK^T and PV
+    prefill = {"value": T / (pf_ms * 1e-3), "tokens": T, "ms": pf_ms,
+               "frac": pf_flops / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), "tflops": pf_flops / (pf_ms * 1e-3) / 1e12}
+
+    # ---- decode at a batch size: prompts prefilled, then W + K steps of the captured step ---------
+    def decode_run(batch, k_steps, w_steps):
+        ids = [("dec", batch, i) for i in range(batch)]
+        firsts = []
+        for rid, toks in zip(ids, prompts[:batch]):
+            lg = prefill_once(rid, toks)
+            firsts.append(int(lg.argmax(-1).item()))
+        sess = DecodeSession(runner, batch, CONTEXT, greedy=True, feed_back=True)
+        sess.bind(ids, w_steps + k_steps, firsts)
+        before = kernel_lib.LAUNCH_CALLS
+        sess.step()                                   # eager + capture
+        per_step_calls = (kernel_lib.LAUNCH_CALLS - before) // 2
+        for _ in range(w_steps - 1):
+            sess.step()
+        torch.cuda.synchronize()
+        mark = len(clocks.samples)
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(k_steps):
+            sess.step()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / k_steps
+        kv_tokens = sum(runner.length(r) for r in ids) - batch * k_steps // 2   # mean over the timed steps
+        for r in ids:
+            runner.release(r)
+        return ms, per_step_calls, kv_tokens, mark
+
+    if args.only == "prefill":
+        clocks.stop()
+        print(json.dumps({"only": "prefill", "ms": pf_ms, "tflops": prefill["tflops"], "layers": L}))
+        return 0
+    if args.only == "decode":
+        ms, calls, _, _ = decode_run(args.batch, steps, warmup)
+        clocks.stop()
+        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": ms, "launches_per_step": calls, "layers": L}))
+        return 0
+    ms8, calls, kv_tokens, mark = decode_run(BATCH, steps, warmup)
+    clock_summary = clocks.summary(mark)
+    value = BATCH / (ms8 * 1e-3)
+    step_bytes = weight_bytes + kv_tokens * kv_bytes_per_token + BATCH * d * 2
+    achieved = step_bytes / (ms8 * 1e-3) / 1e9
+    points = {}
+    if not args.no_points:
+        for b, k in ((1, max(16, steps // 2)), (64, max(16, steps // 2))):
+            ms, _, _, _ = decode_run(b, k, warmup)
+            points[f"decode_b{b}"] = b / (ms * 1e-3)
+
+    # ---- end to end: Engine.generate, host token lists in and out ------------------------------
+    n_new = steps + 1
+    engine.generate(prompts[:BATCH], max_new_tokens=max(engine.graph_min_steps + 1, min(n_new, 12)), use_eos=False)   # warm-up: captures the graph
+    h0, d0, g0 = engine.h2d_bytes, engine.d2h_bytes, engine.graph_steps
+    res = engine.generate(prompts[:BATCH], max_new_tokens=n_new, use_eos=False)
+    gen = sum(r.stats.generated_tokens - 1 for r in res)
+    dec_ms = max(r.stats.decode_ms for r in res)
+    graph_steps = max(1, engine.graph_steps - g0)
+    e2e = {"value": gen / (dec_ms * 1e-3) if dec_ms > 0 else None, "unit": "tokens/s",
+           "h2d_bytes_per_step": (engine.h2d_bytes - h0) / graph_steps, "d2h_bytes_per_step": (engine.d2h_bytes - d0) / graph_steps,
+           "graph_steps": graph_steps}
+    clocks.stop()
+
+    out = {
+        "metric": "decode tokens/s, Qwen2.5-7B-shaped bf16, batch 8, 2048-token prompts (context 4096)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms8,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random bf16 weights, uniform-random token ids",
+        "config": {"model": "Qwen2.5-7B-shaped", "layers": L, "layers_of_config": full_layers, "hidden": d, "heads": mcfg.num_attention_heads,
+                   "kv_heads": mcfg.num_key_value_heads, "head_dim": mcfg.head_dim, "intermediate": F, "vocab": V,
+                   "global_batch": BATCH, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE_SIZE,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 15 GB per step)",
+                   "decode": "CUDA graph of the step, greedy sampling on device"},
+        "e2e": e2e, "gpu_launches": calls * steps, "launches_per_step": calls,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm_gbs"], "bytes_per_step": step_bytes, "peaks": peaks["source"]},
+        "points": points, "clocks": clock_summary,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

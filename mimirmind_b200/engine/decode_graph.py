@@ -1,0 +1,150 @@
+"""Steady-state decoding of a fixed set of requests as one replayed CUDA graph.
+
+When every running request is decoding, a step is the same sequence of launches with the
+same shapes each time: only token ids, positions and block-table entries change, and they
+live in device buffers the graph reads.  The step (forward, sampling, position advance) is
+captured once per (batch size, context bound, sampling kind) and replayed, which removes
+the per-launch host cost of ~10 kernels per layer.  The reference has graph replay of its
+decode blocks as an opt-in (src/runtime/InferenceEngine.cpp:1826-1842, 1944-1998) and names
+the missing default as its largest single-user gap (doc/perf-notes-gb10.md:135-138).
+
+A session is *bound* to a set of requests for a number of steps (the horizon); pages for
+the whole horizon are reserved at binding, so the tables are final and no host work is
+needed between replays except committing lengths.  The buffers and the captured graph
+outlive the binding and serve the next set of requests of the same shape.
+"""
+from __future__ import annotations
+
+from typing import Hashable, List, Optional, Sequence
+
+import torch
+
+from ..kernels import ops
+from ..parts.base import StepContext
+from ..sampling.params import SamplingParams
+from .runner import ModelRunner
+
+
+def context_bound(n: int, floor: int = 256) -> int:
+    """Smallest power of two >= n (at least ``floor``): the bucket a session's buffers are sized for."""
+    b = floor
+    while b < n:
+        b *= 2
+    return b
+
+
+class DecodeSession:
+    def __init__(self, runner: ModelRunner, batch: int, kv_bound: int, greedy: bool = True, feed_back: bool = True):
+        """``kv_bound``: no bound request may grow beyond this many tokens.  ``feed_back``: the graph writes
+        each sampled token into the next step's input itself; otherwise the caller fills ``token_ids``
+        before every step."""
+        self.runner = runner
+        self.batch = batch
+        self.kv_bound = min(kv_bound, runner.max_seq_len)
+        self.greedy = greedy
+        self.feed_back = feed_back
+        dev, ps = runner.rt.device, runner.page_size
+        self.width = max(1, (self.kv_bound + ps - 1) // ps)
+        b = batch
+        self.token_ids = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.positions = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.slots = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.tables = {g: torch.full((b, self.width), -1, dtype=torch.int32, device=dev) for g in runner.manager.groups}
+        ar = torch.arange(b, dtype=torch.int32, device=dev)
+        self.ctx = StepContext(
+            n_tokens=b, n_requests=b, token_ids=self.token_ids, positions=self.positions, token_req=ar,
+            q_start=list(range(b)), q_len=[1] * b, kv_len=[self.kv_bound] * b, req_meta=None, state_slots=self.slots,
+            block_tables=self.tables, logit_rows=ar, n_logit_rows=b, page_size=ps, runtime=runner.rt,
+            max_kv_len=self.kv_bound, max_q_len=1)
+        self.out_tokens = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.logits: Optional[torch.Tensor] = None
+        if not greedy:
+            self.temperature = torch.zeros(b, dtype=torch.float32, device=dev)
+            self.top_k = torch.zeros(b, dtype=torch.int32, device=dev)
+            self.top_p = torch.ones(b, dtype=torch.float32, device=dev)
+            self.seeds = torch.zeros(b, dtype=torch.int64, device=dev)
+            self.counters = torch.zeros(b, dtype=torch.int64, device=dev)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.ids: List[Hashable] = []
+        self.horizon = 0
+        self.steps_done = 0
+
+    # ---- binding -----------------------------------------------------------------------
+    def bind(self, request_ids: Sequence[Hashable], horizon: int, first_tokens: Sequence[int],
+             sampling: Optional[Sequence[SamplingParams]] = None, draw_counters: Optional[Sequence[int]] = None) -> None:
+        """Points the session at ``request_ids`` for ``horizon`` steps.  Raises MemoryError (and changes
+        nothing) when the pages for the horizon are not free, ValueError when the bound is too small."""
+        mgr, dev = self.runner.manager, self.runner.rt.device
+        if len(request_ids) != self.batch:
+            raise ValueError("wrong number of requests for this session")
+        lengths = [mgr.length(r) for r in request_ids]
+        finals = [n + horizon for n in lengths]
+        if max(finals) > self.kv_bound:
+            raise ValueError(f"requests would grow to {max(finals)} tokens, the session is bound to {self.kv_bound}")
+        need = {g: 0 for g in mgr.groups}
+        for rid, fl in zip(request_ids, finals):
+            for g, n in mgr.pages_needed(rid, fl).items():
+                need[g] += n
+        for g, n in need.items():
+            if n > mgr.free_pages(g):
+                raise MemoryError(f"decode session needs {n} pages in group {g}, {mgr.free_pages(g)} are free")
+        for rid, fl in zip(request_ids, finals):
+            ok = mgr.reserve(rid, fl)
+            assert ok
+        self.ids, self.horizon, self.steps_done = list(request_ids), horizon, 0
+        for g in mgr.groups:
+            t = torch.full((self.batch, self.width), -1, dtype=torch.int32)
+            for i, rid in enumerate(self.ids):
+                tab = mgr.table(rid, g)[:self.width]
+                t[i, :len(tab)] = torch.tensor(tab, dtype=torch.int32)
+            self.tables[g].copy_(t.to(dev, non_blocking=False))
+        self.positions.copy_(torch.tensor(lengths, dtype=torch.int32))
+        self.slots.copy_(torch.tensor([mgr.slot(r) for r in self.ids], dtype=torch.int32))
+        self.token_ids.copy_(torch.tensor(list(first_tokens), dtype=torch.int32))
+        if not self.greedy:
+            params = list(sampling)
+            self.temperature.copy_(torch.tensor([0.0 if p.greedy else p.temperature for p in params], dtype=torch.float32))
+            self.top_k.copy_(torch.tensor([p.top_k for p in params], dtype=torch.int32))
+            self.top_p.copy_(torch.tensor([p.top_p for p in params], dtype=torch.float32))
+            self.seeds.copy_(torch.tensor([p.seed & 0x7FFFFFFFFFFFFFFF for p in params], dtype=torch.int64))
+            self.counters.copy_(torch.tensor(list(draw_counters or [0] * self.batch), dtype=torch.int64))
+
+    # ---- one step's launches --------------------------------------------------------------
+    def _launch(self) -> None:
+        self.logits = self.runner.forward(self.ctx)
+        if self.greedy:
+            ops.argmax_rows(self.logits, self.out_tokens)
+        else:
+            ops.sample_rows(self.logits, self.temperature, self.top_k, self.top_p, self.seeds, self.counters, self.out_tokens)
+            self.counters += 1
+        self.positions += 1
+        if self.feed_back:
+            self.token_ids.copy_(self.out_tokens)
+
+    def step(self) -> torch.Tensor:
+        """One decode step for every bound request; returns the device tensor of sampled tokens (valid
+        until the next step).  The first step ever runs eagerly and is then captured."""
+        if self.steps_done >= self.horizon:
+            raise RuntimeError("decode session is past its horizon")
+        if self.graph is None:
+            self.ctx.plans.clear()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._launch()        # warms up every kernel and library workspace on a non-default stream
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):   # records the launches; nothing runs, buffers keep their contents
+                self._launch()
+            self.graph = graph
+        else:
+            self.graph.replay()
+        mgr = self.runner.manager
+        for rid in self.ids:
+            mgr.commit(rid, mgr.length(rid) + 1)
+        self.steps_done += 1
+        return self.out_tokens
+
+    def remaining(self) -> int:
+        return self.horizon - self.steps_done

@@ -16,6 +16,7 @@ from typing import Callable, Dict, Hashable, List, Optional, Sequence
 import torch
 
 from ..sampling import Sampler, SamplingParams
+from .decode_graph import DecodeSession, context_bound
 from .loader import load_model, random_model
 from .model import Model
 from .runner import ModelRunner, StepEntry
@@ -43,7 +44,7 @@ class GenerateResult:
 
 class Engine:
     def __init__(self, model: Model, *, page_size: int = 16, cache_tokens: int = 0, max_context: int = 8192,
-                 token_budget: int = 512, max_active: int = 32, prefill_chunk: int = 0):
+                 token_budget: int = 512, max_active: int = 32, prefill_chunk: int = 0, use_graphs: bool = True):
         self.model = model
         max_context = min(max_context, model.spec.max_positions)
         if cache_tokens <= 0:
@@ -56,6 +57,12 @@ class Engine:
         self.sampler = Sampler(model.rt.device)
         self.eos_ids = tuple(model.spec.eos_token_ids)
         self.last_metrics = None
+        self.use_graphs = use_graphs
+        self.graph_min_steps = 8            # shorter decode runs are stepped eagerly
+        self._sessions: Dict[tuple, DecodeSession] = {}
+        self.graph_steps = 0                # decode steps that were graph replays (statistics)
+        self.h2d_bytes = 0                  # bytes copied host→device / device→host by generate()
+        self.d2h_bytes = 0
 
     # ---- construction ----------------------------------------------------------------
     @classmethod
@@ -100,6 +107,8 @@ class Engine:
         for r in reqs:
             sched.add(r)
         while sched.has_work():
+            if self.use_graphs and sched.all_decoding() and self._decode_run(sched, first_at, last_at, on_token):
+                continue
             plan = sched.schedule()
             if not plan:
                 if sched.has_work():
@@ -130,6 +139,62 @@ class Engine:
             out.append(GenerateResult(list(r.generated), st))
         return out
 
+    def _decode_run(self, sched: Scheduler, first_at, last_at, on_token) -> bool:
+        """Runs the current set of decoding requests through a captured graph until one of them finishes
+        or the horizon ends.  Returns False (nothing done) when a graph run is not possible or not worth it."""
+        reqs = list(sched.running)
+        if any(r.sampling.penalties_active or r.sampling.final_logit_softcap > 0 for r in reqs):
+            return False
+        mgr = self.runner.manager
+        horizon = min(min(r.max_new - len(r.generated) for r in reqs),
+                      min(self.sched_cfg.max_seq_len - len(r.tokens) for r in reqs))
+        if horizon < self.graph_min_steps:
+            return False
+        longest = max(len(r.tokens) for r in reqs)
+        bound = context_bound(longest + horizon)
+        if bound > self.runner.max_seq_len:
+            bound = self.runner.max_seq_len
+        greedy = all(r.sampling.greedy for r in reqs)
+        key = (len(reqs), bound, greedy)
+        sess = self._sessions.get(key)
+        if sess is None:
+            sess = DecodeSession(self.runner, len(reqs), bound, greedy=greedy, feed_back=False)
+            self._sessions[key] = sess
+        ids = [r.id for r in reqs]
+        firsts = [r.tokens[-1] for r in reqs]
+        while True:
+            try:
+                sess.bind(ids, horizon, firsts, [r.sampling for r in reqs], [len(r.generated) for r in reqs])
+                break
+            except MemoryError:
+                horizon //= 2          # fewer pages ahead; below the threshold the eager path (and preemption) decides
+                if horizon < self.graph_min_steps:
+                    return False
+        host_in = torch.empty(len(reqs), dtype=torch.int32, pin_memory=True)
+        host_out = torch.empty(len(reqs), dtype=torch.int32, pin_memory=True)
+        finished = False
+        while not finished and sess.remaining() > 0:
+            out = sess.step()
+            host_out.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            self.d2h_bytes += host_out.numel() * 4
+            self.graph_steps += 1
+            now = time.perf_counter()
+            toks = host_out.tolist()
+            for r, tok in zip(reqs, toks):
+                first_at.setdefault(r.id, now)
+                last_at[r.id] = now
+                done = sched.accept_token(r, tok)
+                finished |= done
+                if on_token is not None and on_token(r.id[1], tok) is False and not done:
+                    sched.cancel(r.id)
+                    finished = True
+            if not finished and sess.remaining() > 0:
+                host_in.copy_(host_out)
+                sess.token_ids.copy_(host_in, non_blocking=True)      # next step's inputs, from pinned memory
+                self.h2d_bytes += host_in.numel() * 4
+        return True
+
     def _run_plan(self, plan: Sequence[PlannedEntry]) -> Dict[Hashable, int]:
         entries = [StepEntry(p.request.id, p.tokens, [p.count - 1] if p.samples else []) for p in plan]
         ctx = self.runner._build_context(entries)
@@ -144,6 +209,7 @@ class Engine:
                                        [len(p.request.generated) for p in rows],
                                        [p.request.tokens for p in rows])
             host = toks.cpu().tolist()
+            self.d2h_bytes += 4 * len(host)
             for p, t in zip(rows, host):
                 sampled[p.request.id] = t
         return sampled

@@ -227,24 +227,34 @@ class Scheduler:
             self.manager.commit(req.id, p.start + p.count)
             if not p.samples:
                 continue
-            tok = int(sampled[req.id])
-            req.tokens.append(tok)
-            req.generated.append(tok)
-            reason = None
-            if tok in req.stop_ids:
-                reason = "stop"
-            elif len(req.generated) >= req.max_new:
-                reason = "length"
-            elif len(req.tokens) >= self.cfg.max_seq_len:
-                reason = "context"
-            if reason is not None:
-                req.state, req.finish_reason = FINISHED, reason
-                self.manager.release(req.id)
-                self.running.remove(req)
-                self.finished.append(req)
-                self.metrics.finished += 1
+            if self.accept_token(req, int(sampled[req.id])):
                 done.append(req)
         return done
+
+    def accept_token(self, req: Request, tok: int) -> bool:
+        """Appends a sampled token to a running request whose cache length is already advanced; retires
+        the request and frees its pages if it is finished.  Returns True when it finished."""
+        req.tokens.append(tok)
+        req.generated.append(tok)
+        reason = None
+        if tok in req.stop_ids:
+            reason = "stop"
+        elif len(req.generated) >= req.max_new:
+            reason = "length"
+        elif len(req.tokens) >= self.cfg.max_seq_len:
+            reason = "context"
+        if reason is None:
+            return False
+        req.state, req.finish_reason = FINISHED, reason
+        self.manager.release(req.id)
+        self.running.remove(req)
+        self.finished.append(req)
+        self.metrics.finished += 1
+        return True
+
+    def all_decoding(self) -> bool:
+        """Nothing waits and every running request has exactly its last token left to feed."""
+        return bool(self.running) and not self.waiting and all(self._remaining(r) == 1 for r in self.running)
 
     def cancel(self, rid: Hashable) -> bool:
         for req in list(self.running):

@@ -71,7 +71,12 @@ def declare(name: str, argtypes, restype=c_int):
     return fn
 
 
+LAUNCH_CALLS = 0   # entry points called so far (each launches one kernel, the split attention two)
+
+
 def check(code: int, what: str) -> None:
+    global LAUNCH_CALLS
+    LAUNCH_CALLS += 1
     if code != 0:
         msg = load().mm_last_error().decode("utf-8", "replace")
         raise KernelError(f"{what} failed (code {code}): {msg}")
