@@ -525,3 +525,59 @@ MM_EXPORT int mm_attention_decode_bf16(const void* q, const void* k_pages, const
     mm_set_last_error("attention_decode: the tensor-core kernel is built for head_dim 64 and 128");
     return MM_ERR_UNSUPPORTED;
 }
+
+// ---------------------------------------------------------------------------
+// Split-key decode attention for callers that cannot allocate (see no_alloc.h).
+// ---------------------------------------------------------------------------
+#include "no_alloc.h"
+#include <stdio.h>
+
+// The scratch of the no-allocation entry point.  In host code this name is only a handle
+// for cudaGetSymbolAddress: it is not a device address and must never be passed to a kernel.
+static __device__ __align__(256) float g_no_alloc_scratch[MM_NO_ALLOC_SCRATCH_FLOATS];
+
+#define MM_NO_ALLOC_MAX_DEVICES 64
+static float* g_no_alloc_scratch_ptr[MM_NO_ALLOC_MAX_DEVICES];   // device address of the array, per device
+
+MM_EXPORT int mm_attention_decode_bf16_no_alloc(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                                const void* items, int n_items, const void* positions,
+                                                const void* token_req, const void* block_table, int table_width,
+                                                int page_size, int H, int G, int hd, int window, float scale,
+                                                int split_len, int max_splits, void* stream) {
+    MM_REQUIRE(n_items >= 0 && H > 0 && hd > 0 && max_splits >= 1, "attention_decode_no_alloc: bad sizes");
+    float* part_o = nullptr;
+    float* part_ml = nullptr;
+    if (max_splits > 1) {
+        const long long rows = (long long)n_items * H * max_splits;
+        const long long need = rows * ((long long)hd + 2);
+        if (need > (long long)MM_NO_ALLOC_SCRATCH_FLOATS) {
+            char msg[256];
+            snprintf(msg, sizeof(msg),
+                     "attention_decode_no_alloc: this call needs %lld floats of scratch (items %d x heads %d x splits %d x "
+                     "(head_dim %d + 2)), the built-in scratch holds %d",
+                     need, n_items, H, max_splits, hd, (int)MM_NO_ALLOC_SCRATCH_FLOATS);
+            mm_set_last_error(msg);
+            return MM_ERR_BAD_ARG;
+        }
+        int dev = -1;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MM_NO_ALLOC_MAX_DEVICES) {
+            mm_set_last_error("attention_decode_no_alloc: no current CUDA device (or its index is above 63)");
+            return MM_ERR_DRIVER;
+        }
+        if (g_no_alloc_scratch_ptr[dev] == nullptr) {
+            // one-time set-up for this device, with this device current
+            void* p = nullptr;
+            const cudaError_t e = cudaGetSymbolAddress(&p, g_no_alloc_scratch);
+            if (e != cudaSuccess || p == nullptr) {
+                mm_set_last_error(cudaGetErrorString(e));
+                return MM_ERR_DRIVER;
+            }
+            g_no_alloc_scratch_ptr[dev] = (float*)p;
+        }
+        part_o = g_no_alloc_scratch_ptr[dev];        // [rows, hd]
+        part_ml = part_o + rows * hd;                // [rows, 2]; rows * hd * 4 bytes is a multiple of 8
+    }
+    return mm_attention_decode_bf16(q, k_pages, v_pages, out, part_o, part_ml, items, n_items, positions, token_req,
+                                    block_table, table_width, page_size, H, G, hd, window, scale, split_len, max_splits,
+                                    stream);
+}
