@@ -19,6 +19,7 @@
 
 #define KT 64            // keys per tile
 #define ATT_THREADS 128  // 4 warps
+#define DEC_STAGES 3     // K/V tiles in flight per CTA of the decode kernel
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -48,26 +49,57 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Gathers 64 key rows (or value rows) of one KV head into shared memory [64][HD + 8].
-// Rows outside [lo, hi) are zero-filled so that masked probabilities multiply zeros.
+// Gathers 64 key rows and the same 64 value rows of one KV head into shared memory
+// [64][HD + 8] each.  The page of a row is looked up once for both.  Rows outside [lo, hi)
+// are zero-filled so that masked probabilities multiply zeros.
 template <int HD>
-__device__ __forceinline__ void load_tile(__nv_bfloat16* dst, const __nv_bfloat16* __restrict__ pool,
-                                          const int32_t* __restrict__ table, int key0, int lo, int hi, int G, int g,
-                                          int page_size) {
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dK, __nv_bfloat16* dV, const __nv_bfloat16* __restrict__ kpool,
+                                             const __nv_bfloat16* __restrict__ vpool, const int32_t* __restrict__ table,
+                                             int key0, int lo, int hi, int G, int g, int page_size, int page_shift) {
     constexpr int STRIDE = HD + 8;
-    constexpr int CHUNKS = HD / 8;  // 16-byte chunks per row
-    for (int c = threadIdx.x; c < KT * CHUNKS; c += ATT_THREADS) {
-        const int r = c / CHUNKS, part = c - r * CHUNKS;
+    constexpr int CHUNKS = HD / 8;                     // 16-byte chunks per row
+    constexpr int ROWS_PER_PASS = ATT_THREADS / CHUNKS;
+    const int part = threadIdx.x % CHUNKS;
+#pragma unroll
+    for (int r = threadIdx.x / CHUNKS; r < KT; r += ROWS_PER_PASS) {
         const int key = key0 + r;
-        __nv_bfloat16* d = dst + r * STRIDE + part * 8;
+        __nv_bfloat16* dk = dK + r * STRIDE + part * 8;
+        __nv_bfloat16* dv = dV + r * STRIDE + part * 8;
         if (key >= lo && key < hi) {
-            const int page = table[key / page_size];
-            const __nv_bfloat16* src = pool + (((size_t)page * G + g) * page_size + (key % page_size)) * HD + part * 8;
-            cp_async16(d, src);
+            const int pidx = page_shift >= 0 ? (key >> page_shift) : (key / page_size);
+            const int slot = key - pidx * page_size;
+            const size_t off = (((size_t)table[pidx] * G + g) * page_size + slot) * HD + part * 8;
+            cp_async16(dk, kpool + off);
+            cp_async16(dv, vpool + off);
         } else {
-            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
         }
     }
+}
+
+// How a token's key range [lo, hi) is cut into splits.  split_len > 0: by absolute position,
+// split s covers [s*split_len, (s+1)*split_len).  split_len == 0: the range (from lo rounded
+// down to a tile) is cut evenly into at most max_splits pieces of whole tiles, so that every
+// token uses the whole grid whatever its length.
+struct SplitInfo {
+    int first, last, len, base;
+};
+__device__ __forceinline__ SplitInfo split_info(int lo, int hi, int split_len, int max_splits) {
+    SplitInfo s;
+    if (split_len > 0) {
+        s.first = lo / split_len;
+        s.last = (hi - 1) / split_len;
+        s.len = split_len;
+        s.base = 0;
+    } else {
+        s.base = (lo / KT) * KT;
+        const int span = hi - s.base;
+        s.len = ((span + max_splits - 1) / max_splits + KT - 1) / KT * KT;
+        s.first = 0;
+        s.last = (span - 1) / s.len;
+    }
+    return s;
 }
 
 // ---------------------------------------------------------------------------
@@ -106,8 +138,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_prefill_kernel(
         *reinterpret_cast<uint4*>(sQ + r * STRIDE + part * 8) = v;
     }
     // first K/V tile
-    load_tile<HD>(sK, k_pages, table, kt_begin * KT, lo_all, hi_all, G, g, page_size);
-    load_tile<HD>(sV, v_pages, table, kt_begin * KT, lo_all, hi_all, G, g, page_size);
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+    load_kv_tile<HD>(sK, sV, k_pages, v_pages, table, kt_begin * KT, lo_all, hi_all, G, g, page_size, page_shift);
     cp_async_commit();
     __syncthreads();
 
@@ -134,8 +166,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_prefill_kernel(
     for (int kt = kt_begin; kt < kt_end; ++kt) {
         const int buf = (kt - kt_begin) & 1;
         if (kt + 1 < kt_end) {
-            load_tile<HD>(sK + (buf ^ 1) * KT * STRIDE, k_pages, table, (kt + 1) * KT, lo_all, hi_all, G, g, page_size);
-            load_tile<HD>(sV + (buf ^ 1) * KT * STRIDE, v_pages, table, (kt + 1) * KT, lo_all, hi_all, G, g, page_size);
+            load_kv_tile<HD>(sK + (buf ^ 1) * KT * STRIDE, sV + (buf ^ 1) * KT * STRIDE, k_pages, v_pages, table, (kt + 1) * KT,
+                             lo_all, hi_all, G, g, page_size, page_shift);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -250,26 +282,32 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(
     constexpr int KSTEPS = HD / 16;
     constexpr int NT_O = HD / 8;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][64][STRIDE]
-    __nv_bfloat16* sV = sK + 2 * KT * STRIDE;                        // [2][64][STRIDE]
+    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [DEC_STAGES][64][STRIDE]
+    __nv_bfloat16* sV = sK + DEC_STAGES * KT * STRIDE;               // [DEC_STAGES][64][STRIDE]
 
     const int item = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
     const int t = items ? items[item] : item;
     const int pos = positions[t];
     const int hi = pos + 1;
     const int lo = (window > 0 && hi > window) ? hi - window : 0;
-    const int first_split = lo / split_len, last_split = (hi - 1) / split_len;
-    if (split < first_split || split > last_split) return;
-    const bool single = first_split == last_split;
-    const int k_begin = max(lo, split * split_len), k_end = min(hi, (split + 1) * split_len);
+    const SplitInfo sp = split_info(lo, hi, split_len, max_splits);
+    if (split < sp.first || split > sp.last) return;
+    const bool single = sp.first == sp.last;
+    const int k_begin = max(lo, sp.base + split * sp.len), k_end = min(hi, sp.base + (split + 1) * sp.len);
     const int kt_begin = k_begin / KT, kt_end = (k_end + KT - 1) / KT;
     const int32_t* table = block_table + (size_t)token_req[t] * table_width;
     const int qpg = H / G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
-    load_tile<HD>(sK, k_pages, table, kt_begin * KT, k_begin, k_end, G, g, page_size);
-    load_tile<HD>(sV, v_pages, table, kt_begin * KT, k_begin, k_end, G, g, page_size);
-    cp_async_commit();
+    // prologue: the first DEC_STAGES - 1 tiles, one commit group each (empty groups keep the count uniform)
+#pragma unroll
+    for (int st = 0; st < DEC_STAGES - 1; ++st) {
+        if (kt_begin + st < kt_end)
+            load_kv_tile<HD>(sK + st * KT * STRIDE, sV + st * KT * STRIDE, k_pages, v_pages, table, (kt_begin + st) * KT,
+                             k_begin, k_end, G, g, page_size, page_shift);
+        cp_async_commit();
+    }
 
     // Q fragments: rows are the query heads of this KV head (rows >= qpg are zero)
     uint32_t qf[KSTEPS][4];
@@ -292,14 +330,16 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
 
     for (int kt = kt_begin; kt < kt_end; ++kt) {
-        const int buf = (kt - kt_begin) & 1;
-        if (kt + 1 < kt_end) {
-            load_tile<HD>(sK + (buf ^ 1) * KT * STRIDE, k_pages, table, (kt + 1) * KT, k_begin, k_end, G, g, page_size);
-            load_tile<HD>(sV + (buf ^ 1) * KT * STRIDE, v_pages, table, (kt + 1) * KT, k_begin, k_end, G, g, page_size);
+        const int buf = (kt - kt_begin) % DEC_STAGES;
+        {
+            const int nxt = kt + DEC_STAGES - 1;
+            if (nxt < kt_end) {
+                const int nb = (nxt - kt_begin) % DEC_STAGES;
+                load_kv_tile<HD>(sK + nb * KT * STRIDE, sV + nb * KT * STRIDE, k_pages, v_pages, table, nxt * KT, k_begin, k_end,
+                                 G, g, page_size, page_shift);
+            }
             cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
+            cp_async_wait<DEC_STAGES - 1>();
         }
         __syncthreads();
         const __nv_bfloat16* tK = sK + buf * KT * STRIDE + warp * 16 * STRIDE;   // this warp's 16 keys
@@ -367,6 +407,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
 
+    cp_async_wait<0>();
     // merge the four warps through shared memory (the K/V buffers are free now)
     float* mo = reinterpret_cast<float*>(smem_raw);         // [4][16][HD]
     float* mml = mo + 4 * 16 * HD;                          // [4][16][2]
@@ -425,7 +466,8 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
     const int t = items ? items[item] : item;
     const int hi = positions[t] + 1;
     const int lo = (window > 0 && hi > window) ? hi - window : 0;
-    const int first_split = lo / split_len, last_split = (hi - 1) / split_len;
+    const SplitInfo sp = split_info(lo, hi, split_len, max_splits);
+    const int first_split = sp.first, last_split = sp.last;
     if (first_split == last_split) return;   // written by the attention kernel itself
     const size_t base = ((size_t)item * H + h) * max_splits;
     float m = -INFINITY;
@@ -480,7 +522,7 @@ static int launch_decode(const void* q, const void* k, const void* v, void* out,
                          const void* items, int n_items, const void* positions, const void* token_req,
                          const void* table, int table_width, int page_size, int H, int G, int window, float scale,
                          int split_len, int max_splits, cudaStream_t s) {
-    size_t smem = (size_t)(4 * KT) * (HD + 8) * sizeof(__nv_bfloat16);
+    size_t smem = (size_t)(2 * DEC_STAGES * KT) * (HD + 8) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float);
     if (merge > smem) smem = merge;
     static bool configured = false;
@@ -506,7 +548,9 @@ static int launch_decode(const void* q, const void* k, const void* v, void* out,
 }
 
 // Scratch: part_o needs n_items*H*max_splits*hd floats, part_ml n_items*H*max_splits*2 floats
-// (both may be null when max_splits == 1).  max_splits must cover ceil(max position + 1 / split_len).
+// (both may be null when max_splits == 1).  With split_len > 0, max_splits must cover
+// ceil((max position + 1) / split_len); with split_len == 0 each token's range is cut evenly into
+// at most max_splits pieces.
 MM_EXPORT int mm_attention_decode_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, void* part_o,
                                        void* part_ml, const void* items, int n_items, const void* positions,
                                        const void* token_req, const void* block_table, int table_width, int page_size,
@@ -515,7 +559,7 @@ MM_EXPORT int mm_attention_decode_bf16(const void* q, const void* k_pages, const
     MM_REQUIRE(n_items >= 0 && H > 0 && G > 0 && H % G == 0, "attention_decode: bad head counts");
     MM_REQUIRE(H / G <= 16, "attention_decode: more than 16 query heads per KV head");
     MM_REQUIRE(page_size > 0 && table_width > 0 && window >= 0, "attention_decode: bad page geometry or window");
-    MM_REQUIRE(split_len > 0 && split_len % KT == 0 && max_splits >= 1 && max_splits <= 65535, "attention_decode: split_len must be a positive multiple of 64");
+    MM_REQUIRE(split_len >= 0 && split_len % KT == 0 && max_splits >= 1 && max_splits <= 65535, "attention_decode: split_len must be 0 (even cut) or a positive multiple of 64");
     MM_REQUIRE(max_splits == 1 || (part_o != nullptr && part_ml != nullptr), "attention_decode: scratch missing");
     MM_REQUIRE(G <= 65535, "attention_decode: too many KV heads");
     if (n_items == 0) return MM_OK;

@@ -91,6 +91,67 @@ MM_EXPORT int mm_argmax_rows(const void* logits, void* out, int R, int V, void* 
     return MM_OK;
 }
 
+// Two stages for wide rows: P blocks per row find (max, lowest index) of their slice, then one
+// block per row reduces the P pairs.  `part` holds R*P pairs of (float value, int index).
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ part_val,
+                                      int32_t* __restrict__ part_idx, int V, int P) {
+    const int r = blockIdx.y, p = blockIdx.x;
+    const int chunk = (V + P - 1) / P;
+    const int begin = p * chunk, end = min(V, begin + chunk);
+    const float* row = logits + (size_t)r * V;
+    __shared__ ArgmaxPair red[32];
+    ArgmaxPair best{-INFINITY, 0x7fffffff};
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = row[i];
+        if (v > best.v || (v == best.v && i < best.i)) best = ArgmaxPair{v, i};
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgmaxPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) red[warp] = best;
+    __syncthreads();
+    if (warp == 0) {
+        ArgmaxPair b = (lane < (int)(blockDim.x >> 5)) ? red[lane] : ArgmaxPair{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgmaxPair other{__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+            b = better(b, other);
+        }
+        if (lane == 0) {
+            part_val[(size_t)r * P + p] = b.v;
+            part_idx[(size_t)r * P + p] = b.i;
+        }
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int32_t* __restrict__ part_idx,
+                                    int32_t* __restrict__ out, int P) {
+    const int r = blockIdx.x, lane = threadIdx.x;
+    ArgmaxPair best{-INFINITY, 0x7fffffff};
+    for (int p = lane; p < P; p += 32) best = better(best, ArgmaxPair{part_val[(size_t)r * P + p], part_idx[(size_t)r * P + p]});
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgmaxPair other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+        best = better(best, other);
+    }
+    if (lane == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
+}
+
+MM_EXPORT int mm_argmax_rows_split(const void* logits, void* out, void* part_val, void* part_idx, int R, int V, int P,
+                                   void* stream) {
+    MM_REQUIRE(R >= 0 && V > 0 && P >= 1 && P <= 1024 && R <= 65535, "argmax: bad sizes");
+    if (R == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    argmax_partial_kernel<<<dim3(P, R), 256, 0, s>>>((const float*)logits, (float*)part_val, (int32_t*)part_idx, V, P);
+    MM_CHECK_LAUNCH();
+    argmax_final_kernel<<<R, 32, 0, s>>>((const float*)part_val, (const int32_t*)part_idx, (int32_t*)out, P);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
 // ---- radix select over weighted candidates -----------------------------------
 // Candidates are the elements with key >= floor_key.  In the order (key descending,
 // index ascending) find the first element whose cumulative weight exceeds `target`.

@@ -21,8 +21,8 @@ from .lib import check
 
 PREFILL_MIN = 16       # shorter portions go token by token through the decode kernel
 TILE_ROWS = 64
-MIN_SPLIT = 128
-TARGET_CTAS = 2 * 148
+TARGET_CTAS = 4 * 148  # decode CTAs wanted in flight: three fit on an SM
+FIXED_SPLIT = None     # tests set a split length in keys to cut by absolute position instead
 
 _declared = False
 
@@ -54,11 +54,12 @@ class AttentionPlan:
 
 
 def choose_split(n_items: int, num_kv_heads: int, max_kv_len: int):
-    """Split length (a multiple of 64) and the number of splits that cover ``max_kv_len`` keys."""
+    """(split_len, max_splits) for the decode kernel.  split_len 0: every token's key range is cut evenly
+    into at most max_splits pieces of whole 64-key tiles, so the grid is full whatever the lengths."""
+    if FIXED_SPLIT:
+        return FIXED_SPLIT, max(1, -(-max_kv_len // FIXED_SPLIT))
     wanted = max(1, -(-TARGET_CTAS // max(1, n_items * num_kv_heads)))
-    per = -(-max_kv_len // wanted)
-    split_len = max(MIN_SPLIT, -(-per // 64) * 64)
-    return split_len, max(1, -(-max_kv_len // split_len))
+    return 0, max(1, min(wanted, -(-max_kv_len // 64)))
 
 
 def make_plan(ctx, num_heads: int, num_kv_heads: int, head_dim: int) -> AttentionPlan:
@@ -76,7 +77,7 @@ def make_plan(ctx, num_heads: int, num_kv_heads: int, head_dim: int) -> Attentio
         d_items = None
     else:
         d_items = torch.tensor(items, dtype=torch.int32, device=device) if items else None
-    split_len, max_splits = choose_split(len(items), num_kv_heads, ctx.max_kv_len) if items else (MIN_SPLIT, 1)
+    split_len, max_splits = choose_split(len(items), num_kv_heads, ctx.max_kv_len) if items else (0, 1)
     plan = AttentionPlan(d_tiles, len(tiles), d_items, len(items), split_len, max_splits)
     if items and max_splits > 1:
         plan.part_o = torch.empty((len(items), num_heads, max_splits, head_dim), dtype=torch.float32, device=device)

@@ -36,6 +36,7 @@ _PROTOTYPES = {
     "mm_attention_generic": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
     "mm_gemm_simt": [P, I, P, I, P, I, P, I, I, I, I, I, I, P],
     "mm_argmax_rows": [P, P, I, I, P],
+    "mm_argmax_rows_split": [P, P, P, P, I, I, I, P],
     "mm_sample_rows": [P, P, I, I, P, P, P, P, P, P],
     "mm_apply_penalties": [P, I, I, P, I, P, P, P, P, P],
 }

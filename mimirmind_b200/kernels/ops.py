@@ -194,6 +194,14 @@ def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> tor
     if out is None:
         out = torch.empty(r, dtype=torch.int32, device=logits.device)
     _need(out, "argmax out", torch.int32)
+    if v > 16384:
+        # wide rows: several blocks per row, then one to reduce them
+        p = min(256, -(-v // 4096))
+        part_val = torch.empty((r, p), dtype=torch.float32, device=logits.device)
+        part_idx = torch.empty((r, p), dtype=torch.int32, device=logits.device)
+        check(_lib.load().mm_argmax_rows_split(logits.data_ptr(), out.data_ptr(), part_val.data_ptr(), part_idx.data_ptr(),
+                                               r, v, p, _stream()), "argmax_rows_split")
+        return out
     check(_lib.load().mm_argmax_rows(logits.data_ptr(), out.data_ptr(), r, v, _stream()), "argmax_rows")
     return out
 
