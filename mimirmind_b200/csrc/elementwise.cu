@@ -135,31 +135,37 @@ MM_EXPORT int mm_add_residual(void* residual, const void* delta, int act_dtype, 
 }
 
 // ---------------------------------------------------------------------------
-// SiLU(gate) * up over a [n, 2F] buffer holding gate in columns [0,F) and up in [F,2F)
+// SiLU(gate) * up over a [n, 2F] buffer.  interleave == 0: gate in columns [0,F), up in
+// [F,2F).  interleave == 8: blocks of 8 gate columns alternate with blocks of 8 up columns
+// (gate f at (f/8)*16 + f%8, up f eight columns later), the layout of the fused weight.
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int F) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int F, int interleave) {
     const size_t total = (size_t)n * F;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
         const size_t row = i / F, col = i - row * F;
-        const float g = to_f32<T>(gu[row * 2 * F + col]);
-        const float u = to_f32<T>(gu[row * 2 * F + F + col]);
+        const size_t gc = interleave ? (col / 8) * 16 + col % 8 : col;
+        const size_t uc = interleave ? gc + 8 : F + col;
+        const float g = to_f32<T>(gu[row * 2 * F + gc]);
+        const float u = to_f32<T>(gu[row * 2 * F + uc]);
         out[i] = from_f32<T>(g / (1.0f + expf(-g)) * u);
     }
 }
 
 // 8 bf16 values per thread when F is a multiple of 8
-__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int n, int F) {
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int n, int F, int interleave) {
     const int F8 = F / 8;
     const size_t total = (size_t)n * F8;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; i < total; i += stride) {
         const size_t row = i / F8, c8 = i - row * F8;
-        const uint4 gv = *reinterpret_cast<const uint4*>(gu + row * 2 * F + c8 * 8);
-        const uint4 uv = *reinterpret_cast<const uint4*>(gu + row * 2 * F + F + c8 * 8);
+        const size_t gc = interleave ? c8 * 16 : c8 * 8;
+        const size_t uc = interleave ? gc + 8 : (size_t)F + c8 * 8;
+        const uint4 gv = *reinterpret_cast<const uint4*>(gu + row * 2 * F + gc);
+        const uint4 uv = *reinterpret_cast<const uint4*>(gu + row * 2 * F + uc);
         const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
         const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
         uint4 ov;
@@ -177,19 +183,20 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __n
     }
 }
 
-MM_EXPORT int mm_silu_mul(const void* gu, void* out, int act_dtype, int n, int F, void* stream) {
+MM_EXPORT int mm_silu_mul(const void* gu, void* out, int act_dtype, int n, int F, int interleave, void* stream) {
     MM_REQUIRE(n >= 0 && F > 0, "silu_mul: bad sizes");
+    MM_REQUIRE(interleave == 0 || (interleave == 8 && F % 8 == 0), "silu_mul: interleave must be 0, or 8 with F a multiple of 8");
     if (n == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t total = (size_t)n * F;
     if (act_dtype == MM_BF16 && F % 8 == 0) {
         const size_t work = total / 8;
         const int blocks = (int)((work + 255) / 256 < 148 * 32 ? (work + 255) / 256 : 148 * 32);
-        silu_mul_bf16x8_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F);
+        silu_mul_bf16x8_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F, interleave);
     } else {
         const int blocks = (int)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
-        if (act_dtype == MM_F32) silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, n, F);
-        else if (act_dtype == MM_BF16) silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F);
+        if (act_dtype == MM_F32) silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, n, F, interleave);
+        else if (act_dtype == MM_BF16) silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F, interleave);
         else MM_REQUIRE(false, "silu_mul: dtype must be float32 or bfloat16");
     }
     MM_CHECK_LAUNCH();

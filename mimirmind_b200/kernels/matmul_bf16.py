@@ -1,6 +1,7 @@
 """bfloat16 matrix products y = x · Wᵀ (+ bias) on the tensor cores.
 
-The library route is cuBLAS through ``torch.mm`` (the reference's bf16 library route is
+Up to 16 rows go to this library's weight-streaming kernel (csrc/gemv_bf16.cu).  Beyond that the
+library route is cuBLAS through ``torch.mm`` (the reference's bf16 library route is
 cuBLASLt, src/compute/cuda/GpuMatmul.cpp:786-884); accumulation is fp32 inside the
 product and the result is rounded once to the requested dtype.
 """
@@ -12,6 +13,9 @@ import torch
 
 
 def matmul_nt(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    from . import ops
+    if ops.gemv_supported(x.shape[0], weight.shape[0], weight.shape[1]):
+        return ops.gemv_bf16(x, weight, bias, out_dtype)          # a handful of rows: weight streaming
     if out_dtype == torch.float32:
         y = torch.mm(x, weight.t(), out_dtype=torch.float32)
         if bias is not None:

@@ -38,12 +38,25 @@ class SwiGLU(FeedForward):
         up = weights.take(spec["up"])
         if gate.dtype != up.dtype:
             gate, up = gate.float(), up.float()
-        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()  # [2F, d]
+        f, d = gate.shape
+        # Interleave gate and up rows in blocks of 8 (rows 16j..16j+7 = gate[8j..], 16j+8..16j+15 = up[8j..]):
+        # a tensor-core tile then holds a gate value and its up value together, so the activation can be
+        # an epilogue of the product.  Plain concatenation when the width is not a multiple of 8.
+        self.interleave = 8 if f % 8 == 0 else 0
+        if self.interleave:
+            self.w_gate_up = torch.stack([gate.view(f // 8, 8, d), up.view(f // 8, 8, d)], dim=1).reshape(2 * f, d).contiguous()
+        else:
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()  # [2F, d]
         del gate, up
         self.w_down = weights.take(spec["down"]).contiguous()       # [d, F]
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        gu = linear(x, self.w_gate_up, None, self.rt)
-        act = torch.empty((x.shape[0], self.intermediate), dtype=x.dtype, device=x.device)
-        ops.silu_mul(gu, act)
+        m = x.shape[0]
+        if (self.interleave and x.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and self.rt.matmul != "simt"
+                and ops.gemv_supported(m, 2 * self.intermediate, self.hidden)):
+            act = ops.gemv_bf16(x, self.w_gate_up, None, x.dtype, swiglu=True)    # product and activation in one kernel
+        else:
+            gu = linear(x, self.w_gate_up, None, self.rt)
+            act = torch.empty((m, self.intermediate), dtype=x.dtype, device=x.device)
+            ops.silu_mul(gu, act, self.interleave)
         return linear(act, self.w_down, None, self.rt)

@@ -373,3 +373,65 @@ def test_penalties_and_softcap():
     want0[3] = base[3] * 2.0 - 0.5 * 1 - 0.25              # negative logit: multiplied
     assert np.allclose(got[0], want0, atol=1e-6)
     assert np.allclose(got[1], 2.0 * np.tanh(base / 2.0), atol=1e-6)
+
+
+# ---- weight-streaming products for a handful of rows ----------------------------------------------
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K", [(4608, 3584), (3584, 18944), (160, 256), (1008, 96 * 32), (152064 // 8, 3584)])
+def test_gemv_bf16(M, N, K):
+    rng = np.random.RandomState(M + N + K)
+    x, w, b = t(rng.randn(M, K), torch.bfloat16), t(rng.randn(N, K) * 0.05, torch.bfloat16), t(rng.randn(N), torch.bfloat16)
+    ref = x.double().cpu().numpy() @ w.double().cpu().numpy().T + b.double().cpu().numpy()
+    got32 = ops().gemv_bf16(x, w, b, torch.float32).cpu().numpy()
+    assert np.abs(got32 - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
+    got16 = ops().gemv_bf16(x, w, b, torch.bfloat16).float().cpu().numpy()
+    assert np.abs(got16 - ref).max() <= 2 ** -8 * np.abs(ref).max()
+    nob = ops().gemv_bf16(x, w, None, torch.float32).cpu().numpy()
+    assert np.abs(nob - (ref - b.double().cpu().numpy())).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
+    # a row's result does not depend on the other rows of the batch
+    alone = ops().gemv_bf16(x[M - 1:M].contiguous(), w, b, torch.float32).cpu().numpy()
+    assert np.array_equal(alone[0], got32[M - 1])
+
+
+@pytest.mark.parametrize("M,F,K", [(1, 18944, 3584), (8, 352, 256), (5, 1000, 512)])
+def test_gemv_swiglu_epilogue_and_interleaved_silu(M, F, K):
+    rng = np.random.RandomState(F)
+    gate, up = rng.randn(F, K) * 0.05, rng.randn(F, K) * 0.05
+    x = t(rng.randn(M, K), torch.bfloat16)
+    gate_t, up_t = t(gate, torch.bfloat16), t(up, torch.bfloat16)
+    w = torch.stack([gate_t.view(F // 8, 8, K), up_t.view(F // 8, 8, K)], dim=1).reshape(2 * F, K).contiguous()
+    g = x.double().cpu().numpy() @ gate_t.double().cpu().numpy().T
+    u = x.double().cpu().numpy() @ up_t.double().cpu().numpy().T
+    ref = g / (1 + np.exp(-g)) * u
+    got = ops().gemv_bf16(x, w, None, torch.bfloat16, swiglu=True).float().cpu().numpy()
+    assert got.shape == (M, F)
+    assert np.abs(got - ref).max() <= 2 ** -8 * np.abs(ref).max() + 1e-6
+    # the unfused route over the same interleaved weight: product, then the activation kernel
+    gu = ops().gemv_bf16(x, w, None, torch.bfloat16)
+    act = torch.empty((M, F), dtype=torch.bfloat16, device=DEV)
+    ops().silu_mul(gu, act, 8)
+    assert np.abs(act.float().cpu().numpy() - ref).max() <= 3 * 2 ** -8 * np.abs(ref).max() + 1e-6
+
+
+def test_gemv_refuses_unsupported_shapes():
+    from mimirmind_b200.kernels.lib import KernelError
+    assert not ops().gemv_supported(9, 64, 256) and not ops().gemv_supported(4, 60, 256) and not ops().gemv_supported(4, 64, 100)
+    with pytest.raises(KernelError):
+        ops().gemv_bf16(torch.zeros((4, 100), dtype=torch.bfloat16, device=DEV), torch.zeros((64, 100), dtype=torch.bfloat16, device=DEV), None, torch.float32)
+
+
+@pytest.mark.parametrize("M,rt,ks", [(12, 2, 4), (16, 1, 8), (7, 4, 2), (8, 8, 1)])
+def test_gemv_all_layouts_of_the_kernel(M, rt, ks):
+    """Row-tile / K-split arrangements and the two-tile (up to 16 rows) variant that the dispatcher
+    does not pick by default."""
+    from mimirmind_b200.kernels import lib
+    rng = np.random.RandomState(M)
+    N, K = 272, 1504
+    x, w = t(rng.randn(M, K), torch.bfloat16), t(rng.randn(N, K) * 0.05, torch.bfloat16)
+    out = torch.zeros((M, N), dtype=torch.float32, device=DEV)
+    L = lib.load()
+    rc = L.mm_gemv_bf16(w.data_ptr(), x.data_ptr(), None, 0, out.data_ptr(), 0, M, N, K, K, N, rt, ks, 0,
+                        torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, L.mm_last_error()
+    ref = x.double().cpu().numpy() @ w.double().cpu().numpy().T
+    assert np.abs(out.cpu().numpy() - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
