@@ -1,0 +1,366 @@
+// C[M,N] = A[M,K] * W[N,K]^T in bfloat16 on the fifth-generation tensor cores of sm_100a:
+// operands staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle), products
+// issued by one thread with tcgen05.mma (UMMA 128x256x16, cta_group::1), accumulators in
+// tensor memory (two 256-column accumulators so the epilogue of one tile overlaps the main
+// loop of the next), read back with tcgen05.ld by four epilogue warps.
+//
+// Persistent, warp-specialised: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
+// warps 2..5 = epilogue.  Tiles are walked M-fastest so that CTAs working at the same time
+// share a weight tile in L2.
+//
+// Epilogues (fused, so the product's output makes one trip to memory):
+//   0  store bf16 (+ bias)
+//   1  SwiGLU: columns interleave gate and up in blocks of 8 (the fused gate/up weight);
+//      writes silu(gate) * up, [M, N/2] bf16
+//   2  store fp32 (+ bias)
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the kernel raises an abort
+// flag that all roles watch, lets copies in flight land, frees its tensor memory, writes an
+// error code to `err` and returns, so a fault in the pipeline can never hang the GPU.
+//
+// The reference's counterparts are its wmma 16x16x16 bf16 kernel, one warp per output tile and
+// no pipelining (kernels/cuda/common/matmul_bf16_gemm_tc.cu:37-99), and its cuBLASLt route
+// (src/compute/cuda/GpuMatmul.cpp:786-884).
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 512;
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait (non-blocking test in a counted loop).  Returns false if the limit ran out or another role raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (it > 64u) __nanosleep(40);            // test_wait never blocks, so the limit bounds the time: under 2 s
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile written by TMA with 128-byte swizzle: rows
+// of 64 bf16 (128 bytes), groups of 8 rows 1024 bytes apart (SBO), version 1, layout SWIZZLE_128B.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                    // leading byte offset (unused with swizzle), 16 B
+    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset: 8 rows x 128 B
+    d |= (uint64_t)1 << 46;                    // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
+    return d;
+}
+
+// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N = 256, M = 128.
+constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(IDESC), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
+struct SharedCtl {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ out,
+                    const void* __restrict__ bias, int bias_dtype, int M, int N, int K, int ldo, int* __restrict__ err) {
+    extern __shared__ unsigned char smem_raw[];
+    // 128-byte swizzle wants 1024-byte aligned tiles
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + STAGES * STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &ctl->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&ctl->full[s]), 1);
+            mbar_init(smem_u32(&ctl->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
+            mbar_init(smem_u32(&ctl->tmem_empty[a]), 4);   // one arrival per epilogue warp
+        }
+        ctl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN, k_blocks = (K + BK - 1) / BK;
+    const int total = m_tiles * n_tiles;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ----
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t full = smem_u32(&ctl->full[s]);
+                    mbar_expect_tx(full, STAGE_BYTES);
+                    const uint32_t a_dst = smem_u32(tiles + s * STAGE_BYTES);
+                    tma_load_2d(a_dst, &tmA, kb * BK, m0, full);
+                    tma_load_2d(a_dst + A_BYTES, &tmB, kb * BK, n0, full);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++local) {
+                const uint32_t acc = local & 1, acc_ph = (local >> 1) & 1;
+                if (!mbar_wait(smem_u32(&ctl->tmem_empty[acc]), acc_ph ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(smem_u32(&ctl->full[s]), ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES);
+                    const uint64_t a_desc = make_desc(a_addr), b_desc = make_desc(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // advancing 16 elements (32 bytes) along K inside the swizzled row: +2 in the address field
+                        umma(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), (kb | k) ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&ctl->empty[s]));      // the stage is free once these products have read it
+                }
+                if (ok) umma_commit(smem_u32(&ctl->tmem_full[acc]));
+            }
+        }
+    } else {
+        // ---- epilogue: warp w reads TMEM lanes 32*(w%4) .. +31 ----
+        const int q = warp & 3;
+        uint32_t local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++local) {
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            const uint32_t acc = local & 1, acc_ph = (local >> 1) & 1;
+            if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_ph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int col0 = n0 + c * 32;
+                if (col0 >= N) break;                      // uniform over the warp
+                uint32_t r[32];
+                tmem_ld32(taddr + c * 32, r);
+                if (row >= M) continue;
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                if (EPI != EPI_SWIGLU && bias != nullptr) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + i < N)
+                            v[i] += (bias_dtype == MM_F32) ? ((const float*)bias)[col0 + i] : __bfloat162float(((const __nv_bfloat16*)bias)[col0 + i]);
+                }
+                if (EPI == EPI_BF16) {
+                    __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)row * ldo + col0;
+                    if (col0 + 32 <= N) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            *reinterpret_cast<uint4*>(o + i * 8) = make_uint4(pack2(v[i * 8], v[i * 8 + 1]), pack2(v[i * 8 + 2], v[i * 8 + 3]),
+                                                                              pack2(v[i * 8 + 4], v[i * 8 + 5]), pack2(v[i * 8 + 6], v[i * 8 + 7]));
+                    } else {
+                        for (int i = 0; i < 32 && col0 + i < N; ++i) o[i] = __float2bfloat16_rn(v[i]);
+                    }
+                } else if (EPI == EPI_F32) {
+                    float* o = (float*)out + (size_t)row * ldo + col0;
+                    if (col0 + 32 <= N) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) *reinterpret_cast<float4*>(o + i * 4) = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
+                    } else {
+                        for (int i = 0; i < 32 && col0 + i < N; ++i) o[i] = v[i];
+                    }
+                } else {
+                    // columns: 8 gate, 8 up, 8 gate, 8 up  ->  16 outputs
+                    __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)row * ldo + col0 / 2;
+                    float a[16];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        a[i] = silu_mul(v[i], v[8 + i]);
+                        a[8 + i] = silu_mul(v[16 + i], v[24 + i]);
+                    }
+                    if (col0 + 32 <= N) {
+#pragma unroll
+                        for (int i = 0; i < 2; ++i)
+                            *reinterpret_cast<uint4*>(o + i * 8) = make_uint4(pack2(a[i * 8], a[i * 8 + 1]), pack2(a[i * 8 + 2], a[i * 8 + 3]),
+                                                                              pack2(a[i * 8 + 4], a[i * 8 + 5]), pack2(a[i * 8 + 6], a[i * 8 + 7]));
+                    } else {
+                        for (int i = 0; i < 16 && col0 + (i / 8) * 16 + 8 + (i % 8) < N; ++i) o[i] = __float2bfloat16_rn(a[i]);
+                    }
+                }
+            }
+            // the accumulator may be overwritten once all four warps have read it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
+        }
+    }
+
+    // ---- teardown ----
+    if (*abort_flag) {
+        // give copies and products in flight time to land before the tensor memory is given back
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (threadIdx.x == 0 && ctl->abort_flag && err != nullptr) atomicExch(err, 1);
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// rows x K bf16 matrix, row stride ld elements; box = box_rows x 64 elements, 128-byte swizzle, zero fill outside
+bool make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (enc == nullptr) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int EPI>
+int launch(const CUtensorMap& a, const CUtensorMap& b, void* out, const void* bias, int bias_dtype, int M, int N, int K,
+           int ldo, int* err, int max_ctas, cudaStream_t s) {
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + sizeof(SharedCtl);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            mm_set_last_error("gemm_tcgen05: cannot reserve shared memory");
+            return MM_ERR_LAUNCH;
+        }
+        configured = true;
+    }
+    const int total = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = total < max_ctas ? total : max_ctas;
+    gemm_tcgen05_kernel<EPI><<<grid, GEMM_THREADS, smem, s>>>(a, b, out, bias, bias_dtype, M, N, K, ldo, err);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+}  // namespace
+
+// A [M, lda] bf16 (K leading columns used), W [N, K] bf16, out [M, ldo] (bf16, fp32, or with the SwiGLU epilogue bf16
+// [M, N/2]).  `err`: device int set to 1 if a bounded wait ran out (may be null).
+MM_EXPORT int mm_gemm_tcgen05(const void* A, const void* W, const void* bias, int bias_dtype, void* out, int epilogue, int M,
+                              int N, int K, int lda, int ldo, void* err, void* stream) {
+    MM_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes");
+    MM_REQUIRE(K % 8 == 0 && lda % 8 == 0 && lda >= K, "gemm_tcgen05: K and the row stride of A must be multiples of 8 (16-byte TMA rows)");
+    MM_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && ((uintptr_t)out & 15) == 0, "gemm_tcgen05: pointers must be 16-byte aligned");
+    MM_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tcgen05: unknown epilogue");
+    MM_REQUIRE(epilogue != EPI_SWIGLU || (N % 16 == 0 && bias == nullptr && ldo >= N / 2), "gemm_tcgen05: the SwiGLU epilogue needs N a multiple of 16 and no bias");
+    MM_REQUIRE(ldo % 8 == 0 && (epilogue == EPI_SWIGLU || ldo >= N), "gemm_tcgen05: the row stride of the output must be a multiple of 8 and at least N");
+    CUtensorMap ta, tb;
+    if (!make_map(&ta, A, M, K, lda, BM) || !make_map(&tb, W, N, K, K, BN)) {
+        mm_set_last_error("gemm_tcgen05: cuTensorMapEncodeTiled failed or is not available");
+        return MM_ERR_DRIVER;
+    }
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (epilogue == EPI_BF16) return launch<EPI_BF16>(ta, tb, out, bias, bias_dtype, M, N, K, ldo, (int*)err, sms, s);
+    if (epilogue == EPI_SWIGLU) return launch<EPI_SWIGLU>(ta, tb, out, bias, bias_dtype, M, N, K, ldo, (int*)err, sms, s);
+    return launch<EPI_F32>(ta, tb, out, bias, bias_dtype, M, N, K, ldo, (int*)err, sms, s);
+}

@@ -31,6 +31,7 @@ _PROTOTYPES = {
     "mm_add_rmsnorm": [P, P, P, P, I, P, I, I, I, F, P],
     "mm_add_residual": [P, P, I, c_longlong, P],
     "mm_silu_mul": [P, P, I, I, I, I, P],
+    "mm_gemm_tcgen05": [P, P, P, I, P, I, I, I, I, I, I, P, P],
     "mm_gemv_bf16": [P, P, P, I, P, I, I, I, I, I, I, I, I, I, P],
     "mm_qkv_rope_kvwrite": [P, P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
     "mm_gather_rows": [P, P, P, I, I, I, P],

@@ -55,6 +55,10 @@ class SwiGLU(FeedForward):
         if (self.interleave and x.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and self.rt.matmul != "simt"
                 and ops.gemv_supported(m, 2 * self.intermediate, self.hidden)):
             act = ops.gemv_bf16(x, self.w_gate_up, None, x.dtype, swiglu=True)    # product and activation in one kernel
+        elif (self.interleave and x.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and self.rt.matmul != "simt"
+              and m >= ops.TCGEN05_SWIGLU_MIN_ROWS and ops.gemm_tcgen05_supported(m, 2 * self.intermediate, self.hidden)):
+            # prefill-sized: tcgen05 product with the activation as its epilogue (the [m, 2F] intermediate never exists)
+            act = ops.gemm_tcgen05(x, self.w_gate_up, None, x.dtype, swiglu=True)
         else:
             gu = linear(x, self.w_gate_up, None, self.rt)
             act = torch.empty((m, self.intermediate), dtype=x.dtype, device=x.device)

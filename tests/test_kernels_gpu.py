@@ -435,3 +435,43 @@ def test_gemv_all_layouts_of_the_kernel(M, rt, ks):
     assert rc == 0, L.mm_last_error()
     ref = x.double().cpu().numpy() @ w.double().cpu().numpy().T
     assert np.abs(out.cpu().numpy() - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
+
+
+# ---- tcgen05 / TMA / TMEM matrix product -------------------------------------------------------------
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 8, 64), (200, 520, 192), (300, 264, 1000), (1100, 1048, 328)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tcgen05(M, N, K, out_dtype):
+    rng = np.random.RandomState(M + N + K)
+    x, w, b = t(rng.randn(M, K), torch.bfloat16), t(rng.randn(N, K) * 0.05, torch.bfloat16), t(rng.randn(N), torch.float32)
+    ref = x.double().cpu().numpy() @ w.double().cpu().numpy().T
+    for bias in (None, b):
+        want = ref + (b.double().cpu().numpy() if bias is not None else 0.0)
+        got = ops().gemm_tcgen05(x, w, bias, out_dtype).float().cpu().numpy()
+        ops().check_tcgen05_errors(x.device)
+        tol = 3e-6 * np.sqrt(K) if out_dtype == torch.float32 else 2 ** -8
+        assert np.abs(got - want).max() <= tol * np.abs(want).max() + 1e-5
+
+
+@pytest.mark.parametrize("M,F,K", [(130, 352, 256), (1030, 1000, 512), (64, 72, 64)])
+def test_gemm_tcgen05_swiglu_epilogue(M, F, K):
+    rng = np.random.RandomState(F + M)
+    x = t(rng.randn(M, K), torch.bfloat16)
+    gate_t, up_t = t(rng.randn(F, K) * 0.05, torch.bfloat16), t(rng.randn(F, K) * 0.05, torch.bfloat16)
+    w = torch.stack([gate_t.view(F // 8, 8, K), up_t.view(F // 8, 8, K)], dim=1).reshape(2 * F, K).contiguous()
+    g = x.double().cpu().numpy() @ gate_t.double().cpu().numpy().T
+    u = x.double().cpu().numpy() @ up_t.double().cpu().numpy().T
+    ref = g / (1 + np.exp(-g)) * u
+    got = ops().gemm_tcgen05(x, w, None, torch.bfloat16, swiglu=True).float().cpu().numpy()
+    ops().check_tcgen05_errors(x.device)
+    assert got.shape == (M, F)
+    assert np.abs(got - ref).max() <= 2 ** -8 * np.abs(ref).max() + 1e-6
+
+
+def test_gemm_tcgen05_refuses_unaligned_shapes():
+    from mimirmind_b200.kernels.lib import KernelError
+    z = lambda *s: torch.zeros(s, dtype=torch.bfloat16, device=DEV)
+    assert not ops().gemm_tcgen05_supported(4, 64, 60) and not ops().gemm_tcgen05_supported(4, 63, 64)
+    with pytest.raises(KernelError):
+        ops().gemm_tcgen05(z(4, 60), z(64, 60), None, torch.bfloat16)
+    with pytest.raises(KernelError, match="SwiGLU"):
+        ops().gemm_tcgen05(z(4, 64), z(24, 64), None, torch.bfloat16, swiglu=True)
