@@ -119,7 +119,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_prefill_kernel(
     __nv_bfloat16* sK = sQ + 64 * STRIDE;                            // [2][64][STRIDE]
     __nv_bfloat16* sV = sK + 2 * KT * STRIDE;                        // [2][64][STRIDE]
 
-    const int tile = blockIdx.x, h = blockIdx.y;
+    // the host lists a request's tiles in ascending position; later tiles see more keys, so walk the list backwards:
+    // the longest tiles start first and the short ones fill the tail
+    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
     const int g = (h * G) / H;
     const int req = tiles[tile * 4 + 0], row0 = tiles[tile * 4 + 1], n_rows = tiles[tile * 4 + 2], pos0 = tiles[tile * 4 + 3];
     const int32_t* table = block_table + (size_t)req * table_width;
@@ -195,35 +197,42 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_prefill_kernel(
                     mma_bf16(s[jp * 2 + 1], qf[ks], b2, b3);
                 }
             }
-            // scale, mask, running max
+            // mask (only tiles that touch the diagonal, the window's edge or the tile's ragged end), running max of
+            // the raw scores; the scale is folded into the exponent: p = exp2(s * c - m * c), c = scale * log2(e)
+            const bool interior = (key0 + KT - 1 <= pos0 + warp * 16) && (warp * 16 + 15 < n_rows) && (window == 0 || key0 >= pos0 + warp * 16 + 16 - window);
             float mx_lo = m_lo, mx_hi = m_hi;
+            if (!interior) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+                        const bool hi_row = e >= 2;
+                        const bool ok = hi_row ? (valid_hi && key <= pos_hi && key >= wlo_hi) : (valid_lo && key <= pos_lo && key >= wlo_lo);
+                        if (!ok) s[j][e] = -INFINITY;
+                    }
+                }
+            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
-                    const bool hi_row = e >= 2;
-                    const bool ok = hi_row ? (valid_hi && key <= pos_hi && key >= wlo_hi) : (valid_lo && key <= pos_lo && key >= wlo_lo);
-                    const float v = ok ? s[j][e] * scale_log2 : -INFINITY;
-                    s[j][e] = v;
-                    if (hi_row) mx_hi = fmaxf(mx_hi, v); else mx_lo = fmaxf(mx_lo, v);
-                }
+                mx_lo = fmaxf(mx_lo, fmaxf(s[j][0], s[j][1]));
+                mx_hi = fmaxf(mx_hi, fmaxf(s[j][2], s[j][3]));
             }
             mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
             mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
             mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
             mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-            const float use_lo = (mx_lo == -INFINITY) ? 0.0f : mx_lo;
-            const float use_hi = (mx_hi == -INFINITY) ? 0.0f : mx_hi;
-            const float a_lo = exp2f(m_lo - use_lo), a_hi = exp2f(m_hi - use_hi);
+            const float use_lo = (mx_lo == -INFINITY) ? 0.0f : mx_lo * scale_log2;
+            const float use_hi = (mx_hi == -INFINITY) ? 0.0f : mx_hi * scale_log2;
+            const float a_lo = exp2f(m_lo * scale_log2 - use_lo), a_hi = exp2f(m_hi * scale_log2 - use_hi);
             m_lo = mx_lo;
             m_hi = mx_hi;
             float sum_lo = 0.0f, sum_hi = 0.0f;
             uint32_t pf[4][4];   // P as A fragments: 4 k-steps of 16 keys
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const float p0 = exp2f(s[j][0] - use_lo), p1 = exp2f(s[j][1] - use_lo);
-                const float p2 = exp2f(s[j][2] - use_hi), p3 = exp2f(s[j][3] - use_hi);
+                const float p0 = exp2f(fmaf(s[j][0], scale_log2, -use_lo)), p1 = exp2f(fmaf(s[j][1], scale_log2, -use_lo));
+                const float p2 = exp2f(fmaf(s[j][2], scale_log2, -use_hi)), p3 = exp2f(fmaf(s[j][3], scale_log2, -use_hi));
                 sum_lo += p0 + p1;
                 sum_hi += p2 + p3;
                 pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
