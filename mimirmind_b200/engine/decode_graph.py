@@ -142,7 +142,8 @@ class DecodeSession:
             self.graph.replay()
         mgr = self.runner.manager
         for rid in self.ids:
-            mgr.commit(rid, mgr.length(rid) + 1)
+            if mgr.has(rid):          # a request may have been retired while this step was already in flight
+                mgr.commit(rid, mgr.length(rid) + 1)
         self.steps_done += 1
         return self.out_tokens
 

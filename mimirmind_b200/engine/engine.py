@@ -170,29 +170,56 @@ class Engine:
                 horizon //= 2          # fewer pages ahead; below the threshold the eager path (and preemption) decides
                 if horizon < self.graph_min_steps:
                     return False
-        host_in = torch.empty(len(reqs), dtype=torch.int32, pin_memory=True)
-        host_out = torch.empty(len(reqs), dtype=torch.int32, pin_memory=True)
-        finished = False
-        while not finished and sess.remaining() > 0:
-            out = sess.step()
-            host_out.copy_(out, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
-            self.d2h_bytes += host_out.numel() * 4
-            self.graph_steps += 1
-            now = time.perf_counter()
-            toks = host_out.tolist()
-            for r, tok in zip(reqs, toks):
+        # One step of look-ahead: as soon as a step's tokens are on the host they are copied back as the next
+        # step's inputs and that step is launched; the host's bookkeeping for the step runs while the GPU works.
+        # If the bookkeeping finds that a request stopped (a stop id, a callback), the step already in flight is
+        # still valid for the others; the stopped request's extra token is dropped.
+        n = len(reqs)
+        host_in = torch.empty(n, dtype=torch.int32, pin_memory=True)
+        host_out = [torch.empty(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        stream = torch.cuda.current_stream()
+        alive = [True] * n
+
+        def account(toks, now) -> bool:
+            stop = False
+            for i, (r, tok) in enumerate(zip(reqs, toks)):
+                if not alive[i]:
+                    continue
                 first_at.setdefault(r.id, now)
                 last_at[r.id] = now
                 done = sched.accept_token(r, tok)
-                finished |= done
                 if on_token is not None and on_token(r.id[1], tok) is False and not done:
                     sched.cancel(r.id)
-                    finished = True
-            if not finished and sess.remaining() > 0:
-                host_in.copy_(host_out)
+                    done = True
+                if done:
+                    alive[i] = False
+                    stop = True
+            return stop
+
+        cur = 0
+        host_out[cur].copy_(sess.step(), non_blocking=True)
+        stream.synchronize()
+        while True:
+            self.d2h_bytes += n * 4
+            self.graph_steps += 1
+            now = time.perf_counter()
+            toks = host_out[cur].tolist()
+            more = sess.remaining() > 0
+            if more:
+                host_in.copy_(host_out[cur])
                 sess.token_ids.copy_(host_in, non_blocking=True)      # next step's inputs, from pinned memory
-                self.h2d_bytes += host_in.numel() * 4
+                self.h2d_bytes += n * 4
+                host_out[cur ^ 1].copy_(sess.step(), non_blocking=True)
+            stop = account(toks, now)
+            if not more:
+                break
+            stream.synchronize()
+            cur ^= 1
+            if stop:
+                self.d2h_bytes += n * 4
+                self.graph_steps += 1
+                account(host_out[cur].tolist(), time.perf_counter())
+                break
         return True
 
     def _run_plan(self, plan: Sequence[PlannedEntry]) -> Dict[Hashable, int]:
