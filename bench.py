@@ -97,6 +97,7 @@ def main() -> int:
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="run one phase only and print its timing (for profiling small cases)")
     ap.add_argument("--batch", type=int, default=BATCH, help="decode batch size of --only decode")
+    ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch for the decode kernels (measured slower; for comparison)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -129,6 +130,8 @@ def main() -> int:
     mcfg = arch.parse_config(cfg_json, "bench")
     spec = arch.build_spec(mcfg)
     kernel_lib.load(verbose=True)
+    if args.pdl:
+        kernel_lib.load().mm_set_pdl(1)
     model = random_model(spec, seed=0, dtype="bfloat16")
     L, d, F, V = mcfg.num_hidden_layers, mcfg.hidden_size, mcfg.intermediate_size, mcfg.vocab_size
     qs, kvs = mcfg.q_size, mcfg.kv_size

@@ -85,3 +85,34 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// ---- programmatic dependent launch ------------------------------------------------------
+// The decode step is a chain of ~250 short kernels, each needing the previous one's output.
+// Launched with the programmatic-serialization attribute, a kernel's blocks may be scheduled
+// while the previous kernel is still running; they do whatever does not depend on it (a
+// weight-streaming kernel already issues its first weight loads) and then block in
+// pdl_wait() until the previous grid has completed and its writes are visible.  Every kernel
+// launched this way calls pdl_wait() before its first read of activations and before any
+// write, and pdl_trigger() right after it: its own dependent may then be scheduled while it
+// runs, but never more than one kernel ahead (triggering before the wait let a whole chain of
+// future kernels pile up on the SMs and measured 2.5x slower).  Without the attribute both are
+// no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int g_mm_pdl;   // 1: use the attribute, 0: plain launches (default)
+
+template <typename... KArgs, typename... Args>
+static inline void mm_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_mm_pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}

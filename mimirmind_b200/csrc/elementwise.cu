@@ -21,6 +21,8 @@
 template <typename T>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int vocab, int d, float scale) {
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * d;
@@ -39,9 +41,9 @@ MM_EXPORT int mm_embedding(const void* ids, const void* table, int table_dtype, 
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == MM_F32)
-        embedding_kernel<float><<<n_tokens, threads, 0, s>>>((const int32_t*)ids, (const float*)table, (float*)out, vocab, d, scale);
+        mm_launch_pdl(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const int32_t*)ids, (const float*)table, (float*)out, vocab, d, scale);
     else if (table_dtype == MM_BF16)
-        embedding_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>((const int32_t*)ids, (const __nv_bfloat16*)table, (float*)out, vocab, d, scale);
+        mm_launch_pdl(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const int32_t*)ids, (const __nv_bfloat16*)table, (float*)out, vocab, d, scale);
     else
         MM_REQUIRE(false, "embedding: table dtype must be float32 or bfloat16");
     MM_CHECK_LAUNCH();
@@ -61,6 +63,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
                                    T* __restrict__ out, int d, float eps) {
     extern __shared__ float row_cache[];
     __shared__ float red[32];
+    pdl_wait();
+    pdl_trigger();
     const int i = blockIdx.x;
     const size_t r = rows ? (size_t)rows[i] : (size_t)i;
     float* res = residual + r * d;
@@ -95,7 +99,7 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const int32_t*
         cudaFuncSetAttribute(add_rmsnorm_kernel<T, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
     const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-    add_rmsnorm_kernel<T, WT><<<n_rows, threads, smem, s>>>(residual, (const T*)delta, rows, (const WT*)weight, (T*)out, d, eps);
+    mm_launch_pdl(add_rmsnorm_kernel<T, WT>, dim3(n_rows), dim3(threads), smem, s, residual, (const T*)delta, rows, (const WT*)weight, (T*)out, d, eps);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
@@ -141,6 +145,8 @@ MM_EXPORT int mm_add_residual(void* residual, const void* delta, int act_dtype, 
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int F, int interleave) {
+    pdl_wait();
+    pdl_trigger();
     const size_t total = (size_t)n * F;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -156,6 +162,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 
 // 8 bf16 values per thread when F is a multiple of 8
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int n, int F, int interleave) {
+    pdl_wait();
+    pdl_trigger();
     const int F8 = F / 8;
     const size_t total = (size_t)n * F8;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -192,11 +200,11 @@ MM_EXPORT int mm_silu_mul(const void* gu, void* out, int act_dtype, int n, int F
     if (act_dtype == MM_BF16 && F % 8 == 0) {
         const size_t work = total / 8;
         const int blocks = (int)((work + 255) / 256 < 148 * 32 ? (work + 255) / 256 : 148 * 32);
-        silu_mul_bf16x8_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F, interleave);
+        mm_launch_pdl(silu_mul_bf16x8_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F, interleave);
     } else {
         const int blocks = (int)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
-        if (act_dtype == MM_F32) silu_mul_kernel<float><<<blocks, 256, 0, s>>>((const float*)gu, (float*)out, n, F, interleave);
-        else if (act_dtype == MM_BF16) silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F, interleave);
+        if (act_dtype == MM_F32) mm_launch_pdl(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, (float*)out, n, F, interleave);
+        else if (act_dtype == MM_BF16) mm_launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F, interleave);
         else MM_REQUIRE(false, "silu_mul: dtype must be float32 or bfloat16");
     }
     MM_CHECK_LAUNCH();
@@ -219,6 +227,8 @@ __global__ void qkv_rope_kvwrite_kernel(const T* __restrict__ qkv, const WT* __r
                                         const int32_t* __restrict__ block_table, int table_width, int page_size,
                                         int H, int G, int hd, int rotary_dim, float theta_base) {
     extern __shared__ float cs[];  // cos[half], sin[half]
+    pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = rotary_dim / 2;
@@ -311,7 +321,7 @@ MM_EXPORT int mm_qkv_rope_kvwrite(const void* qkv, const void* bias, int bias_dt
     const size_t smem = (size_t)rotary_dim * sizeof(float);
     const int threads = 256;
 #define MM_LAUNCH_QKV(T, WT)                                                                                       \
-    qkv_rope_kvwrite_kernel<T, WT><<<n_tokens, threads, smem, s>>>(                                                \
+    mm_launch_pdl(qkv_rope_kvwrite_kernel<T, WT>, dim3(n_tokens), dim3(threads), smem, s,                           \
         (const T*)qkv, (const WT*)bias, (T*)q_out, (T*)k_pages, (T*)v_pages, (const int32_t*)positions,            \
         (const int32_t*)token_req, (const int32_t*)block_table, table_width, page_size, H, G, hd, rotary_dim,      \
         theta_base)

@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs 
         // Two register buffers: the loads of the next U k-blocks are issued before the mma of the
         // current ones, so a warp always has a full batch of loads in flight.
         uint4 alo[2][U], ahi[2][U], xb[2][U][NT];
-        auto load_batch = [&](int buf, int kb) {
+        auto load_w = [&](int buf, int kb) {
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 if (kb + u < kb_count) {
@@ -91,6 +91,8 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs 
                     ahi[buf][u] = make_uint4(0, 0, 0, 0);
                 }
             }
+        };
+        auto load_x = [&](int buf, int kb) {
 #pragma unroll
             for (int u = 0; u < U; ++u)
 #pragma unroll
@@ -110,13 +112,23 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs 
                 }
             }
         };
-        load_batch(0, 0);
+        // The weights do not depend on the previous kernel: their first loads go out before this kernel waits for
+        // it, so the stream from HBM is already running when the activations become readable.
+        load_w(0, 0);
+        pdl_wait();
+        pdl_trigger();
+        load_x(0, 0);
         for (int kb = 0; kb < kb_count; kb += 2 * U) {
-            load_batch(1, kb + U);
+            load_w(1, kb + U);
+            load_x(1, kb + U);
             mma_batch(0, kb);
-            load_batch(0, kb + 2 * U);
+            load_w(0, kb + 2 * U);
+            load_x(0, kb + 2 * U);
             mma_batch(1, kb + U);
         }
+    } else {
+        pdl_wait();
+        pdl_trigger();
     }
     // sum the K splits of each row tile in a fixed order
     if (a.KS > 1) {
@@ -165,7 +177,7 @@ template <int NT, int U>
 static int launch_gemv(const GemvArgs& a, cudaStream_t s) {
     const int tiles = a.N / 16;
     const int blocks = (tiles + a.RT - 1) / a.RT;
-    gemv_bf16_kernel<NT, U><<<blocks, GEMV_THREADS, 0, s>>>(a);
+    mm_launch_pdl(gemv_bf16_kernel<NT, U>, dim3(blocks), dim3(GEMV_THREADS), 0, s, a);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }

@@ -21,7 +21,7 @@ from .lib import check
 
 PREFILL_MIN = 16       # shorter portions go token by token through the decode kernel
 TILE_ROWS = 64
-TARGET_CTAS = 4 * 148  # decode CTAs wanted in flight: three fit on an SM
+TARGET_CTAS = 2 * 148  # decode CTAs wanted (measured: 2 per SM beat 1 and 4 at batch 8; batch 64 is best unsplit)
 FIXED_SPLIT = None     # tests set a split length in keys to cut by absolute position instead
 
 _declared = False
@@ -58,7 +58,10 @@ def choose_split(n_items: int, num_kv_heads: int, max_kv_len: int):
     into at most max_splits pieces of whole 64-key tiles, so the grid is full whatever the lengths."""
     if FIXED_SPLIT:
         return FIXED_SPLIT, max(1, -(-max_kv_len // FIXED_SPLIT))
-    wanted = max(1, -(-TARGET_CTAS // max(1, n_items * num_kv_heads)))
+    ctas = max(1, n_items * num_kv_heads)
+    if ctas >= TARGET_CTAS // 2:
+        return 0, 1              # one CTA per SM or more already: a split would only add the merge pass
+    wanted = -(-TARGET_CTAS // ctas)
     return 0, max(1, min(wanted, -(-max_kv_len // 64)))
 
 
