@@ -1,0 +1,325 @@
+// Paged causal prefill attention on the tcgen05 tensor cores, head size 128, bfloat16.
+//
+// One CTA per (tile of up to 128 query tokens of one request, query head).  Q stays in shared
+// memory; keys and values stream in tiles of 128 keys, fetched page by page with TMA straight
+// from the page pool (in this cache layout one page of one KV head is one contiguous
+// [page_size, 128] block).  Per key tile:
+//     S  = Q K^T          tcgen05.mma 128x128x16 x 8, both operands K-major, S in tensor memory
+//     softmax             128 threads, one query row each: tcgen05.ld of the row, mask by
+//                         position, running max/sum in fp32, P rounded to bf16 into shared memory
+//                         in the 128-byte-swizzled K-major layout the tensor core reads
+//     PV = P V            tcgen05.mma 128x128x16 x 8, V read MN-major (as stored: keys x head dim)
+//     O  = O * alpha + PV  in registers (a thread holds its row of O), so tensor memory is never
+//                         written by threads
+// Warp 0 = TMA producer, warp 1 = MMA issuer and tensor-memory owner, warps 2..5 = softmax and
+// output.  Same formula as the other attention kernels (reference src/compute/Attention.cpp:43-94).
+// All mbarrier waits are bounded; on a time-out the kernel frees its tensor memory, sets `err`
+// and returns.
+#include "tcgen05.cuh"
+
+namespace {
+
+using namespace tc;
+
+constexpr int HD = 128;          // head size
+constexpr int BM = 128;          // query rows per CTA (tensor-memory lanes)
+constexpr int BN = 128;          // keys per tile
+constexpr int KV_STAGES = 2;
+constexpr int HALF_BYTES = 128 * 64 * 2;        // a [128 rows x 64 columns] bf16 sub-tile, 128 bytes per row
+constexpr int TILE_BYTES = 2 * HALF_BYTES;      // [128 x 128] as two column halves
+constexpr int ATT_TC_THREADS = 192;
+constexpr int TMEM_COLS_ATT = 256;              // S: columns 0..127, PV: columns 128..255
+
+struct AttCtl {
+    uint64_t q_full;
+    uint64_t kv_full[KV_STAGES];
+    uint64_t kv_empty[KV_STAGES];
+    uint64_t s_full;
+    uint64_t p_full;
+    uint64_t pv_full;
+    uint64_t o_done;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// tiles: int32 [n_tiles, 4] = (request index, first token row, rows in the tile (<= 128), position of the first row)
+__global__ void __launch_bounds__(ATT_TC_THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                            const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
+                            const int32_t* __restrict__ tiles, const int32_t* __restrict__ block_table, int table_width,
+                            int page_size, int H, int G, int window, float scale_log2, int* __restrict__ err) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = base;                                   // TILE_BYTES
+    unsigned char* sP = sQ + TILE_BYTES;                        // TILE_BYTES
+    unsigned char* sK = sP + TILE_BYTES;                        // KV_STAGES * TILE_BYTES
+    unsigned char* sV = sK + KV_STAGES * TILE_BYTES;            // KV_STAGES * TILE_BYTES
+    AttCtl* ctl = reinterpret_cast<AttCtl*>(sV + KV_STAGES * TILE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile int* abort_flag = &ctl->abort_flag;
+
+    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;   // later (longer) tiles first
+    const int g = (h * G) / H;
+    const int req = tiles[tile * 4 + 0], row0 = tiles[tile * 4 + 1], n_rows = tiles[tile * 4 + 2], pos0 = tiles[tile * 4 + 3];
+    const int32_t* table = block_table + (size_t)req * table_width;
+    const int hi_all = pos0 + n_rows;
+    const int lo_all = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
+    const int kt_begin = lo_all / BN, kt_end = (hi_all + BN - 1) / BN;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&ctl->q_full), 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(smem_u32(&ctl->kv_full[s]), 1);
+            mbar_init(smem_u32(&ctl->kv_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&ctl->s_full), 1);
+        mbar_init(smem_u32(&ctl->p_full), 128);
+        mbar_init(smem_u32(&ctl->pv_full), 1);
+        mbar_init(smem_u32(&ctl->o_done), 128);
+        ctl->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Value tiles must never hold non-finite leftovers: rows of a page that was not fetched are multiplied by P = 0.
+    for (int i = threadIdx.x; i < KV_STAGES * TILE_BYTES / 16; i += ATT_TC_THREADS) reinterpret_cast<uint4*>(sV)[i] = make_uint4(0, 0, 0, 0);
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(TMEM_COLS_ATT) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctl->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ----
+            const uint32_t qbar = smem_u32(&ctl->q_full);
+            mbar_expect_tx(qbar, TILE_BYTES);
+            tma_load_2d(smem_u32(sQ), &tmQ, h * HD, row0, qbar);
+            tma_load_2d(smem_u32(sQ) + HALF_BYTES, &tmQ, h * HD + 64, row0, qbar);
+            const int pages_per_tile = BN / page_size;
+            const uint32_t page_bytes = (uint32_t)page_size * 128u;       // one column half of a page
+            uint32_t it = 0;
+            for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
+                const int s = it % KV_STAGES;
+                const uint32_t ph = (it / KV_STAGES) & 1;
+                if (!mbar_wait(smem_u32(&ctl->kv_empty[s]), ph ^ 1, abort_flag)) break;
+                // which pages of this tile hold keys some row of the tile may see
+                int first_page = kt * pages_per_tile, n_pages = 0;
+                int page_ids[16];
+                for (int j = 0; j < pages_per_tile; ++j) {
+                    const int key_lo = kt * BN + j * page_size;
+                    const bool wanted = key_lo < hi_all && key_lo + page_size > lo_all;
+                    const int pid = wanted ? table[first_page + j] : -1;
+                    page_ids[j] = pid;
+                    n_pages += pid >= 0;
+                }
+                const uint32_t full = smem_u32(&ctl->kv_full[s]);
+                mbar_expect_tx(full, (uint32_t)n_pages * page_bytes * 4u);
+                const uint32_t k_dst = smem_u32(sK + s * TILE_BYTES), v_dst = smem_u32(sV + s * TILE_BYTES);
+                for (int j = 0; j < pages_per_tile; ++j) {
+                    if (page_ids[j] < 0) continue;
+                    const int pool_row = (page_ids[j] * G + g) * page_size;
+                    const uint32_t off = (uint32_t)j * page_bytes;
+                    tma_load_2d(k_dst + off, &tmK, 0, pool_row, full);
+                    tma_load_2d(k_dst + HALF_BYTES + off, &tmK, 64, pool_row, full);
+                    tma_load_2d(v_dst + off, &tmV, 0, pool_row, full);
+                    tma_load_2d(v_dst + HALF_BYTES + off, &tmV, 64, pool_row, full);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            constexpr uint32_t IDESC_QK = idesc_bf16(BM, BN, false);
+            constexpr uint32_t IDESC_PV = idesc_bf16(BM, HD, true);
+            const uint32_t s_tmem = tmem_base, pv_tmem = tmem_base + 128;
+            bool ok = mbar_wait(smem_u32(&ctl->q_full), 0, abort_flag);
+            uint32_t it = 0;
+            for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
+                const int s = it % KV_STAGES;
+                const uint32_t ph = (it / KV_STAGES) & 1, tph = it & 1;
+                // S and PV of the previous tile have been read
+                if (!mbar_wait(smem_u32(&ctl->o_done), tph ^ 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&ctl->kv_full[s]), ph, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK + s * TILE_BYTES), v_addr = smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;      // 16 columns = 32 bytes inside the swizzled row
+                    umma_bf16(s_tmem, smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), IDESC_QK, k ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&ctl->s_full));
+                if (!mbar_wait(smem_u32(&ctl->p_full), tph, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t p_addr = smem_u32(sP);
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k) {
+                    const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;    // P: K-major over the keys
+                    const uint32_t b_off = (uint32_t)k * 16 * 128;                  // V: 16 key rows of 128 bytes further
+                    umma_bf16(pv_tmem, smem_desc_sw128(p_addr + a_off, 16, 1024), smem_desc_sw128(v_addr + b_off, HALF_BYTES, 1024), IDESC_PV, k ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&ctl->pv_full));
+                umma_commit(smem_u32(&ctl->kv_empty[s]));
+            }
+        }
+    } else {
+        // ---- softmax and output: thread = query row ----
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const int pos = pos0 + row;
+        const bool row_valid = row < n_rows;
+        const int wlo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        float o[HD];
+#pragma unroll
+        for (int i = 0; i < HD; ++i) o[i] = 0.0f;
+        float m = -INFINITY, l = 0.0f;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
+            const uint32_t tph = it & 1;
+            if (!mbar_wait(smem_u32(&ctl->s_full), tph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int key0 = kt * BN;
+            // pass 1: the row's maximum over this tile
+            float mx = m;
+            uint32_t sreg[32];
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                tmem_ld32_nowait(lane_addr + c * 32, sreg);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int key = key0 + c * 32 + i;
+                    const bool vis = row_valid && key <= pos && key >= wlo;
+                    if (vis) mx = fmaxf(mx, __uint_as_float(sreg[i]));
+                }
+            }
+            const float use = (mx == -INFINITY) ? 0.0f : mx * scale_log2;
+            const float alpha = exp2f(m * scale_log2 - use);
+            m = mx;
+            // pass 2: probabilities, rounded to bf16 as the tensor core will read them
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                tmem_ld32_nowait(lane_addr + c * 32, sreg);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int key = key0 + c * 32 + i;
+                    const bool v0 = row_valid && key <= pos && key >= wlo;
+                    const bool v1 = row_valid && key + 1 <= pos && key + 1 >= wlo;
+                    const float p0 = v0 ? exp2f(fmaf(__uint_as_float(sreg[i]), scale_log2, -use)) : 0.0f;
+                    const float p1 = v1 ? exp2f(fmaf(__uint_as_float(sreg[i + 1]), scale_log2, -use)) : 0.0f;
+                    sum += p0 + p1;
+                    packed[i >> 1] = pack_bf16x2(p0, p1);
+                }
+                // 32 keys = 4 chunks of 16 bytes in this row of the [128 x 64] half c/2; chunk index is xor-ed with row % 8
+                unsigned char* prow = sP + (c >> 1) * HALF_BYTES + row * 128;
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int logical = (c & 1) * 4 + ch;
+                    *reinterpret_cast<uint4*>(prow + ((logical ^ (row & 7)) << 4)) =
+                        make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
+                }
+            }
+            l = l * alpha + sum;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P is read by the tensor core (async proxy)
+            tc_fence_before();
+            mbar_arrive(smem_u32(&ctl->p_full));
+            // O = O * alpha + P V
+            if (!mbar_wait(smem_u32(&ctl->pv_full), tph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                tmem_ld32_nowait(lane_addr + 128 + c * 32, sreg);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(sreg[i]));
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&ctl->o_done));
+        }
+        if (ok && row_valid) {
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            __nv_bfloat16* orow = out + ((size_t)(row0 + row) * H + h) * HD;
+#pragma unroll
+            for (int i = 0; i < HD; i += 8) {
+                *reinterpret_cast<uint4*>(orow + i) = make_uint4(pack_bf16x2(o[i] * inv, o[i + 1] * inv), pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv),
+                                                                 pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv), pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv));
+            }
+        }
+    }
+
+    // ---- teardown ----
+    if (*abort_flag) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (threadIdx.x == 0 && ctl->abort_flag && err != nullptr) atomicExch(err, 2);
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS_ATT) : "memory");
+    }
+}
+
+}  // namespace
+
+// q, out: [n_tokens, H*128] bf16; k_pages, v_pages: [num_pages, G, page_size, 128] bf16 of one layer;
+// tiles: int32 [n_tiles, 4] (request, first row, rows <= 128, first position).  `err`: device int set to 2 when a
+// bounded wait ran out (may be null).
+MM_EXPORT int mm_attention_prefill_tcgen05(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                           const void* tiles, int n_tiles, const void* block_table, int table_width,
+                                           int page_size, int num_pages, int n_tokens, int H, int G, int hd, int window,
+                                           float scale, void* err, void* stream) {
+    MM_REQUIRE(hd == 128, "attention_prefill_tcgen05: built for head_dim 128");
+    MM_REQUIRE(n_tiles >= 0 && H > 0 && G > 0 && H % G == 0 && n_tokens > 0 && num_pages > 0, "attention_prefill_tcgen05: bad sizes");
+    MM_REQUIRE(page_size >= 8 && page_size <= 128 && (128 % page_size) == 0, "attention_prefill_tcgen05: page_size must be 8, 16, 32, 64 or 128");
+    MM_REQUIRE(table_width > 0 && window >= 0, "attention_prefill_tcgen05: bad table or window");
+    if (n_tiles == 0) return MM_OK;
+    CUtensorMap tq, tk, tv;
+    const long long pool_rows = (long long)num_pages * G * page_size;
+    if (!tc::make_map_bf16(&tq, q, n_tokens, H * 128, (long long)H * 128, 128) ||
+        !tc::make_map_bf16(&tk, k_pages, pool_rows, 128, 128, page_size) ||
+        !tc::make_map_bf16(&tv, v_pages, pool_rows, 128, 128, page_size)) {
+        mm_set_last_error("attention_prefill_tcgen05: cuTensorMapEncodeTiled failed or is not available");
+        return MM_ERR_DRIVER;
+    }
+    const size_t smem = (size_t)(2 + 2 * KV_STAGES) * TILE_BYTES + 1024 + sizeof(AttCtl);
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            mm_set_last_error("attention_prefill_tcgen05: cannot reserve shared memory");
+            return MM_ERR_LAUNCH;
+        }
+        configured = true;
+    }
+    const float LOG2E = 1.4426950408889634f;
+    dim3 grid(n_tiles, H);
+    attention_prefill_tc_kernel<<<grid, ATT_TC_THREADS, smem, (cudaStream_t)stream>>>(
+        tq, tk, tv, (__nv_bfloat16*)out, (const int32_t*)tiles, (const int32_t*)block_table, table_width, page_size, H, G,
+        window, scale * LOG2E, (int*)err);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}

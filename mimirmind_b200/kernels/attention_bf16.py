@@ -20,7 +20,9 @@ from . import lib as _lib
 from .lib import check
 
 PREFILL_MIN = 16       # shorter portions go token by token through the decode kernel
-TILE_ROWS = 64
+TILE_ROWS = 64         # query rows per CTA of the mma.sync prefill kernel
+TILE_ROWS_TC = 128     # ... of the tcgen05 prefill kernel (head size 128)
+USE_TCGEN05_PREFILL = True
 TARGET_CTAS = 2 * 148  # decode CTAs wanted (measured: 2 per SM beat 1 and 4 at batch 8; batch 64 is best unsplit)
 FIXED_SPLIT = None     # tests set a split length in keys to cut by absolute position instead
 
@@ -33,6 +35,7 @@ def _declare():
         return
     P, I, F = c_void_p, c_int, c_float
     _lib.declare("mm_attention_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, F, P])
+    _lib.declare("mm_attention_prefill_tcgen05", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P])
     _lib.declare("mm_attention_decode_bf16", [P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P])
     _declared = True
 
@@ -45,6 +48,7 @@ def supports(head_dim: int, num_heads: int, num_kv_heads: int) -> bool:
 class AttentionPlan:
     tiles: Optional[torch.Tensor]      # int32 [n_tiles, 4] or None
     n_tiles: int
+    tile_rows: int                     # 64: mma.sync kernel, 128: tcgen05 kernel
     items: Optional[torch.Tensor]      # int32 [n_items]; None with n_items > 0 means "every token"
     n_items: int
     split_len: int
@@ -65,14 +69,19 @@ def choose_split(n_items: int, num_kv_heads: int, max_kv_len: int):
     return 0, max(1, min(wanted, -(-max_kv_len // 64)))
 
 
+def tcgen05_prefill_usable(head_dim: int, page_size: int) -> bool:
+    return USE_TCGEN05_PREFILL and head_dim == 128 and page_size in (8, 16, 32, 64, 128)
+
+
 def make_plan(ctx, num_heads: int, num_kv_heads: int, head_dim: int) -> AttentionPlan:
     device = ctx.positions.device
     tiles, items = [], []
+    tile_rows = TILE_ROWS_TC if tcgen05_prefill_usable(head_dim, ctx.page_size) else TILE_ROWS
     for r in range(ctx.n_requests):
         s, n, kv = ctx.q_start[r], ctx.q_len[r], ctx.kv_len[r]
         if n >= PREFILL_MIN:
-            for off in range(0, n, TILE_ROWS):
-                tiles.append((r, s + off, min(TILE_ROWS, n - off), kv - n + off))
+            for off in range(0, n, tile_rows):
+                tiles.append((r, s + off, min(tile_rows, n - off), kv - n + off))
         else:
             items.extend(range(s, s + n))
     d_tiles = torch.tensor(tiles, dtype=torch.int32, device=device) if tiles else None
@@ -81,7 +90,7 @@ def make_plan(ctx, num_heads: int, num_kv_heads: int, head_dim: int) -> Attentio
     else:
         d_items = torch.tensor(items, dtype=torch.int32, device=device) if items else None
     split_len, max_splits = choose_split(len(items), num_kv_heads, ctx.max_kv_len) if items else (0, 1)
-    plan = AttentionPlan(d_tiles, len(tiles), d_items, len(items), split_len, max_splits)
+    plan = AttentionPlan(d_tiles, len(tiles), tile_rows, d_items, len(items), split_len, max_splits)
     if items and max_splits > 1:
         plan.part_o = torch.empty((len(items), num_heads, max_splits, head_dim), dtype=torch.float32, device=device)
         plan.part_ml = torch.empty((len(items), num_heads, max_splits, 2), dtype=torch.float32, device=device)
@@ -98,7 +107,14 @@ def run(q, cache, out, ctx, num_heads: int, num_kv_heads: int, head_dim: int, wi
     lib = _lib.load()
     stream = torch.cuda.current_stream().cuda_stream
     table = cache.block_table
-    if plan.n_tiles:
+    if plan.n_tiles and plan.tile_rows == TILE_ROWS_TC:
+        from . import ops
+        check(lib.mm_attention_prefill_tcgen05(q.data_ptr(), cache.k_pages.data_ptr(), cache.v_pages.data_ptr(), out.data_ptr(),
+                                               plan.tiles.data_ptr(), plan.n_tiles, table.data_ptr(), table.shape[1],
+                                               cache.page_size, cache.k_pages.shape[0], q.shape[0], num_heads, num_kv_heads,
+                                               head_dim, window, float(scale), ops.tcgen05_error_flag(q.device).data_ptr(), stream),
+              "attention_prefill_tcgen05")
+    elif plan.n_tiles:
         check(lib.mm_attention_prefill_bf16(q.data_ptr(), cache.k_pages.data_ptr(), cache.v_pages.data_ptr(),
                                             out.data_ptr(), plan.tiles.data_ptr(), plan.n_tiles, table.data_ptr(),
                                             table.shape[1], cache.page_size, num_heads, num_kv_heads, head_dim, window,
