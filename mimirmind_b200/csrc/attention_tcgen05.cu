@@ -11,6 +11,9 @@
 //     PV = P V            tcgen05.mma 128x128x16 x 8, V read MN-major (as stored: keys x head dim)
 //     O  = O * alpha + PV  in registers (a thread holds its row of O), so tensor memory is never
 //                         written by threads
+// S, P and PV are double-buffered: while the softmax threads work on tile t the tensor core already
+// computes S of tile t+1 and P V of tile t, and a thread adds P V of tile t into its O only after it
+// has published P of tile t+1.
 // Warp 0 = TMA producer, warp 1 = MMA issuer and tensor-memory owner, warps 2..5 = softmax and
 // output.  Same formula as the other attention kernels (reference src/compute/Attention.cpp:43-94).
 // All mbarrier waits are bounded; on a time-out the kernel frees its tensor memory, sets `err`
@@ -28,16 +31,17 @@ constexpr int KV_STAGES = 2;
 constexpr int HALF_BYTES = 128 * 64 * 2;        // a [128 rows x 64 columns] bf16 sub-tile, 128 bytes per row
 constexpr int TILE_BYTES = 2 * HALF_BYTES;      // [128 x 128] as two column halves
 constexpr int ATT_TC_THREADS = 192;
-constexpr int TMEM_COLS_ATT = 256;              // S: columns 0..127, PV: columns 128..255
+constexpr int TMEM_COLS_ATT = 512;              // S0, S1: columns 0..255; PV0, PV1: columns 256..511
 
 struct AttCtl {
     uint64_t q_full;
     uint64_t kv_full[KV_STAGES];
     uint64_t kv_empty[KV_STAGES];
-    uint64_t s_full;
-    uint64_t p_full;
-    uint64_t pv_full;
-    uint64_t o_done;
+    uint64_t s_full[2];      // S buffer b holds Q K^T of a tile (tensor core -> softmax)
+    uint64_t s_free[2];      // ... has been read (softmax -> tensor core), 128 arrivals
+    uint64_t p_full[2];      // P buffer b is written and fenced (softmax -> tensor core), 128 arrivals
+    uint64_t pv_full[2];     // PV buffer b holds P V of a tile (tensor core -> softmax)
+    uint64_t pv_free[2];     // ... has been added into O (softmax -> tensor core), 128 arrivals
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -68,8 +72,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = base;                                   // TILE_BYTES
-    unsigned char* sP = sQ + TILE_BYTES;                        // TILE_BYTES
-    unsigned char* sK = sP + TILE_BYTES;                        // KV_STAGES * TILE_BYTES
+    unsigned char* sP = sQ + TILE_BYTES;                        // 2 * TILE_BYTES
+    unsigned char* sK = sP + 2 * TILE_BYTES;                    // KV_STAGES * TILE_BYTES
     unsigned char* sV = sK + KV_STAGES * TILE_BYTES;            // KV_STAGES * TILE_BYTES
     AttCtl* ctl = reinterpret_cast<AttCtl*>(sV + KV_STAGES * TILE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -89,10 +93,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
             mbar_init(smem_u32(&ctl->kv_full[s]), 1);
             mbar_init(smem_u32(&ctl->kv_empty[s]), 1);
         }
-        mbar_init(smem_u32(&ctl->s_full), 1);
-        mbar_init(smem_u32(&ctl->p_full), 128);
-        mbar_init(smem_u32(&ctl->pv_full), 1);
-        mbar_init(smem_u32(&ctl->o_done), 128);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&ctl->s_full[b]), 1);
+            mbar_init(smem_u32(&ctl->s_free[b]), 128);
+            mbar_init(smem_u32(&ctl->p_full[b]), 128);
+            mbar_init(smem_u32(&ctl->pv_full[b]), 1);
+            mbar_init(smem_u32(&ctl->pv_free[b]), 128);
+        }
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -151,33 +158,41 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
             // ---- MMA issuer ----
             constexpr uint32_t IDESC_QK = idesc_bf16(BM, BN, false);
             constexpr uint32_t IDESC_PV = idesc_bf16(BM, HD, true);
-            const uint32_t s_tmem = tmem_base, pv_tmem = tmem_base + 128;
+            const int n_tiles_k = kt_end - kt_begin;
+            const uint32_t q_addr = smem_u32(sQ);
             bool ok = mbar_wait(smem_u32(&ctl->q_full), 0, abort_flag);
-            uint32_t it = 0;
-            for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
+            // S[it % 2] = Q K(it)^T; the buffer was last read by the softmax of tile it - 2
+            auto issue_qk = [&](uint32_t it) -> bool {
                 const int s = it % KV_STAGES;
-                const uint32_t ph = (it / KV_STAGES) & 1, tph = it & 1;
-                // S and PV of the previous tile have been read
-                if (!mbar_wait(smem_u32(&ctl->o_done), tph ^ 1, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(smem_u32(&ctl->kv_full[s]), ph, abort_flag)) { ok = false; break; }
+                const uint32_t b = it & 1, u = it >> 1;
+                if (!mbar_wait(smem_u32(&ctl->s_free[b]), (u & 1) ^ 1, abort_flag)) return false;
+                if (!mbar_wait(smem_u32(&ctl->kv_full[s]), (it / KV_STAGES) & 1, abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK + s * TILE_BYTES), v_addr = smem_u32(sV + s * TILE_BYTES);
+                const uint32_t k_addr = smem_u32(sK + s * TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;      // 16 columns = 32 bytes inside the swizzled row
-                    umma_bf16(s_tmem, smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), IDESC_QK, k ? 1u : 0u);
+                    umma_bf16(tmem_base + b * 128, smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), IDESC_QK, k ? 1u : 0u);
                 }
-                umma_commit(smem_u32(&ctl->s_full));
-                if (!mbar_wait(smem_u32(&ctl->p_full), tph, abort_flag)) { ok = false; break; }
+                umma_commit(smem_u32(&ctl->s_full[b]));
+                return true;
+            };
+            if (ok && n_tiles_k > 0) ok = issue_qk(0);
+            for (uint32_t it = 0; (int)it < n_tiles_k && ok; ++it) {
+                if ((int)it + 1 < n_tiles_k && !issue_qk(it + 1)) { ok = false; break; }
+                const int s = it % KV_STAGES;
+                const uint32_t b = it & 1, u = it >> 1;
+                if (!mbar_wait(smem_u32(&ctl->p_full[b]), u & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&ctl->pv_free[b]), (u & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t p_addr = smem_u32(sP);
+                const uint32_t p_addr = smem_u32(sP + b * TILE_BYTES), v_addr = smem_u32(sV + s * TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k) {
                     const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;    // P: K-major over the keys
                     const uint32_t b_off = (uint32_t)k * 16 * 128;                  // V: 16 key rows of 128 bytes further
-                    umma_bf16(pv_tmem, smem_desc_sw128(p_addr + a_off, 16, 1024), smem_desc_sw128(v_addr + b_off, HALF_BYTES, 1024), IDESC_PV, k ? 1u : 0u);
+                    umma_bf16(tmem_base + 256 + b * 128, smem_desc_sw128(p_addr + a_off, 16, 1024), smem_desc_sw128(v_addr + b_off, HALF_BYTES, 1024), IDESC_PV, k ? 1u : 0u);
                 }
-                umma_commit(smem_u32(&ctl->pv_full));
+                umma_commit(smem_u32(&ctl->pv_full[b]));
                 umma_commit(smem_u32(&ctl->kv_empty[s]));
             }
         }
@@ -193,25 +208,49 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
 #pragma unroll
         for (int i = 0; i < HD; ++i) o[i] = 0.0f;
         float m = -INFINITY, l = 0.0f;
+        float alpha_prev = 1.0f;      // the factor that goes with the P V result not yet added into O
         uint32_t it = 0;
         bool ok = true;
-        for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
-            const uint32_t tph = it & 1;
-            if (!mbar_wait(smem_u32(&ctl->s_full), tph, abort_flag)) { ok = false; break; }
+        uint32_t sreg[32];
+        // adds P V of tile `t` into O (O was scaled for the maximum at the time P of that tile was made)
+        auto add_pv = [&](uint32_t t, float alpha) -> bool {
+            const uint32_t b = t & 1, u = t >> 1;
+            if (!mbar_wait(smem_u32(&ctl->pv_full[b]), u & 1, abort_flag)) return false;
             tc_fence_after();
-            const int key0 = kt * BN;
-            // pass 1: the row's maximum over this tile
-            float mx = m;
-            uint32_t sreg[32];
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                tmem_ld32_nowait(lane_addr + c * 32, sreg);
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                tmem_ld32_nowait(lane_addr + 256 + b * 128 + c * 32, sreg);
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + c * 32 + i;
-                    const bool vis = row_valid && key <= pos && key >= wlo;
-                    if (vis) mx = fmaxf(mx, __uint_as_float(sreg[i]));
+                for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(sreg[i]));
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&ctl->pv_free[b]));
+            return true;
+        };
+        for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
+            const uint32_t b = it & 1, u = it >> 1;
+            if (!mbar_wait(smem_u32(&ctl->s_full[b]), u & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int key0 = kt * BN;
+            const uint32_t s_addr = lane_addr + b * 128;
+            // a tile every key of which this row sees needs no mask
+            const bool interior = row_valid && key0 + BN - 1 <= pos && key0 >= wlo;
+            // pass 1: the row's maximum over this tile
+            float mx = m;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                tmem_ld32_nowait(s_addr + c * 32, sreg);
+                tmem_ld_wait();
+                if (interior) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sreg[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + c * 32 + i;
+                        if (row_valid && key <= pos && key >= wlo) mx = fmaxf(mx, __uint_as_float(sreg[i]));
+                    }
                 }
             }
             const float use = (mx == -INFINITY) ? 0.0f : mx * scale_log2;
@@ -219,23 +258,34 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
             m = mx;
             // pass 2: probabilities, rounded to bf16 as the tensor core will read them
             float sum = 0.0f;
+            unsigned char* p_buf = sP + b * TILE_BYTES;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
-                tmem_ld32_nowait(lane_addr + c * 32, sreg);
+                tmem_ld32_nowait(s_addr + c * 32, sreg);
                 tmem_ld_wait();
                 uint32_t packed[16];
+                if (interior) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int key = key0 + c * 32 + i;
-                    const bool v0 = row_valid && key <= pos && key >= wlo;
-                    const bool v1 = row_valid && key + 1 <= pos && key + 1 >= wlo;
-                    const float p0 = v0 ? exp2f(fmaf(__uint_as_float(sreg[i]), scale_log2, -use)) : 0.0f;
-                    const float p1 = v1 ? exp2f(fmaf(__uint_as_float(sreg[i + 1]), scale_log2, -use)) : 0.0f;
-                    sum += p0 + p1;
-                    packed[i >> 1] = pack_bf16x2(p0, p1);
+                    for (int i = 0; i < 32; i += 2) {
+                        const float p0 = exp2f(fmaf(__uint_as_float(sreg[i]), scale_log2, -use));
+                        const float p1 = exp2f(fmaf(__uint_as_float(sreg[i + 1]), scale_log2, -use));
+                        sum += p0 + p1;
+                        packed[i >> 1] = pack_bf16x2(p0, p1);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int key = key0 + c * 32 + i;
+                        const bool v0 = row_valid && key <= pos && key >= wlo;
+                        const bool v1 = row_valid && key + 1 <= pos && key + 1 >= wlo;
+                        const float p0 = v0 ? exp2f(fmaf(__uint_as_float(sreg[i]), scale_log2, -use)) : 0.0f;
+                        const float p1 = v1 ? exp2f(fmaf(__uint_as_float(sreg[i + 1]), scale_log2, -use)) : 0.0f;
+                        sum += p0 + p1;
+                        packed[i >> 1] = pack_bf16x2(p0, p1);
+                    }
                 }
                 // 32 keys = 4 chunks of 16 bytes in this row of the [128 x 64] half c/2; chunk index is xor-ed with row % 8
-                unsigned char* prow = sP + (c >> 1) * HALF_BYTES + row * 128;
+                unsigned char* prow = p_buf + (c >> 1) * HALF_BYTES + row * 128;
 #pragma unroll
                 for (int ch = 0; ch < 4; ++ch) {
                     const int logical = (c & 1) * 4 + ch;
@@ -244,22 +294,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 }
             }
             l = l * alpha + sum;
+            tc_fence_before();
+            mbar_arrive(smem_u32(&ctl->s_free[b]));                           // S of this tile is consumed
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P is read by the tensor core (async proxy)
-            tc_fence_before();
-            mbar_arrive(smem_u32(&ctl->p_full));
-            // O = O * alpha + P V
-            if (!mbar_wait(smem_u32(&ctl->pv_full), tph, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-#pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
-                tmem_ld32_nowait(lane_addr + 128 + c * 32, sreg);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(sreg[i]));
-            }
-            tc_fence_before();
-            mbar_arrive(smem_u32(&ctl->o_done));
+            mbar_arrive(smem_u32(&ctl->p_full[b]));
+            // while the tensor core multiplies this P with V, take in the previous tile's P V
+            if (it >= 1 && !add_pv(it - 1, alpha_prev)) { ok = false; break; }
+            alpha_prev = alpha;
         }
+        if (ok && it >= 1) ok = add_pv(it - 1, alpha_prev);
         if (ok && row_valid) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             __nv_bfloat16* orow = out + ((size_t)(row0 + row) * H + h) * HD;
@@ -306,7 +349,7 @@ MM_EXPORT int mm_attention_prefill_tcgen05(const void* q, const void* k_pages, c
         mm_set_last_error("attention_prefill_tcgen05: cuTensorMapEncodeTiled failed or is not available");
         return MM_ERR_DRIVER;
     }
-    const size_t smem = (size_t)(2 + 2 * KV_STAGES) * TILE_BYTES + 1024 + sizeof(AttCtl);
+    const size_t smem = (size_t)(3 + 2 * KV_STAGES) * TILE_BYTES + 1024 + sizeof(AttCtl);
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
