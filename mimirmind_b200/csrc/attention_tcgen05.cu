@@ -5,16 +5,18 @@
 // from the page pool (in this cache layout one page of one KV head is one contiguous
 // [page_size, 128] block).  Per key tile:
 //     S  = Q K^T          tcgen05.mma 128x128x16 x 8, both operands K-major, S in tensor memory
-//     softmax             128 threads, one query row each: tcgen05.ld of the row, mask by
-//                         position, running max/sum in fp32, P rounded to bf16 into shared memory
-//                         in the 128-byte-swizzled K-major layout the tensor core reads
+//     softmax             256 threads, two per query row (64 keys and 64 output columns each):
+//                         tcgen05.ld of the row, mask by position, running max/sum in fp32 (the two
+//                         halves of a row exchange their maxima through shared memory), P rounded
+//                         to bf16 into shared memory in the 128-byte-swizzled K-major layout the
+//                         tensor core reads
 //     PV = P V            tcgen05.mma 128x128x16 x 8, V read MN-major (as stored: keys x head dim)
 //     O  = O * alpha + PV  in registers (a thread holds its row of O), so tensor memory is never
 //                         written by threads
 // S, P and PV are double-buffered: while the softmax threads work on tile t the tensor core already
 // computes S of tile t+1 and P V of tile t, and a thread adds P V of tile t into its O only after it
 // has published P of tile t+1.
-// Warp 0 = TMA producer, warp 1 = MMA issuer and tensor-memory owner, warps 2..5 = softmax and
+// Warp 0 = TMA producer, warp 1 = MMA issuer and tensor-memory owner, warps 2..9 = softmax and
 // output.  Same formula as the other attention kernels (reference src/compute/Attention.cpp:43-94).
 // All mbarrier waits are bounded; on a time-out the kernel frees its tensor memory, sets `err`
 // and returns.
@@ -30,20 +32,27 @@ constexpr int BN = 128;          // keys per tile
 constexpr int KV_STAGES = 2;
 constexpr int HALF_BYTES = 128 * 64 * 2;        // a [128 rows x 64 columns] bf16 sub-tile, 128 bytes per row
 constexpr int TILE_BYTES = 2 * HALF_BYTES;      // [128 x 128] as two column halves
-constexpr int ATT_TC_THREADS = 192;
+constexpr int ATT_TC_THREADS = 320;            // producer warp, MMA warp, 8 softmax warps
+constexpr int SOFTMAX_WARPS = 8;               // barriers between the softmax warps and the tensor core count warps, not
+                                               // threads: one arrival per softmax warp on one mbarrier serialise and cost more than the math
 constexpr int TMEM_COLS_ATT = 512;              // S0, S1: columns 0..255; PV0, PV1: columns 256..511
 
 struct AttCtl {
     uint64_t q_full;
-    uint64_t kv_full[KV_STAGES];
-    uint64_t kv_empty[KV_STAGES];
+    uint64_t k_full[KV_STAGES];     // keys and values have rings of their own: a key tile is free as soon as Q K^T has read
+    uint64_t k_empty[KV_STAGES];    // it, so the next keys are fetched a whole tile earlier than if they waited for P V
+    uint64_t v_full[KV_STAGES];
+    uint64_t v_empty[KV_STAGES];
     uint64_t s_full[2];      // S buffer b holds Q K^T of a tile (tensor core -> softmax)
-    uint64_t s_free[2];      // ... has been read (softmax -> tensor core), 128 arrivals
-    uint64_t p_full[2];      // P buffer b is written and fenced (softmax -> tensor core), 128 arrivals
+    uint64_t s_free[2];      // ... has been read (softmax -> tensor core), one arrival per softmax warp
+    uint64_t p_full[2];      // P buffer b is written and fenced (softmax -> tensor core), one arrival per softmax warp
     uint64_t pv_full[2];     // PV buffer b holds P V of a tile (tensor core -> softmax)
-    uint64_t pv_free[2];     // ... has been added into O (softmax -> tensor core), 128 arrivals
+    uint64_t pv_free[2];     // ... has been added into O (softmax -> tensor core), one arrival per softmax warp
     uint32_t tmem_base;
     int abort_flag;
+    uint64_t x_full[2];      // both halves of every row have posted their maximum (one arrival per softmax warp)
+    uint64_t l_full;         // ... their sum, at the end
+    float xchg[2][2][128];   // [tile parity][half of the row][row]: row maxima; after the last tile [0][..][..] carries the row sums
 };
 
 __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
@@ -58,9 +67,22 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// 2^x on the special-function unit in one instruction (relative error 2^-22, far below the bf16 rounding of P)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Every lane has done its part (and its fences); one lane arrives for the warp.
+__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
 }
 
 // tiles: int32 [n_tiles, 4] = (request index, first token row, rows in the tile (<= 128), position of the first row)
@@ -69,9 +91,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                             const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
                             const int32_t* __restrict__ tiles, const int32_t* __restrict__ block_table, int table_width,
                             int page_size, int H, int G, int window, float scale_log2, int* __restrict__ err) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* sQ = base;                                   // TILE_BYTES
+    extern __shared__ __align__(1024) unsigned char smem_raw[];   // 128-byte swizzle wants 1024-byte aligned tiles
+    if ((smem_u32(smem_raw) & 1023u) != 0) {                      // never seen; without the alignment nothing below is valid
+        if (threadIdx.x == 0 && err != nullptr) atomicExch(err, 3);
+        return;
+    }
+    unsigned char* sQ = smem_raw;                               // TILE_BYTES
     unsigned char* sP = sQ + TILE_BYTES;                        // 2 * TILE_BYTES
     unsigned char* sK = sP + 2 * TILE_BYTES;                    // KV_STAGES * TILE_BYTES
     unsigned char* sV = sK + KV_STAGES * TILE_BYTES;            // KV_STAGES * TILE_BYTES
@@ -90,16 +115,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&ctl->q_full), 1);
         for (int s = 0; s < KV_STAGES; ++s) {
-            mbar_init(smem_u32(&ctl->kv_full[s]), 1);
-            mbar_init(smem_u32(&ctl->kv_empty[s]), 1);
+            mbar_init(smem_u32(&ctl->k_full[s]), 1);
+            mbar_init(smem_u32(&ctl->k_empty[s]), 1);
+            mbar_init(smem_u32(&ctl->v_full[s]), 1);
+            mbar_init(smem_u32(&ctl->v_empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&ctl->s_full[b]), 1);
-            mbar_init(smem_u32(&ctl->s_free[b]), 128);
-            mbar_init(smem_u32(&ctl->p_full[b]), 128);
+            mbar_init(smem_u32(&ctl->s_free[b]), SOFTMAX_WARPS);
+            mbar_init(smem_u32(&ctl->p_full[b]), SOFTMAX_WARPS);
             mbar_init(smem_u32(&ctl->pv_full[b]), 1);
-            mbar_init(smem_u32(&ctl->pv_free[b]), 128);
+            mbar_init(smem_u32(&ctl->pv_free[b]), SOFTMAX_WARPS);
+            mbar_init(smem_u32(&ctl->x_full[b]), SOFTMAX_WARPS);
         }
+        mbar_init(smem_u32(&ctl->l_full), SOFTMAX_WARPS);
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -128,7 +157,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
             for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
                 const int s = it % KV_STAGES;
                 const uint32_t ph = (it / KV_STAGES) & 1;
-                if (!mbar_wait(smem_u32(&ctl->kv_empty[s]), ph ^ 1, abort_flag)) break;
                 // which pages of this tile hold keys some row of the tile may see
                 int first_page = kt * pages_per_tile, n_pages = 0;
                 int page_ids[16];
@@ -139,17 +167,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                     page_ids[j] = pid;
                     n_pages += pid >= 0;
                 }
-                const uint32_t full = smem_u32(&ctl->kv_full[s]);
-                mbar_expect_tx(full, (uint32_t)n_pages * page_bytes * 4u);
+                if (!mbar_wait(smem_u32(&ctl->k_empty[s]), ph ^ 1, abort_flag)) break;
+                const uint32_t kfull = smem_u32(&ctl->k_full[s]);
+                mbar_expect_tx(kfull, (uint32_t)n_pages * page_bytes * 2u);
                 const uint32_t k_dst = smem_u32(sK + s * TILE_BYTES), v_dst = smem_u32(sV + s * TILE_BYTES);
                 for (int j = 0; j < pages_per_tile; ++j) {
                     if (page_ids[j] < 0) continue;
                     const int pool_row = (page_ids[j] * G + g) * page_size;
                     const uint32_t off = (uint32_t)j * page_bytes;
-                    tma_load_2d(k_dst + off, &tmK, 0, pool_row, full);
-                    tma_load_2d(k_dst + HALF_BYTES + off, &tmK, 64, pool_row, full);
-                    tma_load_2d(v_dst + off, &tmV, 0, pool_row, full);
-                    tma_load_2d(v_dst + HALF_BYTES + off, &tmV, 64, pool_row, full);
+                    tma_load_2d(k_dst + off, &tmK, 0, pool_row, kfull);
+                    tma_load_2d(k_dst + HALF_BYTES + off, &tmK, 64, pool_row, kfull);
+                }
+                if (!mbar_wait(smem_u32(&ctl->v_empty[s]), ph ^ 1, abort_flag)) break;
+                const uint32_t vfull = smem_u32(&ctl->v_full[s]);
+                mbar_expect_tx(vfull, (uint32_t)n_pages * page_bytes * 2u);
+                for (int j = 0; j < pages_per_tile; ++j) {
+                    if (page_ids[j] < 0) continue;
+                    const int pool_row = (page_ids[j] * G + g) * page_size;
+                    const uint32_t off = (uint32_t)j * page_bytes;
+                    tma_load_2d(v_dst + off, &tmV, 0, pool_row, vfull);
+                    tma_load_2d(v_dst + HALF_BYTES + off, &tmV, 64, pool_row, vfull);
                 }
             }
         }
@@ -166,7 +203,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 const int s = it % KV_STAGES;
                 const uint32_t b = it & 1, u = it >> 1;
                 if (!mbar_wait(smem_u32(&ctl->s_free[b]), (u & 1) ^ 1, abort_flag)) return false;
-                if (!mbar_wait(smem_u32(&ctl->kv_full[s]), (it / KV_STAGES) & 1, abort_flag)) return false;
+                if (!mbar_wait(smem_u32(&ctl->k_full[s]), (it / KV_STAGES) & 1, abort_flag)) return false;
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(sK + s * TILE_BYTES);
 #pragma unroll
@@ -175,6 +212,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                     umma_bf16(tmem_base + b * 128, smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024), IDESC_QK, k ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&ctl->s_full[b]));
+                umma_commit(smem_u32(&ctl->k_empty[s]));        // the key tile is free once these products have read it
                 return true;
             };
             if (ok && n_tiles_k > 0) ok = issue_qk(0);
@@ -184,6 +222,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 const uint32_t b = it & 1, u = it >> 1;
                 if (!mbar_wait(smem_u32(&ctl->p_full[b]), u & 1, abort_flag)) { ok = false; break; }
                 if (!mbar_wait(smem_u32(&ctl->pv_free[b]), (u & 1) ^ 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&ctl->v_full[s]), (it / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t p_addr = smem_u32(sP + b * TILE_BYTES), v_addr = smem_u32(sV + s * TILE_BYTES);
 #pragma unroll
@@ -193,121 +232,110 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                     umma_bf16(tmem_base + 256 + b * 128, smem_desc_sw128(p_addr + a_off, 16, 1024), smem_desc_sw128(v_addr + b_off, HALF_BYTES, 1024), IDESC_PV, k ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&ctl->pv_full[b]));
-                umma_commit(smem_u32(&ctl->kv_empty[s]));
+                umma_commit(smem_u32(&ctl->v_empty[s]));
             }
         }
     } else {
-        // ---- softmax and output: thread = query row ----
+        // ---- softmax and output: two threads per query row ----
+        // Warp w may read tensor-memory lanes 32*(w%4)..+31; warps 2..5 take keys/columns 0..63, warps 6..9 take 64..127.
         const int q = warp & 3;
+        const int hsel = (warp - 2) >> 2;
         const int row = q * 32 + lane;
         const int pos = pos0 + row;
         const bool row_valid = row < n_rows;
         const int wlo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-        float o[HD];
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + hsel * 64;
+        float o[64];
 #pragma unroll
-        for (int i = 0; i < HD; ++i) o[i] = 0.0f;
-        float m = -INFINITY, l = 0.0f;
-        float alpha_prev = 1.0f;      // the factor that goes with the P V result not yet added into O
+        for (int i = 0; i < 64; ++i) o[i] = 0.0f;
+        float m = -INFINITY, l = 0.0f;     // m: maximum of the whole row; l: sum over this thread's keys only
+        float alpha_prev = 1.0f;           // the factor that goes with the P V result not yet added into O
         uint32_t it = 0;
         bool ok = true;
-        uint32_t sreg[32];
-        // adds P V of tile `t` into O (O was scaled for the maximum at the time P of that tile was made)
+        uint32_t sreg[64];
+        // adds this thread's 64 columns of P V of tile `t` into O
         auto add_pv = [&](uint32_t t, float alpha) -> bool {
             const uint32_t b = t & 1, u = t >> 1;
             if (!mbar_wait(smem_u32(&ctl->pv_full[b]), u & 1, abort_flag)) return false;
             tc_fence_after();
+            tmem_ld32_nowait(lane_addr + 256 + b * 128, sreg);
+            tmem_ld32_nowait(lane_addr + 256 + b * 128 + 32, sreg + 32);
+            tmem_ld_wait();
 #pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
-                tmem_ld32_nowait(lane_addr + 256 + b * 128 + c * 32, sreg);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha, __uint_as_float(sreg[i]));
-            }
+            for (int i = 0; i < 64; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(sreg[i]));
             tc_fence_before();
-            mbar_arrive(smem_u32(&ctl->pv_free[b]));
+            warp_arrive(smem_u32(&ctl->pv_free[b]), lane);
             return true;
         };
         for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
             const uint32_t b = it & 1, u = it >> 1;
             if (!mbar_wait(smem_u32(&ctl->s_full[b]), u & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const int key0 = kt * BN;
-            const uint32_t s_addr = lane_addr + b * 128;
-            // a tile every key of which this row sees needs no mask
-            const bool interior = row_valid && key0 + BN - 1 <= pos && key0 >= wlo;
-            // pass 1: the row's maximum over this tile
-            float mx = m;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                tmem_ld32_nowait(s_addr + c * 32, sreg);
-                tmem_ld_wait();
-                if (interior) {
+            const int key0 = kt * BN + hsel * 64;          // first key of this thread's half
+            tmem_ld32_nowait(lane_addr + b * 128, sreg);
+            tmem_ld32_nowait(lane_addr + b * 128 + 32, sreg + 32);
+            tmem_ld_wait();
+            tc_fence_before();
+            warp_arrive(smem_u32(&ctl->s_free[b]), lane);  // S of this tile is in registers
+            // a half tile every key of which this row sees needs no mask
+            const bool interior = row_valid && key0 + 63 <= pos && key0 >= wlo;
+            float mx = -INFINITY;
+            if (interior) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sreg[i]));
-                } else {
+                for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sreg[i]));
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int key = key0 + c * 32 + i;
-                        if (row_valid && key <= pos && key >= wlo) mx = fmaxf(mx, __uint_as_float(sreg[i]));
-                    }
+                for (int i = 0; i < 64; ++i) {
+                    const int key = key0 + i;
+                    if (!(row_valid && key <= pos && key >= wlo)) sreg[i] = 0xff800000u;      // -inf
+                    mx = fmaxf(mx, __uint_as_float(sreg[i]));
                 }
             }
+            // the row's maximum is over both halves
+            // (a bounded mbarrier wait, not bar.sync: a thread that gave up elsewhere must not leave the others hanging)
+            ctl->xchg[b][hsel][row] = mx;
+            warp_arrive(smem_u32(&ctl->x_full[b]), lane);
+            if (!mbar_wait(smem_u32(&ctl->x_full[b]), u & 1, abort_flag)) { ok = false; break; }
+            mx = fmaxf(fmaxf(mx, ctl->xchg[b][hsel ^ 1][row]), m);
             const float use = (mx == -INFINITY) ? 0.0f : mx * scale_log2;
-            const float alpha = exp2f(m * scale_log2 - use);
+            const float alpha = fast_exp2(m * scale_log2 - use);
             m = mx;
-            // pass 2: probabilities, rounded to bf16 as the tensor core will read them
+            // probabilities, rounded to bf16 as the tensor core will read them; this thread's 64 keys are the
+            // [128 x 64] half `hsel` of P: 8 chunks of 16 bytes in row `row`, chunk index xor-ed with row % 8
             float sum = 0.0f;
-            unsigned char* p_buf = sP + b * TILE_BYTES;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                tmem_ld32_nowait(s_addr + c * 32, sreg);
-                tmem_ld_wait();
-                uint32_t packed[16];
-                if (interior) {
+            unsigned char* prow = sP + b * TILE_BYTES + hsel * HALF_BYTES + row * 128;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float p0 = exp2f(fmaf(__uint_as_float(sreg[i]), scale_log2, -use));
-                        const float p1 = exp2f(fmaf(__uint_as_float(sreg[i + 1]), scale_log2, -use));
-                        sum += p0 + p1;
-                        packed[i >> 1] = pack_bf16x2(p0, p1);
-                    }
-                } else {
+            for (int ch = 0; ch < 8; ++ch) {
+                uint32_t packed[4];
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const int key = key0 + c * 32 + i;
-                        const bool v0 = row_valid && key <= pos && key >= wlo;
-                        const bool v1 = row_valid && key + 1 <= pos && key + 1 >= wlo;
-                        const float p0 = v0 ? exp2f(fmaf(__uint_as_float(sreg[i]), scale_log2, -use)) : 0.0f;
-                        const float p1 = v1 ? exp2f(fmaf(__uint_as_float(sreg[i + 1]), scale_log2, -use)) : 0.0f;
-                        sum += p0 + p1;
-                        packed[i >> 1] = pack_bf16x2(p0, p1);
-                    }
+                for (int i = 0; i < 4; ++i) {
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sreg[ch * 8 + 2 * i]), scale_log2, -use));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sreg[ch * 8 + 2 * i + 1]), scale_log2, -use));
+                    sum += p0 + p1;
+                    packed[i] = pack_bf16x2(p0, p1);
                 }
-                // 32 keys = 4 chunks of 16 bytes in this row of the [128 x 64] half c/2; chunk index is xor-ed with row % 8
-                unsigned char* prow = p_buf + (c >> 1) * HALF_BYTES + row * 128;
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    const int logical = (c & 1) * 4 + ch;
-                    *reinterpret_cast<uint4*>(prow + ((logical ^ (row & 7)) << 4)) =
-                        make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
-                }
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
             l = l * alpha + sum;
-            tc_fence_before();
-            mbar_arrive(smem_u32(&ctl->s_free[b]));                           // S of this tile is consumed
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P is read by the tensor core (async proxy)
-            mbar_arrive(smem_u32(&ctl->p_full[b]));
+            warp_arrive(smem_u32(&ctl->p_full[b]), lane);
             // while the tensor core multiplies this P with V, take in the previous tile's P V
             if (it >= 1 && !add_pv(it - 1, alpha_prev)) { ok = false; break; }
             alpha_prev = alpha;
         }
         if (ok && it >= 1) ok = add_pv(it - 1, alpha_prev);
+        // the row sum is the sum of the two halves (both are scaled to the same final maximum)
+        // the buffer the last tile did not use: everyone finished reading it before arriving for the last tile's exchange
+        const int lb = it & 1;
+        ctl->xchg[lb][hsel][row] = l;
+        warp_arrive(smem_u32(&ctl->l_full), lane);
+        if (ok) ok = mbar_wait(smem_u32(&ctl->l_full), 0, abort_flag);
+        l += ctl->xchg[lb][hsel ^ 1][row];
         if (ok && row_valid) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            __nv_bfloat16* orow = out + ((size_t)(row0 + row) * H + h) * HD;
+            __nv_bfloat16* orow = out + ((size_t)(row0 + row) * H + h) * HD + hsel * 64;
 #pragma unroll
-            for (int i = 0; i < HD; i += 8) {
+            for (int i = 0; i < 64; i += 8) {
                 *reinterpret_cast<uint4*>(orow + i) = make_uint4(pack_bf16x2(o[i] * inv, o[i + 1] * inv), pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv),
                                                                  pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv), pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv));
             }
@@ -349,7 +377,7 @@ MM_EXPORT int mm_attention_prefill_tcgen05(const void* q, const void* k_pages, c
         mm_set_last_error("attention_prefill_tcgen05: cuTensorMapEncodeTiled failed or is not available");
         return MM_ERR_DRIVER;
     }
-    const size_t smem = (size_t)(3 + 2 * KV_STAGES) * TILE_BYTES + 1024 + sizeof(AttCtl);
+    const size_t smem = (size_t)(3 + 2 * KV_STAGES) * TILE_BYTES + sizeof(AttCtl);
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
