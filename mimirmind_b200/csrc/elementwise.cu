@@ -87,9 +87,69 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     }
 }
 
+// bfloat16 activations, width a multiple of 8 and at most 8192: every thread keeps 8 consecutive elements in
+// registers (two float4 of the residual, one 16-byte load of the branch output), so a row makes one trip.
+template <typename WT>
+__global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ residual, const __nv_bfloat16* __restrict__ delta,
+                                          const int32_t* __restrict__ rows, const WT* __restrict__ weight,
+                                          __nv_bfloat16* __restrict__ out, int d, float eps) {
+    __shared__ float red[32];
+    pdl_wait();
+    pdl_trigger();
+    const int i = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    const int c = threadIdx.x * 8;
+    const bool active = c < d;
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = 0.0f;
+    if (active) {
+        const float4 a = *reinterpret_cast<const float4*>(residual + r * d + c);
+        const float4 b = *reinterpret_cast<const float4*>(residual + r * d + c + 4);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        if (delta) {
+            const uint4 dv = *reinterpret_cast<const uint4*>(delta + r * d + c);
+            const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(d2[k]);
+                v[2 * k] += f.x;
+                v[2 * k + 1] += f.y;
+            }
+        }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss = fmaf(v[k], v[k], ss);
+    const float total = block_sum(ss, red);
+    const float inv_rms = 1.0f / sqrtf(total / (float)d + eps);
+    if (!active) return;
+    if (rows == nullptr && delta != nullptr) {
+        *reinterpret_cast<float4*>(residual + r * d + c) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(residual + r * d + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float w0 = to_f32<WT>(weight[c + 2 * k]), w1 = to_f32<WT>(weight[c + 2 * k + 1]);
+        o2[k] = __floats2bfloat162_rn(v[2 * k] * w0 * inv_rms, v[2 * k + 1] * w1 * inv_rms);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)i * d + c) = ov;
+}
+
 template <typename T, typename WT>
 static int launch_add_rmsnorm(float* residual, const void* delta, const int32_t* rows, const void* weight, void* out,
                               int n_rows, int d, float eps, cudaStream_t s) {
+    if constexpr (sizeof(T) == 2) {
+        if (d % 8 == 0 && d <= 8192) {
+            const int threads = ((d / 8 + 31) / 32) * 32;
+            mm_launch_pdl(add_rmsnorm_bf16x8_kernel<WT>, dim3(n_rows), dim3(threads), 0, s, residual, (const __nv_bfloat16*)delta, rows,
+                          (const WT*)weight, (__nv_bfloat16*)out, d, eps);
+            MM_CHECK_LAUNCH();
+            return MM_OK;
+        }
+    }
     const size_t smem = (size_t)d * sizeof(float);
     if (smem > 48 * 1024) {
         if (smem > 200 * 1024) {
@@ -308,6 +368,96 @@ __global__ void qkv_rope_kvwrite_kernel(const T* __restrict__ qkv, const WT* __r
     }
 }
 
+// bfloat16, full rotary (rotary_dim == hd) with hd a multiple of 16: a thread rotates 8 consecutive pairs, two
+// 16-byte loads and two 16-byte stores.
+template <typename WT>
+__global__ void qkv_rope_kvwrite_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const WT* __restrict__ bias,
+                                               __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pages,
+                                               __nv_bfloat16* __restrict__ v_pages, const int32_t* __restrict__ positions,
+                                               const int32_t* __restrict__ token_req, const int32_t* __restrict__ block_table,
+                                               int table_width, int page_size, int H, int G, int hd, float theta_base) {
+    extern __shared__ float cs[];  // cos[half], sin[half]
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = hd / 2;
+    float* cosv = cs;
+    float* sinv = cs + half;
+    {
+        const float inv_dim = 1.0f / (float)hd;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float freq = powf(theta_base, -(float)(2 * i) * inv_dim);
+            const float ang = (float)pos * freq;
+            cosv[i] = cosf(ang);
+            sinv[i] = sinf(ang);
+        }
+    }
+    __syncthreads();
+    const int row_width = (H + 2 * G) * hd;
+    const __nv_bfloat16* src = qkv + (size_t)t * row_width;
+    __nv_bfloat16* kdst = nullptr;
+    __nv_bfloat16* vdst = nullptr;
+    if (k_pages != nullptr) {
+        const int page = block_table[(size_t)token_req[t] * table_width + pos / page_size];
+        if (page >= 0) {
+            const size_t base = ((size_t)page * G * page_size + (size_t)(pos % page_size)) * hd;
+            kdst = k_pages + base;
+            vdst = v_pages + base;
+        }
+    }
+    const size_t head_stride_in_page = (size_t)page_size * hd;
+    const int chunks = half / 8;                      // 8-pair chunks per head
+    auto load8 = [&](int col, float* f) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + col);
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 x = __bfloat1622float2(p2[k]);
+            f[2 * k] = x.x;
+            f[2 * k + 1] = x.y;
+        }
+        if (bias) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) f[k] += to_f32<WT>(bias[col + k]);
+        }
+    };
+    auto store8 = [&](__nv_bfloat16* dst, const float* f) {
+        uint4 ov;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o2[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+        *reinterpret_cast<uint4*>(dst) = ov;
+    };
+    for (int idx = threadIdx.x; idx < (H + G) * chunks; idx += blockDim.x) {
+        const int h = idx / chunks, i0 = (idx - h * chunks) * 8;
+        float a[8], b[8], ra[8], rb[8];
+        load8(h * hd + i0, a);
+        load8(h * hd + i0 + half, b);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float c = cosv[i0 + k], sn = sinv[i0 + k];
+            ra[k] = a[k] * c - b[k] * sn;
+            rb[k] = a[k] * sn + b[k] * c;
+        }
+        __nv_bfloat16* dst = nullptr;
+        if (h < H) dst = q_out + (size_t)t * H * hd + (size_t)h * hd;
+        else if (kdst) dst = kdst + (size_t)(h - H) * head_stride_in_page;
+        if (dst) {
+            store8(dst + i0, ra);
+            store8(dst + i0 + half, rb);
+        }
+    }
+    if (vdst) {
+        for (int idx = threadIdx.x; idx < G * hd / 8; idx += blockDim.x) {
+            const int g = (idx * 8) / hd, i0 = idx * 8 - g * hd;
+            float a[8];
+            load8((H + G) * hd + idx * 8, a);
+            store8(vdst + (size_t)g * head_stride_in_page + i0, a);
+        }
+    }
+}
+
 MM_EXPORT int mm_qkv_rope_kvwrite(const void* qkv, const void* bias, int bias_dtype, void* q_out, void* k_pages,
                                   void* v_pages, int act_dtype, const void* positions, const void* token_req,
                                   const void* block_table, int table_width, int page_size, int n_tokens, int H, int G,
@@ -326,6 +476,19 @@ MM_EXPORT int mm_qkv_rope_kvwrite(const void* qkv, const void* bias, int bias_dt
         (const int32_t*)token_req, (const int32_t*)block_table, table_width, page_size, H, G, hd, rotary_dim,      \
         theta_base)
     if (bias == nullptr) bias_dtype = MM_F32;
+    if (act_dtype == MM_BF16 && rotary_dim == hd && hd % 16 == 0) {
+        typedef __nv_bfloat16 bf;
+        if (bias_dtype == MM_F32)
+            mm_launch_pdl(qkv_rope_kvwrite_bf16x8_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, (const bf*)qkv, (const float*)bias,
+                          (bf*)q_out, (bf*)k_pages, (bf*)v_pages, (const int32_t*)positions, (const int32_t*)token_req,
+                          (const int32_t*)block_table, table_width, page_size, H, G, hd, theta_base);
+        else
+            mm_launch_pdl(qkv_rope_kvwrite_bf16x8_kernel<bf>, dim3(n_tokens), dim3(threads), smem, s, (const bf*)qkv, (const bf*)bias,
+                          (bf*)q_out, (bf*)k_pages, (bf*)v_pages, (const int32_t*)positions, (const int32_t*)token_req,
+                          (const int32_t*)block_table, table_width, page_size, H, G, hd, theta_base);
+        MM_CHECK_LAUNCH();
+        return MM_OK;
+    }
     if (act_dtype == MM_F32 && bias_dtype == MM_F32) MM_LAUNCH_QKV(float, float);
     else if (act_dtype == MM_F32 && bias_dtype == MM_BF16) MM_LAUNCH_QKV(float, __nv_bfloat16);
     else if (act_dtype == MM_BF16 && bias_dtype == MM_F32) MM_LAUNCH_QKV(__nv_bfloat16, float);
