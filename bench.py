@@ -89,7 +89,7 @@ class ClockSampler:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
@@ -189,9 +189,9 @@ def main() -> int:
             firsts.append(int(lg.argmax(-1).item()))
         sess = DecodeSession(runner, batch, CONTEXT, greedy=True, feed_back=True)
         sess.bind(ids, w_steps + k_steps, firsts)
-        before = kernel_lib.LAUNCH_CALLS
-        sess.step()                                   # eager + capture
-        per_step_calls = (kernel_lib.LAUNCH_CALLS - before) // 2
+        before = kernel_lib.launch_count()
+        sess.step()                                   # eager + capture: the step's kernels are launched twice
+        per_step_calls = (kernel_lib.launch_count() - before) // 2
         for _ in range(w_steps - 1):
             sess.step()
         torch.cuda.synchronize()
@@ -224,12 +224,12 @@ def main() -> int:
     achieved = step_bytes / (ms8 * 1e-3) / 1e9
     points = {}
     if not args.no_points:
-        for b, k in ((1, max(16, steps // 2)), (64, max(16, steps // 2))):
+        for b, k in ((1, max(16, steps // 4)), (64, max(16, steps // 4))):
             ms, _, _, _ = decode_run(b, k, warmup)
             points[f"decode_b{b}"] = b / (ms * 1e-3)
 
     # ---- end to end: Engine.generate, host token lists in and out ------------------------------
-    n_new = steps + 1
+    n_new = min(steps, 256) + 1
     engine.generate(prompts[:BATCH], max_new_tokens=max(engine.graph_min_steps + 1, min(n_new, 12)), use_eos=False)   # warm-up: captures the graph
     h0, d0, g0 = engine.h2d_bytes, engine.d2h_bytes, engine.graph_steps
     res = engine.generate(prompts[:BATCH], max_new_tokens=n_new, use_eos=False)

@@ -31,7 +31,10 @@
             mm_set_last_error(cudaGetErrorString(e__));    \
             return MM_ERR_LAUNCH;                          \
         }                                                  \
+        ++g_mm_launch_count;                               \
     } while (0)
+
+extern long long g_mm_launch_count;   // kernels of this library launched (or captured) so far
 
 #define MM_REQUIRE(cond, msg)          \
     do {                               \

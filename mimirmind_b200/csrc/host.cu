@@ -16,3 +16,7 @@ extern "C" __attribute__((visibility("default"))) const char* mm_last_error() { 
 int g_mm_pdl = 0;
 extern "C" __attribute__((visibility("default"))) void mm_set_pdl(int on) { g_mm_pdl = on ? 1 : 0; }
 extern "C" __attribute__((visibility("default"))) int mm_get_pdl() { return g_mm_pdl; }
+
+// Every kernel launch of this library counts itself here (MM_CHECK_LAUNCH).
+long long g_mm_launch_count = 0;
+extern "C" __attribute__((visibility("default"))) long long mm_launch_count() { return g_mm_launch_count; }

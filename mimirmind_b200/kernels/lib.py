@@ -57,6 +57,8 @@ def load(verbose: bool = True) -> ctypes.CDLL:
         lib.mm_set_pdl.restype = None
         lib.mm_get_pdl.argtypes = []
         lib.mm_get_pdl.restype = c_int
+        lib.mm_launch_count.argtypes = []
+        lib.mm_launch_count.restype = c_longlong
         lib.mm_uniform_from.restype = c_float
         lib.mm_uniform_from.argtypes = [c_ulonglong, c_ulonglong]
         for name, args in _PROTOTYPES.items():
@@ -78,12 +80,12 @@ def declare(name: str, argtypes, restype=c_int):
     return fn
 
 
-LAUNCH_CALLS = 0   # entry points called so far (each launches one kernel, the split attention two)
+def launch_count() -> int:
+    """Kernels of this library launched (or recorded into a graph under capture) so far."""
+    return int(load().mm_launch_count())
 
 
 def check(code: int, what: str) -> None:
-    global LAUNCH_CALLS
-    LAUNCH_CALLS += 1
     if code != 0:
         msg = load().mm_last_error().decode("utf-8", "replace")
         raise KernelError(f"{what} failed (code {code}): {msg}")
