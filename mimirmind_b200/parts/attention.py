@@ -77,6 +77,20 @@ class GQAAttention(Mixer):
             self.b_qkv = torch.cat(bs, dim=0).contiguous()
         self.w_o = weights.take(spec["o"] + ".weight").contiguous()
 
+    def _encode_unfused(self, qkv: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """A position encoding the fused kernel cannot apply: add the bias with the same kernel into contiguous
+        buffers (a pool of one-token pages addressed by token index, no rotation), let the encoding's own
+        ``apply`` work on q [n, H, hd] and k [n, G, hd] in place, and hand back one [n, (H+2G)*hd] buffer."""
+        n = qkv.shape[0]
+        H, G, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        q = torch.empty((n, H * hd), dtype=qkv.dtype, device=qkv.device)
+        k = torch.empty((n, G, 1, hd), dtype=qkv.dtype, device=qkv.device)
+        v = torch.empty_like(k)
+        index = torch.arange(n, dtype=torch.int32, device=qkv.device)
+        ops.qkv_rope_kvwrite(qkv, self.b_qkv, q, k, v, index, torch.zeros_like(index), index.view(1, n).contiguous(), 1, H, G, hd, 0, 1.0)
+        self.position.apply(q.view(n, H, hd), k.view(n, G, hd), ctx.positions)
+        return torch.cat([q, k.view(n, G * hd), v.view(n, G * hd)], dim=1)
+
     def kv_cache_spec(self) -> Optional[KVCacheSpec]:
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
@@ -86,12 +100,16 @@ class GQAAttention(Mixer):
         qkv = linear(x, self.w_qkv, None, self.rt)
         q = torch.empty((n, H * hd), dtype=x.dtype, device=x.device)
         fused = self.position.fused_rotary()
-        if fused is None:
-            raise NotImplementedError("position encodings without a fused form are applied by their own apply()")
-        rotary_dim, theta = fused
-        ops.qkv_rope_kvwrite(qkv, self.b_qkv, q, cache.k_pages if cache.writes else None,
-                             cache.v_pages if cache.writes else None, ctx.positions, ctx.token_req, cache.block_table,
-                             cache.page_size, H, G, hd, rotary_dim, theta)
+        if fused is not None:
+            rotary_dim, theta = fused
+            ops.qkv_rope_kvwrite(qkv, self.b_qkv, q, cache.k_pages if cache.writes else None,
+                                 cache.v_pages if cache.writes else None, ctx.positions, ctx.token_req, cache.block_table,
+                                 cache.page_size, H, G, hd, rotary_dim, theta)
+        else:
+            qkv = self._encode_unfused(qkv, ctx)
+            ops.qkv_rope_kvwrite(qkv, None, q, cache.k_pages if cache.writes else None,
+                                 cache.v_pages if cache.writes else None, ctx.positions, ctx.token_req, cache.block_table,
+                                 cache.page_size, H, G, hd, 0, 1.0)
         out = torch.empty_like(q)
         from ..kernels import attention as attn_kernels
         attn_kernels.paged_attention(q, cache, out, ctx, H, G, hd, self.window, self.scale)

@@ -208,3 +208,105 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     finally:
         registry.MIXERS.unregister("toy_running_mean")
         registry.ARCHITECTURES.unregister("ToyForTest")
+
+
+# ---- another position encoding and a feed-forward with routing, defined here ---------------------------------
+
+def test_toy_position_encoding_and_routed_feed_forward(tmp_path):
+    """A position encoding the fused kernel does not know (each head's q and k are scaled by a factor that depends
+    on the position) and a feed-forward that routes every token to one of two experts by fp32 router logits are
+    registered from outside the package and run through the engine: whole and in portions, against a plain
+    computation put together from the plain implementation's own part functions."""
+    from mimirmind_b200 import registry
+    from mimirmind_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+    from mimirmind_b200.engine.loader import make_runtime
+    from mimirmind_b200.engine.model import Model
+    from mimirmind_b200.engine.runner import ModelRunner, StepEntry
+    from mimirmind_b200.kernels import ops as kops
+    from mimirmind_b200.parts.base import FeedForward, PositionEncoding
+    from mimirmind_b200.weights.store import random_tensors
+    registry._ensure_builtin()
+
+    @registry.POSITION_ENCODINGS.register("toy_position_scale", replace=True)
+    class PositionScale(PositionEncoding):
+        def __init__(self, spec, weights, rt):
+            super().__init__(spec, weights, rt)
+            self.rate = float(spec["rate"])
+
+        def apply(self, q, k, positions):
+            f = (1.0 + self.rate * positions.float()).view(-1, 1, 1)
+            q.mul_(torch.cos(f * 0.1).to(q.dtype))
+            k.mul_(f.to(k.dtype))
+
+    @registry.FEED_FORWARDS.register("toy_two_experts", replace=True)
+    class TwoExperts(FeedForward):
+        @classmethod
+        def tensor_specs(cls, spec, prefix):
+            d = spec["hidden"]
+            return [TensorSpec(prefix + "router.weight", (2, d)), TensorSpec(prefix + "experts.weight", (2, d, d))]
+
+        def __init__(self, spec, weights, rt):
+            super().__init__(spec, weights, rt)
+            self.router = weights.get("router.weight")
+            self.experts = weights.get("experts.weight")
+
+        def forward(self, x, ctx):
+            logits = torch.empty((x.shape[0], 2), dtype=torch.float32, device=x.device)
+            kops.gemm_simt(x, self.router, None, logits)                   # router logits in fp32, per token
+            choice = logits.argmax(-1)
+            out = torch.empty_like(x)
+            for e in range(2):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    y = torch.empty((rows.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+                    kops.gemm_simt(x[rows].contiguous(), self.experts[e].contiguous(), None, y)
+                    out[rows] = y
+            return out
+
+    d, H, G, hd, V = 48, 3, 1, 16, 70
+    norm = lambda name: PartSpec("rmsnorm", {"width": d, "eps": 1e-5, "weight": name})
+    attn = PartSpec("gqa_attention", dict(hidden=d, num_heads=H, num_kv_heads=G, head_dim=hd, window=0, scale=None, qkv_bias=True,
+                                          position=PartSpec("toy_position_scale", {"rate": 0.03}), q="q", k="k", v="v", o="o"))
+    layer = LayerSpec("l0.", PartSpec("pre_norm"), attn, PartSpec("toy_two_experts", {"hidden": d}), norm("n1"), norm("n2"))
+    spec = ModelSpec("ToyRouted", d, V, 256, PartSpec("token_embedding", {"vocab": V, "width": d, "scale": 1.0, "weight": "emb"}),
+                     (layer,), (ScheduleEntry(0),), norm("nf"), PartSpec("lm_head", {"vocab": V, "width": d, "weight": "head", "tied_to": "emb"}))
+    try:
+        rt_ = make_runtime("float32")
+        tensors = random_tensors(spec, 3, torch.float32, rt_.device)
+        w = {k: v.double().cpu().numpy() for k, v in tensors.items()}
+        model = Model(spec, tensors, rt_)
+        toks = random_tokens(V, 50, 4)
+
+        def run(cuts, rid, runner):
+            runner.add_request(rid)
+            outs, p = [], 0
+            for c in cuts:
+                outs.append(runner.step([StepEntry(rid, toks[p:p + c], list(range(c)))]).cpu().numpy())
+                p += c
+            return np.concatenate(outs)
+
+        runner = ModelRunner(model, 16, 16, 4)
+        whole = run([50], "a", runner)
+        parts = run([9, 2, 1, 30, 8], "b", runner)
+        assert np.abs(whole - parts).max() < 1e-5
+        # plain computation from the plain implementation's part functions
+        T = len(toks)
+        pos = np.arange(T)
+        x = plain.embedding(w["emb"], toks)
+        n = plain.rms_norm(x, w["l0.n1"], 1e-5)
+        q = plain.linear(n, w["l0.q.weight"], w["l0.q.bias"]).reshape(T, H, hd)
+        k = plain.linear(n, w["l0.k.weight"], w["l0.k.bias"]).reshape(T, G, hd)
+        v = plain.linear(n, w["l0.v.weight"], w["l0.v.bias"]).reshape(T, G, hd)
+        f = (1.0 + 0.03 * pos).reshape(T, 1, 1)
+        q, k = q * np.cos(f * 0.1), k * f
+        x = x + plain.linear(plain.attention(q, k, v, 0).reshape(T, H * hd), w["l0.o.weight"])
+        n = plain.rms_norm(x, w["l0.n2"], 1e-5)
+        choice = (n @ w["l0.router.weight"].T).argmax(-1)
+        y = np.stack([n[t] @ w["l0.experts.weight"][choice[t]].T for t in range(T)])
+        x = x + y
+        ref = plain.linear(plain.rms_norm(x, w["nf"], 1e-5), w["emb"])
+        assert len(set(choice.tolist())) == 2                      # both experts were used
+        assert np.abs(whole - ref).max() < 2e-5 * max(1.0, np.abs(ref).max())
+    finally:
+        registry.POSITION_ENCODINGS.unregister("toy_position_scale")
+        registry.FEED_FORWARDS.unregister("toy_two_experts")
