@@ -583,6 +583,25 @@ MM_EXPORT int mm_attention_decode_bf16(const void* q, const void* k_pages, const
     return MM_ERR_UNSUPPORTED;
 }
 
+// The merge pass alone, for the decode kernel of attention_decode_tma.cu, which writes the same partial results.
+MM_EXPORT int mm_attention_decode_merge_bf16(void* out, const void* part_o, const void* part_ml, const void* items, int n_items,
+                                             const void* positions, int H, int hd, int window, int split_len, int max_splits,
+                                             void* stream) {
+    MM_REQUIRE(hd == 64 || hd == 128, "attention_decode_merge: head_dim must be 64 or 128");
+    MM_REQUIRE(n_items >= 0 && H > 0 && max_splits >= 1 && part_o != nullptr && part_ml != nullptr, "attention_decode_merge: bad arguments");
+    if (n_items == 0 || max_splits == 1) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 mgrid(n_items, H);
+    if (hd == 128)
+        mm_launch_pdl(attention_merge_kernel<128>, mgrid, dim3(128), 0, s, (__nv_bfloat16*)out, (const float*)part_o, (const float*)part_ml,
+                      (const int32_t*)items, (const int32_t*)positions, H, window, split_len, max_splits);
+    else
+        mm_launch_pdl(attention_merge_kernel<64>, mgrid, dim3(64), 0, s, (__nv_bfloat16*)out, (const float*)part_o, (const float*)part_ml,
+                      (const int32_t*)items, (const int32_t*)positions, H, window, split_len, max_splits);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
 // ---------------------------------------------------------------------------
 // Split-key decode attention for callers that cannot allocate (see no_alloc.h).
 // ---------------------------------------------------------------------------

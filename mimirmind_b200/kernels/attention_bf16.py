@@ -23,6 +23,8 @@ PREFILL_MIN = 16       # shorter portions go token by token through the decode k
 TILE_ROWS = 64         # query rows per CTA of the mma.sync prefill kernel
 TILE_ROWS_TC = 128     # ... of the tcgen05 prefill kernel (head size 128)
 USE_TCGEN05_PREFILL = True
+USE_TMA_DECODE = True   # decode attention with a TMA producer warp (page sizes 8..64)
+TMA_DECODE_STAGES = 3
 TARGET_CTAS = 2 * 148  # decode CTAs wanted (measured: 2 per SM beat 1 and 4 at batch 8; batch 64 is best unsplit)
 FIXED_SPLIT = None     # tests set a split length in keys to cut by absolute position instead
 
@@ -36,6 +38,8 @@ def _declare():
     P, I, F = c_void_p, c_int, c_float
     _lib.declare("mm_attention_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, F, P])
     _lib.declare("mm_attention_prefill_tcgen05", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P])
+    _lib.declare("mm_attention_decode_tma_bf16", [P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P])
+    _lib.declare("mm_attention_decode_merge_bf16", [P, P, P, P, I, P, I, I, I, I, I, P])
     _lib.declare("mm_attention_decode_bf16", [P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P])
     _declared = True
 
@@ -119,7 +123,21 @@ def run(q, cache, out, ctx, num_heads: int, num_kv_heads: int, head_dim: int, wi
                                             out.data_ptr(), plan.tiles.data_ptr(), plan.n_tiles, table.data_ptr(),
                                             table.shape[1], cache.page_size, num_heads, num_kv_heads, head_dim, window,
                                             float(scale), stream), "attention_prefill_bf16")
-    if plan.n_items:
+    if plan.n_items and USE_TMA_DECODE and cache.page_size in (8, 16, 32, 64):
+        from . import ops
+        po = plan.part_o.data_ptr() if plan.part_o is not None else None
+        pm = plan.part_ml.data_ptr() if plan.part_ml is not None else None
+        it = plan.items.data_ptr() if plan.items is not None else None
+        check(lib.mm_attention_decode_tma_bf16(
+            q.data_ptr(), cache.k_pages.data_ptr(), cache.v_pages.data_ptr(), out.data_ptr(), po, pm, it, plan.n_items,
+            ctx.positions.data_ptr(), ctx.token_req.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
+            cache.k_pages.shape[0], num_heads, num_kv_heads, head_dim, window, float(scale), plan.split_len, plan.max_splits,
+            TMA_DECODE_STAGES, ops.tcgen05_error_flag(q.device).data_ptr(), stream), "attention_decode_tma_bf16")
+        if plan.max_splits > 1:
+            check(lib.mm_attention_decode_merge_bf16(out.data_ptr(), po, pm, it, plan.n_items, ctx.positions.data_ptr(), num_heads,
+                                                     head_dim, window, plan.split_len, plan.max_splits, stream),
+                  "attention_decode_merge_bf16")
+    elif plan.n_items:
         check(lib.mm_attention_decode_bf16(
             q.data_ptr(), cache.k_pages.data_ptr(), cache.v_pages.data_ptr(), out.data_ptr(),
             plan.part_o.data_ptr() if plan.part_o is not None else None,

@@ -236,7 +236,7 @@ def test_attention_generic(dtype, H, G, hd, ps, window):
     assert abs(ref[39, H - 1, 0] - 50.0) < 1.0
 
 
-def run_bf16_attention(case, H, G, hd, ps, window, prefill_min=None, split=None, target=None, tc=True):
+def run_bf16_attention(case, H, G, hd, ps, window, prefill_min=None, split=None, target=None, tc=True, tma=True):
     """Through the engine's own plan builder, with a hand-made step context."""
     from mimirmind_b200.kernels import attention_bf16 as ab
     from mimirmind_b200.parts.base import LayerCache, Runtime, StepContext
@@ -248,9 +248,10 @@ def run_bf16_attention(case, H, G, hd, ps, window, prefill_min=None, split=None,
                       logit_rows=None, n_logit_rows=0, page_size=ps, runtime=Runtime(torch.bfloat16, torch.device(DEV)),
                       max_kv_len=max(ctx_lens), max_q_len=max(q_lens))
     cache = LayerCache(k_pages=case["kp"], v_pages=case["vp"], block_table=case["table"], page_size=ps)
-    old = (ab.PREFILL_MIN, ab.FIXED_SPLIT, ab.TARGET_CTAS, ab.USE_TCGEN05_PREFILL)
+    old = (ab.PREFILL_MIN, ab.FIXED_SPLIT, ab.TARGET_CTAS, ab.USE_TCGEN05_PREFILL, ab.USE_TMA_DECODE)
     try:
         ab.USE_TCGEN05_PREFILL = tc
+        ab.USE_TMA_DECODE = tma
         if prefill_min is not None:
             ab.PREFILL_MIN = prefill_min
         if split is not None:
@@ -261,7 +262,7 @@ def run_bf16_attention(case, H, G, hd, ps, window, prefill_min=None, split=None,
         ab.run(case["q"], cache, out, ctx, H, G, hd, window, 1.0 / np.sqrt(hd))
         plan = ctx.plans[("attention_bf16", H, G, hd)]
     finally:
-        ab.PREFILL_MIN, ab.FIXED_SPLIT, ab.TARGET_CTAS, ab.USE_TCGEN05_PREFILL = old
+        ab.PREFILL_MIN, ab.FIXED_SPLIT, ab.TARGET_CTAS, ab.USE_TCGEN05_PREFILL, ab.USE_TMA_DECODE = old
         ops().check_tcgen05_errors(case["q"].device)
     return out, plan
 
@@ -276,7 +277,8 @@ def test_attention_tensor_core_kernels(H, G, hd, ps, window):
     case = make_attention_case(rng, H, G, hd, ps, ctx_lens, q_lens, torch.bfloat16, spike=(0, 199, far, H - 1))
     ref = attention_reference(case, window)
     assert abs(ref[199, H - 1, 0] - 50.0) < 1.0
-    for kwargs in (dict(), dict(prefill_min=10 ** 6, split=128), dict(prefill_min=10 ** 6, target=10 ** 6),
+    for kwargs in (dict(), dict(prefill_min=10 ** 6, split=128), dict(prefill_min=10 ** 6, split=128, tma=False), dict(prefill_min=10 ** 6, target=10 ** 6),
+                   dict(prefill_min=10 ** 6, target=10 ** 6, tma=False),
                    dict(prefill_min=10 ** 6, target=1), dict(prefill_min=1, tc=False), dict(prefill_min=1)):
         out, plan = run_bf16_attention(case, H, G, hd, ps, window, **kwargs)
         got = out.float().cpu().numpy().reshape(ref.shape)
