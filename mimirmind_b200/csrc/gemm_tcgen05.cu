@@ -31,6 +31,7 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;
+constexpr int EPI_STAGE_BYTES = 32 * 256;     // per epilogue warp: 32 rows of 128 bf16, staged so that global stores are whole rows
 constexpr int GEMM_THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
@@ -131,7 +132,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     extern __shared__ unsigned char smem_raw[];
     // 128-byte swizzle wants 1024-byte aligned tiles
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + STAGES * STAGE_BYTES);
+    unsigned char* staging = tiles + STAGES * STAGE_BYTES;                     // 4 epilogue warps x [32 rows][256 bytes]
+    SharedCtl* ctl = reinterpret_cast<SharedCtl*>(staging + 4 * EPI_STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &ctl->abort_flag;
 
@@ -218,57 +220,78 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+            if (EPI == EPI_F32) {
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                const int col0 = n0 + c * 32;
-                if (col0 >= N) break;                      // uniform over the warp
-                uint32_t r[32];
-                tmem_ld32(taddr + c * 32, r);
-                if (row >= M) continue;
-                float v[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-                if (EPI != EPI_SWIGLU && bias != nullptr) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (col0 + i < N)
-                            v[i] += (bias_dtype == MM_F32) ? ((const float*)bias)[col0 + i] : __bfloat162float(((const __nv_bfloat16*)bias)[col0 + i]);
-                }
-                if (EPI == EPI_BF16) {
-                    __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)row * ldo + col0;
-                    if (col0 + 32 <= N) {
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            *reinterpret_cast<uint4*>(o + i * 8) = make_uint4(pack2(v[i * 8], v[i * 8 + 1]), pack2(v[i * 8 + 2], v[i * 8 + 3]),
-                                                                              pack2(v[i * 8 + 4], v[i * 8 + 5]), pack2(v[i * 8 + 6], v[i * 8 + 7]));
-                    } else {
-                        for (int i = 0; i < 32 && col0 + i < N; ++i) o[i] = __float2bfloat16_rn(v[i]);
-                    }
-                } else if (EPI == EPI_F32) {
+                for (int c = 0; c < BN / 32; ++c) {
+                    const int col0 = n0 + c * 32;
+                    if (col0 >= N) break;                      // uniform over the warp
+                    uint32_t r[32];
+                    tmem_ld32(taddr + c * 32, r);
+                    if (row >= M) continue;
                     float* o = (float*)out + (size_t)row * ldo + col0;
-                    if (col0 + 32 <= N) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) *reinterpret_cast<float4*>(o + i * 4) = make_float4(v[i * 4], v[i * 4 + 1], v[i * 4 + 2], v[i * 4 + 3]);
-                    } else {
-                        for (int i = 0; i < 32 && col0 + i < N; ++i) o[i] = v[i];
+                    for (int i = 0; i < 32 && col0 + i < N; ++i) {
+                        float v = __uint_as_float(r[i]);
+                        if (bias != nullptr) v += (bias_dtype == MM_F32) ? ((const float*)bias)[col0 + i] : __bfloat162float(((const __nv_bfloat16*)bias)[col0 + i]);
+                        o[i] = v;
                     }
-                } else {
-                    // columns: 8 gate, 8 up, 8 gate, 8 up  ->  16 outputs
-                    __nv_bfloat16* o = (__nv_bfloat16*)out + (size_t)row * ldo + col0 / 2;
-                    float a[16];
+                }
+            } else {
+                // bf16 outputs: each thread owns a row of the accumulator, which would make every global store a
+                // 64-byte piece of a different row.  The warp stages 128 output columns of its 32 rows in shared memory
+                // (16-byte unit u of row r at u ^ (r & 15): conflict-free both ways) and then stores whole 256-byte rows.
+                constexpr int GROUP_CHUNKS = (EPI == EPI_SWIGLU) ? 8 : 4;      // 32-column accumulator chunks per 128 outputs
+                unsigned char* wstage = staging + q * EPI_STAGE_BYTES;
+                const int n_out = (EPI == EPI_SWIGLU) ? N / 2 : N;
+#pragma unroll 1
+                for (int grp = 0; grp < BN / 32 / GROUP_CHUNKS; ++grp) {
+                    if (n0 + grp * GROUP_CHUNKS * 32 >= N) break;              // uniform over the warp
+#pragma unroll 1
+                    for (int cc = 0; cc < GROUP_CHUNKS; ++cc) {
+                        const int c = grp * GROUP_CHUNKS + cc;
+                        const int col0 = n0 + c * 32;
+                        if (col0 >= N) break;                                 // uniform over the warp
+                        uint32_t r[32];
+                        tmem_ld32(taddr + c * 32, r);
+                        float v[32];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        a[i] = silu_mul(v[i], v[8 + i]);
-                        a[8 + i] = silu_mul(v[16 + i], v[24 + i]);
-                    }
-                    if (col0 + 32 <= N) {
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+                        unsigned char* srow = wstage + lane * 256;
+                        if (EPI == EPI_BF16) {
+                            if (bias != nullptr) {
 #pragma unroll
-                        for (int i = 0; i < 2; ++i)
-                            *reinterpret_cast<uint4*>(o + i * 8) = make_uint4(pack2(a[i * 8], a[i * 8 + 1]), pack2(a[i * 8 + 2], a[i * 8 + 3]),
-                                                                              pack2(a[i * 8 + 4], a[i * 8 + 5]), pack2(a[i * 8 + 6], a[i * 8 + 7]));
-                    } else {
-                        for (int i = 0; i < 16 && col0 + (i / 8) * 16 + 8 + (i % 8) < N; ++i) o[i] = __float2bfloat16_rn(a[i]);
+                                for (int i = 0; i < 32; ++i)
+                                    if (col0 + i < N)
+                                        v[i] += (bias_dtype == MM_F32) ? ((const float*)bias)[col0 + i] : __bfloat162float(((const __nv_bfloat16*)bias)[col0 + i]);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                *reinterpret_cast<uint4*>(srow + (((cc * 4 + i) ^ (lane & 15)) << 4)) =
+                                    make_uint4(pack2(v[i * 8], v[i * 8 + 1]), pack2(v[i * 8 + 2], v[i * 8 + 3]), pack2(v[i * 8 + 4], v[i * 8 + 5]), pack2(v[i * 8 + 6], v[i * 8 + 7]));
+                        } else {
+                            // columns: 8 gate, 8 up, 8 gate, 8 up  ->  16 outputs
+                            float a[16];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                a[i] = silu_mul(v[i], v[8 + i]);
+                                a[8 + i] = silu_mul(v[16 + i], v[24 + i]);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 2; ++i)
+                                *reinterpret_cast<uint4*>(srow + (((cc * 2 + i) ^ (lane & 15)) << 4)) =
+                                    make_uint4(pack2(a[i * 8], a[i * 8 + 1]), pack2(a[i * 8 + 2], a[i * 8 + 3]), pack2(a[i * 8 + 4], a[i * 8 + 5]), pack2(a[i * 8 + 6], a[i * 8 + 7]));
+                        }
                     }
+                    __syncwarp();
+                    const int out_base = (EPI == EPI_SWIGLU) ? n0 / 2 : n0 + grp * 128;
+#pragma unroll 4
+                    for (int it = 0; it < 16; ++it) {
+                        const int r = it * 2 + (lane >> 4), u = lane & 15;
+                        const int grow = m0 + q * 32 + r, gcol = out_base + u * 8;
+                        if (grow < M && gcol < n_out)
+                            *reinterpret_cast<uint4*>((__nv_bfloat16*)out + (size_t)grow * ldo + gcol) =
+                                *reinterpret_cast<const uint4*>(wstage + r * 256 + ((u ^ (r & 15)) << 4));
+                    }
+                    __syncwarp();
                 }
             }
             // the accumulator may be overwritten once all four warps have read it
@@ -323,7 +346,7 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int b
 template <int EPI>
 int launch(const CUtensorMap& a, const CUtensorMap& b, void* out, const void* bias, int bias_dtype, int M, int N, int K,
            int ldo, int* err, int max_ctas, cudaStream_t s) {
-    const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024 + sizeof(SharedCtl);
+    const size_t smem = (size_t)STAGES * STAGE_BYTES + 4 * EPI_STAGE_BYTES + 1024 + sizeof(SharedCtl);
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(gemm_tcgen05_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
