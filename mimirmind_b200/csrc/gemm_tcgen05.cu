@@ -21,11 +21,11 @@
 // The reference's counterparts are its wmma 16x16x16 bf16 kernel, one warp per output tile and
 // no pipelining (kernels/cuda/common/matmul_bf16_gemm_tc.cu:37-99), and its cuBLASLt route
 // (src/compute/cuda/GpuMatmul.cpp:786-884).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
+
+using namespace tc;
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int UMMA_K = 16;
@@ -33,82 +33,18 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int TMEM_COLS = 512;
 constexpr int EPI_STAGE_BYTES = 32 * 256;     // per epilogue warp: 32 rows of 128 bf16, staged so that global stores are whole rows
 constexpr int GEMM_THREADS = 192;
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 enum { EPI_BF16 = 0, EPI_SWIGLU = 1, EPI_F32 = 2 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// K-major tile written by TMA with the 128-byte swizzle: groups of 8 rows 1024 bytes apart
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) { return smem_desc_sw128(smem_addr, 16, 1024); }
 
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Bounded wait (non-blocking test in a counted loop).  Returns false if the limit ran out or another role raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if (it > 64u) __nanosleep(40);            // test_wait never blocks, so the limit bounds the time: under 2 s
-        if ((it & 255u) == 255u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile written by TMA with 128-byte swizzle: rows
-// of 64 bf16 (128 bytes), groups of 8 rows 1024 bytes apart (SBO), version 1, layout SWIZZLE_128B.
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;                    // leading byte offset (unused with swizzle), 16 B
-    d |= (uint64_t)(1024 >> 4) << 32;          // stride byte offset: 8 rows x 128 B
-    d |= (uint64_t)1 << 46;                    // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
-    return d;
-}
-
-// kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N = 256, M = 128.
-constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// fp32 accumulate, bf16 x bf16, both K-major, N = 256, M = 128
+constexpr uint32_t IDESC = idesc_bf16(BM, BN, false);
 
 __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(IDESC), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+    umma_bf16(d_tmem, a_desc, b_desc, IDESC, accumulate);
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -315,34 +251,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
-// rows x K bf16 matrix, row stride ld elements; box = box_rows x 64 elements, 128-byte swizzle, zero fill outside
-bool make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
-    EncodeTiledFn enc = get_encode();
-    if (enc == nullptr) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int EPI>
 int launch(const CUtensorMap& a, const CUtensorMap& b, void* out, const void* bias, int bias_dtype, int M, int N, int K,
            int ldo, int* err, int max_ctas, cudaStream_t s) {
@@ -375,7 +283,7 @@ MM_EXPORT int mm_gemm_tcgen05(const void* A, const void* W, const void* bias, in
     MM_REQUIRE(epilogue != EPI_SWIGLU || (N % 16 == 0 && bias == nullptr && ldo >= N / 2), "gemm_tcgen05: the SwiGLU epilogue needs N a multiple of 16 and no bias");
     MM_REQUIRE(ldo % 8 == 0 && (epilogue == EPI_SWIGLU || ldo >= N), "gemm_tcgen05: the row stride of the output must be a multiple of 8 and at least N");
     CUtensorMap ta, tb;
-    if (!make_map(&ta, A, M, K, lda, BM) || !make_map(&tb, W, N, K, K, BN)) {
+    if (!tc::make_map_bf16(&ta, A, M, K, lda, BM) || !tc::make_map_bf16(&tb, W, N, K, K, BN)) {
         mm_set_last_error("gemm_tcgen05: cuTensorMapEncodeTiled failed or is not available");
         return MM_ERR_DRIVER;
     }
