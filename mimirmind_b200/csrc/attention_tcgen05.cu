@@ -16,8 +16,9 @@
 // S, P and PV are double-buffered: while the softmax threads work on tile t the tensor core already
 // computes S of tile t+1 and P V of tile t, and a thread adds P V of tile t into its O only after it
 // has published P of tile t+1.
-// Warp 0 = TMA producer, warp 1 = MMA issuer and tensor-memory owner, warps 2..9 = softmax and
-// output.  Same formula as the other attention kernels (reference src/compute/Attention.cpp:43-94).
+// Warp 0 = TMA producer for keys (and Q), warp 10 = TMA producer for values: every lane fetches one half of one
+// page, so the 16 to 32 small copies of a tile are issued at once (one thread issuing them in turn was the
+// bottleneck of the whole kernel); warp 1 = MMA issuer and tensor-memory owner; warps 2..9 = softmax and output.  Same formula as the other attention kernels (reference src/compute/Attention.cpp:43-94).
 // All mbarrier waits are bounded; on a time-out the kernel frees its tensor memory, sets `err`
 // and returns.
 #include "tcgen05.cuh"
@@ -32,7 +33,8 @@ constexpr int BN = 128;          // keys per tile
 constexpr int KV_STAGES = 2;
 constexpr int HALF_BYTES = 128 * 64 * 2;        // a [128 rows x 64 columns] bf16 sub-tile, 128 bytes per row
 constexpr int TILE_BYTES = 2 * HALF_BYTES;      // [128 x 128] as two column halves
-constexpr int ATT_TC_THREADS = 320;            // producer warp, MMA warp, 8 softmax warps
+constexpr int ATT_TC_THREADS = 352;            // K producer warp, MMA warp, 8 softmax warps, V producer warp
+constexpr int V_PRODUCER_WARP = 10;
 constexpr int SOFTMAX_WARPS = 8;               // barriers between the softmax warps and the tensor core count warps, not
                                                // threads: one arrival per softmax warp on one mbarrier serialise and cost more than the math
 constexpr int TMEM_COLS_ATT = 512;              // S0, S1: columns 0..255; PV0, PV1: columns 256..511
@@ -144,51 +146,40 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
 
-    if (warp == 0) {
-        if (lane == 0) {
-            // ---- TMA producer ----
+    if (warp == 0 || warp == V_PRODUCER_WARP) {
+        // ---- TMA producers: warp 0 keys (and Q), warp 10 values; lane = (page of the tile, column half) ----
+        const bool for_k = warp == 0;
+        if (for_k && lane == 0) {
             const uint32_t qbar = smem_u32(&ctl->q_full);
             mbar_expect_tx(qbar, TILE_BYTES);
             tma_load_2d(smem_u32(sQ), &tmQ, h * HD, row0, qbar);
             tma_load_2d(smem_u32(sQ) + HALF_BYTES, &tmQ, h * HD + 64, row0, qbar);
-            const int pages_per_tile = BN / page_size;
-            const uint32_t page_bytes = (uint32_t)page_size * 128u;       // one column half of a page
-            uint32_t it = 0;
-            for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
-                const int s = it % KV_STAGES;
-                const uint32_t ph = (it / KV_STAGES) & 1;
-                // which pages of this tile hold keys some row of the tile may see
-                int first_page = kt * pages_per_tile, n_pages = 0;
-                int page_ids[16];
-                for (int j = 0; j < pages_per_tile; ++j) {
-                    const int key_lo = kt * BN + j * page_size;
-                    const bool wanted = key_lo < hi_all && key_lo + page_size > lo_all;
-                    const int pid = wanted ? table[first_page + j] : -1;
-                    page_ids[j] = pid;
-                    n_pages += pid >= 0;
-                }
-                if (!mbar_wait(smem_u32(&ctl->k_empty[s]), ph ^ 1, abort_flag)) break;
-                const uint32_t kfull = smem_u32(&ctl->k_full[s]);
-                mbar_expect_tx(kfull, (uint32_t)n_pages * page_bytes * 2u);
-                const uint32_t k_dst = smem_u32(sK + s * TILE_BYTES), v_dst = smem_u32(sV + s * TILE_BYTES);
-                for (int j = 0; j < pages_per_tile; ++j) {
-                    if (page_ids[j] < 0) continue;
-                    const int pool_row = (page_ids[j] * G + g) * page_size;
-                    const uint32_t off = (uint32_t)j * page_bytes;
-                    tma_load_2d(k_dst + off, &tmK, 0, pool_row, kfull);
-                    tma_load_2d(k_dst + HALF_BYTES + off, &tmK, 64, pool_row, kfull);
-                }
-                if (!mbar_wait(smem_u32(&ctl->v_empty[s]), ph ^ 1, abort_flag)) break;
-                const uint32_t vfull = smem_u32(&ctl->v_full[s]);
-                mbar_expect_tx(vfull, (uint32_t)n_pages * page_bytes * 2u);
-                for (int j = 0; j < pages_per_tile; ++j) {
-                    if (page_ids[j] < 0) continue;
-                    const int pool_row = (page_ids[j] * G + g) * page_size;
-                    const uint32_t off = (uint32_t)j * page_bytes;
-                    tma_load_2d(v_dst + off, &tmV, 0, pool_row, vfull);
-                    tma_load_2d(v_dst + HALF_BYTES + off, &tmV, 64, pool_row, vfull);
-                }
+        }
+        const int pages_per_tile = BN / page_size;
+        const uint32_t page_bytes = (uint32_t)page_size * 128u;       // one column half of a page
+        const int j = lane >> 1, hf = lane & 1;                       // this lane's page and half
+        const CUtensorMap* map = for_k ? &tmK : &tmV;
+        unsigned char* ring = for_k ? sK : sV;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
+            const int s = it % KV_STAGES;
+            const uint32_t ph = (it / KV_STAGES) & 1;
+            // pages of this tile that hold keys some row of the tile may see
+            int pid = -1;
+            if (j < pages_per_tile) {
+                const int key_lo = kt * BN + j * page_size;
+                if (key_lo < hi_all && key_lo + page_size > lo_all) pid = table[kt * pages_per_tile + j];
             }
+            const uint32_t have = __ballot_sync(0xffffffffu, pid >= 0);
+            const uint32_t full = smem_u32(for_k ? &ctl->k_full[s] : &ctl->v_full[s]);
+            if (lane == 0) {
+                ok = mbar_wait(smem_u32(for_k ? &ctl->k_empty[s] : &ctl->v_empty[s]), ph ^ 1, abort_flag);
+                if (ok) mbar_expect_tx(full, (uint32_t)__popc(have) * page_bytes);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (ok && pid >= 0)
+                tma_load_2d(smem_u32(ring + s * TILE_BYTES) + hf * HALF_BYTES + (uint32_t)j * page_bytes, map, hf * 64, (pid * G + g) * page_size, full);
         }
     } else if (warp == 1) {
         if (lane == 0) {
