@@ -123,37 +123,33 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     __syncthreads();
 
     if (warp == DT_CONSUMERS) {
-        // ---- producer ----
-        if (lane == 0) {
-            const int pages_per_tile = DT_KT / page_size;
-            const uint32_t page_bytes = (uint32_t)page_size * 128u;          // one column half of a page
-            uint32_t it = 0;
-            for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1;
-                int page_ids[8], n_pages = 0;
-                for (int j = 0; j < pages_per_tile; ++j) {
-                    const int key_lo = kt * DT_KT + j * page_size;
-                    const bool wanted = key_lo < k_end && key_lo + page_size > k_begin;
-                    const int pid = wanted ? table[kt * pages_per_tile + j] : -1;
-                    page_ids[j] = pid;
-                    n_pages += pid >= 0;
-                }
-                if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1, abort_flag)) break;
-                const uint32_t full = smem_u32(&ctl->full[s]);
-                mbar_expect_tx(full, (uint32_t)n_pages * page_bytes * 2u * HALVES);
-                const uint32_t k_dst = smem_u32(sK + s * TILE), v_dst = smem_u32(sV + s * TILE);
-                for (int j = 0; j < pages_per_tile; ++j) {
-                    if (page_ids[j] < 0) continue;
-                    const int pool_row = (page_ids[j] * G + g) * page_size;
-                    const uint32_t off = (uint32_t)j * page_bytes;
-#pragma unroll
-                    for (int hf = 0; hf < HALVES; ++hf) {
-                        tma_load_2d(k_dst + hf * (DT_KT * 128) + off, &tmK, hf * 64, pool_row, full);
-                        tma_load_2d(v_dst + hf * (DT_KT * 128) + off, &tmV, hf * 64, pool_row, full);
-                    }
-                }
+        // ---- producer: lane = (page of the tile, K or V, column half), all copies of a tile issued at once ----
+        const int pages_per_tile = DT_KT / page_size;
+        const uint32_t page_bytes = (uint32_t)page_size * 128u;          // one column half of a page
+        const int per_page = 2 * HALVES;                                 // copies per page: K and V, each column half
+        const int j = lane / per_page, sub = lane % per_page;
+        const bool is_v = sub >= HALVES;
+        const int hf = sub % HALVES;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1;
+            int pid = -1;
+            if (j < pages_per_tile) {
+                const int key_lo = kt * DT_KT + j * page_size;
+                if (key_lo < k_end && key_lo + page_size > k_begin) pid = table[kt * pages_per_tile + j];
             }
+            const uint32_t have = __ballot_sync(0xffffffffu, pid >= 0);
+            const uint32_t full = smem_u32(&ctl->full[s]);
+            if (lane == 0) {
+                ok = mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1, abort_flag);
+                if (ok) mbar_expect_tx(full, (uint32_t)__popc(have) * page_bytes);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (ok && pid >= 0)
+                tma_load_2d(smem_u32((is_v ? sV : sK) + s * TILE) + hf * (DT_KT * 128) + (uint32_t)j * page_bytes, is_v ? &tmV : &tmK,
+                            hf * 64, (pid * G + g) * page_size, full);
         }
         return;     // the producer warp takes no part in the merge
     }
