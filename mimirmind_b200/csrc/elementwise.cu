@@ -369,13 +369,16 @@ __global__ void qkv_rope_kvwrite_kernel(const T* __restrict__ qkv, const WT* __r
 }
 
 // bfloat16, full rotary (rotary_dim == hd) with hd a multiple of 16: a thread rotates 8 consecutive pairs, two
-// 16-byte loads and two 16-byte stores.
+// 16-byte loads and two 16-byte stores.  `interleave`: the columns of qkv (and bias) of every q and k head hold
+// the head's halves alternating in blocks of 8 (the row order of the weight that the fused decode product wants,
+// see gemv_bf16.cu); the outputs are in natural order either way.
 template <typename WT>
 __global__ void qkv_rope_kvwrite_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const WT* __restrict__ bias,
                                                __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pages,
                                                __nv_bfloat16* __restrict__ v_pages, const int32_t* __restrict__ positions,
                                                const int32_t* __restrict__ token_req, const int32_t* __restrict__ block_table,
-                                               int table_width, int page_size, int H, int G, int hd, float theta_base) {
+                                               int table_width, int page_size, int H, int G, int hd, float theta_base,
+                                               int interleave) {
     extern __shared__ float cs[];  // cos[half], sin[half]
     pdl_wait();
     pdl_trigger();
@@ -432,8 +435,9 @@ __global__ void qkv_rope_kvwrite_bf16x8_kernel(const __nv_bfloat16* __restrict__
     for (int idx = threadIdx.x; idx < (H + G) * chunks; idx += blockDim.x) {
         const int h = idx / chunks, i0 = (idx - h * chunks) * 8;
         float a[8], b[8], ra[8], rb[8];
-        load8(h * hd + i0, a);
-        load8(h * hd + i0 + half, b);
+        // interleaved input: the two halves of a q or k head alternate in blocks of 8 columns
+        load8(interleave ? h * hd + 2 * i0 : h * hd + i0, a);
+        load8(interleave ? h * hd + 2 * i0 + 8 : h * hd + i0 + half, b);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             const float c = cosv[i0 + k], sn = sinv[i0 + k];
@@ -461,8 +465,10 @@ __global__ void qkv_rope_kvwrite_bf16x8_kernel(const __nv_bfloat16* __restrict__
 MM_EXPORT int mm_qkv_rope_kvwrite(const void* qkv, const void* bias, int bias_dtype, void* q_out, void* k_pages,
                                   void* v_pages, int act_dtype, const void* positions, const void* token_req,
                                   const void* block_table, int table_width, int page_size, int n_tokens, int H, int G,
-                                  int hd, int rotary_dim, float theta_base, void* stream) {
+                                  int hd, int rotary_dim, float theta_base, int interleave, void* stream) {
     MM_REQUIRE(n_tokens >= 0 && H > 0 && G > 0 && hd > 0, "qkv_rope_kvwrite: bad sizes");
+    MM_REQUIRE(interleave == 0 || (act_dtype == MM_BF16 && rotary_dim == hd && hd % 16 == 0),
+               "qkv_rope_kvwrite: interleaved halves need bfloat16, full rotation and a head size that is a multiple of 16");
     MM_REQUIRE(rotary_dim >= 0 && rotary_dim <= hd && rotary_dim % 2 == 0, "qkv_rope_kvwrite: rotary_dim must be even and at most head_dim");
     MM_REQUIRE(page_size > 0 && table_width > 0, "qkv_rope_kvwrite: bad page geometry");
     MM_REQUIRE((k_pages == nullptr) == (v_pages == nullptr), "qkv_rope_kvwrite: k and v pools must both be given or both be null");
@@ -481,11 +487,11 @@ MM_EXPORT int mm_qkv_rope_kvwrite(const void* qkv, const void* bias, int bias_dt
         if (bias_dtype == MM_F32)
             mm_launch_pdl(qkv_rope_kvwrite_bf16x8_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, (const bf*)qkv, (const float*)bias,
                           (bf*)q_out, (bf*)k_pages, (bf*)v_pages, (const int32_t*)positions, (const int32_t*)token_req,
-                          (const int32_t*)block_table, table_width, page_size, H, G, hd, theta_base);
+                          (const int32_t*)block_table, table_width, page_size, H, G, hd, theta_base, interleave);
         else
             mm_launch_pdl(qkv_rope_kvwrite_bf16x8_kernel<bf>, dim3(n_tokens), dim3(threads), smem, s, (const bf*)qkv, (const bf*)bias,
                           (bf*)q_out, (bf*)k_pages, (bf*)v_pages, (const int32_t*)positions, (const int32_t*)token_req,
-                          (const int32_t*)block_table, table_width, page_size, H, G, hd, theta_base);
+                          (const int32_t*)block_table, table_width, page_size, H, G, hd, theta_base, interleave);
         MM_CHECK_LAUNCH();
         return MM_OK;
     }
@@ -516,6 +522,52 @@ MM_EXPORT int mm_gather_rows(const void* src, const void* rows, void* out, int d
     if (dtype == MM_F32) gather_rows_kernel<float><<<n_rows, 256, 0, s>>>((const float*)src, (const int32_t*)rows, (float*)out, d);
     else if (dtype == MM_BF16) gather_rows_kernel<__nv_bfloat16><<<n_rows, 256, 0, s>>>((const __nv_bfloat16*)src, (const int32_t*)rows, (__nv_bfloat16*)out, d);
     else MM_REQUIRE(false, "gather_rows: dtype must be float32 or bfloat16");
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Per-step tables shared by all layers of a cache group / rotary encoding (read by the fused decode projection):
+//   rope_table[t, 0:half] = cos(pos_t * theta^(-2i/dim)), rope_table[t, half:dim] = sin(...), i < half = dim / 2
+//   slots[t] = page * page_size + pos_t % page_size with page = block_table[req_t, pos_t / page_size], or -1
+// Same angle arithmetic as the rotary kernels above.
+// ---------------------------------------------------------------------------
+__global__ void rope_table_kernel(const int32_t* __restrict__ positions, float* __restrict__ out, int dim, float theta_base) {
+    const int t = blockIdx.x, half = dim / 2;
+    const int pos = positions[t];
+    const float inv_dim = 1.0f / (float)dim;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float freq = powf(theta_base, -(float)(2 * i) * inv_dim);
+        const float ang = (float)pos * freq;
+        out[(size_t)t * dim + i] = cosf(ang);
+        out[(size_t)t * dim + half + i] = sinf(ang);
+    }
+}
+
+MM_EXPORT int mm_rope_table(const void* positions, void* out, int n_tokens, int dim, float theta_base, void* stream) {
+    MM_REQUIRE(n_tokens >= 0 && dim >= 2 && dim % 2 == 0 && theta_base > 0.0f, "rope_table: bad sizes");
+    if (n_tokens == 0) return MM_OK;
+    rope_table_kernel<<<n_tokens, 64, 0, (cudaStream_t)stream>>>((const int32_t*)positions, (float*)out, dim, theta_base);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+__global__ void slot_mapping_kernel(const int32_t* __restrict__ positions, const int32_t* __restrict__ token_req,
+                                    const int32_t* __restrict__ block_table, int table_width, int page_size, int n,
+                                    int32_t* __restrict__ out) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n) return;
+    const int pos = positions[t];
+    const int page = block_table[(size_t)token_req[t] * table_width + pos / page_size];
+    out[t] = page >= 0 ? page * page_size + pos % page_size : -1;
+}
+
+MM_EXPORT int mm_slot_mapping(const void* positions, const void* token_req, const void* block_table, int table_width,
+                              int page_size, int n_tokens, void* out, void* stream) {
+    MM_REQUIRE(n_tokens >= 0 && table_width >= 1 && page_size >= 1, "slot_mapping: bad sizes");
+    if (n_tokens == 0) return MM_OK;
+    slot_mapping_kernel<<<(n_tokens + 127) / 128, 128, 0, (cudaStream_t)stream>>>(
+        (const int32_t*)positions, (const int32_t*)token_req, (const int32_t*)block_table, table_width, page_size, n_tokens, (int32_t*)out);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }

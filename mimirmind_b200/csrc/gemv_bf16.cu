@@ -13,9 +13,19 @@
 // splits of one row tile are summed through shared memory in a fixed order.  x is read from
 // global memory through L1 (it is small and stays in L2; a copy per CTA into shared memory
 // measured slower).  Loads are software-pipelined two batches deep in registers.
-// Epilogues: bias; fp32 or bf16 output; SwiGLU when the weight rows interleave gate and up
-// in blocks of 8 (rows 16j..16j+7 = gate[8j..], rows 16j+8..16j+15 = up[8j..]), so that one
-// thread holds a gate value and its up value.
+// Epilogues (one template instance each), chosen so that a decode layer is five launches:
+//   PLAIN   bias; fp32 or bf16 output.
+//   SWIGLU  the weight rows interleave gate and up in blocks of 8 (rows 16j..16j+7 = gate[8j..],
+//           rows 16j+8..16j+15 = up[8j..]): one thread holds a gate value and its up value.
+//   RESID   the product is added to the fp32 residual stream in place; if a norm weight is given,
+//           the rows of residual * weight (bf16) and, per 16-column tile, the partial sums of
+//           squares of the new residual are written too: RMSNorm(x) = (x * w) / rms(x), and the
+//           1/rms factor commutes with the next matrix product, which applies it (below).
+//   ROPE    q/k/v projection: bias, rotary position encoding of q and k (split-half pairs; the
+//           weight rows of each q and k head interleave the two halves in blocks of 8, so a thread
+//           holds a pair), q written as [M, H * hd], k and v written into their cache pages.
+// Input row scale: with `in_ss` the accumulators of row m are multiplied by
+// 1 / sqrt(sum_j in_ss[j][m] / in_dim + eps) before the epilogue (the deferred 1/rms of RESID).
 //
 // The reference's counterparts are its bf16 GEMV and small-M GEMM
 // (kernels/cuda/common/matmul_bf16_vec.cu:53-99: warp per output row, M launches;
@@ -33,8 +43,26 @@ struct GemvArgs {
     int M, N, K, ldx, ldo;
     int bias_dtype, out_dtype;
     int RT, KS;
-    int swiglu;
+    // deferred 1/rms of the input rows (null: none): partial sums of squares [in_tiles][16]
+    const float* in_ss;
+    int in_tiles, in_dim;
+    float in_eps;
+    // RESID
+    float* residual;            // [M, N] fp32, updated in place
+    const void* norm_w;         // [N] or null
+    int norm_w_dtype;
+    __nv_bfloat16* xw_out;      // [M, N]
+    float* out_ss;              // [N / 16][16]
+    // ROPE
+    __nv_bfloat16* q_out;       // [M, H * hd]
+    __nv_bfloat16* k_pages;     // [pages, G, page_size, hd] or null
+    __nv_bfloat16* v_pages;
+    const float* rope_table;    // [M, hd]: cos of the hd/2 angles of the row's position, then their sin
+    const int32_t* slots;       // [M]: page * page_size + place in the page of the row's position, or -1 (null: no cache write)
+    int page_size, H, G, hd;
 };
+
+enum { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_RESID = 2, EPI_ROPE = 3 };
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     uint4 v;
@@ -42,15 +70,19 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
 __device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT, int U>
-__global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs a) {
+template <int NT, int U, int EPI>
+__global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvArgs a) {
     __shared__ float red[GEMV_WARPS][32][4 * NT];
+    __shared__ float in_scale[16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = lane & 3, r = lane >> 2;
     const int K = a.K;
@@ -61,6 +93,69 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs 
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+
+    // Small operands of the epilogue are copied to shared memory with cp.async while the weights stream (no register
+    // is held and no warp waits for them before the epilogue):
+    //   every EPI  the producer's partial sums of squares of the input rows, [in_tiles][M4] (dynamic shared memory)
+    //   RESID      the residual values [rt][m][16 cols] and the norm weights [rt][16] of this CTA's columns
+    //   ROPE       cos and sin [rt][m][8] of every (row, pair) of this CTA's tiles, the bias [rt][16], each row's slot
+    constexpr bool kStaged = (EPI == EPI_RESID || EPI == EPI_ROPE);
+    extern __shared__ __align__(16) float ss_s[];
+    __shared__ __align__(16) float stage_a[kStaged ? GEMV_WARPS * 16 * 16 : 4];
+    __shared__ __align__(16) float stage_b[kStaged ? GEMV_WARPS * 16 : 4];
+    __shared__ int slot_s[EPI == EPI_ROPE ? 16 : 1];
+    const int M4 = (a.M + 3) & ~3;
+    auto stage = [&]() {
+        if (a.in_ss != nullptr) {
+            const int per = M4 / 4;                                   // 16-byte pieces per tile
+            for (int idx = threadIdx.x; idx < a.in_tiles * per; idx += GEMV_THREADS) {
+                const int j = idx / per, c = idx - j * per;
+                cp_async16(&ss_s[j * M4 + c * 4], a.in_ss + j * 16 + c * 4);
+            }
+        }
+        if constexpr (EPI == EPI_RESID) {
+            for (int idx = threadIdx.x; idx < a.RT * 64; idx += GEMV_THREADS) {     // (tile, row, 4 columns)
+                const int ti = idx >> 6, m = (idx >> 2) & 15, c4 = idx & 3;
+                const int col = (blockIdx.x * a.RT + ti) * 16 + c4 * 4;
+                if (m < a.M && col < a.N) cp_async16(&stage_a[(ti * 16 + m) * 16 + c4 * 4], a.residual + (size_t)m * a.N + col);
+            }
+            if (a.norm_w != nullptr) {
+                const int bytes16 = (a.norm_w_dtype == MM_F32) ? 4 : 2;             // 16-byte pieces per tile
+                for (int idx = threadIdx.x; idx < a.RT * bytes16; idx += GEMV_THREADS) {
+                    const int ti = idx / bytes16, c = idx - ti * bytes16;
+                    const int col = (blockIdx.x * a.RT + ti) * 16;
+                    if (col < a.N)
+                        cp_async16(reinterpret_cast<char*>(&stage_b[ti * 16]) + c * 16,
+                                   reinterpret_cast<const char*>(a.norm_w) + (size_t)col * (a.norm_w_dtype == MM_F32 ? 4 : 2) + c * 16);
+                }
+            }
+        }
+        if constexpr (EPI == EPI_ROPE) {
+            for (int idx = threadIdx.x; idx < a.RT * 64; idx += GEMV_THREADS) {     // (tile, row, cos|sin, 4 pairs)
+                const int ti = idx >> 6, m = (idx >> 2) & 15, part = idx & 3;
+                const int tile0 = (blockIdx.x * a.RT + ti) * 16;
+                const int head = tile0 / a.hd, within = tile0 - head * a.hd;
+                if (m < a.M && tile0 < a.N && head < a.H + a.G)
+                    cp_async16(&stage_a[(ti * 16 + m) * 16 + part * 4],
+                               a.rope_table + (size_t)m * a.hd + (part >> 1) * (a.hd / 2) + within / 2 + (part & 1) * 4);
+            }
+            if (a.bias != nullptr) {
+                const int bytes16 = (a.bias_dtype == MM_F32) ? 4 : 2;
+                for (int idx = threadIdx.x; idx < a.RT * bytes16; idx += GEMV_THREADS) {
+                    const int ti = idx / bytes16, c = idx - ti * bytes16;
+                    const int row = (blockIdx.x * a.RT + ti) * 16;
+                    if (row < a.N)
+                        cp_async16(reinterpret_cast<char*>(&stage_b[ti * 16]) + c * 16,
+                                   reinterpret_cast<const char*>(a.bias) + (size_t)row * (a.bias_dtype == MM_F32 ? 4 : 2) + c * 16);
+                }
+            }
+            if (threadIdx.x < 16) slot_s[threadIdx.x] = (threadIdx.x < a.M && a.slots != nullptr) ? a.slots[threadIdx.x] : -1;
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    auto staged_f32 = [&](const float* base, int dtype, int i) -> float {
+        return dtype == MM_F32 ? base[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[i]);
+    };
 
     if (active) {
         // this warp's share of the 32-wide k blocks
@@ -118,6 +213,7 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs 
         pdl_wait();
         pdl_trigger();
         load_x(0, 0);
+        stage();
         for (int kb = 0; kb < kb_count; kb += 2 * U) {
             load_w(1, kb + U);
             load_x(1, kb + U);
@@ -129,37 +225,115 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs 
     } else {
         pdl_wait();
         pdl_trigger();
+        stage();
     }
+    asm volatile("cp.async.wait_all;\n" ::: "memory");
     // sum the K splits of each row tile in a fixed order
+    const bool need_sync = a.KS > 1 || a.in_ss != nullptr || kStaged;
     if (a.KS > 1) {
 #pragma unroll
         for (int j = 0; j < NT; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) red[warp][lane][j * 4 + e] = acc[j][e];
+    }
+    if (need_sync) __syncthreads();
+    if (a.in_ss != nullptr) {
+        // 1/rms of the input rows: thread (m, part) adds every 16th partial of row m, a shuffle tree adds the 16 parts
+        const int m = threadIdx.x >> 4, part = threadIdx.x & 15;
+        float ssum = 0.0f;
+        if (m < a.M)
+            for (int j = part; j < a.in_tiles; j += 16) ssum += ss_s[j * M4 + m];
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+        if (part == 0) in_scale[m] = 1.0f / sqrtf(ssum / (float)a.in_dim + a.in_eps);
         __syncthreads();
-        if (ks == 0) {
-            for (int s = 1; s < a.KS; ++s)
+    }
+    if (a.KS > 1 && ks == 0) {
+        for (int sI = 1; sI < a.KS; ++sI)
 #pragma unroll
-                for (int j = 0; j < NT; ++j)
+            for (int j = 0; j < NT; ++j)
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) acc[j][e] += red[warp + s][lane][j * 4 + e];
-        }
+                for (int e = 0; e < 4; ++e) acc[j][e] += red[warp + sI][lane][j * 4 + e];
     }
     if (!active || ks != 0) return;
 
-    // epilogue: acc[j] = {(row r, col 2t), (row r, col 2t+1), (row r+8, col 2t), (row r+8, col 2t+1)} of batch tile j
+    // acc[j] = {(row r, col 2t), (row r, col 2t+1), (row r+8, col 2t), (row r+8, col 2t+1)} of batch tile j
+    if (a.in_ss != nullptr) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float sc = in_scale[j * 8 + t * 2 + e];
+                acc[j][e] *= sc;
+                acc[j][2 + e] *= sc;
+            }
+    }
 #pragma unroll
     for (int j = 0; j < NT; ++j) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
             const int m = j * 8 + t * 2 + e;
-            if (m >= a.M) continue;
-            if (a.swiglu) {
+            const bool live = m < a.M;
+            if constexpr (EPI == EPI_SWIGLU) {
+                if (!live) continue;
                 const float g = acc[j][e], u = acc[j][2 + e];
                 const float v = g / (1.0f + expf(-g)) * u;
                 const size_t o = (size_t)m * a.ldo + n0 / 2 + r;
                 if (a.out_dtype == MM_F32) ((float*)a.out)[o] = v; else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(v);
+            } else if constexpr (EPI == EPI_RESID) {
+                float sq = 0.0f;
+                if (live) {
+#pragma unroll
+                    for (int hi = 0; hi < 2; ++hi) {
+                        const int c = r + hi * 8, col = n0 + c;
+                        const size_t o = (size_t)m * a.N + col;
+                        const float v = stage_a[(rt * 16 + m) * 16 + c] + acc[j][hi * 2 + e];
+                        a.residual[o] = v;
+                        if (a.norm_w != nullptr) {
+                            a.xw_out[o] = __float2bfloat16_rn(v * staged_f32(&stage_b[rt * 16], a.norm_w_dtype, c));
+                            sq = fmaf(v, v, sq);
+                        }
+                    }
+                }
+                // the 16 columns of this tile for row m: lanes with the same t (every r)
+                sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+                sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+                sq += __shfl_xor_sync(0xffffffffu, sq, 16);
+                if (live && r == 0 && a.norm_w != nullptr) a.out_ss[(n0 / 16) * 16 + m] = sq;
+            } else if constexpr (EPI == EPI_ROPE) {
+                if (!live) continue;
+                const int hd = a.hd, head = n0 / hd, within = n0 - head * hd;
+                float x1 = acc[j][e], x2 = acc[j][2 + e];
+                if (a.bias) {
+                    x1 += staged_f32(&stage_b[rt * 16], a.bias_dtype, r);
+                    x2 += staged_f32(&stage_b[rt * 16], a.bias_dtype, 8 + r);
+                }
+                int i1, i2;
+                if (head < a.H + a.G) {
+                    // rows interleave the halves: this thread holds element i of the first half and its partner
+                    const int i = within / 2 + r;
+                    const float c = stage_a[(rt * 16 + m) * 16 + r], sn = stage_a[(rt * 16 + m) * 16 + 8 + r];
+                    const float ra = x1 * c - x2 * sn, rb = x1 * sn + x2 * c;
+                    x1 = ra; x2 = rb; i1 = i; i2 = i + hd / 2;
+                } else {
+                    i1 = within + r; i2 = i1 + 8;
+                }
+                __nv_bfloat16* dst = nullptr;
+                if (head < a.H) {
+                    dst = a.q_out + ((size_t)m * a.H + head) * hd;
+                } else if (slot_s[m] >= 0) {
+                    // slot = page * page_size + place in the page; the pool is [pages, G, page_size, hd]
+                    const bool is_v = head >= a.H + a.G;
+                    const int g = head - a.H - (is_v ? a.G : 0);
+                    const int page = slot_s[m] / a.page_size, in_page = slot_s[m] - page * a.page_size;
+                    dst = (is_v ? a.v_pages : a.k_pages) + (((size_t)page * a.G + g) * a.page_size + in_page) * hd;
+                }
+                if (dst != nullptr) {
+                    dst[i1] = __float2bfloat16_rn(x1);
+                    dst[i2] = __float2bfloat16_rn(x2);
+                }
             } else {
+                if (!live) continue;
 #pragma unroll
                 for (int hi = 0; hi < 2; ++hi) {
                     const int row = n0 + r + hi * 8;
@@ -173,33 +347,93 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_bf16_kernel(const GemvArgs 
     }
 }
 
-template <int NT, int U>
+template <int EPI>
 static int launch_gemv(const GemvArgs& a, cudaStream_t s) {
     const int tiles = a.N / 16;
     const int blocks = (tiles + a.RT - 1) / a.RT;
-    mm_launch_pdl(gemv_bf16_kernel<NT, U>, dim3(blocks), dim3(GEMV_THREADS), 0, s, a);
+    // dynamic shared memory: the staged partial sums of the input rows
+    const size_t smem = a.in_ss ? (size_t)a.in_tiles * ((a.M + 3) & ~3) * sizeof(float) : 0;
+    if (smem > 16 * 1024) {
+        mm_set_last_error("gemv: too many partial sums for the input scale (rows x producer tiles above 4096)");
+        return MM_ERR_UNSUPPORTED;
+    }
+    if (a.M <= 8) mm_launch_pdl(gemv_bf16_kernel<1, 4, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
+    else mm_launch_pdl(gemv_bf16_kernel<2, 2, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
 
-// out[M, ldo] = x[M, ldx(K)] * W[N,K]^T (+ bias), or with swiglu != 0: out[M, N/2] = silu(gate) * up for
-// W rows interleaved gate/up in blocks of 8.  rt * ks must be 8.
-MM_EXPORT int mm_gemv_bf16(const void* W, const void* x, const void* bias, int bias_dtype, void* out, int out_dtype,
-                           int M, int N, int K, int ldx, int ldo, int rt, int ks, int swiglu, void* stream) {
+// Checks shared by the entry points; fills the common fields.
+static int gemv_common(GemvArgs& a, const void* W, const void* x, int M, int N, int K, int ldx, int rt, int ks,
+                       const void* in_ss, int in_tiles, int in_dim, float in_eps) {
     MM_REQUIRE(M >= 1 && M <= 16, "gemv: M must be in 1..16");
     MM_REQUIRE(N > 0 && N % 16 == 0, "gemv: N must be a multiple of 16");
     MM_REQUIRE(K > 0 && K % 32 == 0, "gemv: K must be a multiple of 32");
     MM_REQUIRE(ldx >= K && ldx % 8 == 0, "gemv: x rows must be 16-byte aligned");
     MM_REQUIRE(rt >= 1 && ks >= 1 && rt * ks == GEMV_WARPS, "gemv: rt * ks must be 8");
     MM_REQUIRE(ks <= K / 32, "gemv: more K splits than 32-wide blocks");
+    MM_REQUIRE(in_ss == nullptr || (in_tiles >= 1 && in_dim >= 1 && in_eps > 0.0f), "gemv: bad input-scale sizes");
+    MM_REQUIRE((reinterpret_cast<uintptr_t>(in_ss) & 15) == 0, "gemv: the partial sums must be 16-byte aligned");
+    a = GemvArgs();
+    a.W = (const __nv_bfloat16*)W; a.x = (const __nv_bfloat16*)x;
+    a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.RT = rt; a.KS = ks;
+    a.in_ss = (const float*)in_ss; a.in_tiles = in_tiles; a.in_dim = in_dim; a.in_eps = in_eps;
+    return MM_OK;
+}
+
+// out[M, ldo] = x[M, ldx(K)] * W[N,K]^T (+ bias), or with swiglu != 0: out[M, N/2] = silu(gate) * up for
+// W rows interleaved gate/up in blocks of 8.  rt * ks must be 8.  in_ss (or null): partial sums of squares
+// [in_tiles][16] of the rows that x was made from; row m of the product is scaled by 1/sqrt(sum/in_dim + in_eps).
+MM_EXPORT int mm_gemv_bf16(const void* W, const void* x, const void* bias, int bias_dtype, void* out, int out_dtype,
+                           int M, int N, int K, int ldx, int ldo, int rt, int ks, int swiglu,
+                           const void* in_ss, int in_tiles, int in_dim, float in_eps, void* stream) {
+    GemvArgs a;
+    const int rc = gemv_common(a, W, x, M, N, K, ldx, rt, ks, in_ss, in_tiles, in_dim, in_eps);
+    if (rc != MM_OK) return rc;
     MM_REQUIRE(out_dtype == MM_F32 || out_dtype == MM_BF16, "gemv: out dtype must be float32 or bfloat16");
     MM_REQUIRE(!swiglu || (bias == nullptr && ldo >= N / 2), "gemv: the SwiGLU epilogue takes no bias and writes N/2 columns");
     MM_REQUIRE(swiglu || ldo >= N, "gemv: ldo too small");
-    GemvArgs a;
-    a.W = (const __nv_bfloat16*)W; a.x = (const __nv_bfloat16*)x; a.bias = bias; a.out = out;
-    a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldo = ldo; a.bias_dtype = bias_dtype; a.out_dtype = out_dtype;
-    a.RT = rt; a.KS = ks; a.swiglu = swiglu;
-    const int nt = M <= 8 ? 1 : 2;
+    a.bias = bias; a.bias_dtype = bias_dtype; a.out = out; a.out_dtype = out_dtype; a.ldo = ldo;
     cudaStream_t s = (cudaStream_t)stream;
-    return nt == 1 ? launch_gemv<1, 4>(a, s) : launch_gemv<2, 2>(a, s);
+    return swiglu ? launch_gemv<EPI_SWIGLU>(a, s) : launch_gemv<EPI_PLAIN>(a, s);
+}
+
+// residual[M, N] (fp32) += x * W^T.  With norm_w: also xw_out[M, N] = bf16(residual * norm_w) and
+// out_ss[N/16][16] = per-tile sums of squares of the new residual rows (column m of a tile's 16 is row m).
+MM_EXPORT int mm_gemv_bf16_residual(const void* W, const void* x, void* residual, const void* norm_w, int norm_w_dtype,
+                                    void* xw_out, void* out_ss, int M, int N, int K, int ldx, int rt, int ks,
+                                    const void* in_ss, int in_tiles, int in_dim, float in_eps, void* stream) {
+    GemvArgs a;
+    const int rc = gemv_common(a, W, x, M, N, K, ldx, rt, ks, in_ss, in_tiles, in_dim, in_eps);
+    if (rc != MM_OK) return rc;
+    MM_REQUIRE(residual != nullptr, "gemv: no residual");
+    MM_REQUIRE(norm_w == nullptr || (xw_out != nullptr && out_ss != nullptr), "gemv: a norm weight needs both outputs");
+    MM_REQUIRE(norm_w_dtype == MM_F32 || norm_w_dtype == MM_BF16, "gemv: norm weight dtype must be float32 or bfloat16");
+    MM_REQUIRE(((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(norm_w)) & 15) == 0, "gemv: residual and norm weight must be 16-byte aligned");
+    a.residual = (float*)residual; a.norm_w = norm_w; a.norm_w_dtype = norm_w_dtype;
+    a.xw_out = (__nv_bfloat16*)xw_out; a.out_ss = (float*)out_ss;
+    return launch_gemv<EPI_RESID>(a, (cudaStream_t)stream);
+}
+
+// q/k/v projection with bias, rotary encoding and cache write.  W [(H + 2G) * hd, K]: the rows of every q and k
+// head interleave the head's two halves in blocks of 8 (rows 16b..16b+7 = elements 8b.. of the first half, rows
+// 16b+8..16b+15 = the same elements of the second half); v rows and the layout of bias follow W.
+// rope_table [M, hd] fp32 (mm_rope_table) and slots [M] (mm_slot_mapping) are per step, shared by all layers.
+MM_EXPORT int mm_gemv_bf16_qkv_rope(const void* W, const void* x, const void* bias, int bias_dtype, void* q_out,
+                                    void* k_pages, void* v_pages, const void* rope_table, const void* slots,
+                                    int page_size, int H, int G, int hd, int M, int K, int ldx, int rt, int ks,
+                                    const void* in_ss, int in_tiles, int in_dim, float in_eps, void* stream) {
+    MM_REQUIRE(H >= 1 && G >= 1 && hd >= 16 && hd % 16 == 0, "gemv qkv: head size must be a multiple of 16");
+    GemvArgs a;
+    const int rc = gemv_common(a, W, x, M, (H + 2 * G) * hd, K, ldx, rt, ks, in_ss, in_tiles, in_dim, in_eps);
+    if (rc != MM_OK) return rc;
+    MM_REQUIRE(q_out != nullptr && rope_table != nullptr, "gemv qkv: q_out and the rotation table are needed");
+    MM_REQUIRE((k_pages == nullptr) == (v_pages == nullptr), "gemv qkv: k_pages and v_pages go together");
+    MM_REQUIRE(k_pages == nullptr || (slots != nullptr && page_size >= 1), "gemv qkv: a cache write needs the slots");
+    MM_REQUIRE(((reinterpret_cast<uintptr_t>(rope_table) | reinterpret_cast<uintptr_t>(bias)) & 15) == 0, "gemv qkv: table and bias must be 16-byte aligned");
+    a.bias = bias; a.bias_dtype = bias_dtype;
+    a.q_out = (__nv_bfloat16*)q_out; a.k_pages = (__nv_bfloat16*)k_pages; a.v_pages = (__nv_bfloat16*)v_pages;
+    a.rope_table = (const float*)rope_table; a.slots = k_pages ? (const int32_t*)slots : nullptr;
+    a.page_size = page_size > 0 ? page_size : 1; a.H = H; a.G = G; a.hd = hd;
+    return launch_gemv<EPI_ROPE>(a, (cudaStream_t)stream);
 }

@@ -111,6 +111,7 @@ class DecodeSession:
 
     # ---- one step's launches --------------------------------------------------------------
     def _launch(self) -> None:
+        self.ctx.derived.clear()
         self.logits = self.runner.forward(self.ctx)
         if self.greedy:
             ops.argmax_rows(self.logits, self.out_tokens)

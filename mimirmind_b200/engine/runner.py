@@ -172,8 +172,10 @@ class ModelRunner:
         m = self.model
         residual = m.embedding.forward(ctx.token_ids)
         pending = None
+        last = len(m.schedule) - 1
         for i, e in enumerate(m.schedule):
-            pending = m.layers[e.layer].forward(residual, pending, ctx, self.storage.layer_cache(i, ctx))
+            successor = m.layers[m.schedule[i + 1].layer] if i < last else None
+            pending = m.layers[e.layer].forward(residual, pending, ctx, self.storage.layer_cache(i, ctx), successor=successor)
         if ctx.n_logit_rows == 0:
             return None
         normed = m.final_norm.forward(residual, pending, rows=ctx.logit_rows, n_rows=ctx.n_logit_rows)

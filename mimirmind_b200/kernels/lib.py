@@ -32,8 +32,12 @@ _PROTOTYPES = {
     "mm_add_residual": [P, P, I, c_longlong, P],
     "mm_silu_mul": [P, P, I, I, I, I, P],
     "mm_gemm_tcgen05": [P, P, P, I, P, I, I, I, I, I, I, P, P],
-    "mm_gemv_bf16": [P, P, P, I, P, I, I, I, I, I, I, I, I, I, P],
-    "mm_qkv_rope_kvwrite": [P, P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
+    "mm_gemv_bf16": [P, P, P, I, P, I, I, I, I, I, I, I, I, I, P, I, I, F, P],
+    "mm_gemv_bf16_residual": [P, P, P, P, I, P, P, I, I, I, I, I, I, P, I, I, F, P],
+    "mm_gemv_bf16_qkv_rope": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, I, F, P],
+    "mm_rope_table": [P, P, I, I, F, P],
+    "mm_slot_mapping": [P, P, P, I, I, I, P, P],
+    "mm_qkv_rope_kvwrite": [P, P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P],
     "mm_gather_rows": [P, P, P, I, I, I, P],
     "mm_attention_generic": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
     "mm_gemm_simt": [P, I, P, I, P, I, P, I, I, I, I, I, I, P],

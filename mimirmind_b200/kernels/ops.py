@@ -6,6 +6,7 @@ operation here runs a kernel of this library.
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -107,8 +108,9 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, interleave: int = 0) -> t
 def qkv_rope_kvwrite(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
                      k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], positions: torch.Tensor,
                      token_req: torch.Tensor, block_table: torch.Tensor, page_size: int, num_heads: int,
-                     num_kv_heads: int, head_dim: int, rotary_dim: int, theta: float) -> None:
-    """Adds the bias, rotates q and k by position, writes q to ``q_out`` and k, v into their pages."""
+                     num_kv_heads: int, head_dim: int, rotary_dim: int, theta: float, interleave: bool = False) -> None:
+    """Adds the bias, rotates q and k by position, writes q to ``q_out`` and k, v into their pages.
+    ``interleave``: the q and k columns of ``qkv`` and ``bias`` are in the order of :func:`interleave_halves`."""
     _need(qkv, "qkv")
     n = qkv.shape[0]
     width = (num_heads + 2 * num_kv_heads) * head_dim
@@ -135,7 +137,7 @@ def qkv_rope_kvwrite(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_out: tor
         qkv.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, q_out.data_ptr(),
         _ptr(k_pages), _ptr(v_pages), dtype_code(qkv.dtype), positions.data_ptr(), token_req.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], page_size, n, num_heads, num_kv_heads, head_dim, rotary_dim,
-        float(theta), _stream()), "qkv_rope_kvwrite")
+        float(theta), int(interleave), _stream()), "qkv_rope_kvwrite")
 
 
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -196,19 +198,18 @@ def gemv_supported(m: int, n: int, k: int) -> bool:
     return 1 <= m <= GEMV_MAX_ROWS and n % 16 == 0 and k % 32 == 0 and k >= 256
 
 
-def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-              swiglu: bool = False) -> torch.Tensor:
-    """x[M<=16, K] @ w[N, K]^T (+ bias) with the weight-streaming kernel.  ``swiglu``: w interleaves gate and
-    up rows in blocks of 8 and the result is silu(gate) * up, [M, N/2]."""
-    _need(x, "gemv x", torch.bfloat16)
-    _need(w, "gemv w", torch.bfloat16)
-    m, k = x.shape
-    n = w.shape[0]
-    if w.shape != (n, k) or not gemv_supported(m, n, k):
-        raise KernelError(f"gemv: shapes x{tuple(x.shape)} w{tuple(w.shape)} are not supported")
-    if bias is not None:
-        _need(bias, "gemv bias")
-    out = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
+@dataclass
+class RowScale:
+    """The deferred 1/rms of rows that were written as ``residual * norm_weight``: per 16-column tile of the
+    producer, the partial sums of squares of each row ([tiles, 16] fp32).  A consuming matrix product multiplies
+    row m of its result by ``1 / sqrt(sum_j ss[j, m] / dim + eps)``."""
+
+    ss: torch.Tensor
+    dim: int
+    eps: float
+
+
+def _gemv_layout(n: int, k: int):
     # 8 warps per CTA as row tiles x K splits: enough CTAs to fill the GPU, else split K inside the CTA
     # Measured: with enough row tiles for two CTAs per SM, 8 row tiles per CTA stream best (6.0 TB/s on the
     # gate/up product, 6.6 TB/s on the head); smaller products need all 8 warps of a CTA on one row tile.
@@ -218,10 +219,134 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     while ks > k // 32:
         ks //= 2
         rt *= 2
+    return rt, ks
+
+
+def _scale_args(scale: Optional["RowScale"], m: int):
+    if scale is None:
+        return None, 0, 0, 0.0
+    _need(scale.ss, "row scale", torch.float32)
+    if scale.ss.dim() != 2 or scale.ss.shape[1] != 16 or m > 16:
+        raise KernelError("row scale: expected [tiles, 16] partial sums")
+    return scale.ss.data_ptr(), scale.ss.shape[0], int(scale.dim), float(scale.eps)
+
+
+def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+              swiglu: bool = False, scale: Optional[RowScale] = None) -> torch.Tensor:
+    """x[M<=16, K] @ w[N, K]^T (+ bias) with the weight-streaming kernel.  ``swiglu``: w interleaves gate and
+    up rows in blocks of 8 and the result is silu(gate) * up, [M, N/2].  ``scale``: rows of the product are
+    multiplied by the deferred 1/rms before bias and activation."""
+    _need(x, "gemv x", torch.bfloat16)
+    _need(w, "gemv w", torch.bfloat16)
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape != (n, k) or not gemv_supported(m, n, k):
+        raise KernelError(f"gemv: shapes x{tuple(x.shape)} w{tuple(w.shape)} are not supported")
+    if bias is not None:
+        _need(bias, "gemv bias")
+    out = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
+    rt, ks = _gemv_layout(n, k)
     check(_lib.load().mm_gemv_bf16(w.data_ptr(), x.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
                                    out.data_ptr(), dtype_code(out_dtype), m, n, k, k, out.shape[1], rt, ks, int(swiglu),
-                                   _stream()), "gemv_bf16")
+                                   *_scale_args(scale, m), _stream()), "gemv_bf16")
     return out
+
+
+def gemv_bf16_residual(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_weight: Optional[torch.Tensor],
+                       eps: float = 0.0, scale: Optional[RowScale] = None):
+    """residual[M, N] (fp32, in place) += x @ w^T.  With ``norm_weight`` returns (xw, RowScale): the rows of
+    ``residual * norm_weight`` in bfloat16 and the partial sums for their 1/rms; else returns None."""
+    _need(x, "gemv x", torch.bfloat16)
+    _need(w, "gemv w", torch.bfloat16)
+    _need(residual, "gemv residual", torch.float32)
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape != (n, k) or residual.shape != (m, n) or not gemv_supported(m, n, k):
+        raise KernelError(f"gemv residual: shapes x{tuple(x.shape)} w{tuple(w.shape)} residual{tuple(residual.shape)} are not supported")
+    xw = ss = None
+    if norm_weight is not None:
+        _need(norm_weight, "norm weight")
+        if norm_weight.shape != (n,):
+            raise KernelError("gemv residual: norm weight has the wrong length")
+        xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+        ss = torch.empty((n // 16, 16), dtype=torch.float32, device=x.device)
+    rt, ks = _gemv_layout(n, k)
+    check(_lib.load().mm_gemv_bf16_residual(w.data_ptr(), x.data_ptr(), residual.data_ptr(), _ptr(norm_weight),
+                                            dtype_code(norm_weight.dtype) if norm_weight is not None else F32, _ptr(xw), _ptr(ss),
+                                            m, n, k, k, rt, ks, *_scale_args(scale, m), _stream()), "gemv_bf16_residual")
+    return None if norm_weight is None else (xw, RowScale(ss, n, float(eps)))
+
+
+def interleave_halves(t: torch.Tensor, num_rot_heads: int, head_dim: int) -> torch.Tensor:
+    """Row order the fused q/k/v product wants: within each of the first ``num_rot_heads`` heads (q and k), rows
+    16b..16b+7 are elements 8b.. of the head's first half and rows 16b+8..16b+15 the same elements of the second
+    half, so the thread that holds an element holds its rotation partner.  Other rows (v) keep their place."""
+    hd, half = head_dim, head_dim // 2
+    if hd % 16:
+        raise KernelError("interleave_halves: the head size must be a multiple of 16")
+    rot = num_rot_heads * hd
+    head = t[:rot].reshape(num_rot_heads, 2, half // 8, 8, *t.shape[1:])     # [head, half, block, 8, ...]
+    head = head.transpose(1, 2).reshape(rot, *t.shape[1:])                   # [head, block, half, 8, ...]
+    return torch.cat([head, t[rot:]], dim=0).contiguous()
+
+
+def rope_table(positions: torch.Tensor, dim: int, theta: float) -> torch.Tensor:
+    """[n, dim] fp32: cos of the dim/2 rotation angles of every token's position, then their sin."""
+    _need(positions, "positions", torch.int32)
+    out = torch.empty((positions.numel(), dim), dtype=torch.float32, device=positions.device)
+    check(_lib.load().mm_rope_table(positions.data_ptr(), out.data_ptr(), positions.numel(), dim, float(theta), _stream()), "rope_table")
+    return out
+
+
+def slot_mapping(positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor, page_size: int) -> torch.Tensor:
+    """[n] int32: where each token's key and value go in a page pool (page * page_size + place in the page), -1: nowhere."""
+    _need(positions, "positions", torch.int32)
+    _need(token_req, "token_req", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    if block_table.dim() != 2:
+        raise KernelError("block_table: expected [requests, width]")
+    out = torch.empty(positions.numel(), dtype=torch.int32, device=positions.device)
+    check(_lib.load().mm_slot_mapping(positions.data_ptr(), token_req.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                                      page_size, positions.numel(), out.data_ptr(), _stream()), "slot_mapping")
+    return out
+
+
+def gemv_bf16_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                       k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], table: torch.Tensor,
+                       slots: Optional[torch.Tensor], page_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                       scale: Optional[RowScale] = None) -> None:
+    """The q/k/v projection of up to 16 tokens with bias, rotary encoding and cache write in its epilogue.
+    ``w`` and ``bias`` are in the order of :func:`interleave_halves`; q_out, k and v are in natural order.
+    ``table``: :func:`rope_table` of the tokens for this head size; ``slots``: :func:`slot_mapping`."""
+    _need(x, "gemv x", torch.bfloat16)
+    _need(w, "gemv w", torch.bfloat16)
+    m, k = x.shape
+    n = (num_heads + 2 * num_kv_heads) * head_dim
+    if w.shape != (n, k) or not gemv_supported(m, n, k) or head_dim % 16:
+        raise KernelError(f"gemv qkv: shapes x{tuple(x.shape)} w{tuple(w.shape)} are not supported")
+    _need(q_out, "q_out", torch.bfloat16)
+    if q_out.shape != (m, num_heads * head_dim):
+        raise KernelError("q_out: wrong shape")
+    if bias is not None:
+        _need(bias, "qkv bias")
+        if bias.shape != (n,):
+            raise KernelError("qkv bias: wrong shape")
+    _need(table, "rope table", torch.float32)
+    if table.shape != (m, head_dim):
+        raise KernelError("rope table: expected [tokens, head_dim]")
+    if k_pages is not None:
+        for name, pool in (("k_pages", k_pages), ("v_pages", v_pages)):
+            _need(pool, name, torch.bfloat16)
+            if pool.dim() != 4 or pool.shape[1:] != (num_kv_heads, page_size, head_dim):
+                raise KernelError(f"{name}: shape {tuple(pool.shape)} is not [pages, {num_kv_heads}, {page_size}, {head_dim}]")
+        _need(slots, "slots", torch.int32)
+        if slots.numel() != m:
+            raise KernelError("slots: one per token")
+    rt, ks = _gemv_layout(n, k)
+    check(_lib.load().mm_gemv_bf16_qkv_rope(
+        w.data_ptr(), x.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, q_out.data_ptr(),
+        _ptr(k_pages), _ptr(v_pages), table.data_ptr(), _ptr(slots) if k_pages is not None else None, page_size,
+        num_heads, num_kv_heads, head_dim, m, k, k, rt, ks, *_scale_args(scale, m), _stream()), "gemv_bf16_qkv_rope")
 
 
 _TC_ERR = {}

@@ -21,7 +21,7 @@ import torch
 from ..config.spec import PartSpec, TensorSpec
 from ..kernels import ops
 from ..registry import MIXERS, POSITION_ENCODINGS
-from .base import KVCacheSpec, LayerCache, Mixer, Runtime, StepContext, WeightView
+from .base import FactoredRows, KVCacheSpec, LayerCache, Mixer, ResidualSink, Runtime, StepContext, WeightView
 from .linear import linear
 
 
@@ -76,6 +76,18 @@ class GQAAttention(Mixer):
                 bs = [b.float() for b in bs]
             self.b_qkv = torch.cat(bs, dim=0).contiguous()
         self.w_o = weights.take(spec["o"] + ".weight").contiguous()
+        # With a rotation of the whole head that the kernels can apply, the q and k rows of the projection are
+        # stored with each head's halves interleaved in blocks of 8: the weight-streaming product of a decode
+        # step then holds rotation partners in one thread and encodes and caches in its epilogue.
+        fused = self.position.fused_rotary()
+        self.interleaved = bool(
+            fused is not None and fused[0] == self.head_dim and self.head_dim % 16 == 0 and rt.dtype == torch.bfloat16
+            and self.w_qkv.dtype == torch.bfloat16 and self.w_o.dtype == torch.bfloat16 and rt.matmul != "simt")
+        if self.interleaved:
+            rot_heads = self.num_heads + self.num_kv_heads
+            self.w_qkv = ops.interleave_halves(self.w_qkv, rot_heads, self.head_dim)
+            if self.b_qkv is not None:
+                self.b_qkv = ops.interleave_halves(self.b_qkv, rot_heads, self.head_dim)
 
     def _encode_unfused(self, qkv: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         """A position encoding the fused kernel cannot apply: add the bias with the same kernel into contiguous
@@ -94,23 +106,47 @@ class GQAAttention(Mixer):
     def kv_cache_spec(self) -> Optional[KVCacheSpec]:
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+    def fuses(self, n_tokens: int) -> bool:
+        width = (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
+        return (self.interleaved and ops.gemv_supported(n_tokens, width, self.hidden)
+                and ops.gemv_supported(n_tokens, self.hidden, self.num_heads * self.head_dim))
+
+    def forward(self, x, ctx: StepContext, cache: LayerCache, sink: Optional[ResidualSink] = None):
         n = x.shape[0]
         H, G, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = linear(x, self.w_qkv, None, self.rt)
-        q = torch.empty((n, H * hd), dtype=x.dtype, device=x.device)
+        k_pages, v_pages = (cache.k_pages, cache.v_pages) if cache.writes else (None, None)
         fused = self.position.fused_rotary()
-        if fused is not None:
-            rotary_dim, theta = fused
-            ops.qkv_rope_kvwrite(qkv, self.b_qkv, q, cache.k_pages if cache.writes else None,
-                                 cache.v_pages if cache.writes else None, ctx.positions, ctx.token_req, cache.block_table,
-                                 cache.page_size, H, G, hd, rotary_dim, theta)
+        fuses = self.fuses(n)
+        q = torch.empty((n, H * hd), dtype=self.rt.dtype, device=x.xw.device if isinstance(x, FactoredRows) else x.device)
+        if fuses:
+            # a few tokens: projection, 1/rms of a factored input, bias, rotation and cache write in one launch
+            xin, scale = (x.xw, x.scale) if isinstance(x, FactoredRows) else (x, None)
+            # rotation angles and cache slots are the same in every layer that shares them: made once per step
+            key = ("rope_table", hd, fused[1])
+            if key not in ctx.derived:
+                ctx.derived[key] = ops.rope_table(ctx.positions, hd, fused[1])
+            slots = None
+            if k_pages is not None:
+                skey = ("slots", cache.block_table.data_ptr(), cache.page_size)
+                if skey not in ctx.derived:
+                    ctx.derived[skey] = ops.slot_mapping(ctx.positions, ctx.token_req, cache.block_table, cache.page_size)
+                slots = ctx.derived[skey]
+            ops.gemv_bf16_qkv_rope(xin, self.w_qkv, self.b_qkv, q, k_pages, v_pages, ctx.derived[key], slots,
+                                   cache.page_size, H, G, hd, scale=scale)
         else:
-            qkv = self._encode_unfused(qkv, ctx)
-            ops.qkv_rope_kvwrite(qkv, None, q, cache.k_pages if cache.writes else None,
-                                 cache.v_pages if cache.writes else None, ctx.positions, ctx.token_req, cache.block_table,
-                                 cache.page_size, H, G, hd, 0, 1.0)
+            qkv = linear(x, self.w_qkv, None, self.rt)
+            if fused is not None:
+                rotary_dim, theta = fused
+                ops.qkv_rope_kvwrite(qkv, self.b_qkv, q, k_pages, v_pages, ctx.positions, ctx.token_req, cache.block_table,
+                                     cache.page_size, H, G, hd, rotary_dim, theta, interleave=self.interleaved)
+            else:
+                qkv = self._encode_unfused(qkv, ctx)
+                ops.qkv_rope_kvwrite(qkv, None, q, k_pages, v_pages, ctx.positions, ctx.token_req, cache.block_table,
+                                     cache.page_size, H, G, hd, 0, 1.0)
         out = torch.empty_like(q)
         from ..kernels import attention as attn_kernels
         attn_kernels.paged_attention(q, cache, out, ctx, H, G, hd, self.window, self.scale)
-        return linear(out, self.w_o, None, self.rt)
+        if sink is None:
+            return linear(out, self.w_o, None, self.rt)
+        made = ops.gemv_bf16_residual(out, self.w_o, sink.residual, sink.norm_weight, sink.eps)
+        return FactoredRows(*made) if made is not None else None

@@ -111,6 +111,35 @@ class StepContext:
     plans: Dict[Any, Any] = field(default_factory=dict)  # per-step launch plans, shared between layers
     max_kv_len: int = 0
     max_q_len: int = 0
+    # device tensors derived from this step's inputs and shared between layers (rotation tables, cache slots);
+    # whoever runs a context more than once (a captured decode step) clears this before every forward
+    derived: Dict[Any, torch.Tensor] = field(default_factory=dict)
+
+
+@dataclass
+class FactoredRows:
+    """Rows of ``norm(x)`` in factored form, for norms of the kind ``x * w / rms(x)``: ``xw`` holds ``x * w`` in the
+    activation dtype and ``scale`` (kernels.ops.RowScale) what is needed for each row's ``1 / rms``.  The factor
+    is a scalar per row, so a matrix product may apply it to its result instead of its input; a part that says
+    ``fuses(n)`` takes its input in this form."""
+
+    xw: torch.Tensor
+    scale: Any
+
+    @property
+    def shape(self):
+        return self.xw.shape
+
+
+@dataclass
+class ResidualSink:
+    """Where a fusing part adds its output itself: the fp32 residual stream (in place) and, if a norm follows whose
+    consumer takes factored rows, that norm's weight and eps.  The part then returns FactoredRows of the new
+    residual (or None when ``norm_weight`` is None) instead of its output."""
+
+    residual: torch.Tensor
+    norm_weight: Optional[torch.Tensor] = None
+    eps: float = 0.0
 
 
 class Part:
@@ -131,6 +160,11 @@ class Norm(Part):
         """residual (fp32, [n, width]) += delta; returns the normalised rows in the activation dtype.
         With ``rows`` only those rows are produced and the residual is not written."""
         raise NotImplementedError
+
+    def factors(self) -> Optional[Tuple[torch.Tensor, float]]:
+        """(weight, eps) if the norm is ``x * weight / sqrt(mean(x^2) + eps)``, so that a product's epilogue can
+        prepare it in factored form (FactoredRows); None for any other norm."""
+        return None
 
 
 class PositionEncoding(Part):
@@ -154,10 +188,20 @@ class Mixer(Part):
         """x: normalised activations [n_tokens, hidden] → the mixer's output [n_tokens, hidden]."""
         raise NotImplementedError
 
+    def fuses(self, n_tokens: int) -> bool:
+        """True if, for a step of ``n_tokens``, ``forward`` takes FactoredRows as ``x`` and a keyword ``sink``
+        (ResidualSink).  Parts that do not override this are never given either."""
+        return False
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
+
+    def fuses(self, n_tokens: int) -> bool:
+        """True if, for a step of ``n_tokens``, ``forward`` takes FactoredRows as ``x`` and a keyword ``sink``
+        (ResidualSink).  Parts that do not override this are never given either."""
+        return False
 
 
 class Block(Part):
@@ -172,8 +216,13 @@ class Block(Part):
         self.ffn_norm = ffn_norm
         self.feed_forward = feed_forward
 
-    def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
-                cache: LayerCache) -> Optional[torch.Tensor]:
+    def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: LayerCache,
+                successor: Optional["Block"] = None):
         """Runs the layer.  ``pending`` is a branch output not yet added to ``residual`` (so the add
-        fuses into the next norm); returns the new pending output."""
+        fuses into the next norm), or FactoredRows of the up-to-date residual prepared for this block's first
+        norm; returns the new pending value.  ``successor``: the block that runs next, if any."""
         raise NotImplementedError
+
+    def entry_norm(self, n_tokens: int) -> Optional[Tuple[torch.Tensor, float]]:
+        """(weight, eps) of this block's first norm if a predecessor may hand over FactoredRows for it."""
+        return None

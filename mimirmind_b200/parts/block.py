@@ -12,14 +12,32 @@ from typing import Optional
 import torch
 
 from ..registry import BLOCKS
-from .base import Block, LayerCache, StepContext
+from .base import Block, FactoredRows, LayerCache, ResidualSink, StepContext
 
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
-    def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
-                cache: LayerCache) -> Optional[torch.Tensor]:
-        h = self.mixer_norm.forward(residual, pending)
-        mixed = self.mixer.forward(h, ctx, cache)
-        h = self.ffn_norm.forward(residual, mixed)
-        return self.feed_forward.forward(h, ctx)
+    """With parts that fuse (a few tokens in bfloat16), the residual add and the norm move into the epilogue of
+    the branch's last matrix product and the 1/rms into the next product: a layer is five launches."""
+
+    def entry_norm(self, n_tokens: int):
+        f = self.mixer_norm.factors()
+        return f if f is not None and self.mixer.fuses(n_tokens) else None
+
+    def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: LayerCache,
+                successor: Optional[Block] = None):
+        n = residual.shape[0]
+        mixer_fuses, ffn_fuses = self.mixer.fuses(n), self.feed_forward.fuses(n)
+        h = pending if isinstance(pending, FactoredRows) else self.mixer_norm.forward(residual, pending)
+        between = self.ffn_norm.factors() if (mixer_fuses and ffn_fuses) else None
+        if between is not None:
+            h = self.mixer.forward(h, ctx, cache, sink=ResidualSink(residual, between[0], between[1]))
+        else:
+            h = self.ffn_norm.forward(residual, self.mixer.forward(h, ctx, cache))
+        if not ffn_fuses:
+            return self.feed_forward.forward(h, ctx)
+        after = successor.entry_norm(n) if successor is not None else None
+        if successor is not None and after is None:
+            return self.feed_forward.forward(h, ctx)       # the next block wants a plain pending sum
+        sink = ResidualSink(residual, after[0], after[1]) if after is not None else ResidualSink(residual)
+        return self.feed_forward.forward(h, ctx, sink=sink)

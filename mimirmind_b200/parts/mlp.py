@@ -6,14 +6,14 @@ that one product feeds the activation kernel.
 """
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 import torch
 
 from ..config.spec import PartSpec, TensorSpec
 from ..kernels import ops
 from ..registry import FEED_FORWARDS
-from .base import FeedForward, Runtime, StepContext, WeightView
+from .base import FactoredRows, FeedForward, ResidualSink, Runtime, StepContext, WeightView
 from .linear import linear
 
 
@@ -50,13 +50,26 @@ class SwiGLU(FeedForward):
         del gate, up
         self.w_down = weights.take(spec["down"]).contiguous()       # [d, F]
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def _tensor_cores(self) -> bool:
+        return bool(self.interleave) and self.rt.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 \
+            and self.w_down.dtype == torch.bfloat16 and self.rt.matmul != "simt"
+
+    def fuses(self, n_tokens: int) -> bool:
+        return (self._tensor_cores() and ops.gemv_supported(n_tokens, 2 * self.intermediate, self.hidden)
+                and ops.gemv_supported(n_tokens, self.hidden, self.intermediate))
+
+    def forward(self, x, ctx: StepContext, sink: Optional[ResidualSink] = None):
         m = x.shape[0]
-        if (self.interleave and x.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and self.rt.matmul != "simt"
-                and ops.gemv_supported(m, 2 * self.intermediate, self.hidden)):
-            act = ops.gemv_bf16(x, self.w_gate_up, None, x.dtype, swiglu=True)    # product and activation in one kernel
-        elif (self.interleave and x.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and self.rt.matmul != "simt"
-              and m >= ops.TCGEN05_SWIGLU_MIN_ROWS and ops.gemm_tcgen05_supported(m, 2 * self.intermediate, self.hidden)):
+        if self.fuses(m):
+            # a few tokens: two weight-streaming products; 1/rms and activation in the first one's epilogue,
+            # residual add and the next norm in the second one's
+            xin, scale = (x.xw, x.scale) if isinstance(x, FactoredRows) else (x, None)
+            act = ops.gemv_bf16(xin, self.w_gate_up, None, xin.dtype, swiglu=True, scale=scale)
+            if sink is None:
+                return ops.gemv_bf16(act, self.w_down, None, xin.dtype)
+            made = ops.gemv_bf16_residual(act, self.w_down, sink.residual, sink.norm_weight, sink.eps)
+            return FactoredRows(*made) if made is not None else None
+        if self._tensor_cores() and m >= ops.TCGEN05_SWIGLU_MIN_ROWS and ops.gemm_tcgen05_supported(m, 2 * self.intermediate, self.hidden):
             # prefill-sized: tcgen05 product with the activation as its epilogue (the [m, 2F] intermediate never exists)
             act = ops.gemm_tcgen05(x, self.w_gate_up, None, x.dtype, swiglu=True)
         else:

@@ -31,6 +31,9 @@ class RMSNorm(Norm):
         self.eps = float(spec["eps"])
         self.weight = weights.get(spec["weight"]).contiguous()
 
+    def factors(self):
+        return self.weight, self.eps
+
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
                 n_rows: Optional[int] = None) -> torch.Tensor:
         n = residual.shape[0] if rows is None else (n_rows if n_rows is not None else rows.numel())

@@ -435,10 +435,137 @@ def test_gemv_all_layouts_of_the_kernel(M, rt, ks):
     out = torch.zeros((M, N), dtype=torch.float32, device=DEV)
     L = lib.load()
     rc = L.mm_gemv_bf16(w.data_ptr(), x.data_ptr(), None, 0, out.data_ptr(), 0, M, N, K, K, N, rt, ks, 0,
-                        torch.cuda.current_stream().cuda_stream)
+                        None, 0, 0, 0.0, torch.cuda.current_stream().cuda_stream)
     assert rc == 0, L.mm_last_error()
     ref = x.double().cpu().numpy() @ w.double().cpu().numpy().T
     assert np.abs(out.cpu().numpy() - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
+
+
+# ---- weight-streaming product with the decode-layer epilogues ----------------------------------------
+def _row_scale(rng, M, tiles, dim, eps):
+    """Partial sums of squares as a producer would leave them, and the 1/rms they stand for."""
+    ss = np.abs(rng.randn(tiles, 16)).astype(np.float32) * dim / tiles
+    ss[:, M:] = np.nan                                  # rows that do not exist are never read into a result
+    rstd = 1.0 / np.sqrt(ss[:, :M].astype(np.float64).sum(0) / dim + eps)
+    return ops().RowScale(t(ss), dim, eps), rstd
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 48, 256), (5, 272, 1504), (8, 1040, 352)])
+def test_gemv_input_row_scale(M, N, K):
+    rng = np.random.RandomState(M + N)
+    x, w, b = t(rng.randn(M, K), torch.bfloat16), t(rng.randn(N, K) * 0.05, torch.bfloat16), t(rng.randn(N), torch.float32)
+    scale, rstd = _row_scale(rng, M, 37, K, 1e-5)
+    ref = (x.double().cpu().numpy() @ w.double().cpu().numpy().T) * rstd[:, None] + b.double().cpu().numpy()
+    got = ops().gemv_bf16(x, w, b, torch.float32, scale=scale).cpu().numpy()
+    assert np.abs(got - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
+    # the SwiGLU epilogue sees the scaled gate and up
+    if N % 16 == 0 and (N // 2) % 8 == 0:
+        F = N // 2
+        gate, up = w[:F].float().cpu().numpy().astype(np.float64), w[F:].float().cpu().numpy().astype(np.float64)
+        wi = torch.stack([w[:F].view(F // 8, 8, K), w[F:].view(F // 8, 8, K)], dim=1).reshape(N, K).contiguous()
+        xs = x.double().cpu().numpy()
+        g, u = (xs @ gate.T) * rstd[:, None], (xs @ up.T) * rstd[:, None]
+        ref2 = g / (1.0 + np.exp(-g)) * u
+        got2 = ops().gemv_bf16(x, wi, None, torch.float32, swiglu=True, scale=scale).cpu().numpy()
+        assert np.abs(got2 - ref2).max() <= 1e-5 * np.sqrt(K) * np.abs(ref2).max() + 1e-5
+
+
+@pytest.mark.parametrize("M,N,K,wdt", [(1, 256, 256, torch.float32), (6, 288, 1504, torch.bfloat16), (8, 1056, 352, torch.bfloat16)])
+def test_gemv_residual_epilogue(M, N, K, wdt):
+    """residual += x W^T in fp32; rows of residual * norm weight; partial sums whose total is the row's sum of squares."""
+    rng = np.random.RandomState(N)
+    x, w = t(rng.randn(M, K), torch.bfloat16), t(rng.randn(N, K) * 0.05, torch.bfloat16)
+    res0 = rng.randn(M, N).astype(np.float32) * 3
+    nw = t(1.0 + 0.3 * rng.randn(N), wdt)
+    scale_in, rstd_in = _row_scale(rng, M, 11, K, 1e-6)
+    for sc, factor in ((None, np.ones(M)), (scale_in, rstd_in)):
+        residual = t(res0)
+        made = ops().gemv_bf16_residual(x, w, residual, nw, 1e-5, scale=sc)
+        ref = res0.astype(np.float64) + (x.double().cpu().numpy() @ w.double().cpu().numpy().T) * factor[:, None]
+        got = residual.cpu().numpy()
+        assert np.abs(got - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
+        xw, rs = made
+        assert rs.dim == N and rs.eps == 1e-5 and rs.ss.shape == (N // 16, 16)
+        ref_xw = bf16_round(got.astype(np.float64) * nw.double().cpu().numpy())
+        assert np.abs(xw.float().cpu().numpy() - ref_xw).max() <= 2 ** -8 * np.abs(ref_xw).max()
+        ss = rs.ss.cpu().numpy()[:, :M].astype(np.float64).sum(0)
+        assert np.abs(ss - (got.astype(np.float64) ** 2).sum(1)).max() <= 1e-5 * ss.max()
+        # the factored rows, consumed by a product with the row scale, equal RMSNorm followed by the product
+        w2 = t(rng.randn(32, N) * 0.05, torch.bfloat16)
+        y = ops().gemv_bf16(xw, w2, None, torch.float32, scale=rs).cpu().numpy()
+        normed = plain.rms_norm(got.astype(np.float64), nw.double().cpu().numpy(), 1e-5)
+        ref_y = normed @ w2.double().cpu().numpy().T
+        assert np.abs(y - ref_y).max() <= 2 ** -7 * np.abs(ref_y).max()
+    # without a norm weight only the residual is written
+    residual = t(res0)
+    assert ops().gemv_bf16_residual(x, w, residual, None) is None
+    ref = res0.astype(np.float64) + x.double().cpu().numpy() @ w.double().cpu().numpy().T
+    assert np.abs(residual.cpu().numpy() - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
+
+
+@pytest.mark.parametrize("H,G,hd,ps,K,M", [(4, 2, 16, 16, 256, 3), (6, 3, 48, 8, 288, 8), (7, 1, 128, 16, 352, 5), (2, 2, 80, 32, 320, 1)])
+@pytest.mark.parametrize("with_scale", [False, True])
+def test_gemv_qkv_rope_epilogue_and_interleaved_rope_kernel(H, G, hd, ps, K, M, with_scale):
+    """The fused decode projection (interleaved weight rows, bias, rotation, cache write) against the formulas, and
+    the stand-alone rotary kernel reading the same interleaved columns."""
+    rng = np.random.RandomState(H * hd + M)
+    theta = 1e4
+    lens_before = [0, 37, 130, 5, 64, 15, 16, 900][:M]
+    table, pages = paged_layout(rng, [a + 1 for a in lens_before], ps)
+    pos = np.asarray(lens_before, dtype=np.int32)
+    req = np.arange(M, dtype=np.int32)
+    width = (H + 2 * G) * hd
+    x = t(rng.randn(M, K), torch.bfloat16)
+    w = t(rng.randn(width, K) * 0.1, torch.bfloat16)
+    bias = t(rng.randn(width) * 0.5, torch.bfloat16)
+    wi, bi = ops().interleave_halves(w, H + G, hd), ops().interleave_halves(bias, H + G, hd)
+    assert wi.shape == w.shape and torch.equal(wi[(H + G) * hd:], w[(H + G) * hd:])
+    assert torch.equal(wi[8:16], w[hd // 2:hd // 2 + 8]) and torch.equal(wi[0:8], w[0:8])
+    scale, rstd = _row_scale(rng, M, 9, K, 1e-6) if with_scale else (None, np.ones(M))
+    kp = torch.full((pages, G, ps, hd), 768.0, dtype=torch.bfloat16, device=DEV)
+    vp = torch.full((pages, G, ps, hd), 768.0, dtype=torch.bfloat16, device=DEV)
+    q_out = torch.empty((M, H * hd), dtype=torch.bfloat16, device=DEV)
+    pos_d, req_d, table_d = t(pos, torch.int32), t(req, torch.int32), t(table, torch.int32)
+    angles = ops().rope_table(pos_d, hd, theta)
+    inv = theta ** (-np.arange(0, hd, 2, dtype=np.float64) / hd)
+    ang_ref = pos[:, None].astype(np.float64) * inv[None, :]
+    assert np.abs(angles.cpu().numpy() - np.concatenate([np.cos(ang_ref), np.sin(ang_ref)], axis=1)).max() <= 3e-6 * max(1.0, pos.max() / 50)
+    slots = ops().slot_mapping(pos_d, req_d, table_d, ps)
+    assert slots.cpu().numpy().tolist() == [int(table[req[i], pos[i] // ps]) * ps + int(pos[i]) % ps for i in range(M)]
+    ops().gemv_bf16_qkv_rope(x, wi, bi, q_out, kp, vp, angles, slots, ps, H, G, hd, scale=scale)
+    y = (x.double().cpu().numpy() @ w.double().cpu().numpy().T) * rstd[:, None] + bias.double().cpu().numpy()
+    q_ref = plain.rope(y[:, :H * hd].reshape(M, H, hd), pos, theta)
+    k_ref = plain.rope(y[:, H * hd:(H + G) * hd].reshape(M, G, hd), pos, theta)
+    v_ref = y[:, (H + G) * hd:].reshape(M, G, hd)
+    tol = 2 ** -8
+    assert np.abs(q_out.float().cpu().numpy().reshape(M, H, hd) - q_ref).max() <= tol * np.abs(q_ref).max()
+    kp_h, vp_h = kp.float().cpu().numpy(), vp.float().cpu().numpy()
+    written = np.zeros((pages, ps), dtype=bool)
+    for i in range(M):
+        page, slot = table[req[i], pos[i] // ps], pos[i] % ps
+        written[page, slot] = True
+        assert np.abs(kp_h[page, :, slot] - k_ref[i]).max() <= tol * np.abs(k_ref).max()
+        assert np.abs(vp_h[page, :, slot] - v_ref[i]).max() <= tol * np.abs(v_ref).max()
+    untouched = ~written[:, None, :].repeat(G, axis=1)
+    assert (kp_h[untouched] == 768.0).all() and (vp_h[untouched] == 768.0).all()
+    # no cache to write (a layer that reads another layer's cache): q only
+    q2 = torch.empty_like(q_out)
+    ops().gemv_bf16_qkv_rope(x, wi, bi, q2, None, None, angles, None, ps, H, G, hd, scale=scale)
+    assert torch.equal(q2, q_out)
+    if not with_scale:
+        # the stand-alone kernel on the interleaved product gives what it gives on the natural one
+        prod = ops().gemv_bf16(x, w, None, torch.bfloat16)
+        prod_i = ops().gemv_bf16(x, wi, None, torch.bfloat16)
+        outs = []
+        for p_, b_, il in ((prod, bias, False), (prod_i, bi, True)):
+            kq = torch.zeros((pages, G, ps, hd), dtype=torch.bfloat16, device=DEV)
+            vq = torch.zeros_like(kq)
+            qq = torch.empty_like(q_out)
+            ops().qkv_rope_kvwrite(p_, b_, qq, kq, vq, t(pos, torch.int32), t(req, torch.int32), t(table, torch.int32),
+                                   ps, H, G, hd, hd, theta, interleave=il)
+            outs.append((qq, kq, vq))
+        for a_, b_ in zip(outs[0], outs[1]):
+            assert torch.equal(a_, b_)
 
 
 # ---- tcgen05 / TMA / TMEM matrix product -------------------------------------------------------------
