@@ -11,6 +11,12 @@
 //
 // Tiles are written with the 128-byte swizzle; ldmatrix row addresses apply the same xor.
 // Waits are bounded; on a time-out the CTA gives up and sets `err`.
+//
+// CLUSTER variant (at most 8 splits): the splits of one (token, KV head) are one thread-block cluster.  Each CTA
+// leaves its partial result in its own shared memory; after a cluster barrier every CTA merges a slice of the
+// output columns, reading the partials of its peers through distributed shared memory, and writes bf16 output:
+// no scratch in global memory and no merge launch.  Every thread of every CTA reaches both cluster barriers on
+// every path (a CTA without keys, a failed wait), so the barriers cannot be left waiting.
 #include "tcgen05.cuh"
 
 namespace {
@@ -72,7 +78,30 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
     return (uint32_t)((chunk >> 3) * (DT_KT * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
 
-template <int HD, int STAGES>
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;\n" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r));
+    return r;
+}
+// value of a float in the shared memory of CTA `rank` of this cluster, at the place `local` has in this CTA's
+__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <int HD, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(DT_THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                             const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
@@ -96,7 +125,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     const int hi = pos + 1;
     const int lo = (window > 0 && hi > window) ? hi - window : 0;
     const SplitRange sp = split_range(lo, hi, split_len, max_splits);
-    if (split < sp.first || split > sp.last) return;
+    const bool has_keys = split >= sp.first && split <= sp.last;
+    if (!CLUSTER && !has_keys) return;
     const bool single = sp.first == sp.last;
     const int k_begin = max(lo, sp.base + split * sp.len), k_end = min(hi, sp.base + (split + 1) * sp.len);
     const int kt_begin = k_begin / DT_KT, kt_end = (k_end + DT_KT - 1) / DT_KT;
@@ -104,9 +134,15 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     const int qpg = H / G;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    if ((smem_u32(smem_raw) & 1023u) != 0) {
+    // the partial result of this CTA for the cluster merge: [16 heads][HD] sums, then [16][2] (max, sum of weights);
+    // behind the scratch of the four-warp merge inside the key ring
+    float* fin_o = reinterpret_cast<float*>(sK) + 4 * 16 * HD + 4 * 16 * 2;
+    float* fin_ml = fin_o + 16 * HD;
+    static_assert((4 * 16 * HD + 4 * 16 * 2 + 16 * HD + 16 * 2) * sizeof(float) <= (size_t)STAGES * TILE, "merge scratch must fit in the key ring");
+    bool good = (smem_u32(smem_raw) & 1023u) == 0;
+    if (!good) {
         if (threadIdx.x == 0 && err != nullptr) atomicExch(err, 5);
-        return;
+        if (!CLUSTER) return;
     }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -122,7 +158,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
 
-    if (warp == DT_CONSUMERS) {
+    if (good && has_keys && warp == DT_CONSUMERS) {
         // ---- producer: lane = (page of the tile, K or V, column half), all copies of a tile issued at once ----
         const int pages_per_tile = DT_KT / page_size;
         const uint32_t page_bytes = (uint32_t)page_size * 128u;          // one column half of a page
@@ -132,14 +168,24 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         const int hf = sub % HALVES;
         uint32_t it = 0;
         bool ok = true;
+        // page ids are read a few tiles ahead: the load from the block table would otherwise sit, with its full
+        // latency, between every two tiles
+        auto page_of = [&](int kt) -> int {
+            if (kt >= kt_end || j >= pages_per_tile) return -1;
+            const int key_lo = kt * DT_KT + j * page_size;
+            return (key_lo < k_end && key_lo + page_size > k_begin) ? table[kt * pages_per_tile + j] : -1;
+        };
+        constexpr int AHEAD = 4;
+        int ahead[AHEAD];
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) ahead[i] = page_of(kt_begin + i);
         for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1;
-            int pid = -1;
-            if (j < pages_per_tile) {
-                const int key_lo = kt * DT_KT + j * page_size;
-                if (key_lo < k_end && key_lo + page_size > k_begin) pid = table[kt * pages_per_tile + j];
-            }
+            const int pid = ahead[0];
+#pragma unroll
+            for (int i = 0; i + 1 < AHEAD; ++i) ahead[i] = ahead[i + 1];
+            ahead[AHEAD - 1] = page_of(kt + AHEAD);
             const uint32_t have = __ballot_sync(0xffffffffu, pid >= 0);
             const uint32_t full = smem_u32(&ctl->full[s]);
             if (lane == 0) {
@@ -151,9 +197,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
                 tma_load_2d(smem_u32((is_v ? sV : sK) + s * TILE) + hf * (DT_KT * 128) + (uint32_t)j * page_bytes, is_v ? &tmV : &tmK,
                             hf * 64, (pid * G + g) * page_size, full);
         }
-        return;     // the producer warp takes no part in the merge
-    }
-
+        if (!CLUSTER) return;     // the producer warp takes no part in the merge inside the CTA
+    } else if (good && has_keys) {
     // ---- consumers ----
     // Q fragments: rows are the query heads of this KV head (rows >= qpg are zero)
     uint32_t qf[KSTEPS][4];
@@ -250,10 +295,12 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     if (lane == 0) mbar_arrive(smem_u32(&ctl->done));
     if (!ok || !mbar_wait(smem_u32(&ctl->done), 0, abort_flag)) {
         if (lane == 0 && err != nullptr) atomicExch(err, 4);
-        return;
+        if (!CLUSTER) return;
+        good = false;
     }
     float* mo = reinterpret_cast<float*>(sK);                 // [4][16][HD]
     float* mml = mo + 4 * 16 * HD;                            // [4][16][2]
+    if (good) {
     {
         const int r_lo = lane >> 2, r_hi = r_lo + 8;
 #pragma unroll
@@ -276,8 +323,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     if (lane == 0) mbar_arrive(smem_u32(&ctl->done));          // second phase: the partial results are in shared memory
     if (!mbar_wait(smem_u32(&ctl->done), 1, abort_flag)) {
         if (lane == 0 && err != nullptr) atomicExch(err, 4);
-        return;
+        if (!CLUSTER) return;
+        good = false;
     }
+    }
+    if (good)
     for (int idx = threadIdx.x; idx < qpg * HD; idx += DT_CONSUMERS * 32) {
         const int r = idx / HD, col = idx - r * HD;
         float m = -INFINITY;
@@ -292,7 +342,13 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
             acc += mo[((size_t)w * 16 + r) * HD + col] * f;
         }
         const int h = g * qpg + r;
-        if (single) {
+        if (CLUSTER) {
+            fin_o[r * HD + col] = acc;
+            if (col == 0) {
+                fin_ml[r * 2] = m;
+                fin_ml[r * 2 + 1] = l;
+            }
+        } else if (single) {
             out[((size_t)t * H + h) * HD + col] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
         } else {
             const size_t p = ((size_t)item * H + h) * max_splits + split;
@@ -303,9 +359,40 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
             }
         }
     }
+    }   // consumers
+
+    if constexpr (CLUSTER) {
+        // a CTA without keys (or one that gave up) contributes nothing: weight 0
+        if ((!has_keys || !good) && threadIdx.x < 16) {
+            fin_ml[threadIdx.x * 2] = -INFINITY;
+            fin_ml[threadIdx.x * 2 + 1] = 0.0f;
+        }
+        cluster_sync_all();
+        // this CTA's slice of the qpg * HD output values; partials in split order, as the merge kernel sums them
+        const int n_ranks = (int)cluster_size(), rank = (int)cluster_rank();
+        const int total = qpg * HD, chunk = (total + n_ranks - 1) / n_ranks;
+        const int end = min(total, (rank + 1) * chunk);
+        for (int idx = rank * chunk + (int)threadIdx.x; idx < end; idx += DT_THREADS) {
+            const int r = idx / HD, col = idx - r * HD;
+            float m = -INFINITY;
+            for (int sI = 0; sI < n_ranks; ++sI) m = fmaxf(m, ld_peer_f32(&fin_ml[r * 2], sI));
+            const float mu = (m == -INFINITY) ? 0.0f : m;
+            float l = 0.0f, acc = 0.0f;
+            for (int sI = 0; sI < n_ranks; ++sI) {
+                const float lp = ld_peer_f32(&fin_ml[r * 2 + 1], sI);
+                if (lp > 0.0f) {                       // a peer without keys holds no sums
+                    const float f = exp2f(ld_peer_f32(&fin_ml[r * 2], sI) - mu);
+                    l += lp * f;
+                    acc += ld_peer_f32(&fin_o[r * HD + col], sI) * f;
+                }
+            }
+            out[((size_t)t * H + g * qpg + r) * HD + col] = __float2bfloat16_rn(l > 0.0f ? acc / l : 0.0f);
+        }
+        cluster_sync_all();                            // peers may still be reading this CTA's shared memory
+    }
 }
 
-template <int HD, int STAGES>
+template <int HD, int STAGES, bool CLUSTER>
 int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* q, void* out, void* part_o, void* part_ml,
                       const void* items, int n_items, const void* positions, const void* token_req, const void* table,
                       int table_width, int page_size, int H, int G, int window, float scale, int split_len, int max_splits,
@@ -314,35 +401,77 @@ int launch_decode_tma(const CUtensorMap& tk, const CUtensorMap& tv, const void* 
     const size_t smem = (size_t)2 * STAGES * TILE + sizeof(DecCtl<STAGES>);
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attention_decode_tma_kernel<HD, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        if (cudaFuncSetAttribute(attention_decode_tma_kernel<HD, STAGES, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             mm_set_last_error("attention_decode_tma: cannot reserve shared memory");
             return MM_ERR_LAUNCH;
         }
         configured = true;
     }
-    dim3 grid(n_items, G, max_splits);
-    attention_decode_tma_kernel<HD, STAGES><<<grid, DT_THREADS, smem, s>>>(
-        tk, tv, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (float*)part_o, (float*)part_ml, (const int32_t*)items,
-        (const int32_t*)positions, (const int32_t*)token_req, (const int32_t*)table, table_width, page_size, H, G, window,
-        scale * 1.4426950408889634f, split_len, max_splits, err);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_items, G, max_splits);
+    cfg.blockDim = dim3(DT_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = max_splits;       // the splits of one (token, KV head) are one cluster
+    cfg.attrs = attr;
+    cfg.numAttrs = CLUSTER ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, attention_decode_tma_kernel<HD, STAGES, CLUSTER>, tk, tv, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
+                       (float*)part_o, (float*)part_ml, (const int32_t*)items, (const int32_t*)positions, (const int32_t*)token_req,
+                       (const int32_t*)table, table_width, page_size, H, G, window, scale * 1.4426950408889634f, split_len,
+                       max_splits, err);
     MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+// How many clusters of `cluster_size` CTAs of the cluster variant can be resident on the device at once.
+template <int HD>
+int max_active_clusters(int cluster_size, int* out) {
+    constexpr int STAGES = 3, TILE = DT_KT * HD * 2;
+    const size_t smem = (size_t)2 * STAGES * TILE + sizeof(DecCtl<STAGES>);
+    if (cudaFuncSetAttribute(attention_decode_tma_kernel<HD, STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        mm_set_last_error("attention_decode_tma: cannot reserve shared memory");
+        return MM_ERR_LAUNCH;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, cluster_size);
+    cfg.blockDim = dim3(DT_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = cluster_size;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(out, attention_decode_tma_kernel<HD, STAGES, true>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        mm_set_last_error("attention_decode_tma: cudaOccupancyMaxActiveClusters failed");
+        return MM_ERR_LAUNCH;
+    }
     return MM_OK;
 }
 
 }  // namespace
 
 // The attention part only: the caller runs the merge of attention_mma.cu afterwards when max_splits > 1
-// (mm_attention_decode_merge_bf16).  Arguments as mm_attention_decode_bf16, plus the pool size for the tensor maps.
+// (mm_attention_decode_merge_bf16), unless `cluster` is set: then 2 <= max_splits <= 8, the splits are merged inside the
+// kernel by a thread-block cluster, no scratch is used and `out` is final.
+// Arguments as mm_attention_decode_bf16, plus the pool size for the tensor maps.
 MM_EXPORT int mm_attention_decode_tma_bf16(const void* q, const void* k_pages, const void* v_pages, void* out, void* part_o,
                                            void* part_ml, const void* items, int n_items, const void* positions,
                                            const void* token_req, const void* block_table, int table_width, int page_size,
                                            int num_pages, int H, int G, int hd, int window, float scale, int split_len,
-                                           int max_splits, int stages, void* err, void* stream) {
+                                           int max_splits, int stages, int cluster, void* err, void* stream) {
     MM_REQUIRE(hd == 64 || hd == 128, "attention_decode_tma: built for head_dim 64 and 128");
     MM_REQUIRE(n_items >= 0 && H > 0 && G > 0 && H % G == 0 && H / G <= 16 && num_pages > 0, "attention_decode_tma: bad head counts");
     MM_REQUIRE(page_size >= 8 && page_size <= 64 && (64 % page_size) == 0, "attention_decode_tma: page_size must be 8, 16, 32 or 64");
     MM_REQUIRE(split_len >= 0 && split_len % 64 == 0 && max_splits >= 1 && max_splits <= 65535 && G <= 65535, "attention_decode_tma: bad split");
-    MM_REQUIRE(max_splits == 1 || (part_o != nullptr && part_ml != nullptr), "attention_decode_tma: scratch missing");
+    MM_REQUIRE(cluster || max_splits == 1 || (part_o != nullptr && part_ml != nullptr), "attention_decode_tma: scratch missing");
+    MM_REQUIRE(!cluster || (max_splits >= 2 && max_splits <= 8), "attention_decode_tma: a cluster merges 2 to 8 splits");
     MM_REQUIRE(stages == 3 || stages == 6, "attention_decode_tma: stages must be 3 or 6");
     if (n_items == 0) return MM_OK;
     CUtensorMap tk, tv;
@@ -352,9 +481,18 @@ MM_EXPORT int mm_attention_decode_tma_bf16(const void* q, const void* k_pages, c
         return MM_ERR_DRIVER;
     }
     cudaStream_t s = (cudaStream_t)stream;
-#define MM_DT(HDV, ST) launch_decode_tma<HDV, ST>(tk, tv, q, out, part_o, part_ml, items, n_items, positions, token_req, block_table, \
-                                                  table_width, page_size, H, G, window, scale, split_len, max_splits, (int*)err, s)
-    if (hd == 128) return stages == 3 ? MM_DT(128, 3) : MM_DT(128, 6);
-    return stages == 3 ? MM_DT(64, 3) : MM_DT(64, 6);
+#define MM_DT(HDV, ST, CL) launch_decode_tma<HDV, ST, CL>(tk, tv, q, out, part_o, part_ml, items, n_items, positions, token_req, block_table, \
+                                                          table_width, page_size, H, G, window, scale, split_len, max_splits, (int*)err, s)
+    if (cluster) return hd == 128 ? MM_DT(128, 3, true) : MM_DT(64, 3, true);
+    if (hd == 128) return stages == 3 ? MM_DT(128, 3, false) : MM_DT(128, 6, false);
+    return stages == 3 ? MM_DT(64, 3, false) : MM_DT(64, 6, false);
 #undef MM_DT
+}
+
+// Clusters of `cluster_size` (2..8) CTAs of the cluster variant that fit on the current device at the same time; a
+// launch with more clusters than this runs in waves.
+MM_EXPORT int mm_attention_decode_tma_max_clusters(int hd, int cluster_size, int* out) {
+    MM_REQUIRE(hd == 64 || hd == 128, "attention_decode_tma: built for head_dim 64 and 128");
+    MM_REQUIRE(cluster_size >= 2 && cluster_size <= 8 && out != nullptr, "attention_decode_tma: cluster size must be 2..8");
+    return hd == 128 ? max_active_clusters<128>(cluster_size, out) : max_active_clusters<64>(cluster_size, out);
 }

@@ -162,15 +162,24 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         unsigned char* ring = for_k ? sK : sV;
         uint32_t it = 0;
         bool ok = true;
+        // pages of a tile that hold keys some row of the tile may see.  The ids are read a few tiles ahead: the load
+        // from the block table would otherwise sit, with its full latency, between every two tiles.
+        auto page_of = [&](int kt) -> int {
+            if (kt >= kt_end || j >= pages_per_tile) return -1;
+            const int key_lo = kt * BN + j * page_size;
+            return (key_lo < hi_all && key_lo + page_size > lo_all) ? table[kt * pages_per_tile + j] : -1;
+        };
+        constexpr int AHEAD = 4;
+        int ahead[AHEAD];
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) ahead[i] = page_of(kt_begin + i);
         for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
             const int s = it % KV_STAGES;
             const uint32_t ph = (it / KV_STAGES) & 1;
-            // pages of this tile that hold keys some row of the tile may see
-            int pid = -1;
-            if (j < pages_per_tile) {
-                const int key_lo = kt * BN + j * page_size;
-                if (key_lo < hi_all && key_lo + page_size > lo_all) pid = table[kt * pages_per_tile + j];
-            }
+            const int pid = ahead[0];
+#pragma unroll
+            for (int i = 0; i + 1 < AHEAD; ++i) ahead[i] = ahead[i + 1];
+            ahead[AHEAD - 1] = page_of(kt + AHEAD);
             const uint32_t have = __ballot_sync(0xffffffffu, pid >= 0);
             const uint32_t full = smem_u32(for_k ? &ctl->k_full[s] : &ctl->v_full[s]);
             if (lane == 0) {

@@ -26,6 +26,8 @@ USE_TCGEN05_PREFILL = True
 USE_TMA_DECODE = True   # decode attention with a TMA producer warp (page sizes 8..64)
 TMA_DECODE_STAGES = 3
 TARGET_CTAS = 2 * 148  # decode CTAs wanted (measured: 2 per SM beat 1 and 4 at batch 8; batch 64 is best unsplit)
+USE_CLUSTER_MERGE = True   # up to 8 splits per token: one thread-block cluster merges them through shared memory
+CLUSTER_MAX_WANTED = 12    # ... preferred over more splits and a merge launch when up to this many were wanted
 FIXED_SPLIT = None     # tests set a split length in keys to cut by absolute position instead
 
 _declared = False
@@ -38,7 +40,8 @@ def _declare():
     P, I, F = c_void_p, c_int, c_float
     _lib.declare("mm_attention_prefill_bf16", [P, P, P, P, P, I, P, I, I, I, I, I, I, F, P])
     _lib.declare("mm_attention_prefill_tcgen05", [P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, P])
-    _lib.declare("mm_attention_decode_tma_bf16", [P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, P, P])
+    _lib.declare("mm_attention_decode_tma_bf16", [P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, P])
+    _lib.declare("mm_attention_decode_tma_max_clusters", [I, I, P])
     _lib.declare("mm_attention_decode_merge_bf16", [P, P, P, P, I, P, I, I, I, I, I, P])
     _lib.declare("mm_attention_decode_bf16", [P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P])
     _declared = True
@@ -59,18 +62,41 @@ class AttentionPlan:
     max_splits: int
     part_o: Optional[torch.Tensor] = None
     part_ml: Optional[torch.Tensor] = None
+    cluster: bool = False              # the splits of a token are one thread-block cluster that merges them itself
 
 
-def choose_split(n_items: int, num_kv_heads: int, max_kv_len: int):
-    """(split_len, max_splits) for the decode kernel.  split_len 0: every token's key range is cut evenly
-    into at most max_splits pieces of whole 64-key tiles, so the grid is full whatever the lengths."""
+_cluster_capacity = {}
+
+
+def cluster_capacity(head_dim: int, size: int) -> int:
+    """Clusters of ``size`` decode CTAs that are resident on the current device at once (asked of the runtime)."""
+    key = (torch.cuda.current_device(), head_dim, size)
+    if key not in _cluster_capacity:
+        _declare()
+        n = c_int(0)
+        check(_lib.load().mm_attention_decode_tma_max_clusters(head_dim, size, ctypes.byref(n)), "attention_decode_tma_max_clusters")
+        _cluster_capacity[key] = n.value
+    return _cluster_capacity[key]
+
+
+def choose_split(n_items: int, num_kv_heads: int, max_kv_len: int, head_dim: int = 0, page_size: int = 0):
+    """(split_len, max_splits, cluster) for the decode kernel.  split_len 0: every token's key range is cut evenly
+    into at most max_splits pieces of whole 64-key tiles, so the grid is full whatever the lengths.  cluster: the
+    splits of a token are one thread-block cluster and merge themselves."""
     if FIXED_SPLIT:
-        return FIXED_SPLIT, max(1, -(-max_kv_len // FIXED_SPLIT))
+        return FIXED_SPLIT, max(1, -(-max_kv_len // FIXED_SPLIT)), False
     ctas = max(1, n_items * num_kv_heads)
     if ctas >= TARGET_CTAS // 2:
-        return 0, 1              # one CTA per SM or more already: a split would only add the merge pass
-    wanted = -(-TARGET_CTAS // ctas)
-    return 0, max(1, min(wanted, -(-max_kv_len // 64)))
+        return 0, 1, False       # one CTA per SM or more already: a split would only add the merge pass
+    # never more CTAs than are resident at once (two per SM): a second, nearly empty wave costs a whole pass
+    wanted = max(1, min(TARGET_CTAS // ctas, -(-max_kv_len // 64)))
+    # Clusters of 2, 4 or 8 place well on the GPU (measured: 3 and 6 do not), and only as many as are resident at
+    # once.  Worth a few splits less (12 -> 8 measured faster), not half of them (6 -> 4, 3 -> 2 measured slower).
+    if USE_TMA_DECODE and USE_CLUSTER_MERGE and head_dim in (64, 128) and page_size in (8, 16, 32, 64) and wanted >= 2:
+        size = 1 << (min(wanted, 8).bit_length() - 1)
+        if (wanted >= 8 or 4 * size >= 3 * wanted) and wanted <= CLUSTER_MAX_WANTED and ctas <= cluster_capacity(head_dim, size):
+            return 0, size, True
+    return 0, wanted, False
 
 
 def tcgen05_prefill_usable(head_dim: int, page_size: int) -> bool:
@@ -93,9 +119,9 @@ def make_plan(ctx, num_heads: int, num_kv_heads: int, head_dim: int) -> Attentio
         d_items = None
     else:
         d_items = torch.tensor(items, dtype=torch.int32, device=device) if items else None
-    split_len, max_splits = choose_split(len(items), num_kv_heads, ctx.max_kv_len) if items else (0, 1)
-    plan = AttentionPlan(d_tiles, len(tiles), tile_rows, d_items, len(items), split_len, max_splits)
-    if items and max_splits > 1:
+    split_len, max_splits, cluster = choose_split(len(items), num_kv_heads, ctx.max_kv_len, head_dim, ctx.page_size) if items else (0, 1, False)
+    plan = AttentionPlan(d_tiles, len(tiles), tile_rows, d_items, len(items), split_len, max_splits, cluster=cluster)
+    if items and max_splits > 1 and not plan.cluster:
         plan.part_o = torch.empty((len(items), num_heads, max_splits, head_dim), dtype=torch.float32, device=device)
         plan.part_ml = torch.empty((len(items), num_heads, max_splits, 2), dtype=torch.float32, device=device)
     return plan
@@ -132,8 +158,8 @@ def run(q, cache, out, ctx, num_heads: int, num_kv_heads: int, head_dim: int, wi
             q.data_ptr(), cache.k_pages.data_ptr(), cache.v_pages.data_ptr(), out.data_ptr(), po, pm, it, plan.n_items,
             ctx.positions.data_ptr(), ctx.token_req.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
             cache.k_pages.shape[0], num_heads, num_kv_heads, head_dim, window, float(scale), plan.split_len, plan.max_splits,
-            TMA_DECODE_STAGES, ops.tcgen05_error_flag(q.device).data_ptr(), stream), "attention_decode_tma_bf16")
-        if plan.max_splits > 1:
+            TMA_DECODE_STAGES, int(plan.cluster), ops.tcgen05_error_flag(q.device).data_ptr(), stream), "attention_decode_tma_bf16")
+        if plan.max_splits > 1 and not plan.cluster:
             check(lib.mm_attention_decode_merge_bf16(out.data_ptr(), po, pm, it, plan.n_items, ctx.positions.data_ptr(), num_heads,
                                                      head_dim, window, plan.split_len, plan.max_splits, stream),
                   "attention_decode_merge_bf16")

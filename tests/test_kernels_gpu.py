@@ -287,6 +287,34 @@ def test_attention_tensor_core_kernels(H, G, hd, ps, window):
     assert plan.n_tiles > 0 and plan.n_items == 0                  # the last run was all tiles
 
 
+@pytest.mark.parametrize("H,G,hd,ps,n,size", [(28, 4, 128, 16, 8, 8), (28, 4, 128, 16, 16, 4), (28, 4, 128, 16, 30, 2), (8, 2, 64, 32, 16, 8), (6, 2, 64, 8, 32, 4)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_attention_decode_cluster_merge(H, G, hd, ps, n, size, window):
+    """Single tokens of n requests: the splits of a token are a thread-block cluster that merges its partial results
+    through shared memory.  Contexts from one key (most CTAs of the cluster have no keys) to many tiles per split."""
+    rng = np.random.RandomState(n * 7 + hd + window)
+    base = [1, 63, 64, 65, 300, 1000, 129, 2, 511, 512, 513, 17]
+    ctx_lens = [base[i % len(base)] + (i // len(base)) * 37 for i in range(n)]
+    far = 3 if not window else 1000 - 1 - 99
+    case = make_attention_case(rng, H, G, hd, ps, ctx_lens, [1] * n, torch.bfloat16, spike=(5, 0, far, H - 1))
+    ref = attention_reference(case, window)
+    assert abs(ref[5, H - 1, 0] - 50.0) < 1.0
+    out, plan = run_bf16_attention(case, H, G, hd, ps, window)
+    assert plan.cluster and plan.max_splits == size and plan.part_o is None
+    err = np.abs(out.float().cpu().numpy().reshape(ref.shape) - ref)
+    assert err.max() <= 2.5 * 2 ** -8 * np.abs(ref).max(), np.unravel_index(err.argmax(), err.shape)
+    # the same through scratch memory and the merge kernel
+    from mimirmind_b200.kernels import attention_bf16 as ab
+    old = ab.USE_CLUSTER_MERGE
+    try:
+        ab.USE_CLUSTER_MERGE = False
+        out2, plan2 = run_bf16_attention(case, H, G, hd, ps, window)
+    finally:
+        ab.USE_CLUSTER_MERGE = old
+    assert not plan2.cluster and plan2.part_o is not None
+    assert np.abs(out2.float().cpu().numpy() - out.float().cpu().numpy()).max() <= 2 ** -7 * np.abs(ref).max()
+
+
 def test_attention_window_edge_is_exact():
     """A dominant key exactly one place outside the window must not be seen; one place inside must."""
     H, G, hd, ps, W = 4, 2, 64, 16, 48
