@@ -27,6 +27,13 @@
 // Input row scale: with `in_ss` the accumulators of row m are multiplied by
 // 1 / sqrt(sum_j in_ss[j][m] / in_dim + eps) before the epilogue (the deferred 1/rms of RESID).
 //
+// Chain: up to GEMV_CHAIN_MAX products, each reading what the one before wrote, run as ONE cooperative launch of
+// a persistent grid (every CTA takes the work items of every phase in turn) with a grid-wide barrier between
+// phases.  Before a CTA enters the barrier it has already issued the first weight loads of its next item, so the
+// stream from HBM does not stop at the hand-over the way it does between two kernels.  The barrier is a counter in
+// global memory (release add, acquire poll) with a bounded number of polls; on a time-out the CTA sets the error
+// flag and goes on, so a launch always ends.
+//
 // The reference's counterparts are its bf16 GEMV and small-M GEMM
 // (kernels/cuda/common/matmul_bf16_vec.cu:53-99: warp per output row, M launches;
 // matmul_bf16_gemm.cu: scalar, M <= 16).
@@ -70,8 +77,14 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+// activations may have been written earlier in the same (chained) launch by another SM: plain loads, never .nc
+__device__ __forceinline__ uint4 ld_act(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
 }
 __device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -79,17 +92,77 @@ __device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, ui
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+#define GEMV_CHAIN_MAX 4
+
+struct GemvChainArgs {
+    int n;
+    int epi[GEMV_CHAIN_MAX];
+    GemvArgs phase[GEMV_CHAIN_MAX];
+    unsigned* sync;             // [2]: arrivals at the barriers, CTAs that have finished; both zero between launches
+    int* err;
+};
+
+// shared memory of a CTA, reused by every item and phase
+struct GemvSmem {
+    float red[GEMV_WARPS][32][8];                 // K-split partial sums (4 floats per batch tile)
+    float in_scale[16];                           // 1/rms of the input rows
+    __align__(16) float stage_a[GEMV_WARPS * 16 * 16];   // RESID: residual [rt][m][16 cols]; ROPE: cos[8], sin[8] per [rt][m]
+    __align__(16) float stage_b[GEMV_WARPS * 16];        // RESID: norm weights [rt][16]; ROPE: bias [rt][16]
+    int slot_s[16];                               // ROPE: cache slot of each row
+};
+
+template <int U>
+struct GemvFirst {                                // the first batch of weight loads of an item, issued ahead of its turn
+    uint4 lo[U], hi[U];
+};
+
+// this warp's place in an item: row tile, K split, its 32-wide k blocks
+struct GemvPlace {
+    int rt, ks, n0, kb_begin, kb_count;
+    bool active;
+};
+__device__ __forceinline__ GemvPlace gemv_place(const GemvArgs& a, int item) {
+    GemvPlace p;
+    const int warp = threadIdx.x >> 5;
+    p.rt = warp / a.KS;
+    p.ks = warp - p.rt * a.KS;
+    p.n0 = (item * a.RT + p.rt) * 16;
+    p.active = p.n0 < a.N;
+    const int nkb = a.K / 32, base = nkb / a.KS, rem = nkb % a.KS;
+    p.kb_begin = p.ks * base + min(p.ks, rem);
+    p.kb_count = base + (p.ks < rem ? 1 : 0);
+    return p;
+}
+
+template <int U>
+__device__ __forceinline__ void gemv_first_weights(const GemvArgs& a, int item, GemvFirst<U>& f) {
+    const GemvPlace p = gemv_place(a, item);
+    const int lane = threadIdx.x & 31, t = lane & 3, r = lane >> 2;
+    const __nv_bfloat16* wlo = a.W + (size_t)(p.n0 + r) * a.K + (size_t)p.kb_begin * 32 + t * 8;
+    const __nv_bfloat16* whi = wlo + (size_t)8 * a.K;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        if (p.active && u < p.kb_count) {
+            f.lo[u] = ldg_stream(wlo + (size_t)u * 32);
+            f.hi[u] = ldg_stream(whi + (size_t)u * 32);
+        } else {
+            f.lo[u] = make_uint4(0, 0, 0, 0);
+            f.hi[u] = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// One work item (RT row tiles of 16 weight rows, all of K) of one product, by the whole CTA.  `first` holds the
+// item's first weight batch, already requested.  Ends with the item's results written to global memory; the
+// caller separates items that share `sm` by a CTA barrier.
 template <int NT, int U, int EPI>
-__global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvArgs a) {
-    __shared__ float red[GEMV_WARPS][32][4 * NT];
-    __shared__ float in_scale[16];
+__device__ __forceinline__ void gemv_item(const GemvArgs& a, int item, const GemvFirst<U>& first, GemvSmem& sm, float* ss_s) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = lane & 3, r = lane >> 2;
     const int K = a.K;
-
-    const int rt = warp / a.KS, ks = warp - rt * a.KS;
-    const int n0 = (blockIdx.x * a.RT + rt) * 16;
-    const bool active = n0 < a.N;
+    const GemvPlace pl = gemv_place(a, item);
+    const int rt = pl.rt, ks = pl.ks, n0 = pl.n0;
+    const bool active = pl.active;
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
@@ -100,10 +173,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
     //   RESID      the residual values [rt][m][16 cols] and the norm weights [rt][16] of this CTA's columns
     //   ROPE       cos and sin [rt][m][8] of every (row, pair) of this CTA's tiles, the bias [rt][16], each row's slot
     constexpr bool kStaged = (EPI == EPI_RESID || EPI == EPI_ROPE);
-    extern __shared__ __align__(16) float ss_s[];
-    __shared__ __align__(16) float stage_a[kStaged ? GEMV_WARPS * 16 * 16 : 4];
-    __shared__ __align__(16) float stage_b[kStaged ? GEMV_WARPS * 16 : 4];
-    __shared__ int slot_s[EPI == EPI_ROPE ? 16 : 1];
+    float* stage_a = sm.stage_a;
+    float* stage_b = sm.stage_b;
+    int* slot_s = sm.slot_s;
     const int M4 = (a.M + 3) & ~3;
     auto stage = [&]() {
         if (a.in_ss != nullptr) {
@@ -116,14 +188,14 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
         if constexpr (EPI == EPI_RESID) {
             for (int idx = threadIdx.x; idx < a.RT * 64; idx += GEMV_THREADS) {     // (tile, row, 4 columns)
                 const int ti = idx >> 6, m = (idx >> 2) & 15, c4 = idx & 3;
-                const int col = (blockIdx.x * a.RT + ti) * 16 + c4 * 4;
+                const int col = (item * a.RT + ti) * 16 + c4 * 4;
                 if (m < a.M && col < a.N) cp_async16(&stage_a[(ti * 16 + m) * 16 + c4 * 4], a.residual + (size_t)m * a.N + col);
             }
             if (a.norm_w != nullptr) {
                 const int bytes16 = (a.norm_w_dtype == MM_F32) ? 4 : 2;             // 16-byte pieces per tile
                 for (int idx = threadIdx.x; idx < a.RT * bytes16; idx += GEMV_THREADS) {
                     const int ti = idx / bytes16, c = idx - ti * bytes16;
-                    const int col = (blockIdx.x * a.RT + ti) * 16;
+                    const int col = (item * a.RT + ti) * 16;
                     if (col < a.N)
                         cp_async16(reinterpret_cast<char*>(&stage_b[ti * 16]) + c * 16,
                                    reinterpret_cast<const char*>(a.norm_w) + (size_t)col * (a.norm_w_dtype == MM_F32 ? 4 : 2) + c * 16);
@@ -133,7 +205,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
         if constexpr (EPI == EPI_ROPE) {
             for (int idx = threadIdx.x; idx < a.RT * 64; idx += GEMV_THREADS) {     // (tile, row, cos|sin, 4 pairs)
                 const int ti = idx >> 6, m = (idx >> 2) & 15, part = idx & 3;
-                const int tile0 = (blockIdx.x * a.RT + ti) * 16;
+                const int tile0 = (item * a.RT + ti) * 16;
                 const int head = tile0 / a.hd, within = tile0 - head * a.hd;
                 if (m < a.M && tile0 < a.N && head < a.H + a.G)
                     cp_async16(&stage_a[(ti * 16 + m) * 16 + part * 4],
@@ -143,7 +215,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
                 const int bytes16 = (a.bias_dtype == MM_F32) ? 4 : 2;
                 for (int idx = threadIdx.x; idx < a.RT * bytes16; idx += GEMV_THREADS) {
                     const int ti = idx / bytes16, c = idx - ti * bytes16;
-                    const int row = (blockIdx.x * a.RT + ti) * 16;
+                    const int row = (item * a.RT + ti) * 16;
                     if (row < a.N)
                         cp_async16(reinterpret_cast<char*>(&stage_b[ti * 16]) + c * 16,
                                    reinterpret_cast<const char*>(a.bias) + (size_t)row * (a.bias_dtype == MM_F32 ? 4 : 2) + c * 16);
@@ -158,11 +230,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
     };
 
     if (active) {
-        // this warp's share of the 32-wide k blocks
-        const int nkb = K / 32, base = nkb / a.KS, rem = nkb % a.KS;
-        const int kb_begin = ks * base + min(ks, rem);
-        const int kb_count = base + (ks < rem ? 1 : 0);
-        const __nv_bfloat16* wlo = a.W + (size_t)(n0 + r) * K + (size_t)kb_begin * 32 + t * 8;
+        const int kb_count = pl.kb_count;
+        const __nv_bfloat16* wlo = a.W + (size_t)(n0 + r) * K + (size_t)pl.kb_begin * 32 + t * 8;
         const __nv_bfloat16* whi = wlo + (size_t)8 * K;
         const __nv_bfloat16* xg[NT];
         bool xok[NT];
@@ -170,7 +239,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
         for (int j = 0; j < NT; ++j) {
             const int n = j * 8 + r;
             xok[j] = n < a.M;
-            xg[j] = a.x + (size_t)(xok[j] ? n : 0) * a.ldx + (size_t)kb_begin * 32 + t * 8;
+            xg[j] = a.x + (size_t)(xok[j] ? n : 0) * a.ldx + (size_t)pl.kb_begin * 32 + t * 8;
         }
         // Two register buffers: the loads of the next U k-blocks are issued before the mma of the
         // current ones, so a warp always has a full batch of loads in flight.
@@ -192,9 +261,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
             for (int u = 0; u < U; ++u)
 #pragma unroll
                 for (int j = 0; j < NT; ++j)
-                    xb[buf][u][j] = (kb + u < kb_count && xok[j])
-                                        ? __ldg(reinterpret_cast<const uint4*>(xg[j] + (size_t)(kb + u) * 32))
-                                        : make_uint4(0, 0, 0, 0);
+                    xb[buf][u][j] = (kb + u < kb_count && xok[j]) ? ld_act(xg[j] + (size_t)(kb + u) * 32) : make_uint4(0, 0, 0, 0);
         };
         auto mma_batch = [&](int buf, int kb) {
 #pragma unroll
@@ -207,11 +274,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
                 }
             }
         };
-        // The weights do not depend on the previous kernel: their first loads go out before this kernel waits for
-        // it, so the stream from HBM is already running when the activations become readable.
-        load_w(0, 0);
-        pdl_wait();
-        pdl_trigger();
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            alo[0][u] = first.lo[u];
+            ahi[0][u] = first.hi[u];
+        }
         load_x(0, 0);
         stage();
         for (int kb = 0; kb < kb_count; kb += 2 * U) {
@@ -223,8 +290,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
             mma_batch(1, kb + U);
         }
     } else {
-        pdl_wait();
-        pdl_trigger();
         stage();
     }
     asm volatile("cp.async.wait_all;\n" ::: "memory");
@@ -234,7 +299,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
 #pragma unroll
         for (int j = 0; j < NT; ++j)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) red[warp][lane][j * 4 + e] = acc[j][e];
+            for (int e = 0; e < 4; ++e) sm.red[warp][lane][j * 4 + e] = acc[j][e];
     }
     if (need_sync) __syncthreads();
     if (a.in_ss != nullptr) {
@@ -245,7 +310,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
             for (int j = part; j < a.in_tiles; j += 16) ssum += ss_s[j * M4 + m];
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
-        if (part == 0) in_scale[m] = 1.0f / sqrtf(ssum / (float)a.in_dim + a.in_eps);
+        if (part == 0) sm.in_scale[m] = 1.0f / sqrtf(ssum / (float)a.in_dim + a.in_eps);
         __syncthreads();
     }
     if (a.KS > 1 && ks == 0) {
@@ -253,7 +318,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
 #pragma unroll
             for (int j = 0; j < NT; ++j)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) acc[j][e] += red[warp + sI][lane][j * 4 + e];
+                for (int e = 0; e < 4; ++e) acc[j][e] += sm.red[warp + sI][lane][j * 4 + e];
     }
     if (!active || ks != 0) return;
 
@@ -263,7 +328,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
         for (int j = 0; j < NT; ++j)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const float sc = in_scale[j * 8 + t * 2 + e];
+                const float sc = sm.in_scale[j * 8 + t * 2 + e];
                 acc[j][e] *= sc;
                 acc[j][2 + e] *= sc;
             }
@@ -347,18 +412,188 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
     }
 }
 
+
+template <int NT, int U, int EPI>
+__global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvArgs a) {
+    __shared__ GemvSmem sm;
+    extern __shared__ __align__(16) float ss_s[];
+    // The weights do not depend on the previous kernel: their first loads go out before this kernel waits for
+    // it, so the stream from HBM is already running when the activations become readable.
+    GemvFirst<U> first;
+    gemv_first_weights<U>(a, blockIdx.x, first);
+    pdl_wait();
+    pdl_trigger();
+    gemv_item<NT, U, EPI>(a, blockIdx.x, first, sm, ss_s);
+}
+
+// Grid-wide barrier of a cooperative launch: every CTA adds one to the counter (release) and thread 0 polls it
+// (acquire) until `target` arrivals are in, at most GRID_SYNC_POLLS times.
+#define GRID_SYNC_POLLS (1u << 22)
+__device__ __forceinline__ void grid_sync(unsigned* count, unsigned target, int* err) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;\n" ::"l"(count) : "memory");
+        unsigned v = 0;
+        for (unsigned polls = 0; polls < GRID_SYNC_POLLS; ++polls) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(count) : "memory");
+            if (v >= target) break;
+            if (polls > 32) __nanosleep(64);
+        }
+        if (v < target && err != nullptr) atomicExch(err, 6);
+    }
+    __syncthreads();
+}
+
+template <int U>
+__device__ __forceinline__ void gemv_chain_item(const GemvChainArgs& c, int p, int item, const GemvFirst<U>& first, GemvSmem& sm, float* ss_s) {
+    switch (c.epi[p]) {
+        case EPI_SWIGLU: gemv_item<1, U, EPI_SWIGLU>(c.phase[p], item, first, sm, ss_s); break;
+        case EPI_RESID: gemv_item<1, U, EPI_RESID>(c.phase[p], item, first, sm, ss_s); break;
+        case EPI_ROPE: gemv_item<1, U, EPI_ROPE>(c.phase[p], item, first, sm, ss_s); break;
+        default: gemv_item<1, U, EPI_PLAIN>(c.phase[p], item, first, sm, ss_s); break;
+    }
+}
+
+// Persistent grid, at most 8 batch rows.  Phase p's items are dealt round-robin to the CTAs.
+__global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_chain_kernel(const __grid_constant__ GemvChainArgs c) {
+    constexpr int U = 4;
+    __shared__ GemvSmem sm;
+    extern __shared__ __align__(16) float ss_s[];
+    GemvFirst<U> first;
+    auto items_of = [&](int p) { return (c.phase[p].N / 16 + c.phase[p].RT - 1) / c.phase[p].RT; };
+    if ((int)blockIdx.x < items_of(0)) gemv_first_weights<U>(c.phase[0], blockIdx.x, first);
+    for (int p = 0; p < c.n; ++p) {
+        const int n_items = items_of(p);
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            gemv_chain_item<U>(c, p, item, first, sm, ss_s);
+            const int next = item + gridDim.x;
+            if (next < n_items) {
+                gemv_first_weights<U>(c.phase[p], next, first);
+                __syncthreads();                        // the shared buffers are free for the next item
+            }
+        }
+        if (p + 1 < c.n) {
+            // the next phase's first weights are requested before the barrier: HBM keeps streaming through it
+            if ((int)blockIdx.x < items_of(p + 1)) gemv_first_weights<U>(c.phase[p + 1], blockIdx.x, first);
+            grid_sync(c.sync, (unsigned)(p + 1) * gridDim.x, c.err);
+        }
+    }
+    // the last CTA to finish leaves both counters at zero for the next launch
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned done = atomicAdd(c.sync + 1, 1u);
+        if (done == gridDim.x - 1) {
+            c.sync[0] = 0;
+            c.sync[1] = 0;
+            __threadfence();
+        }
+    }
+}
+
+// An open chain collects the products of this thread's next calls instead of launching them.
+static thread_local bool t_chain_open = false;
+static thread_local GemvChainArgs t_chain;
+
+static size_t gemv_dynamic_smem(const GemvArgs& a) {
+    return a.in_ss ? (size_t)a.in_tiles * ((a.M + 3) & ~3) * sizeof(float) : 0;   // the staged partial sums of the input rows
+}
+
 template <int EPI>
-static int launch_gemv(const GemvArgs& a, cudaStream_t s) {
+static int launch_gemv_now(const GemvArgs& a, cudaStream_t s) {
     const int tiles = a.N / 16;
     const int blocks = (tiles + a.RT - 1) / a.RT;
-    // dynamic shared memory: the staged partial sums of the input rows
-    const size_t smem = a.in_ss ? (size_t)a.in_tiles * ((a.M + 3) & ~3) * sizeof(float) : 0;
-    if (smem > 16 * 1024) {
+    const size_t smem = gemv_dynamic_smem(a);
+    if (a.M <= 8) mm_launch_pdl(gemv_bf16_kernel<1, 4, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
+    else mm_launch_pdl(gemv_bf16_kernel<2, 2, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
+static int launch_gemv_by_code(int epi, const GemvArgs& a, cudaStream_t s) {
+    switch (epi) {
+        case EPI_SWIGLU: return launch_gemv_now<EPI_SWIGLU>(a, s);
+        case EPI_RESID: return launch_gemv_now<EPI_RESID>(a, s);
+        case EPI_ROPE: return launch_gemv_now<EPI_ROPE>(a, s);
+        default: return launch_gemv_now<EPI_PLAIN>(a, s);
+    }
+}
+
+template <int EPI>
+static int launch_gemv(const GemvArgs& a, cudaStream_t s) {
+    if (gemv_dynamic_smem(a) > 16 * 1024) {
         mm_set_last_error("gemv: too many partial sums for the input scale (rows x producer tiles above 4096)");
         return MM_ERR_UNSUPPORTED;
     }
-    if (a.M <= 8) mm_launch_pdl(gemv_bf16_kernel<1, 4, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
-    else mm_launch_pdl(gemv_bf16_kernel<2, 2, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
+    if (t_chain_open) {
+        MM_REQUIRE(a.M <= 8, "gemv chain: at most 8 rows");
+        MM_REQUIRE(t_chain.n < GEMV_CHAIN_MAX, "gemv chain: full (flush first)");
+        t_chain.phase[t_chain.n] = a;
+        t_chain.epi[t_chain.n] = EPI;
+        ++t_chain.n;
+        return MM_OK;
+    }
+    return launch_gemv_now<EPI>(a, s);
+}
+
+// From now on this thread's mm_gemv_bf16* calls are collected (up to GEMV_CHAIN_MAX, each reading what the one before
+// wrote; at most 8 rows) until mm_gemv_chain_flush launches them together.  Nothing runs before the flush.
+MM_EXPORT int mm_gemv_chain_begin() {
+    MM_REQUIRE(!t_chain_open, "gemv chain: already open");
+    t_chain_open = true;
+    t_chain.n = 0;
+    return MM_OK;
+}
+
+MM_EXPORT int mm_gemv_chain_length() { return t_chain_open ? t_chain.n : -1; }
+
+// Forgets the collected products without running them (after an error between begin and flush).
+MM_EXPORT int mm_gemv_chain_discard() {
+    t_chain_open = false;
+    t_chain.n = 0;
+    return MM_OK;
+}
+
+// Launches the collected products: one as its ordinary kernel; several as one cooperative launch of a persistent grid
+// with grid-wide barriers between them.  sync: two zeroed uint32 in device memory that only these launches use
+// (they are left zero); err: device int set to 6 if a barrier gave up waiting.
+MM_EXPORT int mm_gemv_chain_flush(void* sync, void* err, void* stream) {
+    MM_REQUIRE(t_chain_open, "gemv chain: not open");
+    t_chain_open = false;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (t_chain.n == 0) return MM_OK;
+    if (t_chain.n == 1) return launch_gemv_by_code(t_chain.epi[0], t_chain.phase[0], s);
+    MM_REQUIRE(sync != nullptr, "gemv chain: no barrier counters");
+    size_t smem = 0;
+    int items = 0;
+    for (int p = 0; p < t_chain.n; ++p) {
+        const GemvArgs& a = t_chain.phase[p];
+        smem = smem > gemv_dynamic_smem(a) ? smem : gemv_dynamic_smem(a);
+        const int n = (a.N / 16 + a.RT - 1) / a.RT;
+        items = items > n ? items : n;
+    }
+    int dev = 0, sms = 0, per_sm = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_chain_kernel, GEMV_THREADS, smem) != cudaSuccess || per_sm < 1) {
+        cudaGetLastError();
+        mm_set_last_error("gemv chain: the persistent kernel does not fit on an SM");
+        return MM_ERR_LAUNCH;
+    }
+    // every CTA must be resident at once (they wait for one another): a cooperative launch checks that
+    const int capacity = sms * (per_sm < 2 ? per_sm : 2);
+    t_chain.sync = (unsigned*)sync;
+    t_chain.err = (int*)err;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(items < capacity ? items : capacity);
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, gemv_chain_kernel, t_chain);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }

@@ -198,6 +198,54 @@ def gemv_supported(m: int, n: int, k: int) -> bool:
     return 1 <= m <= GEMV_MAX_ROWS and n % 16 == 0 and k % 32 == 0 and k >= 256
 
 
+GEMV_CHAIN_MAX = 4
+_CHAIN_SYNC = {}
+
+
+class GemvChain:
+    """Weight-streaming products of a few rows that read one another's results, launched together: calls of
+    gemv_bf16 / gemv_bf16_residual / gemv_bf16_qkv_rope with ``chain=`` are only recorded (their outputs are
+    allocated and returned, not yet written); ``flush`` runs them as one persistent cooperative kernel with a
+    grid-wide barrier between consecutive products, so the stream of weights from HBM does not stop between them.
+    Whoever reads an output with anything but another product of the same chain flushes first."""
+
+    def __init__(self):
+        self._open = False
+        self._keep = []
+
+    def __len__(self) -> int:
+        return _lib.load().mm_gemv_chain_length() if self._open else 0
+
+    def record(self, *tensors) -> None:
+        self._keep.extend(t for t in tensors if t is not None)     # operands stay alive until the launch
+
+    def begin(self) -> None:
+        if self._open and len(self) >= GEMV_CHAIN_MAX:
+            self.flush()
+        if not self._open:
+            check(_lib.load().mm_gemv_chain_begin(), "gemv_chain_begin")
+            self._open = True
+
+    def flush(self) -> None:
+        if not self._open:
+            return
+        self._open = False
+        dev = torch.cuda.current_device()
+        if dev not in _CHAIN_SYNC:
+            _CHAIN_SYNC[dev] = torch.zeros(2, dtype=torch.int32, device=f"cuda:{dev}")
+        err = tcgen05_error_flag(torch.device("cuda", dev))
+        try:
+            check(_lib.load().mm_gemv_chain_flush(_CHAIN_SYNC[dev].data_ptr(), err.data_ptr(), _stream()), "gemv_chain_flush")
+        finally:
+            self._keep.clear()
+
+    def discard(self) -> None:
+        if self._open:
+            _lib.load().mm_gemv_chain_discard()
+            self._open = False
+        self._keep.clear()
+
+
 @dataclass
 class RowScale:
     """The deferred 1/rms of rows that were written as ``residual * norm_weight``: per 16-column tile of the
@@ -232,7 +280,7 @@ def _scale_args(scale: Optional["RowScale"], m: int):
 
 
 def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-              swiglu: bool = False, scale: Optional[RowScale] = None) -> torch.Tensor:
+              swiglu: bool = False, scale: Optional[RowScale] = None, chain: Optional[GemvChain] = None) -> torch.Tensor:
     """x[M<=16, K] @ w[N, K]^T (+ bias) with the weight-streaming kernel.  ``swiglu``: w interleaves gate and
     up rows in blocks of 8 and the result is silu(gate) * up, [M, N/2].  ``scale``: rows of the product are
     multiplied by the deferred 1/rms before bias and activation."""
@@ -246,6 +294,9 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
         _need(bias, "gemv bias")
     out = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
     rt, ks = _gemv_layout(n, k)
+    if chain is not None:
+        chain.begin()
+        chain.record(x, w, bias, out, scale.ss if scale is not None else None)
     check(_lib.load().mm_gemv_bf16(w.data_ptr(), x.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
                                    out.data_ptr(), dtype_code(out_dtype), m, n, k, k, out.shape[1], rt, ks, int(swiglu),
                                    *_scale_args(scale, m), _stream()), "gemv_bf16")
@@ -253,7 +304,7 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
 
 
 def gemv_bf16_residual(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_weight: Optional[torch.Tensor],
-                       eps: float = 0.0, scale: Optional[RowScale] = None):
+                       eps: float = 0.0, scale: Optional[RowScale] = None, chain: Optional[GemvChain] = None):
     """residual[M, N] (fp32, in place) += x @ w^T.  With ``norm_weight`` returns (xw, RowScale): the rows of
     ``residual * norm_weight`` in bfloat16 and the partial sums for their 1/rms; else returns None."""
     _need(x, "gemv x", torch.bfloat16)
@@ -271,6 +322,9 @@ def gemv_bf16_residual(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor,
         xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
         ss = torch.empty((n // 16, 16), dtype=torch.float32, device=x.device)
     rt, ks = _gemv_layout(n, k)
+    if chain is not None:
+        chain.begin()
+        chain.record(x, w, residual, norm_weight, xw, ss, scale.ss if scale is not None else None)
     check(_lib.load().mm_gemv_bf16_residual(w.data_ptr(), x.data_ptr(), residual.data_ptr(), _ptr(norm_weight),
                                             dtype_code(norm_weight.dtype) if norm_weight is not None else F32, _ptr(xw), _ptr(ss),
                                             m, n, k, k, rt, ks, *_scale_args(scale, m), _stream()), "gemv_bf16_residual")
@@ -314,7 +368,7 @@ def slot_mapping(positions: torch.Tensor, token_req: torch.Tensor, block_table: 
 def gemv_bf16_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
                        k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], table: torch.Tensor,
                        slots: Optional[torch.Tensor], page_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                       scale: Optional[RowScale] = None) -> None:
+                       scale: Optional[RowScale] = None, chain: Optional[GemvChain] = None) -> None:
     """The q/k/v projection of up to 16 tokens with bias, rotary encoding and cache write in its epilogue.
     ``w`` and ``bias`` are in the order of :func:`interleave_halves`; q_out, k and v are in natural order.
     ``table``: :func:`rope_table` of the tokens for this head size; ``slots``: :func:`slot_mapping`."""
@@ -343,6 +397,9 @@ def gemv_bf16_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Te
         if slots.numel() != m:
             raise KernelError("slots: one per token")
     rt, ks = _gemv_layout(n, k)
+    if chain is not None:
+        chain.begin()
+        chain.record(x, w, bias, q_out, k_pages, v_pages, table, slots, scale.ss if scale is not None else None)
     check(_lib.load().mm_gemv_bf16_qkv_rope(
         w.data_ptr(), x.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, q_out.data_ptr(),
         _ptr(k_pages), _ptr(v_pages), table.data_ptr(), _ptr(slots) if k_pages is not None else None, page_size,

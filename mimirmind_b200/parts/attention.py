@@ -132,7 +132,9 @@ class GQAAttention(Mixer):
                     ctx.derived[skey] = ops.slot_mapping(ctx.positions, ctx.token_req, cache.block_table, cache.page_size)
                 slots = ctx.derived[skey]
             ops.gemv_bf16_qkv_rope(xin, self.w_qkv, self.b_qkv, q, k_pages, v_pages, ctx.derived[key], slots,
-                                   cache.page_size, H, G, hd, scale=scale)
+                                   cache.page_size, H, G, hd, scale=scale, chain=ctx.chain)
+            if ctx.chain is not None:
+                ctx.chain.flush()            # attention is not one of the chain's products: q, k and v must be there
         else:
             qkv = linear(x, self.w_qkv, None, self.rt)
             if fused is not None:
@@ -148,5 +150,5 @@ class GQAAttention(Mixer):
         attn_kernels.paged_attention(q, cache, out, ctx, H, G, hd, self.window, self.scale)
         if sink is None:
             return linear(out, self.w_o, None, self.rt)
-        made = ops.gemv_bf16_residual(out, self.w_o, sink.residual, sink.norm_weight, sink.eps)
+        made = ops.gemv_bf16_residual(out, self.w_o, sink.residual, sink.norm_weight, sink.eps, chain=ctx.chain)
         return FactoredRows(*made) if made is not None else None

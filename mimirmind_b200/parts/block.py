@@ -27,6 +27,8 @@ class PreNormBlock(Block):
     def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: LayerCache,
                 successor: Optional[Block] = None):
         n = residual.shape[0]
+        if ctx.chain is not None and not isinstance(pending, FactoredRows):
+            ctx.chain.flush()                # the first norm is a kernel of its own
         mixer_fuses, ffn_fuses = self.mixer.fuses(n), self.feed_forward.fuses(n)
         h = pending if isinstance(pending, FactoredRows) else self.mixer_norm.forward(residual, pending)
         between = self.ffn_norm.factors() if (mixer_fuses and ffn_fuses) else None

@@ -596,6 +596,57 @@ def test_gemv_qkv_rope_epilogue_and_interleaved_rope_kernel(H, G, hd, ps, K, M, 
             assert torch.equal(a_, b_)
 
 
+def test_gemv_chain_equals_separate_launches():
+    """Four dependent products (output projection into the residual, gated feed-forward, down projection into the
+    residual, q/k/v projection with rotation and cache write) as one persistent cooperative launch: bit-equal to the
+    same four launched one by one, twice in a row (the barrier counters are left at zero)."""
+    rng = np.random.RandomState(5)
+    M, d, F, H, G, hd, ps = 5, 512, 1024, 4, 2, 64, 16
+    width = (H + 2 * G) * hd
+    attn = t(rng.randn(M, H * hd), torch.bfloat16)
+    w_o, w_gu = t(rng.randn(d, H * hd) * 0.05, torch.bfloat16), t(rng.randn(2 * F, d) * 0.05, torch.bfloat16)
+    w_down, w_qkv = t(rng.randn(d, F) * 0.05, torch.bfloat16), t(rng.randn(width, d) * 0.05, torch.bfloat16)
+    nw1, nw2, bias = t(1 + 0.1 * rng.randn(d), torch.bfloat16), t(1 + 0.1 * rng.randn(d), torch.bfloat16), t(rng.randn(width), torch.bfloat16)
+    res0 = t(rng.randn(M, d))
+    pos = t(np.arange(M) * 7, torch.int32)
+    req = t(np.arange(M), torch.int32)
+    table = t(np.arange(M * 4).reshape(M, 4), torch.int32)
+    angles, slots = ops().rope_table(pos, hd, 1e4), ops().slot_mapping(pos, req, table, ps)
+
+    def run(chain):
+        residual = res0.clone()
+        kp = torch.zeros((M * 4, G, ps, hd), dtype=torch.bfloat16, device=DEV)
+        vp = torch.zeros_like(kp)
+        q = torch.zeros((M, H * hd), dtype=torch.bfloat16, device=DEV)
+        xw1, s1 = ops().gemv_bf16_residual(attn, w_o, residual, nw1, 1e-6, chain=chain)
+        act = ops().gemv_bf16(xw1, w_gu, None, torch.bfloat16, swiglu=True, scale=s1, chain=chain)
+        xw2, s2 = ops().gemv_bf16_residual(act, w_down, residual, nw2, 1e-6, chain=chain)
+        ops().gemv_bf16_qkv_rope(xw2, w_qkv, bias, q, kp, vp, angles, slots, ps, H, G, hd, scale=s2, chain=chain)
+        if chain is not None:
+            assert len(chain) == 4
+            chain.flush()
+            assert len(chain) == 0
+        return residual, xw1, act, xw2, q, kp, vp
+
+    ref = run(None)
+    for _ in range(2):
+        got = run(ops().GemvChain())
+        ops().check_tcgen05_errors(torch.device(DEV))
+        for a_, b_ in zip(ref, got):
+            assert torch.equal(a_, b_)
+    # a fifth product flushes the first four by itself; discard forgets what was recorded
+    chain = ops().GemvChain()
+    for _ in range(5):
+        out = ops().gemv_bf16(attn, w_o, None, torch.float32, chain=chain)
+    assert len(chain) == 1
+    chain.discard()
+    assert len(chain) == 0
+    # the thread's launches are direct again
+    direct = ops().gemv_bf16(attn, w_o, None, torch.float32).cpu().numpy()
+    ref_o = attn.double().cpu().numpy() @ w_o.double().cpu().numpy().T
+    assert np.abs(direct - ref_o).max() <= 3e-6 * np.sqrt(H * hd) * np.abs(ref_o).max() + 1e-5
+
+
 # ---- tcgen05 / TMA / TMEM matrix product -------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 8, 64), (200, 520, 192), (300, 264, 1000), (1100, 1048, 328)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
