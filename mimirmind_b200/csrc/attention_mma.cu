@@ -121,7 +121,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_prefill_kernel(
 
     // the host lists a request's tiles in ascending position; later tiles see more keys, so walk the list backwards:
     // the longest tiles start first and the short ones fill the tail
-    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;
+    // heads fastest, later (longer) tiles first: the longest tiles of every head start in the first wave
+    const int tile = gridDim.y - 1 - blockIdx.y, h = blockIdx.x;
     const int g = (h * G) / H;
     const int req = tiles[tile * 4 + 0], row0 = tiles[tile * 4 + 1], n_rows = tiles[tile * 4 + 2], pos0 = tiles[tile * 4 + 3];
     const int32_t* table = block_table + (size_t)req * table_width;
@@ -509,7 +510,7 @@ static int launch_prefill(const void* q, const void* k, const void* v, void* out
         cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         configured = true;
     }
-    dim3 grid(n_tiles, H);
+    dim3 grid(H, n_tiles);
     attention_prefill_kernel<HD><<<grid, ATT_THREADS, smem, s>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)out,
         (const int32_t*)tiles, (const int32_t*)table, table_width, page_size, H, G, window, scale * LOG2E);
@@ -521,6 +522,7 @@ MM_EXPORT int mm_attention_prefill_bf16(const void* q, const void* k_pages, cons
                                         const void* tiles, int n_tiles, const void* block_table, int table_width,
                                         int page_size, int H, int G, int hd, int window, float scale, void* stream) {
     MM_REQUIRE(n_tiles >= 0 && H > 0 && G > 0 && H % G == 0, "attention_prefill: bad head counts");
+    MM_REQUIRE(n_tiles <= 65535, "attention_prefill: more than 65535 tiles in one launch");
     MM_REQUIRE(page_size > 0 && table_width > 0 && window >= 0, "attention_prefill: bad page geometry or window");
     if (n_tiles == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;

@@ -106,7 +106,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &ctl->abort_flag;
 
-    const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y;   // later (longer) tiles first
+    // heads fastest, later (longer) tiles first: the longest tiles of every head start in the first wave
+    const int tile = gridDim.y - 1 - blockIdx.y, h = blockIdx.x;
     const int g = (h * G) / H;
     const int req = tiles[tile * 4 + 0], row0 = tiles[tile * 4 + 1], n_rows = tiles[tile * 4 + 2], pos0 = tiles[tile * 4 + 3];
     const int32_t* table = block_table + (size_t)req * table_width;
@@ -387,7 +388,8 @@ MM_EXPORT int mm_attention_prefill_tcgen05(const void* q, const void* k_pages, c
         configured = true;
     }
     const float LOG2E = 1.4426950408889634f;
-    dim3 grid(n_tiles, H);
+    MM_REQUIRE(n_tiles <= 65535, "attention_prefill_tcgen05: more than 65535 tiles in one launch");
+    dim3 grid(H, n_tiles);
     attention_prefill_tc_kernel<<<grid, ATT_TC_THREADS, smem, (cudaStream_t)stream>>>(
         tq, tk, tv, (__nv_bfloat16*)out, (const int32_t*)tiles, (const int32_t*)block_table, table_width, page_size, H, G,
         window, scale * LOG2E, (int*)err);

@@ -114,6 +114,7 @@ def make_plan(ctx, num_heads: int, num_kv_heads: int, head_dim: int) -> Attentio
                 tiles.append((r, s + off, min(tile_rows, n - off), kv - n + off))
         else:
             items.extend(range(s, s + n))
+    tiles.sort(key=lambda tile: tile[3] + tile[2])   # by keys seen, ascending: the kernels start from the far end
     d_tiles = torch.tensor(tiles, dtype=torch.int32, device=device) if tiles else None
     if len(items) == ctx.n_tokens:
         d_items = None
