@@ -35,6 +35,9 @@ _PROTOTYPES = {
     "mm_gemv_bf16": [P, P, P, I, P, I, I, I, I, I, I, I, I, I, P, I, I, F, P],
     "mm_gemv_bf16_residual": [P, P, P, P, I, P, P, I, I, I, I, I, I, P, I, I, F, P],
     "mm_gemv_bf16_qkv_rope": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, I, F, P],
+    "mm_gemm_skinny": [P, P, P, I, P, I, I, I, I, I, I, I, I, P, I, I, I, F, P, P],
+    "mm_gemm_skinny_residual": [P, P, P, P, I, P, P, I, I, I, I, I, I, P, I, I, I, F, P, P],
+    "mm_gemm_skinny_qkv_rope": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P, I, I, I, F, P, P],
     "mm_gemv_chain_begin": [],
     "mm_gemv_chain_length": [],
     "mm_gemv_chain_discard": [],

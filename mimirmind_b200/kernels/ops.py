@@ -191,11 +191,42 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     return out
 
 
-GEMV_MAX_ROWS = 8      # measured on B200: up to 8 rows the streaming kernel beats the library, at 16 it does not
+GEMV_MAX_ROWS = 12     # measured on B200 (7B shapes, whole decode step): fused streaming kernel vs library + separate norm/rotary/activation kernels: 9 rows 3.59 vs 3.66 ms, 12 rows 3.65 vs 3.70, 16 rows 3.77 vs 3.65
+
+
+# Above the streaming kernel's rows and up to here the tcgen05 weight-streaming product (with the fused epilogues) is
+# used.  Measured per layer on B200 (7B shapes, sum of the four products against library products + separate norm,
+# rotary and activation kernels): 16 rows 94.6 vs 106.9 us, 64 rows 100.6 vs 109.8 us, 128 rows 119 vs 114 us.
+SKINNY_MAX_ROWS = 64
 
 
 def gemv_supported(m: int, n: int, k: int) -> bool:
     return 1 <= m <= GEMV_MAX_ROWS and n % 16 == 0 and k % 32 == 0 and k >= 256
+
+
+def skinny_supported(m: int, n: int, k: int) -> bool:
+    return GEMV_MAX_ROWS < m <= SKINNY_MAX_ROWS and n % 16 == 0 and k % 8 == 0 and k >= 64
+
+
+def small_batch_supported(m: int, n: int, k: int) -> bool:
+    """True if the products of a few rows (and their fused epilogues) take these sizes: the register-streaming
+    kernel up to GEMV_MAX_ROWS rows, the tcgen05 one up to SKINNY_MAX_ROWS."""
+    return gemv_supported(m, n, k) or skinny_supported(m, n, k)
+
+
+def _skinny_pad(m: int) -> int:
+    return 16 if m <= 16 else (32 if m <= 32 else (64 if m <= 64 else 128))
+
+
+def _skinny_splits(n: int, k: int) -> int:
+    """K splits (= cluster size) of the tcgen05 product: enough CTAs to fill the GPU when the weight has few
+    128-row tiles, but no more clusters than are resident at once (256 CTAs in clusters of 8 on 148 SMs), at least
+    6 blocks of 64 along K per CTA, and a power of two (other cluster sizes place badly)."""
+    tiles, k_blocks = -(-n // 128), -(-k // 64)
+    s = 1
+    while s < 8 and tiles * s * 2 <= 256 and k_blocks // (s * 2) >= 6:
+        s *= 2
+    return s
 
 
 GEMV_CHAIN_MAX = 4
@@ -271,12 +302,23 @@ def _gemv_layout(n: int, k: int):
 
 
 def _scale_args(scale: Optional["RowScale"], m: int):
+    """(pointer, tiles, dim, eps) for the register-streaming kernel: partial sums [tiles, 16]."""
     if scale is None:
         return None, 0, 0, 0.0
     _need(scale.ss, "row scale", torch.float32)
     if scale.ss.dim() != 2 or scale.ss.shape[1] != 16 or m > 16:
         raise KernelError("row scale: expected [tiles, 16] partial sums")
     return scale.ss.data_ptr(), scale.ss.shape[0], int(scale.dim), float(scale.eps)
+
+
+def _skinny_scale_args(scale: Optional["RowScale"], m: int):
+    """(pointer, tiles, dim, row stride, eps) for the tcgen05 product: partial sums [tiles, stride >= m]."""
+    if scale is None:
+        return None, 0, 0, 0, 0.0
+    _need(scale.ss, "row scale", torch.float32)
+    if scale.ss.dim() != 2 or scale.ss.shape[1] < m:
+        raise KernelError("row scale: expected [tiles, >= rows] partial sums")
+    return scale.ss.data_ptr(), scale.ss.shape[0], int(scale.dim), scale.ss.shape[1], float(scale.eps)
 
 
 def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
@@ -288,11 +330,19 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     _need(w, "gemv w", torch.bfloat16)
     m, k = x.shape
     n = w.shape[0]
-    if w.shape != (n, k) or not gemv_supported(m, n, k):
+    if w.shape != (n, k) or not small_batch_supported(m, n, k):
         raise KernelError(f"gemv: shapes x{tuple(x.shape)} w{tuple(w.shape)} are not supported")
     if bias is not None:
         _need(bias, "gemv bias")
     out = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=x.device)
+    if m > GEMV_MAX_ROWS:
+        if out.shape[1] % 8:
+            raise KernelError("gemv: the tcgen05 product needs output rows of a multiple of 8 columns")
+        check(_lib.load().mm_gemm_skinny(w.data_ptr(), x.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
+                                         out.data_ptr(), dtype_code(out_dtype), m, n, k, k, out.shape[1], _skinny_splits(n, k),
+                                         int(swiglu), *_skinny_scale_args(scale, m), tcgen05_error_flag(x.device).data_ptr(),
+                                         _stream()), "gemm_skinny")
+        return out
     rt, ks = _gemv_layout(n, k)
     if chain is not None:
         chain.begin()
@@ -312,15 +362,23 @@ def gemv_bf16_residual(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor,
     _need(residual, "gemv residual", torch.float32)
     m, k = x.shape
     n = w.shape[0]
-    if w.shape != (n, k) or residual.shape != (m, n) or not gemv_supported(m, n, k):
+    if w.shape != (n, k) or residual.shape != (m, n) or not small_batch_supported(m, n, k):
         raise KernelError(f"gemv residual: shapes x{tuple(x.shape)} w{tuple(w.shape)} residual{tuple(residual.shape)} are not supported")
+    skinny = m > GEMV_MAX_ROWS
     xw = ss = None
     if norm_weight is not None:
         _need(norm_weight, "norm weight")
         if norm_weight.shape != (n,):
             raise KernelError("gemv residual: norm weight has the wrong length")
         xw = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
-        ss = torch.empty((n // 16, 16), dtype=torch.float32, device=x.device)
+        ss = torch.empty((n // 16, _skinny_pad(m) if skinny else 16), dtype=torch.float32, device=x.device)
+    if skinny:
+        check(_lib.load().mm_gemm_skinny_residual(
+            w.data_ptr(), x.data_ptr(), residual.data_ptr(), _ptr(norm_weight),
+            dtype_code(norm_weight.dtype) if norm_weight is not None else F32, _ptr(xw), _ptr(ss), ss.shape[1] if ss is not None else 0,
+            m, n, k, k, _skinny_splits(n, k), *_skinny_scale_args(scale, m), tcgen05_error_flag(x.device).data_ptr(), _stream()),
+            "gemm_skinny_residual")
+        return None if norm_weight is None else (xw, RowScale(ss, n, float(eps)))
     rt, ks = _gemv_layout(n, k)
     if chain is not None:
         chain.begin()
@@ -376,7 +434,7 @@ def gemv_bf16_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Te
     _need(w, "gemv w", torch.bfloat16)
     m, k = x.shape
     n = (num_heads + 2 * num_kv_heads) * head_dim
-    if w.shape != (n, k) or not gemv_supported(m, n, k) or head_dim % 16:
+    if w.shape != (n, k) or not small_batch_supported(m, n, k) or head_dim % 16:
         raise KernelError(f"gemv qkv: shapes x{tuple(x.shape)} w{tuple(w.shape)} are not supported")
     _need(q_out, "q_out", torch.bfloat16)
     if q_out.shape != (m, num_heads * head_dim):
@@ -396,6 +454,13 @@ def gemv_bf16_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Te
         _need(slots, "slots", torch.int32)
         if slots.numel() != m:
             raise KernelError("slots: one per token")
+    if m > GEMV_MAX_ROWS:
+        check(_lib.load().mm_gemm_skinny_qkv_rope(
+            w.data_ptr(), x.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, q_out.data_ptr(),
+            _ptr(k_pages), _ptr(v_pages), table.data_ptr(), _ptr(slots) if k_pages is not None else None, page_size,
+            num_heads, num_kv_heads, head_dim, m, k, k, _skinny_splits(n, k), *_skinny_scale_args(scale, m),
+            tcgen05_error_flag(x.device).data_ptr(), _stream()), "gemm_skinny_qkv_rope")
+        return
     rt, ks = _gemv_layout(n, k)
     if chain is not None:
         chain.begin()

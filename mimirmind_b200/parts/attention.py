@@ -108,8 +108,8 @@ class GQAAttention(Mixer):
 
     def fuses(self, n_tokens: int) -> bool:
         width = (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
-        return (self.interleaved and ops.gemv_supported(n_tokens, width, self.hidden)
-                and ops.gemv_supported(n_tokens, self.hidden, self.num_heads * self.head_dim))
+        return (self.interleaved and ops.small_batch_supported(n_tokens, width, self.hidden)
+                and ops.small_batch_supported(n_tokens, self.hidden, self.num_heads * self.head_dim))
 
     def forward(self, x, ctx: StepContext, cache: LayerCache, sink: Optional[ResidualSink] = None):
         n = x.shape[0]

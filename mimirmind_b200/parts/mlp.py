@@ -55,8 +55,8 @@ class SwiGLU(FeedForward):
             and self.w_down.dtype == torch.bfloat16 and self.rt.matmul != "simt"
 
     def fuses(self, n_tokens: int) -> bool:
-        return (self._tensor_cores() and ops.gemv_supported(n_tokens, 2 * self.intermediate, self.hidden)
-                and ops.gemv_supported(n_tokens, self.hidden, self.intermediate))
+        return (self._tensor_cores() and ops.small_batch_supported(n_tokens, 2 * self.intermediate, self.hidden)
+                and ops.small_batch_supported(n_tokens, self.hidden, self.intermediate))
 
     def forward(self, x, ctx: StepContext, sink: Optional[ResidualSink] = None):
         m = x.shape[0]

@@ -447,7 +447,12 @@ def test_gemv_swiglu_epilogue_and_interleaved_silu(M, F, K):
 
 def test_gemv_refuses_unsupported_shapes():
     from mimirmind_b200.kernels.lib import KernelError
-    assert not ops().gemv_supported(9, 64, 256) and not ops().gemv_supported(4, 60, 256) and not ops().gemv_supported(4, 64, 100)
+    big = ops().GEMV_MAX_ROWS + 1
+    assert not ops().gemv_supported(big, 64, 256) and not ops().gemv_supported(4, 60, 256) and not ops().gemv_supported(4, 64, 100)
+    assert ops().skinny_supported(big, 64, 256) and not ops().skinny_supported(ops().SKINNY_MAX_ROWS + 1, 64, 256) and not ops().skinny_supported(big, 60, 256)
+    assert not ops().skinny_supported(big, 64, 100) and not ops().small_batch_supported(200, 64, 256)
+    with pytest.raises(KernelError):
+        ops().gemv_bf16(torch.zeros((ops().SKINNY_MAX_ROWS + 1, 256), dtype=torch.bfloat16, device=DEV), torch.zeros((64, 256), dtype=torch.bfloat16, device=DEV), None, torch.float32)
     with pytest.raises(KernelError):
         ops().gemv_bf16(torch.zeros((4, 100), dtype=torch.bfloat16, device=DEV), torch.zeros((64, 100), dtype=torch.bfloat16, device=DEV), None, torch.float32)
 
@@ -472,13 +477,14 @@ def test_gemv_all_layouts_of_the_kernel(M, rt, ks):
 # ---- weight-streaming product with the decode-layer epilogues ----------------------------------------
 def _row_scale(rng, M, tiles, dim, eps):
     """Partial sums of squares as a producer would leave them, and the 1/rms they stand for."""
-    ss = np.abs(rng.randn(tiles, 16)).astype(np.float32) * dim / tiles
+    width = 16 if M <= ops().GEMV_MAX_ROWS else max(M, 16)     # the tcgen05 product takes any row stride >= M
+    ss = np.abs(rng.randn(tiles, width)).astype(np.float32) * dim / tiles
     ss[:, M:] = np.nan                                  # rows that do not exist are never read into a result
     rstd = 1.0 / np.sqrt(ss[:, :M].astype(np.float64).sum(0) / dim + eps)
     return ops().RowScale(t(ss), dim, eps), rstd
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 48, 256), (5, 272, 1504), (8, 1040, 352)])
+@pytest.mark.parametrize("M,N,K", [(1, 48, 256), (5, 272, 1504), (8, 1040, 352), (13, 272, 1504), (16, 48, 256), (40, 1040, 352), (64, 4608, 3584), (50, 272, 200), (64, 400, 1504)])
 def test_gemv_input_row_scale(M, N, K):
     rng = np.random.RandomState(M + N)
     x, w, b = t(rng.randn(M, K), torch.bfloat16), t(rng.randn(N, K) * 0.05, torch.bfloat16), t(rng.randn(N), torch.float32)
@@ -498,7 +504,9 @@ def test_gemv_input_row_scale(M, N, K):
         assert np.abs(got2 - ref2).max() <= 1e-5 * np.sqrt(K) * np.abs(ref2).max() + 1e-5
 
 
-@pytest.mark.parametrize("M,N,K,wdt", [(1, 256, 256, torch.float32), (6, 288, 1504, torch.bfloat16), (8, 1056, 352, torch.bfloat16)])
+@pytest.mark.parametrize("M,N,K,wdt", [(1, 256, 256, torch.float32), (6, 288, 1504, torch.bfloat16), (8, 1056, 352, torch.bfloat16),
+                                       (13, 256, 256, torch.float32), (33, 288, 1504, torch.bfloat16), (64, 3584, 18944, torch.bfloat16),
+                                       (57, 1056, 352, torch.bfloat16)])
 def test_gemv_residual_epilogue(M, N, K, wdt):
     """residual += x W^T in fp32; rows of residual * norm weight; partial sums whose total is the row's sum of squares."""
     rng = np.random.RandomState(N)
@@ -513,7 +521,7 @@ def test_gemv_residual_epilogue(M, N, K, wdt):
         got = residual.cpu().numpy()
         assert np.abs(got - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
         xw, rs = made
-        assert rs.dim == N and rs.eps == 1e-5 and rs.ss.shape == (N // 16, 16)
+        assert rs.dim == N and rs.eps == 1e-5 and rs.ss.shape[0] == N // 16 and rs.ss.shape[1] >= min(M, 16)
         ref_xw = bf16_round(got.astype(np.float64) * nw.double().cpu().numpy())
         assert np.abs(xw.float().cpu().numpy() - ref_xw).max() <= 2 ** -8 * np.abs(ref_xw).max()
         ss = rs.ss.cpu().numpy()[:, :M].astype(np.float64).sum(0)
@@ -531,14 +539,15 @@ def test_gemv_residual_epilogue(M, N, K, wdt):
     assert np.abs(residual.cpu().numpy() - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
 
 
-@pytest.mark.parametrize("H,G,hd,ps,K,M", [(4, 2, 16, 16, 256, 3), (6, 3, 48, 8, 288, 8), (7, 1, 128, 16, 352, 5), (2, 2, 80, 32, 320, 1)])
+@pytest.mark.parametrize("H,G,hd,ps,K,M", [(4, 2, 16, 16, 256, 3), (6, 3, 48, 8, 288, 8), (7, 1, 128, 16, 352, 5), (2, 2, 80, 32, 320, 1),
+                                           (4, 2, 16, 16, 256, 14), (6, 3, 48, 8, 288, 40), (28, 4, 128, 16, 3584, 64), (2, 2, 80, 32, 320, 50)])
 @pytest.mark.parametrize("with_scale", [False, True])
 def test_gemv_qkv_rope_epilogue_and_interleaved_rope_kernel(H, G, hd, ps, K, M, with_scale):
     """The fused decode projection (interleaved weight rows, bias, rotation, cache write) against the formulas, and
     the stand-alone rotary kernel reading the same interleaved columns."""
     rng = np.random.RandomState(H * hd + M)
     theta = 1e4
-    lens_before = [0, 37, 130, 5, 64, 15, 16, 900][:M]
+    lens_before = [[0, 37, 130, 5, 64, 15, 16, 900][i % 8] + (i // 8) * 3 for i in range(M)]
     table, pages = paged_layout(rng, [a + 1 for a in lens_before], ps)
     pos = np.asarray(lens_before, dtype=np.int32)
     req = np.arange(M, dtype=np.int32)
