@@ -86,6 +86,48 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": reasons, "samples": len(rows)}
 
 
+def run_workload(name: str, layers: int) -> int:
+    """One of the larger workloads, end to end through the scheduler (prefill portions, mixed steps, captured decode)."""
+    import time
+
+    import numpy as np
+    import torch
+    from mimirmind_b200.engine.engine import Engine
+    from mimirmind_b200.engine.loader import random_model
+    from mimirmind_b200.kernels import ops
+    from mimirmind_b200.registry import get_architecture
+    cfg = dict(MODEL_7B, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8)
+    rng = np.random.RandomState(0)
+    if name == "14b-serving":
+        cfg.update(num_hidden_layers=48, intermediate_size=13824, rms_norm_eps=1e-5, max_position_embeddings=4096)
+        lens, new, ctx = rng.randint(128, 2049, size=64).tolist(), 256, 4096
+    else:
+        cfg.update(num_hidden_layers=64, intermediate_size=27648, rms_norm_eps=1e-6, max_position_embeddings=16384)
+        lens, new, ctx = [8192] * 8, 128, 16384
+    full_layers = cfg["num_hidden_layers"]
+    if layers:
+        cfg["num_hidden_layers"] = layers
+    arch = get_architecture(cfg["architectures"][0])
+    mcfg = arch.parse_config(cfg, "bench")
+    model = random_model(arch.build_spec(mcfg), seed=0, dtype="bfloat16")
+    engine = Engine(model, page_size=PAGE_SIZE, cache_tokens=sum(lens) + len(lens) * (new + 64), max_context=ctx,
+                    token_budget=2048, max_active=64)
+    prompts = [rng.randint(0, mcfg.vocab_size, size=n).tolist() for n in lens]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    res = engine.generate(prompts, max_new_tokens=new, use_eos=False)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    ops.check_tcgen05_errors(torch.device("cuda"))
+    gen = sum(r.stats.generated_tokens for r in res)
+    print(json.dumps({"workload": name, "layers": mcfg.num_hidden_layers, "layers_of_config": full_layers, "requests": len(lens),
+                      "prompt_tokens": sum(lens), "generated_tokens": gen, "seconds": dt, "tokens_per_s": (sum(lens) + gen) / dt,
+                      "generated_per_s": gen / dt, "graph_steps": engine.graph_steps,
+                      "finish": sorted({r.stats.finish_reason for r in res}),
+                      "device_gib": torch.cuda.max_memory_allocated() / 2 ** 30}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -97,6 +139,10 @@ def main() -> int:
     ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
                     help="run one phase only and print its timing (for profiling small cases)")
     ap.add_argument("--batch", type=int, default=BATCH, help="decode batch size of --only decode")
+    ap.add_argument("--workload", default="", choices=["", "14b-serving", "32b-long"],
+                    help="instead of the default run: another workload of the baseline's list through Engine.generate "
+                         "(14B-shaped, 64 requests of 128..2048 prompt tokens, 256 new tokens each, continuous batching; "
+                         "32B-shaped, 8 requests of 8,192 prompt tokens, 128 new tokens each)")
     ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch for the decode kernels (measured slower; for comparison)")
     args = ap.parse_args()
 
@@ -110,6 +156,8 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if args.workload:
+        return run_workload(args.workload, args.layers)
 
     import torch
     from mimirmind_b200.engine.decode_graph import DecodeSession
