@@ -16,14 +16,18 @@ count only after ``commit``, src/runtime/KvCache.hpp:90-103):
                                  that no later query can reach
   ``release(request)``           everything goes back (src/runtime/serving/PagedKvSequence.cpp:76-87)
 
-Pure host logic: no tensors here.  Block tables index by absolute position
+Pure host logic, in C++ (``csrc/host/runtime.cpp``); this module is its Python face and maps the caller's request
+ids (any hashable) to the integers the library uses.  Block tables index by absolute position
 (``table[pos // page_size]``); an entry of -1 is a page never needed or already given back.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+import itertools
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+from . import host
 from .pages import INVALID_PAGE, PageAllocator
 
 
@@ -42,82 +46,94 @@ class GroupSpec:
     window: int = 0
 
 
-@dataclass
-class _Request:
-    length: int = 0                       # committed tokens
-    reserved: int = 0                     # tokens with pages
-    slot: int = -1
-    tables: Dict[str, List[int]] = field(default_factory=dict)
-    started: bool = False                 # state slot already zeroed by the runner
-
-
 class CacheManager:
     def __init__(self, groups: Sequence[GroupSpec], page_size: int, pages_per_group, max_requests: int):
         if page_size <= 0:
             raise ValueError("page_size must be positive")
+        self._lib = host.load()
         self.page_size = page_size
         self.groups: Dict[str, GroupSpec] = {g.name: g for g in groups}
+        self._index: Dict[str, int] = {g.name: i for i, g in enumerate(groups)}
         if isinstance(pages_per_group, int):
             pages_per_group = {g.name: pages_per_group for g in groups}
-        self.allocators: Dict[str, PageAllocator] = {g.name: PageAllocator(pages_per_group[g.name]) for g in groups}
+        pages = [int(pages_per_group[g.name]) for g in groups]
+        if any(n < 0 for n in pages) or max_requests < 0:
+            raise ValueError("page and request counts must be >= 0")
+        self._h = self._lib.mmh_cache_create(len(pages), host.int_array(pages), host.int_array([int(g.window) for g in groups]),
+                                             page_size, max_requests)
+        if not self._h:
+            raise CacheError("the cache manager could not be created")
         self.max_requests = max_requests
-        self._slots = PageAllocator(max_requests)
-        self._requests: Dict[Hashable, _Request] = {}
+        self.allocators: Dict[str, PageAllocator] = {
+            g.name: PageAllocator(0, _borrowed=self._lib.mmh_cache_allocator(self._h, i), _owner=self) for i, g in enumerate(groups)}
+        self._slots = PageAllocator(0, _borrowed=self._lib.mmh_cache_allocator(self._h, -1), _owner=self)
+        self._ids: Dict[Hashable, int] = {}          # the caller's request id -> the library's
+        self._next_id = itertools.count(1)
+        self._need = (ctypes.c_int * max(1, len(pages)))()
 
-    # ---- requests ----------------------------------------------------------
-    def has(self, rid: Hashable) -> bool:
-        return rid in self._requests
+    def __del__(self):
+        if getattr(self, "_h", None):
+            # handles on the allocators only borrow; nothing else outlives this object
+            self._lib.mmh_cache_destroy(self._h)
+            self._h = None
 
-    def add_request(self, rid: Hashable) -> Optional[int]:
-        """Registers a request and gives it a state slot; None when every slot is taken."""
-        if rid in self._requests:
-            raise CacheError(f"request {rid!r} already exists")
-        slot = self._slots.alloc()
-        if slot == INVALID_PAGE:
-            return None
-        self._requests[rid] = _Request(slot=slot, tables={name: [] for name in self.groups})
-        return slot
-
-    def _req(self, rid: Hashable) -> _Request:
+    # ---- request ids --------------------------------------------------------
+    def handle(self, rid: Hashable) -> int:
+        """The library's id of a live request."""
         try:
-            return self._requests[rid]
+            return self._ids[rid]
         except KeyError:
             raise CacheError(f"unknown request {rid!r}") from None
 
+    def _call(self, rc: int, rid: Hashable) -> int:
+        if rc == -2:
+            raise CacheError(f"request {rid!r}: {host.last_error()}")
+        return rc
+
+    # ---- requests ----------------------------------------------------------
+    def has(self, rid: Hashable) -> bool:
+        return rid in self._ids
+
+    def add_request(self, rid: Hashable) -> Optional[int]:
+        """Registers a request and gives it a state slot; None when every slot is taken."""
+        if rid in self._ids:
+            raise CacheError(f"request {rid!r} already exists")
+        h = next(self._next_id)
+        slot = self._call(self._lib.mmh_cache_add(self._h, h), rid)
+        if slot < 0:
+            return None
+        self._ids[rid] = h
+        return slot
+
+    def adopt(self, rid: Hashable, handle: int) -> None:
+        """Records a request that the scheduler's C++ side registered under ``handle``."""
+        self._ids[rid] = handle
+
+    def forget(self, rid: Hashable) -> None:
+        """Drops the id of a request that the scheduler's C++ side released."""
+        self._ids.pop(rid, None)
+
+    def new_handle(self) -> int:
+        return next(self._next_id)
+
     def length(self, rid: Hashable) -> int:
-        return self._req(rid).length
+        return self._call(self._lib.mmh_cache_request(self._h, self.handle(rid), 0), rid)
 
     def slot(self, rid: Hashable) -> int:
-        return self._req(rid).slot
+        return self._call(self._lib.mmh_cache_request(self._h, self.handle(rid), 1), rid)
 
     def mark_started(self, rid: Hashable) -> bool:
         """True the first time it is called for a request (its state slot must be zeroed then)."""
-        r = self._req(rid)
-        first = not r.started
-        r.started = True
-        return first
+        return bool(self._call(self._lib.mmh_cache_request(self._h, self.handle(rid), 3), rid))
 
     def live_requests(self) -> List[Hashable]:
-        return list(self._requests)
+        return list(self._ids)
 
     # ---- pages ---------------------------------------------------------------
-    def _blocks_for(self, length: int) -> int:
-        return (length + self.page_size - 1) // self.page_size
-
     def pages_needed(self, rid: Hashable, new_len: int) -> Dict[str, int]:
         """New pages each group must find to hold positions up to new_len."""
-        r = self._req(rid)
-        need = {}
-        for name in self.groups:
-            table = r.tables[name]
-            first = r.length // self.page_size
-            last = self._blocks_for(new_len)
-            n = 0
-            for b in range(first, last):
-                if b >= len(table) or table[b] == INVALID_PAGE:
-                    n += 1
-            need[name] = n
-        return need
+        self._call(self._lib.mmh_cache_pages_needed(self._h, self.handle(rid), int(new_len), self._need), rid)
+        return {name: int(self._need[i]) for name, i in self._index.items()}
 
     def can_reserve(self, rid: Hashable, new_len: int) -> bool:
         need = self.pages_needed(rid, new_len)
@@ -126,55 +142,29 @@ class CacheManager:
     def reserve(self, rid: Hashable, new_len: int) -> bool:
         """Pages for positions [length, new_len) in every group; False (and no change) if any group
         cannot supply them."""
-        r = self._req(rid)
-        if new_len < r.length:
-            raise CacheError(f"request {rid!r}: cannot reserve {new_len} below its length {r.length}")
-        if not self.can_reserve(rid, new_len):
-            return False
-        first = r.length // self.page_size
-        last = self._blocks_for(new_len)
-        for name in self.groups:
-            table = r.tables[name]
-            while len(table) < last:
-                table.append(INVALID_PAGE)
-            for b in range(first, last):
-                if table[b] == INVALID_PAGE:
-                    p = self.allocators[name].alloc()
-                    assert p != INVALID_PAGE
-                    table[b] = p
-        r.reserved = max(r.reserved, new_len)
-        return True
+        return bool(self._call(self._lib.mmh_cache_reserve(self._h, self.handle(rid), int(new_len)), rid))
 
     def commit(self, rid: Hashable, new_len: int) -> None:
-        r = self._req(rid)
-        if new_len < r.length or new_len > r.reserved:
-            raise CacheError(f"request {rid!r}: commit to {new_len} outside [{r.length}, {r.reserved}]")
-        r.length = new_len
-        # the next query sits at position new_len and sees keys >= new_len + 1 - W
-        for name, g in self.groups.items():
-            if g.window <= 0:
-                continue
-            dead_before = new_len + 1 - g.window       # positions below this are never read again
-            if dead_before <= 0:
-                continue
-            table = r.tables[name]
-            for b in range(min(dead_before // self.page_size, len(table))):
-                if table[b] != INVALID_PAGE:
-                    self.allocators[name].free(table[b])
-                    table[b] = INVALID_PAGE
+        self._call(self._lib.mmh_cache_commit(self._h, self.handle(rid), int(new_len)), rid)
 
     def release(self, rid: Hashable) -> None:
-        r = self._requests.pop(rid, None)
-        if r is None:
-            raise CacheError(f"unknown request {rid!r}")
-        for name, table in r.tables.items():
-            for p in table:
-                if p != INVALID_PAGE:
-                    self.allocators[name].free(p)
-        self._slots.free(r.slot)
+        h = self.handle(rid)
+        del self._ids[rid]
+        self._call(self._lib.mmh_cache_release(self._h, h), rid)
 
     def table(self, rid: Hashable, group: str) -> List[int]:
-        return self._req(rid).tables[group]
+        h, g = self.handle(rid), self._index[group]
+        n = self._call(self._lib.mmh_cache_table(self._h, h, g, None, 0), rid)
+        buf = (ctypes.c_int * max(1, n))()
+        self._call(self._lib.mmh_cache_table(self._h, h, g, buf, n), rid)
+        return list(buf[:n])
+
+    def fill_tables(self, group: str, rids: Sequence[Hashable], width: int, out_ptr: int) -> None:
+        """Writes the block tables of ``rids`` as int32 rows of ``width`` entries (-1 beyond a table's end) at
+        ``out_ptr``: one call for a whole batch."""
+        ids = host.long_array([self.handle(r) for r in rids])
+        if self._lib.mmh_cache_tables(self._h, self._index[group], len(rids), ids, int(width), ctypes.c_void_p(out_ptr)) != 0:
+            raise CacheError(host.last_error())
 
     # ---- accounting --------------------------------------------------------------
     def free_pages(self, group: Optional[str] = None) -> int:
@@ -192,21 +182,9 @@ class CacheManager:
 
     def check(self) -> None:
         """Invariants: every allocated page is in exactly one table; allocators are consistent."""
-        for name, alloc in self.allocators.items():
-            alloc.check()
-            seen = set()
-            for rid, r in self._requests.items():
-                for p in r.tables[name]:
-                    if p == INVALID_PAGE:
-                        continue
-                    if p in seen:
-                        raise CacheError(f"group {name}: page {p} is in two block tables")
-                    if not alloc.is_allocated(p):
-                        raise CacheError(f"group {name}: page {p} of request {rid!r} is not allocated")
-                    seen.add(p)
-            if len(seen) != alloc.num_used:
-                raise CacheError(f"group {name}: {alloc.num_used} pages are out but tables hold {len(seen)}")
-        self._slots.check()
-        slots = [r.slot for r in self._requests.values()]
-        if len(set(slots)) != len(slots) or len(slots) != self._slots.num_used:
-            raise CacheError("state slots are inconsistent")
+        if self._lib.mmh_cache_check(self._h) != 0:
+            raise CacheError(host.last_error())
+        live = (ctypes.c_longlong * max(1, len(self._ids)))()
+        n = self._lib.mmh_cache_live(self._h, live, len(self._ids))
+        if n != len(self._ids) or set(live[:n]) != set(self._ids.values()):
+            raise CacheError("the request ids of the Python face and of the library differ")

@@ -1,4 +1,4 @@
-"""Page allocator: fixed-size pages handed out from a LIFO free list.
+"""Page allocator: fixed-size pages handed out from a LIFO free list (C++: ``csrc/host/runtime.cpp``).
 
 After the reference's block allocator (src/runtime/serving/PagedKvBlockAllocator.cpp:11-60):
 ids are first handed out in ascending order, a freed id is the next one reused, exhaustion
@@ -10,6 +10,8 @@ from __future__ import annotations
 
 from typing import List, Optional
 
+from . import host
+
 INVALID_PAGE = -1
 
 
@@ -18,61 +20,60 @@ class PageAllocatorError(RuntimeError):
 
 
 class PageAllocator:
-    def __init__(self, num_pages: int):
+    """Thin handle on the C++ allocator.  ``_borrowed``: the object belongs to a cache manager."""
+
+    def __init__(self, num_pages: int, _borrowed=None, _owner=None):
+        self._lib = host.load()
+        if _borrowed is not None:
+            self._h, self._owned, self._owner = _borrowed, False, _owner    # keeps the owner alive
+            return
         if num_pages < 0:
             raise ValueError("num_pages must be >= 0")
-        self.num_pages = num_pages
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))  # pop() gives 0, 1, 2, ...
-        self._out = [False] * num_pages
-        self.total_allocs = 0
-        self.reuses = 0                      # allocations that handed out a page used before
-        self._ever_used = [False] * num_pages
+        self._h, self._owned, self._owner = self._lib.mmh_alloc_create(num_pages), True, None
+
+    def __del__(self):
+        if getattr(self, "_owned", False) and self._h:
+            self._lib.mmh_alloc_destroy(self._h)
+            self._h = None
+
+    @property
+    def num_pages(self) -> int:
+        return int(self._lib.mmh_alloc_stat(self._h, 0))
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return int(self._lib.mmh_alloc_stat(self._h, 1))
 
     @property
     def num_used(self) -> int:
-        return self.num_pages - len(self._free)
+        return int(self._lib.mmh_alloc_stat(self._h, 2))
+
+    @property
+    def total_allocs(self) -> int:
+        return int(self._lib.mmh_alloc_stat(self._h, 3))
+
+    @property
+    def reuses(self) -> int:
+        """Allocations that handed out a page used before."""
+        return int(self._lib.mmh_alloc_stat(self._h, 4))
 
     def alloc(self) -> int:
-        if not self._free:
-            return INVALID_PAGE
-        p = self._free.pop()
-        self._out[p] = True
-        self.total_allocs += 1
-        if self._ever_used[p]:
-            self.reuses += 1
-        self._ever_used[p] = True
-        return p
+        return self._lib.mmh_alloc_alloc(self._h)
 
     def alloc_many(self, n: int) -> Optional[List[int]]:
         """n pages or none at all."""
-        if n > len(self._free):
+        if n > self.num_free:
             return None
         return [self.alloc() for _ in range(n)]
 
     def free(self, page: int) -> None:
-        if not (0 <= page < self.num_pages):
-            raise PageAllocatorError(f"page {page} is outside the pool of {self.num_pages}")
-        if not self._out[page]:
-            raise PageAllocatorError(f"page {page} freed twice or never allocated")
-        self._out[page] = False
-        self._free.append(page)
+        if self._lib.mmh_alloc_free(self._h, int(page)) != 0:
+            raise PageAllocatorError(host.last_error())
 
     def is_allocated(self, page: int) -> bool:
-        return 0 <= page < self.num_pages and self._out[page]
+        return bool(self._lib.mmh_alloc_is_allocated(self._h, int(page)))
 
     def check(self) -> None:
         """Every page is either free exactly once or out: none lost, none held twice."""
-        seen = [0] * self.num_pages
-        for p in self._free:
-            seen[p] += 1
-        for p in range(self.num_pages):
-            if seen[p] > 1:
-                raise PageAllocatorError(f"page {p} is on the free list {seen[p]} times")
-            if seen[p] == 1 and self._out[p]:
-                raise PageAllocatorError(f"page {p} is both free and allocated")
-            if seen[p] == 0 and not self._out[p]:
-                raise PageAllocatorError(f"page {p} is lost: neither free nor allocated")
+        if self._lib.mmh_alloc_check(self._h) != 0:
+            raise PageAllocatorError(host.last_error())

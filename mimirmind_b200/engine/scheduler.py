@@ -19,19 +19,27 @@ Policy, after the reference's serving substrate:
   so its output is the same as without preemption.  A request that is alone and still does
   not fit fails with ``out_of_pages`` (src/runtime/serving/PreemptionPolicy.hpp:32-41).
 
-Pure host logic over the cache manager; no tensors.
+Pure host logic over the cache manager, in C++ (``csrc/host/runtime.cpp``); the classes here are its Python face:
+they hold what the caller reads (token lists, state, reasons) and are brought up to date from the events the
+library reports after every call.
 """
 from __future__ import annotations
 
-import itertools
-from collections import deque
+import ctypes
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+from ..cache import host
 from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+_FINISH = {1: "stop", 2: "length", 3: "context", 4: "out_of_pages", 6: "cancelled"}
+_EV_ADMITTED, _EV_PREEMPTED, _EV_FINISHED = 1, 2, 3
+
+
+class SchedulerError(RuntimeError):
+    pass
 
 
 @dataclass
@@ -41,11 +49,11 @@ class Request:
     max_new: int = 256                      # src/runtime/InferenceEngine.hpp:95-99
     sampling: SamplingParams = field(default_factory=SamplingParams)
     stop_ids: Tuple[int, ...] = ()
-    # --- scheduler state ---
+    # --- scheduler state (kept in step with the library) ---
     state: str = WAITING
     tokens: List[int] = field(default_factory=list)   # prompt ⧺ generated
     generated: List[int] = field(default_factory=list)
-    finish_reason: Optional[str] = None     # "stop", "length", "context", "out_of_pages", "rejected: ..."
+    finish_reason: Optional[str] = None     # "stop", "length", "context", "out_of_pages", "cancelled", "rejected: ..."
     preemptions: int = 0
     admit_seq: int = -1
 
@@ -85,191 +93,162 @@ class PlannedEntry:
         return self.request.tokens[self.start:self.start + self.count]
 
 
-@dataclass
 class Metrics:
-    admitted: int = 0
-    finished: int = 0
-    preempted: int = 0
-    rejected: int = 0
-    steps: int = 0
-    tokens_scheduled: int = 0
+    """Counters of the library's scheduler, read when asked for."""
+
+    _NAMES = ("admitted", "finished", "preempted", "rejected", "steps", "tokens_scheduled")
+
+    def __init__(self, sched: "Scheduler"):
+        self._sched = sched
+
+    def __getattr__(self, name: str) -> int:
+        try:
+            what = Metrics._NAMES.index(name)
+        except ValueError:
+            raise AttributeError(name) from None
+        return int(self._sched._lib.mmh_sched_metric(self._sched._h, what))
 
 
 class Scheduler:
     def __init__(self, cfg: SchedulerConfig, manager: CacheManager):
         self.cfg = cfg
         self.manager = manager
-        self.waiting: Deque[Request] = deque()
-        self.running: List[Request] = []       # in admission order
-        self.finished: List[Request] = []
-        self.metrics = Metrics()
-        self._seq = itertools.count()
+        self._lib = host.load()
+        self._h = self._lib.mmh_sched_create(manager._h, cfg.token_budget, cfg.max_active, cfg.prefill_chunk, cfg.max_seq_len)
+        if not self._h:
+            raise SchedulerError("the scheduler could not be created")
+        self._by_handle: Dict[int, Request] = {}
+        self._handle: Dict[Hashable, int] = {}
+        self.metrics = Metrics(self)
+        cap = 4096
+        self._rids = (ctypes.c_longlong * cap)()
+        self._a = (ctypes.c_int * cap)()
+        self._b = (ctypes.c_int * cap)()
+        self._c = (ctypes.c_int * cap)()
+        self._cap = cap
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.mmh_sched_destroy(self._h)
+            self._h = None
+
+    def _check(self, rc: int) -> int:
+        if rc == -2:
+            raise SchedulerError(host.last_error())
+        return rc
+
+    # ---- keeping the Python face in step ----------------------------------------------------
+    def _apply_events(self) -> List[Request]:
+        """Reads what the last call did to requests; returns those that finished."""
+        n = self._lib.mmh_sched_events(self._h, self._rids, self._a, self._b, self._cap)
+        done: List[Request] = []
+        for i in range(min(n, self._cap)):
+            req = self._by_handle[self._rids[i]]
+            kind, code = self._a[i], self._b[i]
+            if kind == _EV_ADMITTED:
+                req.state, req.admit_seq = RUNNING, code
+                self.manager.adopt(req.id, self._handle[req.id])
+            elif kind == _EV_PREEMPTED:
+                req.state, req.preemptions = WAITING, code
+                self.manager.forget(req.id)
+            elif kind == _EV_FINISHED:
+                req.state, req.finish_reason = FINISHED, _FINISH[code]
+                self.manager.forget(req.id)
+                done.append(req)
+        return done
+
+    def _listed(self, which: int) -> List[Request]:
+        n = self._lib.mmh_sched_list(self._h, which, self._rids, self._cap)
+        if n > self._cap:
+            buf = (ctypes.c_longlong * n)()
+            self._lib.mmh_sched_list(self._h, which, buf, n)
+            return [self._by_handle[h] for h in buf[:n]]
+        return [self._by_handle[self._rids[i]] for i in range(n)]
+
+    @property
+    def waiting(self) -> List[Request]:
+        return self._listed(0)
+
+    @property
+    def running(self) -> List[Request]:
+        """In admission order."""
+        return self._listed(1)
+
+    @property
+    def finished(self) -> List[Request]:
+        return self._listed(2)
 
     # ---- admission ---------------------------------------------------------------
     def add(self, req: Request) -> bool:
         """Queues a request.  Returns False (and finishes it as rejected) when it can never run."""
-        reason = None
-        if not req.prompt:
-            reason = "empty prompt"
-        elif req.max_new < 1:
-            reason = "max_new must be at least 1"
-        elif len(req.prompt) >= self.cfg.max_seq_len:
-            # src/runtime/serving/ContinuousBatcher.cpp:87-123 rejects prompt >= context
-            reason = f"prompt of {len(req.prompt)} tokens does not fit the context of {self.cfg.max_seq_len}"
-        else:
-            ps = self.manager.page_size
-            need = (len(req.prompt) + ps - 1) // ps
-            for name, g in self.manager.groups.items():
-                if g.window <= 0 and need > self.manager.total_pages(name):
-                    reason = f"prompt needs {need} pages, the pool has {self.manager.total_pages(name)}"
-        if reason is not None:
-            req.state, req.finish_reason = FINISHED, "rejected: " + reason
-            self.finished.append(req)
-            self.metrics.rejected += 1
+        if req.id in self._handle:
+            raise SchedulerError(f"request id {req.id!r} already used")
+        h = self.manager.new_handle()
+        prompt = host.int_array([int(t) for t in req.prompt])
+        stops = host.int_array([int(t) for t in req.stop_ids])
+        rc = self._check(self._lib.mmh_sched_add(self._h, h, prompt, len(req.prompt), int(req.max_new), stops, len(req.stop_ids)))
+        self._handle[req.id] = h
+        self._by_handle[h] = req
+        req.tokens = list(req.prompt)
+        if rc == 0:
+            req.state = FINISHED
+            req.finish_reason = "rejected: " + self._lib.mmh_sched_reject_reason(self._h, h).decode()
             return False
         req.state = WAITING
-        self.waiting.append(req)
         return True
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.mmh_sched_has_work(self._h))
 
     # ---- one step's plan -------------------------------------------------------------
-    def _remaining(self, req: Request) -> int:
-        return len(req.tokens) - self.manager.length(req.id)
-
-    def _portion(self, req: Request, budget: int) -> int:
-        n = min(self._remaining(req), budget)
-        if self.cfg.prefill_chunk > 0 and n > 1:
-            n = min(n, self.cfg.prefill_chunk)
-        return n
-
-    def _preempt(self, victim: Request) -> None:
-        self.manager.release(victim.id)
-        self.running.remove(victim)
-        victim.state = WAITING
-        victim.preemptions += 1
-        self.waiting.appendleft(victim)
-        self.metrics.preempted += 1
-
     def schedule(self) -> List[PlannedEntry]:
         """Chooses what the next step runs and reserves its pages.  May preempt or fail requests."""
-        mgr = self.manager
-        preempted_now = False
-        while True:
-            budget = self.cfg.token_budget
-            plan: List[PlannedEntry] = []
-            failed: Optional[Request] = None
-            # decodes first, then prompt portions, both in admission order
-            decodes = [r for r in self.running if self._remaining(r) == 1]
-            prefills = [r for r in self.running if self._remaining(r) > 1]
-            for req in decodes + prefills:
-                if budget <= 0:
-                    break
-                n = self._portion(req, budget)
-                start = mgr.length(req.id)
-                if not mgr.reserve(req.id, start + n):
-                    failed = req
-                    break
-                plan.append(PlannedEntry(req, start, n, start + n == len(req.tokens)))
-                budget -= n
-            if failed is not None:
-                # pages ran out: undo nothing (reserved pages stay with their requests), preempt the
-                # most recently admitted request and plan again
-                victim = self.running[-1]
-                if len(self.running) == 1:
-                    self.manager.release(victim.id)
-                    self.running.remove(victim)
-                    victim.state, victim.finish_reason = FINISHED, "out_of_pages"
-                    self.finished.append(victim)
-                    self.metrics.finished += 1
-                else:
-                    self._preempt(victim)
-                preempted_now = True
-                continue
-            # admit waiting requests, first in first out (not in a step that had to preempt: the
-            # freed pages first serve the requests that were short of them)
-            while not preempted_now and self.waiting and len(self.running) < self.cfg.max_active and budget > 0:
-                req = self.waiting[0]
-                if not mgr.has(req.id):
-                    if mgr.add_request(req.id) is None:
-                        break                      # no state slot free
-                n = self._portion(req, budget)
-                if not mgr.reserve(req.id, n):
-                    mgr.release(req.id)
-                    if not self.running and not plan:
-                        # alone and still too large for the free pages: it can never run
-                        self.waiting.popleft()
-                        req.state, req.finish_reason = FINISHED, "out_of_pages"
-                        self.finished.append(req)
-                        self.metrics.finished += 1
-                        continue
-                    break
-                self.waiting.popleft()
-                req.state = RUNNING
-                req.admit_seq = next(self._seq)
-                self.running.append(req)
-                self.metrics.admitted += 1
-                plan.append(PlannedEntry(req, 0, n, n == len(req.tokens)))
-                budget -= n
-            self.metrics.steps += 1 if plan else 0
-            self.metrics.tokens_scheduled += sum(p.count for p in plan)
-            return plan
+        n = self._check(self._lib.mmh_sched_schedule(self._h))
+        self._apply_events()
+        if n > self._cap:
+            raise SchedulerError(f"a plan of {n} entries exceeds the buffer of {self._cap}")
+        self._lib.mmh_sched_plan(self._h, self._rids, self._a, self._b, self._c, self._cap)
+        return [PlannedEntry(self._by_handle[self._rids[i]], self._a[i], self._b[i], bool(self._c[i])) for i in range(n)]
 
     # ---- after the step ------------------------------------------------------------------
     def commit(self, plan: Sequence[PlannedEntry], sampled: Dict[Hashable, int]) -> List[Request]:
         """Advances the cache lengths, appends the sampled tokens and retires finished requests.
         ``sampled`` maps request id → token for the entries with ``samples``.  Returns the requests
         that finished in this step."""
-        done: List[Request] = []
-        for p in plan:
-            req = p.request
-            self.manager.commit(req.id, p.start + p.count)
-            if not p.samples:
-                continue
-            if self.accept_token(req, int(sampled[req.id])):
-                done.append(req)
-        return done
+        n = len(plan)
+        rids = (ctypes.c_longlong * max(1, n))()
+        starts, counts = (ctypes.c_int * max(1, n))(), (ctypes.c_int * max(1, n))()
+        samples, toks = (ctypes.c_int * max(1, n))(), (ctypes.c_int * max(1, n))()
+        for i, p in enumerate(plan):
+            rids[i], starts[i], counts[i], samples[i] = self._handle[p.request.id], p.start, p.count, int(p.samples)
+            if p.samples:
+                toks[i] = int(sampled[p.request.id])
+                p.request.tokens.append(toks[i])
+                p.request.generated.append(toks[i])
+        self._check(self._lib.mmh_sched_commit(self._h, n, rids, starts, counts, samples, toks))
+        return self._apply_events()
 
     def accept_token(self, req: Request, tok: int) -> bool:
         """Appends a sampled token to a running request whose cache length is already advanced; retires
         the request and frees its pages if it is finished.  Returns True when it finished."""
+        tok = int(tok)
         req.tokens.append(tok)
         req.generated.append(tok)
-        reason = None
-        if tok in req.stop_ids:
-            reason = "stop"
-        elif len(req.generated) >= req.max_new:
-            reason = "length"
-        elif len(req.tokens) >= self.cfg.max_seq_len:
-            reason = "context"
-        if reason is None:
-            return False
-        req.state, req.finish_reason = FINISHED, reason
-        self.manager.release(req.id)
-        self.running.remove(req)
-        self.finished.append(req)
-        self.metrics.finished += 1
-        return True
+        rc = self._check(self._lib.mmh_sched_accept_token(self._h, self._handle[req.id], tok))
+        self._apply_events()
+        return rc == 1
 
     def all_decoding(self) -> bool:
         """Nothing waits and every running request has exactly its last token left to feed."""
-        return bool(self.running) and not self.waiting and all(self._remaining(r) == 1 for r in self.running)
+        return bool(self._lib.mmh_sched_all_decoding(self._h))
 
     def cancel(self, rid: Hashable) -> bool:
-        for req in list(self.running):
-            if req.id == rid:
-                self.manager.release(rid)
-                self.running.remove(req)
-                req.state, req.finish_reason = FINISHED, "cancelled"
-                self.finished.append(req)
-                return True
-        for req in list(self.waiting):
-            if req.id == rid:
-                self.waiting.remove(req)
-                if self.manager.has(rid):
-                    self.manager.release(rid)
-                req.state, req.finish_reason = FINISHED, "cancelled"
-                self.finished.append(req)
-                return True
-        return False
+        h = self._handle.get(rid)
+        if h is None:
+            return False
+        rc = self._check(self._lib.mmh_sched_cancel(self._h, h))
+        if rc == 1:
+            req = self._by_handle[h]
+            req.state, req.finish_reason = FINISHED, "cancelled"
+            self.manager.forget(rid)
+        return rc == 1

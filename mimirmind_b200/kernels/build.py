@@ -144,7 +144,48 @@ def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
     return lib_path
 
 
+HOST_DIR = os.path.join(CSRC_DIR, "host")
+HOST_LIB_NAME = "libmimirmind_host.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def host_library_path(verbose: bool = True) -> str:
+    """Path of the host runtime library (page allocator, cache manager, scheduler: ``csrc/host/*.cpp``, no CUDA),
+    built with the host C++ compiler when missing or stale."""
+    srcs = sorted(f for f in os.listdir(HOST_DIR) if f.endswith((".cpp", ".h")))
+    h = hashlib.sha256(" ".join(HOST_FLAGS).encode())
+    for name in srcs:
+        with open(os.path.join(HOST_DIR, name), "rb") as f:
+            h.update(name.encode())
+            h.update(f.read())
+    digest = h.hexdigest()
+    build_dir = _writable_build_dir()
+    lib_path = os.path.join(build_dir, HOST_LIB_NAME)
+    stamp = lib_path + ".sha256"
+    try:
+        with open(stamp) as f:
+            if f.read().strip() == digest and os.path.isfile(lib_path):
+                return lib_path
+    except OSError:
+        pass
+    cxx = os.environ.get("CXX") or shutil.which("g++") or shutil.which("c++") or shutil.which("clang++")
+    if not cxx:
+        raise BuildError("no C++ compiler found (g++, c++ or clang++; or set CXX): the host runtime cannot be built")
+    if verbose:
+        _log(f"compiling the host runtime into {build_dir}")
+    tmp_lib = lib_path + f".tmp{os.getpid()}"
+    cpps = [os.path.join(HOST_DIR, n) for n in srcs if n.endswith(".cpp")]
+    proc = subprocess.run([cxx] + HOST_FLAGS + ["-o", tmp_lib] + cpps, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise BuildError(f"host runtime build failed:\n{proc.stdout}\n{proc.stderr}")
+    os.replace(tmp_lib, lib_path)
+    with open(stamp, "w") as f:
+        f.write(digest)
+    return lib_path
+
+
 def build_all(verbose: bool = True) -> str:
+    host_library_path(verbose=verbose)
     return library_path(build_if_needed=True, verbose=verbose)
 
 
