@@ -93,10 +93,8 @@ class DecodeSession:
             assert ok
         self.ids, self.horizon, self.steps_done = list(request_ids), horizon, 0
         for g in mgr.groups:
-            t = torch.full((self.batch, self.width), -1, dtype=torch.int32)
-            for i, rid in enumerate(self.ids):
-                tab = mgr.table(rid, g)[:self.width]
-                t[i, :len(tab)] = torch.tensor(tab, dtype=torch.int32)
+            t = torch.empty((self.batch, self.width), dtype=torch.int32)
+            mgr.fill_tables(g, self.ids, self.width, t.data_ptr())     # -1 beyond a table's end
             self.tables[g].copy_(t.to(dev, non_blocking=False))
         self.positions.copy_(torch.tensor(lengths, dtype=torch.int32))
         self.slots.copy_(torch.tensor([mgr.slot(r) for r in self.ids], dtype=torch.int32))

@@ -104,12 +104,10 @@ class ModelRunner:
         max_kv = max(kv_len)
         width = max(1, (max_kv + ps - 1) // ps)
         tables = {}
+        rids = [e.request for e in entries]
         for name in mgr.groups:
-            t = np.full((n_req, width), -1, dtype=np.int32)
-            for r, e in enumerate(entries):
-                tab = mgr.table(e.request, name)
-                m = min(len(tab), width)
-                t[r, :m] = tab[:m]
+            t = np.empty((n_req, width), dtype=np.int32)
+            mgr.fill_tables(name, rids, width, t.ctypes.data)      # -1 beyond a table's end
             tables[name] = t
         meta = np.stack([np.asarray(q_start, np.int32), np.asarray(q_len, np.int32), np.asarray(kv_len, np.int32),
                          np.asarray(slots, np.int32)], axis=1)
