@@ -144,6 +144,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
         if (threadIdx.x == 0 && err != nullptr) atomicExch(err, 5);
         if (!CLUSTER) return;
     }
+    if (threadIdx.x == DT_CONSUMERS * 32) {
+        prefetch_tensormap(&tmK);
+        prefetch_tensormap(&tmV);
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&ctl->full[s]), 1);

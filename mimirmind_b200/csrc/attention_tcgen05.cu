@@ -115,6 +115,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     const int lo_all = (window > 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
     const int kt_begin = lo_all / BN, kt_end = (hi_all + BN - 1) / BN;
 
+    if (threadIdx.x == 64) {
+        prefetch_tensormap(&tmQ);
+        prefetch_tensormap(&tmK);
+        prefetch_tensormap(&tmV);
+    }
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&ctl->q_full), 1);
         for (int s = 0; s < KV_STAGES; ++s) {

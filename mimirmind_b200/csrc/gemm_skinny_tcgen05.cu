@@ -132,6 +132,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     bool good = (smem_u32(smem_raw) & 1023u) == 0;
     if (!good && threadIdx.x == 0 && a.err != nullptr) atomicExch(a.err, 5);
 
+    if (threadIdx.x == 32) {
+        prefetch_tensormap(&tmW);
+        prefetch_tensormap(&tmX);
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&ctl->full[s]), 1);

@@ -73,6 +73,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &ctl->abort_flag;
 
+    if (threadIdx.x == 32) {
+        prefetch_tensormap(&tmA);
+        prefetch_tensormap(&tmB);
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&ctl->full[s]), 1);
