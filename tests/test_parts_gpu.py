@@ -210,6 +210,94 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         registry.ARCHITECTURES.unregister("ToyForTest")
 
 
+def test_fused_handover_beside_a_mixer_that_does_not_fuse():
+    """bfloat16, sizes the fused small-step path takes: a toy mixer that knows nothing of FactoredRows or sinks sits
+    between layers whose attention and feed-forward fuse.  Its neighbours must fall back to the plain hand-over on
+    its side and still fuse on the other; every way of cutting gives the same logits within bfloat16 rounding, and
+    they agree with the same model run in float32."""
+    from mimirmind_b200 import registry
+    from mimirmind_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+    from mimirmind_b200.engine.loader import make_runtime
+    from mimirmind_b200.engine.model import Model
+    from mimirmind_b200.engine.runner import ModelRunner, StepEntry
+    from mimirmind_b200.parts.base import Mixer
+    from mimirmind_b200.weights.store import random_tensors
+    registry._ensure_builtin()
+    calls = {"plain": 0}
+
+    @registry.MIXERS.register("toy_scaled_copy", replace=True)
+    class ScaledCopy(Mixer):
+        """out = x @ W^T, stateless; takes tensors only."""
+
+        @classmethod
+        def tensor_specs(cls, spec, prefix):
+            return [TensorSpec(prefix + "mix.weight", (spec["hidden"], spec["hidden"]))]
+
+        def __init__(self, spec, weights, rt):
+            super().__init__(spec, weights, rt)
+            self.w = weights.get("mix.weight")
+
+        def forward(self, x, ctx, cache):
+            assert isinstance(x, torch.Tensor)                  # never FactoredRows: the part does not say it fuses
+            calls["plain"] += 1
+            return (x.float() @ self.w.float().t()).to(x.dtype)
+
+    def toy_spec(cfg):
+        d = cfg["hidden_size"]
+        norm = lambda name: PartSpec("rmsnorm", {"width": d, "eps": 1e-5, "weight": name})
+        attn = PartSpec("gqa_attention", dict(hidden=d, num_heads=4, num_kv_heads=2, head_dim=64, window=0, scale=None, qkv_bias=True,
+                                              position=PartSpec("rotary_half", {"theta": 100.0, "rotary_dim": 64}),
+                                              q="q", k="k", v="v", o="o"))
+        ffn = PartSpec("swiglu", {"hidden": d, "intermediate": 320, "gate": "g.weight", "up": "u.weight", "down": "d.weight"})
+        layers = (
+            LayerSpec("l0.", PartSpec("pre_norm"), PartSpec("toy_scaled_copy", {"hidden": d}), ffn, norm("n1"), norm("n2")),
+            LayerSpec("l1.", PartSpec("pre_norm"), attn, ffn, norm("n1"), norm("n2")),
+        )
+        return ModelSpec("ToyFusedForTest", d, cfg["vocab_size"], 512,
+                         PartSpec("token_embedding", {"vocab": cfg["vocab_size"], "width": d, "scale": 1.0, "weight": "emb"}),
+                         layers, (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1), ScheduleEntry(0)), norm("nf"),
+                         PartSpec("lm_head", {"vocab": cfg["vocab_size"], "width": d, "weight": "head", "tied_to": "emb"}))
+
+    registry.register_architecture("ToyFusedForTest", lambda obj, where="": obj, toy_spec, replace=True)
+    try:
+        entry = registry.get_architecture("ToyFusedForTest")
+        spec = entry.build_spec(entry.parse_config({"hidden_size": 256, "vocab_size": 90}))
+        rt16, rt32 = make_runtime("bfloat16"), make_runtime("float32")
+        tensors = random_tensors(spec, 11, torch.bfloat16, rt16.device)
+        model16 = Model(spec, {k: v.clone() for k, v in tensors.items()}, rt16)
+        model32 = Model(spec, {k: v.float() for k, v in tensors.items()}, rt32)
+        blocks = model16.layers
+        assert blocks[1].mixer.fuses(5) and blocks[1].mixer.fuses(40) and not blocks[1].mixer.fuses(200)
+        assert blocks[0].feed_forward.fuses(5) and not blocks[0].mixer.fuses(5)
+        assert blocks[1].entry_norm(5) is not None and blocks[0].entry_norm(5) is None
+        toks = random_tokens(90, 70, 4)
+
+        def run(model, cuts, rid):
+            runner = ModelRunner(model, 16, 16, 4)
+            runner.add_request(rid)
+            outs, p = [], 0
+            for c in cuts:
+                outs.append(runner.step([StepEntry(rid, toks[p:p + c], list(range(c)))]).cpu().numpy())
+                p += c
+            return np.concatenate(outs)
+
+        exact = run(model32, [70], "x")
+        scale = np.abs(exact).max()
+        whole = run(model16, [70], "a")                             # one step above 64 tokens: nothing fuses
+        assert np.abs(whole - exact).max() <= 4e-2 * scale
+        for cuts in ([40, 30], [7, 1, 1, 30, 2, 13, 16], [64, 6], [1] * 10 + [60]):
+            before = calls["plain"]
+            got = run(model16, cuts, ("b", len(cuts)))
+            assert calls["plain"] == before + 2 * len(cuts)          # the toy mixer ran in both of its schedule entries
+            assert np.abs(got - exact).max() <= 4e-2 * scale, cuts
+            assert np.abs(got - whole).max() <= 4e-2 * scale, cuts
+        from mimirmind_b200.kernels import ops
+        ops.check_tcgen05_errors(rt16.device)
+    finally:
+        registry.MIXERS.unregister("toy_scaled_copy")
+        registry.ARCHITECTURES.unregister("ToyFusedForTest")
+
+
 # ---- another position encoding and a feed-forward with routing, defined here ---------------------------------
 
 def test_toy_position_encoding_and_routed_feed_forward(tmp_path):
