@@ -224,11 +224,7 @@ class Engine:
 
     def _run_plan(self, plan: Sequence[PlannedEntry]) -> Dict[Hashable, int]:
         entries = [StepEntry(p.request.id, p.tokens, [p.count - 1] if p.samples else []) for p in plan]
-        ctx = self.runner._build_context(entries)
-        for p in plan:
-            if self.runner.manager.mark_started(p.request.id):
-                self.runner.storage.zero_slot(self.runner.manager.slot(p.request.id))
-        logits = self.runner.forward(ctx)
+        logits = self.runner.execute(entries)
         sampled: Dict[Hashable, int] = {}
         rows = [p for p in plan if p.samples]
         if rows:

@@ -34,6 +34,11 @@ from .storage import CacheStorage
 # poll), as much as a kernel boundary in a graph, and CTAs of the cooperative launch start up to 2.3 us apart.
 USE_GEMV_CHAIN = False
 
+# A prompt portion of one request with at least this many tokens, of a size seen before, runs as a replayed CUDA
+# graph (engine/prefill_graph.py); at most PREFILL_GRAPHS sizes are kept.  0 turns it off.
+PREFILL_GRAPH_MIN_TOKENS = 512
+PREFILL_GRAPHS = 4
+
 
 class StepError(RuntimeError):
     pass
@@ -58,6 +63,8 @@ class ModelRunner:
         self.page_size = page_size
         self.vocab = model.spec.vocab_size
         self.steps_run = 0
+        self._prefill_sessions: Dict[Tuple[int, bool], object] = {}
+        self._prefill_seen: Dict[Tuple[int, bool], int] = {}
 
     # ---- request life cycle ---------------------------------------------------
     def add_request(self, rid: Hashable) -> bool:
@@ -164,15 +171,50 @@ class ModelRunner:
         for e in entries:
             ok = mgr.reserve(e.request, mgr.length(e.request) + len(e.tokens))
             assert ok
-        for e in entries:
-            if mgr.mark_started(e.request):
-                self.storage.zero_slot(mgr.slot(e.request))
-        ctx = self._build_context(entries)
-        logits = self.forward(ctx)
+        logits = self.execute(entries)
         for e in entries:
             mgr.commit(e.request, mgr.length(e.request) + len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def execute(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the model on entries whose pages are reserved (by ``step`` or by a scheduler); lengths are not
+        committed here.  Returns fp32 logits [wanted, vocab] or None."""
+        mgr = self.manager
+        for e in entries:
+            if mgr.mark_started(e.request):
+                self.storage.zero_slot(mgr.slot(e.request))
+        session = self._prefill_session(entries)
+        if session is not None:
+            e = entries[0]
+            return session.run(e.request, e.tokens, mgr.length(e.request))
+        return self.forward(self._build_context(entries))
+
+    def _prefill_session(self, entries: Sequence[StepEntry]):
+        """The graph session for this step, or None: one request, bfloat16, a long portion whose size was seen
+        before, logits wanted at its last token or nowhere."""
+        if (PREFILL_GRAPH_MIN_TOKENS <= 0 or len(entries) != 1 or self.rt.dtype != torch.bfloat16
+                or len(entries[0].tokens) < PREFILL_GRAPH_MIN_TOKENS):
+            return None
+        e = entries[0]
+        n = len(e.tokens)
+        want = list(e.want)
+        if want not in ([], [n - 1]):
+            return None
+        if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
+            raise StepError(f"request {e.request!r}: token id outside [0, {self.vocab})")
+        key = (n, bool(want))
+        sess = self._prefill_sessions.get(key)
+        if sess is None:
+            self._prefill_seen[key] = self._prefill_seen.get(key, 0) + 1
+            if self._prefill_seen[key] < 2:
+                return None                      # a size seen once is not worth a capture
+            if len(self._prefill_sessions) >= PREFILL_GRAPHS:
+                self._prefill_sessions.pop(next(iter(self._prefill_sessions)))
+            from .prefill_graph import PrefillSession
+            sess = PrefillSession(self, n, bool(want))
+            self._prefill_sessions[key] = sess
+        return sess
 
     def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
         m = self.model

@@ -165,3 +165,53 @@ def test_many_requests_in_32_bit_are_identical_token_for_token(model_folders):
     alone = Engine.from_folder(folder, dtype="float32", cache_tokens=1024, max_context=512, token_budget=512, max_active=1, use_graphs=False)
     for i, (p, r) in enumerate(zip(prompts, got)):
         assert alone.generate([p], max_new_tokens=30)[0].tokens == r.tokens, f"request {i}"
+
+
+def test_long_prompt_portions_replayed_as_graphs_equal_eager_steps(tmp_path):
+    """A portion of one request of a size seen before runs as a captured graph.  Three requests with the same
+    tokens in portions of 600 (logits wanted, not wanted, wanted): the first runs eagerly, the second captures, the
+    third only replays, at first positions 0, 600 and 1200; all logits equal the eager runner's bit for bit, and a
+    portion with other tokens through the same graphs differs."""
+    import torch
+    from mimirmind_b200.engine import runner as runner_mod
+    from mimirmind_b200.engine.loader import load_model
+    from mimirmind_b200.engine.runner import ModelRunner, StepEntry
+    from mimirmind_b200.kernels import ops
+    from mimirmind_b200.weights import write_random_model
+    cfg = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=400, hidden_size=256, intermediate_size=352,
+               num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
+               rope_theta=10000.0, max_position_embeddings=4096, tie_word_embeddings=False)
+    write_random_model(str(tmp_path), cfg, 21, "bfloat16")
+    model, _ = load_model(str(tmp_path), dtype="bfloat16")
+    toks = random_tokens(400, 1800, 9)
+    other = random_tokens(400, 1800, 10)
+
+    def run(runner, rid, tokens):
+        runner.add_request(rid)
+        a = runner.step([StepEntry(rid, tokens[:600], [599])])
+        b = runner.step([StepEntry(rid, tokens[600:1200], [])])
+        c = runner.step([StepEntry(rid, tokens[1200:], [599])])
+        runner.release(rid)
+        assert b is None
+        return a.cpu().numpy(), c.cpu().numpy()
+
+    old = runner_mod.PREFILL_GRAPH_MIN_TOKENS
+    try:
+        runner_mod.PREFILL_GRAPH_MIN_TOKENS = 0
+        eager = ModelRunner(model, 16, 256, 4, max_seq_len=4096)
+        ref, ref_other = run(eager, "r", toks), run(eager, "o", other)
+        runner_mod.PREFILL_GRAPH_MIN_TOKENS = 512
+        graphs = ModelRunner(model, 16, 256, 4, max_seq_len=4096)
+        for i in range(3):
+            got = run(graphs, ("g", i), toks)
+            assert np.array_equal(got[0], ref[0]) and np.array_equal(got[1], ref[1]), i
+        sessions = graphs._prefill_sessions
+        assert set(sessions) == {(600, True), (600, False)}
+        assert all(s.graph is not None for s in sessions.values()) and sessions[(600, True)].runs == 5 and sessions[(600, False)].runs == 2
+        got = run(graphs, "x", other)
+        assert np.array_equal(got[0], ref_other[0]) and np.array_equal(got[1], ref_other[1])
+        assert not np.array_equal(got[1], ref[1])
+        graphs.manager.check()
+        ops.check_tcgen05_errors(torch.device("cuda"))
+    finally:
+        runner_mod.PREFILL_GRAPH_MIN_TOKENS = old
