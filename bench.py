@@ -113,15 +113,20 @@ def run_workload(name: str, layers: int) -> int:
     engine = Engine(model, page_size=PAGE_SIZE, cache_tokens=sum(lens) + len(lens) * (new + 64), max_context=ctx,
                     token_budget=2048, max_active=64)
     prompts = [rng.randint(0, mcfg.vocab_size, size=n).tolist() for n in lens]
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    res = engine.generate(prompts, max_new_tokens=new, use_eos=False)
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
+    # the first run also captures the CUDA graphs of the decode batches and of the repeated prompt portions (about a
+    # tenth of a second each); the second run is the steady state of a serving process
+    times = []
+    for _ in range(2):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        res = engine.generate(prompts, max_new_tokens=new, use_eos=False)
+        torch.cuda.synchronize()
+        times.append(time.perf_counter() - t0)
+    dt = times[1]
     ops.check_tcgen05_errors(torch.device("cuda"))
     gen = sum(r.stats.generated_tokens for r in res)
     print(json.dumps({"workload": name, "layers": mcfg.num_hidden_layers, "layers_of_config": full_layers, "requests": len(lens),
-                      "prompt_tokens": sum(lens), "generated_tokens": gen, "seconds": dt, "tokens_per_s": (sum(lens) + gen) / dt,
+                      "prompt_tokens": sum(lens), "generated_tokens": gen, "first_run_seconds": times[0], "seconds": dt, "tokens_per_s": (sum(lens) + gen) / dt,
                       "generated_per_s": gen / dt, "graph_steps": engine.graph_steps,
                       "finish": sorted({r.stats.finish_reason for r in res}),
                       "device_gib": torch.cuda.max_memory_allocated() / 2 ** 30}))
