@@ -1,5 +1,6 @@
 // Device-side sampling over fp32 logits [R, V]: argmax, and temperature / top-k / top-p
-// draws, one thread block per row, so no logits leave the GPU.
+// draws (one thread-block cluster per row, the CTAs of a cluster share the row), so no logits
+// leave the GPU.
 //
 // Semantics follow the reference's host sampler (src/compute/Sampling.cpp:119-264):
 //   * temperature <= 0 or top_k == 1 is greedy; greedy is the first strict maximum,
@@ -158,181 +159,353 @@ MM_EXPORT int mm_argmax_rows_split(const void* logits, void* out, void* part_val
     return MM_OK;
 }
 
-// ---- radix select over weighted candidates -----------------------------------
-// Candidates are the elements with key >= floor_key.  In the order (key descending,
-// index ascending) find the first element whose cumulative weight exceeds `target`.
-// Weight is 1 when `by_count`, else the fixed-point probability.  Returns the key of
-// that element and, in *tie_rank, how many equal-key elements precede it.
-struct SelectResult {
-    uint32_t key;
-    unsigned long long tie_rank;
-    unsigned long long weight_of_key;  // weight of one element with that key
+// ---- sampling: one thread-block cluster per row -------------------------------------------------------------
+// The CTAs of a cluster take contiguous slices of the row.  Whatever the whole row decides (its maximum, the mass
+// of the kept set, the histogram of a radix pass, how many elements carry the chosen key) is computed per CTA,
+// published in shared memory, and read by every CTA of the cluster from its peers through distributed shared
+// memory after one cluster barrier; all CTAs then hold the same numbers and take the same branch.  Publications
+// alternate between two buffers, so one barrier per exchange is enough: a CTA can run at most one exchange ahead of
+// a peer that is still reading.  Histograms are per warp (64-bit shared-memory adds collide within a warp only).
+#define SAMPLE_WARPS (SAMPLE_THREADS / 32)
+#define SAMPLE_MAX_CLUSTER 8
+
+struct SampleShared {
+    unsigned long long whist[SAMPLE_WARPS][256];   // per-warp histograms of a radix pass
+    unsigned long long pub[2][256 + 4];            // what this CTA publishes: a histogram, or scalars in [256..]
+    unsigned long long tot[256];                   // the cluster's histogram
+    unsigned long long warp_part[SAMPLE_WARPS];
+    unsigned long long carry;
+    uint32_t chosen;
+    int counts[SAMPLE_THREADS];
+    int result;
 };
+
+struct ClusterCtx {
+    SampleShared* sh;
+    const float* vals;                             // this CTA's slice: its copy in shared memory, or the row itself
+    int vals_begin;                                // index of vals[0] in the row
+    uint32_t rank, n_ranks;
+    uint32_t round;                                // exchanges so far: selects the publication buffer
+};
+
+__device__ __forceinline__ void sample_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;\n" ::: "memory");
+}
+__device__ __forceinline__ unsigned long long ld_peer_u64(const unsigned long long* local, uint32_t rank) {
+    uint32_t remote;
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(local);
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(addr), "r"(rank));
+    unsigned long long v;
+    asm volatile("ld.shared::cluster.u64 %0, [%1];\n" : "=l"(v) : "r"(remote) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+        v = other > v ? other : v;
+    }
+    return v;
+}
+
+// The CTA's value (held by thread 0 after a block reduction through warp_part) is published; returns the sum
+// (or the maximum) over the cluster, the same in every thread of every CTA.
+__device__ unsigned long long cluster_combine(ClusterCtx& c, unsigned long long mine, bool take_max) {
+    SampleShared* sh = c.sh;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    mine = take_max ? warp_max_u64(mine) : warp_sum_u64(mine);
+    if (lane == 0) sh->warp_part[warp] = mine;
+    __syncthreads();
+    const uint32_t b = c.round & 1;
+    if (warp == 0) {
+        unsigned long long v = lane < SAMPLE_WARPS ? sh->warp_part[lane] : 0ull;
+        v = take_max ? warp_max_u64(v) : warp_sum_u64(v);
+        if (lane == 0) sh->pub[b][256] = v;
+    }
+    __syncthreads();
+    sample_cluster_sync();
+    unsigned long long all = 0ull;
+    for (uint32_t r = 0; r < c.n_ranks; ++r) {
+        const unsigned long long v = ld_peer_u64(&sh->pub[b][256], r);
+        all = take_max ? (v > all ? v : all) : all + v;
+    }
+    ++c.round;
+    return all;
+}
 
 __device__ __forceinline__ unsigned long long weight_of(float logit, float inv_t, float max_scaled) {
     const float p = expf(logit * inv_t - max_scaled);
     return (unsigned long long)(p * FIXED_ONE);
 }
 
-__device__ SelectResult radix_select(const float* __restrict__ row, int V, float inv_t, float max_scaled,
-                                     uint32_t floor_key, bool by_count, unsigned long long target,
-                                     unsigned long long* hist /* [256] shared */, uint32_t* bcast /* [2] shared */,
-                                     unsigned long long* carry /* shared */) {
+// Candidates are the elements with key >= floor_key.  In the order (key descending, index ascending) find the
+// first element whose cumulative weight exceeds `target`.  Weight is 1 when `by_count`, else the fixed-point
+// probability.  Returns the key of that element and how many equal-key elements precede it.
+struct SelectResult {
+    uint32_t key;
+    unsigned long long tie_rank;
+};
+
+__device__ SelectResult radix_select(ClusterCtx& c, const float* __restrict__ row, int begin, int end, float inv_t,
+                                     float max_scaled, uint32_t floor_key, bool by_count, unsigned long long target) {
+    SampleShared* sh = c.sh;
+    const int warp = threadIdx.x >> 5;
     uint32_t prefix = 0;
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
-        for (int b = threadIdx.x; b < 256; b += blockDim.x) hist[b] = 0ull;
+        for (int i = threadIdx.x; i < SAMPLE_WARPS * 256; i += SAMPLE_THREADS) (&sh->whist[0][0])[i] = 0ull;
         __syncthreads();
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
-            const float v = row[i];
-            const uint32_t key = order_key(v);
-            if (key < floor_key) continue;
-            if (pass > 0 && (key >> (shift + 8)) != prefix) continue;
-            const unsigned long long w = by_count ? 1ull : weight_of(v, inv_t, max_scaled);
-            if (w) atomicAdd(&hist[(key >> shift) & 0xffu], w);
+        for (int i = begin + (int)threadIdx.x; i < end; i += 4 * SAMPLE_THREADS) {
+            float v[4];                                          // four loads in flight when the slice is in global memory
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int j = i + u * SAMPLE_THREADS;
+                v[u] = j < end ? c.vals[j - c.vals_begin] : __int_as_float(0x7fc00000);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (i + u * SAMPLE_THREADS >= end) continue;
+                const uint32_t key = order_key(v[u]);
+                if (key < floor_key) continue;
+                if (pass > 0 && (key >> (shift + 8)) != prefix) continue;
+                const unsigned long long w = by_count ? 1ull : weight_of(v[u], inv_t, max_scaled);
+                if (w) atomicAdd(&sh->whist[warp][(key >> shift) & 0xffu], w);
+            }
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            unsigned long long cum = 0, rem = 0;
-            int chosen = -1;
-            for (int b = 255; b >= 0; --b) {
-                if (hist[b] && target < cum + hist[b]) {
-                    chosen = b;
-                    break;
-                }
-                cum += hist[b];
+        const uint32_t b = c.round & 1;
+        if (threadIdx.x < 256) {
+            unsigned long long sum = 0ull;
+#pragma unroll 8
+            for (int w = 0; w < SAMPLE_WARPS; ++w) sum += sh->whist[w][threadIdx.x];
+            sh->pub[b][threadIdx.x] = sum;
+        }
+        __syncthreads();
+        sample_cluster_sync();
+        if (threadIdx.x < 256) {
+            unsigned long long sum = 0ull;
+            for (uint32_t r = 0; r < c.n_ranks; ++r) sum += ld_peer_u64(&sh->pub[b][threadIdx.x], r);
+            sh->tot[threadIdx.x] = sum;
+        }
+        ++c.round;
+        __syncthreads();
+        if (warp == 0) {
+            // bins in descending order, eight per lane: lane L holds bins 255 - 8L .. 248 - 8L; the weight of all
+            // bins before a lane's comes from a shuffle scan
+            const int lane = threadIdx.x & 31;
+            unsigned long long h[8], mine = 0ull;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                h[j] = sh->tot[255 - 8 * lane - j];
+                mine += h[j];
             }
-            if (chosen >= 0) {
-                rem = target - cum;
-            } else {
+            unsigned long long incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            unsigned long long cum = incl - mine;
+            int chosen = -1;
+            unsigned long long rem = 0ull;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (chosen < 0 && h[j] && target < cum + h[j]) {
+                    chosen = 255 - 8 * lane - j;
+                    rem = target - cum;
+                }
+                cum += h[j];
+            }
+            const uint32_t found = __ballot_sync(0xffffffffu, chosen >= 0);
+            if (found) {
+                if (lane == __ffs(found) - 1) {                  // the first lane in descending bin order
+                    sh->chosen = (uint32_t)chosen;
+                    sh->carry = rem;
+                }
+            } else if (lane == 0) {
                 // target at or beyond the total (rounding at the tail): the last candidate
-                chosen = 0;
-                for (int b = 0; b < 256; ++b)
-                    if (hist[b]) {
-                        chosen = b;
-                        rem = hist[b] - 1ull;
+                int last = 0;
+                unsigned long long left = 0ull;
+                for (int bin = 0; bin < 256; ++bin)
+                    if (sh->tot[bin]) {
+                        last = bin;
+                        left = sh->tot[bin] - 1ull;
                         break;
                     }
+                sh->chosen = (uint32_t)last;
+                sh->carry = left;
             }
-            bcast[0] = (uint32_t)chosen;
-            *carry = rem;
         }
         __syncthreads();
-        prefix = (prefix << 8) | bcast[0];
-        target = *carry;
+        prefix = (prefix << 8) | sh->chosen;
+        target = sh->carry;
         __syncthreads();
     }
     SelectResult r;
     r.key = prefix;
     // all elements with this key have the same logit, hence the same weight
-    float key_val;
-    {
-        const uint32_t u = (prefix & 0x80000000u) ? (prefix & 0x7fffffffu) : ~prefix;
-        key_val = __uint_as_float(u);
-    }
-    r.weight_of_key = by_count ? 1ull : weight_of(key_val, inv_t, max_scaled);
-    r.tie_rank = r.weight_of_key ? target / r.weight_of_key : 0ull;
+    const uint32_t u = (prefix & 0x80000000u) ? (prefix & 0x7fffffffu) : ~prefix;
+    const unsigned long long w = by_count ? 1ull : weight_of(__uint_as_float(u), inv_t, max_scaled);
+    r.tie_rank = w ? target / w : 0ull;
     return r;
 }
 
-// index of the (rank)-th element (by ascending index) whose key equals `key`
-__device__ int nth_with_key(const float* __restrict__ row, int V, uint32_t key, unsigned long long rank,
-                            int* counts /* [blockDim.x] shared */, int* result /* shared */) {
-    const int chunk = (V + blockDim.x - 1) / blockDim.x;
-    const int begin = threadIdx.x * chunk;
-    const int end = min(V, begin + chunk);
-    int c = 0;
-    for (int i = begin; i < end; ++i) c += (order_key(row[i]) == key);
-    counts[threadIdx.x] = c;
-    if (threadIdx.x == 0) *result = -1;
+// Index of the (rank)-th element, by ascending index, whose key equals `key`; written to out_token by the thread
+// that owns it.  Returns nothing: if no element has the key, rank 0's thread 0 writes `fallback`.
+__device__ void write_nth_with_key(ClusterCtx& c, const float* __restrict__ row, int begin, int end, uint32_t key,
+                                   unsigned long long rank, int fallback, int32_t* out_token) {
+    SampleShared* sh = c.sh;
+    const int len = end - begin;
+    const int sub = (len + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+    const int lo = begin + min(len, (int)threadIdx.x * sub), hi = begin + min(len, ((int)threadIdx.x + 1) * sub);
+    int cnt = 0;
+    for (int i = lo; i < hi; ++i) cnt += (order_key(c.vals[i - c.vals_begin]) == key);
+    sh->counts[threadIdx.x] = cnt;
+    // every CTA publishes how many it holds (cluster_combine would only give the sum: the prefix needs each)
+    const unsigned long long mine = warp_sum_u64((unsigned long long)cnt);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) sh->warp_part[warp] = mine;
     __syncthreads();
+    const uint32_t b = c.round & 1;
     if (threadIdx.x == 0) {
-        // serial scan over at most 1024 partial counts
-        unsigned long long before = 0;
-        int owner = -1;
-        long long total = 0;
-        for (int t = 0; t < (int)blockDim.x; ++t) total += counts[t];
-        if (total > 0 && rank >= (unsigned long long)total) rank = (unsigned long long)total - 1;
-        for (int t = 0; t < (int)blockDim.x; ++t) {
-            if (rank < before + (unsigned long long)counts[t]) {
+        unsigned long long v = 0ull;
+        for (int w = 0; w < SAMPLE_WARPS; ++w) v += sh->warp_part[w];
+        sh->pub[b][256] = v;
+    }
+    __syncthreads();
+    sample_cluster_sync();
+    unsigned long long before = 0ull, total = 0ull;
+    for (uint32_t r = 0; r < c.n_ranks; ++r) {
+        const unsigned long long v = ld_peer_u64(&sh->pub[b][256], r);
+        if (r < c.rank) before += v;
+        total += v;
+    }
+    ++c.round;
+    if (total == 0ull) {
+        if (c.rank == 0 && threadIdx.x == 0) *out_token = fallback;
+        return;
+    }
+    if (rank >= total) rank = total - 1ull;
+    const unsigned long long here = sh->pub[b][256];
+    if (rank < before || rank >= before + here) return;           // another CTA's slice holds it
+    rank -= before;
+    if (threadIdx.x == 0) {
+        unsigned long long seen = 0ull;
+        int owner = 0;
+        for (int t = 0; t < SAMPLE_THREADS; ++t) {
+            if (rank < seen + (unsigned long long)sh->counts[t]) {
                 owner = t;
                 break;
             }
-            before += counts[t];
+            seen += (unsigned long long)sh->counts[t];
         }
-        counts[0] = owner;
-        // reuse *result to carry the remaining rank (fits an int: V < 2^31)
-        *result = (int)(rank - before);
+        sh->chosen = (uint32_t)owner;
+        sh->result = (int)(rank - seen);
     }
     __syncthreads();
-    const int owner = counts[0];
-    const int rem = *result;
-    __syncthreads();
-    if ((int)threadIdx.x == owner) {
+    if (threadIdx.x == sh->chosen) {
         int seen = 0;
-        for (int i = begin; i < end; ++i) {
-            if (order_key(row[i]) == key) {
+        const int rem = sh->result;
+        for (int i = lo; i < hi; ++i)
+            if (order_key(c.vals[i - c.vals_begin]) == key) {
                 if (seen == rem) {
-                    *result = i;
+                    *out_token = i;
                     break;
                 }
                 ++seen;
             }
-        }
     }
-    __syncthreads();
-    return *result;
 }
 
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int V,
                    const float* __restrict__ temperature, const int32_t* __restrict__ top_k,
                    const float* __restrict__ top_p, const unsigned long long* __restrict__ seeds,
-                   const unsigned long long* __restrict__ counters) {
-    __shared__ unsigned long long hist[256];
-    __shared__ uint32_t bcast[2];
-    __shared__ int counts[SAMPLE_THREADS];
-    __shared__ int result;
-    __shared__ unsigned long long total_sh;
-    __shared__ unsigned long long carry_sh;
-    const int r = blockIdx.x;
+                   const unsigned long long* __restrict__ counters, int cache_floats) {
+    extern __shared__ __align__(16) unsigned char sample_smem[];
+    ClusterCtx c;
+    c.sh = reinterpret_cast<SampleShared*>(sample_smem);
+    c.rank = blockIdx.x;                                           // the cluster spans x
+    c.n_ranks = gridDim.x;
+    c.round = 0;
+    const int r = blockIdx.y;
     const float* row = logits + (size_t)r * V;
     const float T = temperature[r];
     const int k = top_k[r];
     const float P = top_p[r];
-    float max_logit;
-    const int best = block_argmax(row, V, &max_logit);
-    if (T <= 0.0f || k == 1) {
-        if (threadIdx.x == 0) out[r] = best;
+    const int chunk = (V + (int)c.n_ranks - 1) / (int)c.n_ranks;
+    const int begin = min(V, (int)c.rank * chunk), end = min(V, begin + chunk);
+
+    // maximum and its lowest index: (order key, ~index) packed so that the larger number is the better pair;
+    // NaN takes no part; a row without any number gives index 0
+    // The slice is read from global memory once, four loads in flight per thread, and kept in shared memory if it
+    // fits (`cache_floats` > 0): the passes below then read it from there.
+    float* cache = reinterpret_cast<float*>(sample_smem + sizeof(SampleShared));
+    const bool cached = cache_floats >= end - begin;
+    unsigned long long best = 0ull;
+    for (int i = begin + (int)threadIdx.x; i < end; i += 4 * SAMPLE_THREADS) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = i + u * SAMPLE_THREADS;
+            v[u] = j < end ? row[j] : __int_as_float(0x7fc00000);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int j = i + u * SAMPLE_THREADS;
+            if (j >= end) continue;
+            if (cached) cache[j - begin] = v[u];
+            if (v[u] != v[u]) continue;
+            const unsigned long long packed = ((unsigned long long)order_key(v[u]) << 32) | (uint32_t)(~(uint32_t)j);
+            best = packed > best ? packed : best;
+        }
+    }
+    c.vals = cached ? cache : row;
+    c.vals_begin = cached ? begin : 0;
+    best = cluster_combine(c, best, true);
+    const int best_index = best ? (int)(~(uint32_t)(best & 0xffffffffull)) : 0;
+    // (every path below ends with a cluster barrier: no CTA may exit while a peer still reads its shared memory)
+    if (T <= 0.0f || k == 1 || best == 0ull) {
+        if (c.rank == 0 && threadIdx.x == 0) out[r] = best_index;
+        sample_cluster_sync();
         return;
+    }
+    float max_logit;
+    {
+        const uint32_t key = (uint32_t)(best >> 32);
+        max_logit = __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
     }
     const float inv_t = 1.0f / T;
     const float max_scaled = max_logit * inv_t;
 
     // top-k: everything at or above the k-th largest logit stays
     uint32_t floor_key = 0;
-    if (k > 0 && k < V) {
-        const SelectResult s = radix_select(row, V, inv_t, max_scaled, 0u, true, (unsigned long long)(k - 1), hist, bcast, &carry_sh);
-        floor_key = s.key;
-    }
-    // mass of the kept set
+    if (k > 0 && k < V) floor_key = radix_select(c, row, begin, end, inv_t, max_scaled, 0u, true, (unsigned long long)(k - 1)).key;
     auto kept_mass = [&](uint32_t fk) -> unsigned long long {
         unsigned long long local = 0;
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
-            const float v = row[i];
-            if (order_key(v) >= fk) local += weight_of(v, inv_t, max_scaled);
+        for (int i = begin + (int)threadIdx.x; i < end; i += 4 * SAMPLE_THREADS) {
+            float v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int j = i + u * SAMPLE_THREADS;
+                v[u] = j < end ? c.vals[j - c.vals_begin] : __int_as_float(0x7fc00000);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (i + u * SAMPLE_THREADS < end && order_key(v[u]) >= fk) local += weight_of(v[u], inv_t, max_scaled);
         }
-        if (threadIdx.x == 0) total_sh = 0ull;
-        __syncthreads();
-        if (local) atomicAdd(&total_sh, local);
-        __syncthreads();
-        const unsigned long long t = total_sh;
-        __syncthreads();
-        return t;
+        return cluster_combine(c, local, false);
     };
     unsigned long long total = kept_mass(floor_key);
     if (total == 0ull) {  // numerical underflow: the reference falls back to the best candidate
-        if (threadIdx.x == 0) out[r] = best;
+        if (c.rank == 0 && threadIdx.x == 0) out[r] = best_index;
+        sample_cluster_sync();
         return;
     }
     // top-p: the smallest prefix whose cumulative share reaches P
@@ -340,7 +513,7 @@ sample_rows_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
         unsigned long long need = (unsigned long long)ceil((double)P * (double)total);
         if (need < 1ull) need = 1ull;
         if (need > total) need = total;
-        const SelectResult s = radix_select(row, V, inv_t, max_scaled, floor_key, false, need - 1ull, hist, bcast, &carry_sh);
+        const SelectResult s = radix_select(c, row, begin, end, inv_t, max_scaled, floor_key, false, need - 1ull);
         if (s.key > floor_key) floor_key = s.key;
         total = kept_mass(floor_key);
     }
@@ -349,18 +522,50 @@ sample_rows_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, 
     const float u = (float)(bits >> 40) * (1.0f / 16777216.0f);  // 24 bits → [0,1)
     unsigned long long target = (unsigned long long)((double)u * (double)total);
     if (target >= total) target = total - 1ull;
-    const SelectResult s = radix_select(row, V, inv_t, max_scaled, floor_key, false, target, hist, bcast, &carry_sh);
-    const int idx = nth_with_key(row, V, s.key, s.tie_rank, counts, &result);
-    if (threadIdx.x == 0) out[r] = idx >= 0 ? idx : best;
+    const SelectResult s = radix_select(c, row, begin, end, inv_t, max_scaled, floor_key, false, target);
+    write_nth_with_key(c, row, begin, end, s.key, s.tie_rank, best_index, &out[r]);
+    sample_cluster_sync();
 }
 
 MM_EXPORT int mm_sample_rows(const void* logits, void* out, int R, int V, const void* temperature, const void* top_k,
                              const void* top_p, const void* seeds, const void* counters, void* stream) {
-    MM_REQUIRE(R >= 0 && V > 0, "sample: bad sizes");
+    MM_REQUIRE(R >= 0 && R <= 65535 && V > 0, "sample: bad sizes");
     if (R == 0) return MM_OK;
-    sample_rows_kernel<<<R, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
-        (const float*)logits, (int32_t*)out, V, (const float*)temperature, (const int32_t*)top_k, (const float*)top_p,
-        (const unsigned long long*)seeds, (const unsigned long long*)counters);
+    // a wide row is shared by a cluster of CTAs (a power of two: other sizes place badly); a narrow one is one CTA's
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int ranks = 1;
+    while (ranks < SAMPLE_MAX_CLUSTER && V / (ranks * 2) >= 4096 && (ranks == 1 || R * ranks * 2 <= 2 * sms)) ranks *= 2;   // one wave of two CTAs per SM
+    // a copy of the CTA's slice in shared memory if it fits beside the histograms
+    const int chunk = (V + ranks - 1) / ranks;
+    const size_t room = 200 * 1024 - sizeof(SampleShared);
+    // (with the copy only one CTA fits on an SM: worth it while every CTA of the launch has an SM of its own)
+    const int cache_floats = ((size_t)chunk * sizeof(float) <= room && R * ranks <= sms) ? chunk : 0;
+    const size_t smem = sizeof(SampleShared) + (size_t)cache_floats * sizeof(float);
+    static size_t ceiling = 0;
+    if (smem > ceiling) {
+        if (cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            mm_set_last_error("sample: cannot reserve shared memory");
+            return MM_ERR_LAUNCH;
+        }
+        ceiling = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ranks, R);
+    cfg.blockDim = dim3(SAMPLE_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ranks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ranks > 1 ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, sample_rows_kernel, (const float*)logits, (int32_t*)out, V, (const float*)temperature,
+                       (const int32_t*)top_k, (const float*)top_p, (const unsigned long long*)seeds,
+                       (const unsigned long long*)counters, cache_floats);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }

@@ -357,14 +357,19 @@ def test_argmax_lowest_index_on_ties():
     assert got[3:] == logits[3:].argmax(-1).cpu().tolist()
 
 
-def test_sample_matches_the_plain_sampler():
-    rng = np.random.RandomState(0)
-    V, R = 1003, 64
+@pytest.mark.parametrize("V,R", [(1003, 64), (152064, 6), (50000, 40), (9001, 150)])
+def test_sample_matches_the_plain_sampler(V, R):
+    """One CTA per row for narrow rows; clusters of 2, 4 or 8 CTAs per row, with or without the slice kept in shared
+    memory, for wide ones.  Ties at the top, among the kept candidates and across the slices of a cluster."""
+    rng = np.random.RandomState(V % 1000)
     logits = (rng.randn(R, V) * 3).astype(np.float32)
     logits[5, 10] = logits[5, 20] = logits[5].max() + 1        # a tie at the top
+    logits[4, V - 3] = logits[4, 7] = logits[4, V // 2] = np.sort(logits[4])[-3]   # equal logits far apart among the best
+    logits[3, :] = np.round(logits[3, :])                      # many ties everywhere
     temps = rng.choice([0.0, 0.7, 1.0, 1.5], size=R).astype(np.float32)
     ks = rng.choice([0, 1, 5, 50], size=R).astype(np.int32)
     ps_ = rng.choice([1.0, 0.9, 0.5, 0.1], size=R).astype(np.float32)
+    temps[3:6], ks[3:6], ps_[3:6] = [1.0, 0.7, 1.5], [0, 50, 5], [0.9, 1.0, 0.5]
     seeds = rng.randint(1, 2 ** 31, size=R).astype(np.int64)
     counters = rng.randint(0, 1000, size=R).astype(np.int64)
     got = ops().sample_rows(t(logits), t(temps), t(ks, torch.int32), t(ps_), t(seeds, torch.int64), t(counters, torch.int64)).cpu().tolist()
