@@ -618,6 +618,27 @@ MM_EXPORT int mm_apply_penalties(void* logits, int R, int V, const void* recent,
     return MM_OK;
 }
 
+// recent: int32 [R, W] rings of the last widths[r] tokens of each row (entries beyond the width, or not yet filled,
+// are -1); lengths[r] counts the row's tokens so far.  Puts tokens[r] at lengths[r] % widths[r] and advances the count:
+// the window of a captured decode step follows the sequence without the host.
+__global__ void window_push_kernel(int32_t* __restrict__ recent, int W, const int32_t* __restrict__ widths,
+                                   long long* __restrict__ lengths, const int32_t* __restrict__ tokens, int R) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    const int w = widths[r] < W ? widths[r] : W;
+    if (w > 0) recent[(size_t)r * W + (int)(lengths[r] % w)] = tokens[r];
+    lengths[r] += 1;
+}
+
+MM_EXPORT int mm_window_push(void* recent, int R, int W, const void* widths, void* lengths, const void* tokens, void* stream) {
+    MM_REQUIRE(R >= 0 && W >= 1, "window_push: bad sizes");
+    if (R == 0) return MM_OK;
+    window_push_kernel<<<(R + 127) / 128, 128, 0, (cudaStream_t)stream>>>((int32_t*)recent, W, (const int32_t*)widths,
+                                                                         (long long*)lengths, (const int32_t*)tokens, R);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
 // uniform number of (seed, counter), exported so the host-side plain sampler draws the same stream
 MM_EXPORT float mm_uniform_from(unsigned long long seed, unsigned long long counter) {
     return (float)(mix64(seed, counter) >> 40) * (1.0f / 16777216.0f);

@@ -34,10 +34,12 @@ def context_bound(n: int, floor: int = 256) -> int:
 
 
 class DecodeSession:
-    def __init__(self, runner: ModelRunner, batch: int, kv_bound: int, greedy: bool = True, feed_back: bool = True):
+    def __init__(self, runner: ModelRunner, batch: int, kv_bound: int, greedy: bool = True, feed_back: bool = True,
+                 penalty_window: int = 0):
         """``kv_bound``: no bound request may grow beyond this many tokens.  ``feed_back``: the graph writes
         each sampled token into the next step's input itself; otherwise the caller fills ``token_ids``
-        before every step."""
+        before every step.  ``penalty_window`` > 0: the step applies soft-cap and repetition / frequency /
+        presence penalties over per-request rings of that many recent tokens, kept on the device."""
         self.runner = runner
         self.batch = batch
         self.kv_bound = min(kv_bound, runner.max_seq_len)
@@ -64,6 +66,12 @@ class DecodeSession:
             self.top_p = torch.ones(b, dtype=torch.float32, device=dev)
             self.seeds = torch.zeros(b, dtype=torch.int64, device=dev)
             self.counters = torch.zeros(b, dtype=torch.int64, device=dev)
+        self.penalty_window = penalty_window
+        if penalty_window > 0:
+            self.recent = torch.full((b, penalty_window), -1, dtype=torch.int32, device=dev)
+            self.widths = torch.zeros(b, dtype=torch.int32, device=dev)
+            self.lengths = torch.zeros(b, dtype=torch.int64, device=dev)
+            self.pen = torch.zeros((4, b), dtype=torch.float32, device=dev)     # repetition, frequency, presence, soft-cap
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.ids: List[Hashable] = []
         self.horizon = 0
@@ -71,7 +79,8 @@ class DecodeSession:
 
     # ---- binding -----------------------------------------------------------------------
     def bind(self, request_ids: Sequence[Hashable], horizon: int, first_tokens: Sequence[int],
-             sampling: Optional[Sequence[SamplingParams]] = None, draw_counters: Optional[Sequence[int]] = None) -> None:
+             sampling: Optional[Sequence[SamplingParams]] = None, draw_counters: Optional[Sequence[int]] = None,
+             histories: Optional[Sequence[Sequence[int]]] = None) -> None:
         """Points the session at ``request_ids`` for ``horizon`` steps.  Raises MemoryError (and changes
         nothing) when the pages for the horizon are not free, ValueError when the bound is too small."""
         mgr, dev = self.runner.manager, self.runner.rt.device
@@ -106,16 +115,40 @@ class DecodeSession:
             self.top_p.copy_(torch.tensor([p.top_p for p in params], dtype=torch.float32))
             self.seeds.copy_(torch.tensor([p.seed & 0x7FFFFFFFFFFFFFFF for p in params], dtype=torch.int64))
             self.counters.copy_(torch.tensor(list(draw_counters or [0] * self.batch), dtype=torch.int64))
+        if self.penalty_window > 0:
+            # every request's ring holds its last `width` tokens, token number n at place n % width
+            params = list(sampling)
+            W = self.penalty_window
+            ring = torch.full((self.batch, W), -1, dtype=torch.int32)
+            widths, pen = [], torch.zeros((4, self.batch), dtype=torch.float32)
+            for i, p in enumerate(params):
+                w = min(p.penalty_window, W) if p.penalties_active else 0
+                widths.append(w)
+                hist = list(histories[i])
+                for n in range(max(0, len(hist) - w), len(hist)):
+                    ring[i, n % w] = hist[n]
+                pen[0, i] = p.repetition_penalty if p.penalties_active else 1.0
+                pen[1, i] = p.frequency_penalty if p.penalties_active else 0.0
+                pen[2, i] = p.presence_penalty if p.penalties_active else 0.0
+                pen[3, i] = p.final_logit_softcap
+            self.recent.copy_(ring)
+            self.widths.copy_(torch.tensor(widths, dtype=torch.int32))
+            self.lengths.copy_(torch.tensor([len(h) for h in histories], dtype=torch.int64))
+            self.pen.copy_(pen)
 
     # ---- one step's launches --------------------------------------------------------------
     def _launch(self) -> None:
         self.ctx.derived.clear()
         self.logits = self.runner.forward(self.ctx)
+        if self.penalty_window > 0:
+            ops.apply_penalties(self.logits, self.recent, self.pen[0], self.pen[1], self.pen[2], self.pen[3])
         if self.greedy:
             ops.argmax_rows(self.logits, self.out_tokens)
         else:
             ops.sample_rows(self.logits, self.temperature, self.top_k, self.top_p, self.seeds, self.counters, self.out_tokens)
             self.counters += 1
+        if self.penalty_window > 0:
+            ops.window_push(self.recent, self.widths, self.lengths, self.out_tokens)
         self.positions += 1
         if self.feed_back:
             self.token_ids.copy_(self.out_tokens)

@@ -143,8 +143,10 @@ class Engine:
         """Runs the current set of decoding requests through a captured graph until one of them finishes
         or the horizon ends.  Returns False (nothing done) when a graph run is not possible or not worth it."""
         reqs = list(sched.running)
+        # soft-cap and penalties run inside the captured step, over rings of recent tokens kept on the device
+        window = 0
         if any(r.sampling.penalties_active or r.sampling.final_logit_softcap > 0 for r in reqs):
-            return False
+            window = context_bound(max([r.sampling.penalty_window for r in reqs if r.sampling.penalties_active] + [1]), floor=16)
         mgr = self.runner.manager
         horizon = min(min(r.max_new - len(r.generated) for r in reqs),
                       min(self.sched_cfg.max_seq_len - len(r.tokens) for r in reqs))
@@ -155,16 +157,17 @@ class Engine:
         if bound > self.runner.max_seq_len:
             bound = self.runner.max_seq_len
         greedy = all(r.sampling.greedy for r in reqs)
-        key = (len(reqs), bound, greedy)
+        key = (len(reqs), bound, greedy, window)
         sess = self._sessions.get(key)
         if sess is None:
-            sess = DecodeSession(self.runner, len(reqs), bound, greedy=greedy, feed_back=False)
+            sess = DecodeSession(self.runner, len(reqs), bound, greedy=greedy, feed_back=False, penalty_window=window)
             self._sessions[key] = sess
         ids = [r.id for r in reqs]
         firsts = [r.tokens[-1] for r in reqs]
         while True:
             try:
-                sess.bind(ids, horizon, firsts, [r.sampling for r in reqs], [len(r.generated) for r in reqs])
+                sess.bind(ids, horizon, firsts, [r.sampling for r in reqs], [len(r.generated) for r in reqs],
+                          [r.tokens for r in reqs] if window else None)
                 break
             except MemoryError:
                 horizon //= 2          # fewer pages ahead; below the threshold the eager path (and preemption) decides

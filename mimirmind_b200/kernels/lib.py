@@ -52,6 +52,7 @@ _PROTOTYPES = {
     "mm_argmax_rows_split": [P, P, P, P, I, I, I, P],
     "mm_sample_rows": [P, P, I, I, P, P, P, P, P, P],
     "mm_apply_penalties": [P, I, I, P, I, P, P, P, P, P],
+    "mm_window_push": [P, I, I, P, P, P, P],
 }
 
 

@@ -578,6 +578,20 @@ def apply_penalties(logits: torch.Tensor, recent: Optional[torch.Tensor], repeti
     return logits
 
 
+def window_push(recent: torch.Tensor, widths: torch.Tensor, lengths: torch.Tensor, tokens: torch.Tensor) -> None:
+    """recent int32 [R, W]: per row a ring of its last widths[r] tokens; writes tokens[r] at lengths[r] % widths[r]
+    and adds one to lengths[r] (int64)."""
+    _need(recent, "recent tokens", torch.int32)
+    _need(widths, "window widths", torch.int32)
+    _need(lengths, "sequence lengths", torch.int64)
+    _need(tokens, "tokens", torch.int32)
+    r, w = recent.shape
+    if widths.numel() != r or lengths.numel() != r or tokens.numel() != r:
+        raise KernelError("window_push: one width, length and token per row")
+    check(_lib.load().mm_window_push(recent.data_ptr(), r, w, widths.data_ptr(), lengths.data_ptr(), tokens.data_ptr(), _stream()),
+          "window_push")
+
+
 def uniform_from(seed: int, counter: int) -> float:
     """The uniform number in [0,1) the device sampler draws for (seed, counter)."""
     return float(_lib.load().mm_uniform_from(seed & 0xFFFFFFFFFFFFFFFF, counter & 0xFFFFFFFFFFFFFFFF))

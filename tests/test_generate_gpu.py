@@ -215,3 +215,34 @@ def test_long_prompt_portions_replayed_as_graphs_equal_eager_steps(tmp_path):
         ops.check_tcgen05_errors(torch.device("cuda"))
     finally:
         runner_mod.PREFILL_GRAPH_MIN_TOKENS = old
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_penalties_and_softcap_inside_the_captured_step_equal_the_eager_steps(model_folders, dtype):
+    """Repetition / frequency / presence penalties and the soft-cap run inside the decode graph over rings of recent
+    tokens kept on the device: same tokens as stepping eagerly, where the host rebuilds the window every step.
+    Windows shorter and longer than the histories, a request without penalties beside them, greedy and sampled."""
+    from mimirmind_b200 import Engine, SamplingParams
+    name = "B" if dtype == "float32" else "E"
+    eng = Engine.from_folder(model_folders(name, dtype), dtype=dtype, cache_tokens=2048, max_context=TINY[name]["max_position_embeddings"],
+                             token_budget=64, max_active=4)
+    V = TINY[name]["vocab_size"]
+    prompts = [random_tokens(V, n, 40 + n) for n in (9, 30, 5, 17)]
+    for greedy in (True, False):
+        t = 0.0 if greedy else 0.9
+        params = [SamplingParams(temperature=t, seed=5, repetition_penalty=1.3, penalty_window=8),
+                  SamplingParams(temperature=t, seed=6, frequency_penalty=0.4, presence_penalty=0.2, penalty_window=200, final_logit_softcap=30.0),
+                  SamplingParams(temperature=t, seed=7),
+                  SamplingParams(temperature=t, seed=8, top_k=20, repetition_penalty=0.8, frequency_penalty=0.1, penalty_window=33)]
+        outs = {}
+        for graphs in (False, True):
+            eng.use_graphs = graphs
+            before = eng.graph_steps
+            res = eng.generate(prompts, max_new_tokens=40, sampling=params, use_eos=False)
+            outs[graphs] = [r.tokens for r in res]
+            assert (eng.graph_steps > before) == graphs
+        assert outs[True] == outs[False], greedy
+        # the penalties matter: without them the first request repeats more
+        eng.use_graphs = True
+        plain_run = eng.generate(prompts[:1], max_new_tokens=40, sampling=SamplingParams(temperature=t, seed=5), use_eos=False)[0].tokens
+        assert plain_run != outs[True][0]
