@@ -86,6 +86,12 @@ class Engine:
                    max_active=cfg.serving.maxActiveRequests, prefill_chunk=cfg.serving.prefillChunk)
 
     # ---- generation --------------------------------------------------------------------
+    def serve(self, max_graph_steps: int = 0) -> "ServingLoop":
+        """A loop to which requests can be added while others run (the counterpart of the reference's
+        ContinuousBatcher::submit, src/runtime/serving/ContinuousBatcher.cpp:87-123).  ``max_graph_steps`` > 0 caps
+        how many captured decode steps run between two chances to admit a new request."""
+        return ServingLoop(self, max_graph_steps)
+
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 256,
                  sampling=None, stop_ids: Sequence[int] = (), use_eos: bool = True,
                  on_token: Optional[Callable[[int, int], bool]] = None) -> List[GenerateResult]:
@@ -97,51 +103,18 @@ class Engine:
         params = list(sampling) if isinstance(sampling, (list, tuple)) else [sampling] * n
         if len(params) != n:
             raise ValueError("one SamplingParams per prompt")
-        stops = tuple(stop_ids) + (self.eos_ids if use_eos else ())
-        sched = Scheduler(self.sched_cfg, self.runner.manager)
-        reqs = [Request(id=("gen", i), prompt=list(p), max_new=max_new_tokens, sampling=params[i].resolved(),
-                        stop_ids=stops) for i, p in enumerate(prompts)]
-        t0 = time.perf_counter()
-        first_at: Dict[Hashable, float] = {}
-        last_at: Dict[Hashable, float] = {}
-        for r in reqs:
-            sched.add(r)
-        while sched.has_work():
-            if self.use_graphs and sched.all_decoding() and self._decode_run(sched, first_at, last_at, on_token):
-                continue
-            plan = sched.schedule()
-            if not plan:
-                if sched.has_work():
-                    raise RuntimeError("scheduler made no progress")   # cannot happen: a lone request fails instead
-                break
-            sampled = self._run_plan(plan)
-            now = time.perf_counter()
-            for p in plan:
-                if p.samples:
-                    first_at.setdefault(p.request.id, now)
-                    last_at[p.request.id] = now
-            sched.commit(plan, sampled)
-            if on_token is not None:
-                for p in plan:
-                    if p.samples and p.request.state != "finished":
-                        if on_token(p.request.id[1], sampled[p.request.id]) is False:
-                            sched.cancel(p.request.id)
-                    elif p.samples:
-                        on_token(p.request.id[1], sampled[p.request.id])
-        self.last_metrics = sched.metrics
-        out = []
-        for r in reqs:
-            st = GenerateStats(prompt_tokens=len(r.prompt), generated_tokens=len(r.generated),
-                               hit_stop=r.hit_stop, finish_reason=r.finish_reason or "", preemptions=r.preemptions)
-            if r.id in first_at:
-                st.prefill_ms = (first_at[r.id] - t0) * 1e3
-                st.decode_ms = (last_at[r.id] - first_at[r.id]) * 1e3
-            out.append(GenerateResult(list(r.generated), st))
-        return out
+        loop = self.serve()
+        handles = [loop.submit(p, max_new_tokens, params[i], stop_ids, use_eos,
+                               (lambda tok, i=i: on_token(i, tok)) if on_token is not None else None)
+                   for i, p in enumerate(prompts)]
+        loop.run_until_idle()
+        self.last_metrics = loop.sched.metrics
+        return [loop.result(h) for h in handles]
 
-    def _decode_run(self, sched: Scheduler, first_at, last_at, on_token) -> bool:
+    def _decode_run(self, loop: "ServingLoop") -> bool:
         """Runs the current set of decoding requests through a captured graph until one of them finishes
         or the horizon ends.  Returns False (nothing done) when a graph run is not possible or not worth it."""
+        sched, first_at, last_at = loop.sched, loop.first_at, loop.last_at
         reqs = list(sched.running)
         # soft-cap and penalties run inside the captured step, over rings of recent tokens kept on the device
         window = 0
@@ -152,6 +125,8 @@ class Engine:
                       min(self.sched_cfg.max_seq_len - len(r.tokens) for r in reqs))
         if horizon < self.graph_min_steps:
             return False
+        if loop.max_graph_steps > 0:
+            horizon = min(horizon, max(loop.max_graph_steps, self.graph_min_steps))
         longest = max(len(r.tokens) for r in reqs)
         bound = context_bound(longest + horizon)
         if bound > self.runner.max_seq_len:
@@ -191,7 +166,7 @@ class Engine:
                 first_at.setdefault(r.id, now)
                 last_at[r.id] = now
                 done = sched.accept_token(r, tok)
-                if on_token is not None and on_token(r.id[1], tok) is False and not done:
+                if loop.deliver(r, tok) is False and not done:
                     sched.cancel(r.id)
                     done = True
                 if done:
@@ -239,3 +214,86 @@ class Engine:
             for p, t in zip(rows, host):
                 sampled[p.request.id] = t
         return sampled
+
+
+class ServingLoop:
+    """Requests in, tokens out, one scheduler step (or one run of captured decode steps) per ``step()``."""
+
+    def __init__(self, engine: Engine, max_graph_steps: int = 0):
+        self.engine = engine
+        self.sched = Scheduler(engine.sched_cfg, engine.runner.manager)
+        self.max_graph_steps = max_graph_steps
+        self.first_at: Dict[Hashable, float] = {}
+        self.last_at: Dict[Hashable, float] = {}
+        self._requests: Dict[int, Request] = {}
+        self._callbacks: Dict[Hashable, Callable[[int], Optional[bool]]] = {}
+        self._submitted_at: Dict[Hashable, float] = {}
+        self._next = 0
+
+    def submit(self, prompt: Sequence[int], max_new_tokens: int = 256, sampling: Optional[SamplingParams] = None,
+               stop_ids: Sequence[int] = (), use_eos: bool = True,
+               on_token: Optional[Callable[[int], Optional[bool]]] = None) -> int:
+        """Queues a request and returns its handle.  ``on_token(token)`` is called for every generated token and may
+        return False to stop the request.  A request that can never run is finished at once (``result`` says why)."""
+        handle = self._next
+        self._next += 1
+        stops = tuple(stop_ids) + (self.engine.eos_ids if use_eos else ())
+        req = Request(id=("gen", handle), prompt=list(prompt), max_new=max_new_tokens,
+                      sampling=(sampling or SamplingParams()).resolved(), stop_ids=stops)
+        self._requests[handle] = req
+        self._submitted_at[req.id] = time.perf_counter()
+        if on_token is not None:
+            self._callbacks[req.id] = on_token
+        self.sched.add(req)
+        return handle
+
+    def deliver(self, req: Request, tok: int) -> Optional[bool]:
+        cb = self._callbacks.get(req.id)
+        return cb(tok) if cb is not None else None
+
+    def has_work(self) -> bool:
+        return self.sched.has_work()
+
+    def step(self) -> bool:
+        """One unit of work.  Returns whether anything is left to do."""
+        eng, sched = self.engine, self.sched
+        if not sched.has_work():
+            return False
+        if eng.use_graphs and sched.all_decoding() and eng._decode_run(self):
+            return sched.has_work()
+        plan = sched.schedule()
+        if not plan:
+            if sched.has_work():
+                raise RuntimeError("scheduler made no progress")   # cannot happen: a lone request fails instead
+            return False
+        sampled = eng._run_plan(plan)
+        now = time.perf_counter()
+        for p in plan:
+            if p.samples:
+                self.first_at.setdefault(p.request.id, now)
+                self.last_at[p.request.id] = now
+        sched.commit(plan, sampled)
+        for p in plan:
+            if p.samples and self.deliver(p.request, sampled[p.request.id]) is False and p.request.state != "finished":
+                sched.cancel(p.request.id)
+        return sched.has_work()
+
+    def run_until_idle(self) -> None:
+        while self.step():
+            pass
+
+    def cancel(self, handle: int) -> bool:
+        return self.sched.cancel(self._requests[handle].id)
+
+    def finished(self, handle: int) -> bool:
+        return self._requests[handle].state == "finished"
+
+    def result(self, handle: int) -> GenerateResult:
+        """Tokens and statistics of a request (complete once ``finished(handle)``)."""
+        r = self._requests[handle]
+        st = GenerateStats(prompt_tokens=len(r.prompt), generated_tokens=len(r.generated),
+                           hit_stop=r.hit_stop, finish_reason=r.finish_reason or "", preemptions=r.preemptions)
+        if r.id in self.first_at:
+            st.prefill_ms = (self.first_at[r.id] - self._submitted_at[r.id]) * 1e3
+            st.decode_ms = (self.last_at[r.id] - self.first_at[r.id]) * 1e3
+        return GenerateResult(list(r.generated), st)

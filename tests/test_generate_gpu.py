@@ -246,3 +246,42 @@ def test_penalties_and_softcap_inside_the_captured_step_equal_the_eager_steps(mo
         eng.use_graphs = True
         plain_run = eng.generate(prompts[:1], max_new_tokens=40, sampling=SamplingParams(temperature=t, seed=5), use_eos=False)[0].tokens
         assert plain_run != outs[True][0]
+
+
+def test_requests_added_while_others_run_get_the_tokens_they_get_alone(model_folders):
+    """The serving loop: two requests start, a third and a fourth are submitted between steps (one while the others
+    decode in captured steps), one is cancelled by its callback.  In float32 every request's tokens equal those it
+    gets alone, token for token."""
+    from mimirmind_b200 import Engine, SamplingParams
+    eng = Engine.from_folder(model_folders("A", "float32"), dtype="float32", cache_tokens=1024,
+                             max_context=TINY["A"]["max_position_embeddings"], token_budget=32, max_active=4)
+    V = TINY["A"]["vocab_size"]
+    prompts = [random_tokens(V, n, 70 + n) for n in (20, 7, 45, 3)]
+    alone = [eng.generate([p], max_new_tokens=30, use_eos=False)[0].tokens for p in prompts]
+    loop = eng.serve(max_graph_steps=8)
+    seen = {i: [] for i in range(4)}
+    stop_third_after = 5
+
+    def cb(i):
+        def on_token(tok):
+            seen[i].append(tok)
+            return not (i == 2 and len(seen[i]) >= stop_third_after)
+        return on_token
+
+    h = [loop.submit(prompts[0], 30, use_eos=False, on_token=cb(0)), loop.submit(prompts[1], 30, use_eos=False, on_token=cb(1))]
+    for _ in range(3):
+        assert loop.step()
+    h.append(loop.submit(prompts[2], 30, use_eos=False, on_token=cb(2)))
+    while not (loop.sched.all_decoding() and len(seen[0]) >= 10):
+        assert loop.step()
+    h.append(loop.submit(prompts[3], 30, SamplingParams(), use_eos=False, on_token=cb(3)))      # arrives during decoding
+    loop.run_until_idle()
+    assert not loop.has_work() and all(loop.finished(x) for x in h)
+    res = [loop.result(x) for x in h]
+    for i in (0, 1, 3):
+        assert res[i].tokens == alone[i] == seen[i], i
+        assert res[i].stats.finish_reason == "length" and res[i].stats.generated_tokens == 30
+    assert res[2].tokens == alone[2][:stop_third_after] and res[2].stats.finish_reason == "cancelled"
+    assert eng.graph_steps > 0
+    eng.runner.manager.check()
+    assert not eng.runner.manager.live_requests()
