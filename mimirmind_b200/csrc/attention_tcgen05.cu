@@ -10,12 +10,14 @@
 //                         halves of a row exchange their maxima through shared memory), P rounded
 //                         to bf16 into shared memory in the 128-byte-swizzled K-major layout the
 //                         tensor core reads
-//     PV = P V            tcgen05.mma 128x128x16 x 8, V read MN-major (as stored: keys x head dim)
-//     O  = O * alpha + PV  in registers (a thread holds its row of O), so tensor memory is never
-//                         written by threads
-// S, P and PV are double-buffered: while the softmax threads work on tile t the tensor core already
-// computes S of tile t+1 and P V of tile t, and a thread adds P V of tile t into its O only after it
-// has published P of tile t+1.
+//     O += P V            tcgen05.mma 128x128x16 x 8, V read MN-major (as stored: keys x head dim), accumulated
+//                         in tensor memory over all key tiles
+// O is rescaled lazily: probabilities are taken relative to a reference maximum that is only moved (and O, in
+// tensor memory, multiplied by the matching factor with tcgen05.ld / tcgen05.st) when the row's maximum has grown
+// by more than 2^8 since; until then P may exceed 1 by that factor, which bf16 and the fp32 sums hold easily.
+// After the first few tiles a row's maximum rarely grows that much, so the threads neither read nor scale O per
+// tile.  S and P are double-buffered: while the softmax threads work on tile t the tensor core already computes S
+// of tile t+1 and adds P V of tile t-1.
 // Warp 0 = TMA producer for keys (and Q), warp 10 = TMA producer for values: every lane fetches one half of one
 // page, so the 16 to 32 small copies of a tile are issued at once (one thread issuing them in turn was the
 // bottleneck of the whole kernel); warp 1 = MMA issuer and tensor-memory owner; warps 2..9 = softmax and output.  Same formula as the other attention kernels (reference src/compute/Attention.cpp:43-94).
@@ -37,7 +39,8 @@ constexpr int ATT_TC_THREADS = 352;            // K producer warp, MMA warp, 8 s
 constexpr int V_PRODUCER_WARP = 10;
 constexpr int SOFTMAX_WARPS = 8;               // barriers between the softmax warps and the tensor core count warps, not
                                                // threads: one arrival per softmax warp on one mbarrier serialise and cost more than the math
-constexpr int TMEM_COLS_ATT = 512;              // S0, S1: columns 0..255; PV0, PV1: columns 256..511
+constexpr int TMEM_COLS_ATT = 512;              // S0, S1: columns 0..255; O: columns 256..383
+constexpr float RESCALE_STEP = 8.0f;            // log2 of how far a row's maximum may run ahead of its reference
 
 struct AttCtl {
     uint64_t q_full;
@@ -48,8 +51,8 @@ struct AttCtl {
     uint64_t s_full[2];      // S buffer b holds Q K^T of a tile (tensor core -> softmax)
     uint64_t s_free[2];      // ... has been read (softmax -> tensor core), one arrival per softmax warp
     uint64_t p_full[2];      // P buffer b is written and fenced (softmax -> tensor core), one arrival per softmax warp
-    uint64_t pv_full[2];     // PV buffer b holds P V of a tile (tensor core -> softmax)
-    uint64_t pv_free[2];     // ... has been added into O (softmax -> tensor core), one arrival per softmax warp
+    uint64_t pv_done[2];     // P V of a tile with parity b has been added into O: P buffer b is free, O is at rest until
+                             // the next P is published (tensor core -> softmax)
     uint32_t tmem_base;
     int abort_flag;
     uint64_t x_full[2];      // both halves of every row have posted their maximum (one arrival per softmax warp)
@@ -68,6 +71,17 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
         : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // 2^x on the special-function unit in one instruction (relative error 2^-22, far below the bf16 rounding of P)
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -132,8 +146,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
             mbar_init(smem_u32(&ctl->s_full[b]), 1);
             mbar_init(smem_u32(&ctl->s_free[b]), SOFTMAX_WARPS);
             mbar_init(smem_u32(&ctl->p_full[b]), SOFTMAX_WARPS);
-            mbar_init(smem_u32(&ctl->pv_full[b]), 1);
-            mbar_init(smem_u32(&ctl->pv_free[b]), SOFTMAX_WARPS);
+            mbar_init(smem_u32(&ctl->pv_done[b]), 1);
             mbar_init(smem_u32(&ctl->x_full[b]), SOFTMAX_WARPS);
         }
         mbar_init(smem_u32(&ctl->l_full), SOFTMAX_WARPS);
@@ -226,8 +239,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 if ((int)it + 1 < n_tiles_k && !issue_qk(it + 1)) { ok = false; break; }
                 const int s = it % KV_STAGES;
                 const uint32_t b = it & 1, u = it >> 1;
-                if (!mbar_wait(smem_u32(&ctl->p_full[b]), u & 1, abort_flag)) { ok = false; break; }
-                if (!mbar_wait(smem_u32(&ctl->pv_free[b]), (u & 1) ^ 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&ctl->p_full[b]), u & 1, abort_flag)) { ok = false; break; }      // P is there, O is rescaled
                 if (!mbar_wait(smem_u32(&ctl->v_full[s]), (it / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t p_addr = smem_u32(sP + b * TILE_BYTES), v_addr = smem_u32(sV + s * TILE_BYTES);
@@ -235,9 +247,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 for (int k = 0; k < BN / 16; ++k) {
                     const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;    // P: K-major over the keys
                     const uint32_t b_off = (uint32_t)k * 16 * 128;                  // V: 16 key rows of 128 bytes further
-                    umma_bf16(tmem_base + 256 + b * 128, smem_desc_sw128(p_addr + a_off, 16, 1024), smem_desc_sw128(v_addr + b_off, HALF_BYTES, 1024), IDESC_PV, k ? 1u : 0u);
+                    umma_bf16(tmem_base + 256, smem_desc_sw128(p_addr + a_off, 16, 1024), smem_desc_sw128(v_addr + b_off, HALF_BYTES, 1024), IDESC_PV, (it | (uint32_t)k) ? 1u : 0u);
                 }
-                umma_commit(smem_u32(&ctl->pv_full[b]));
+                umma_commit(smem_u32(&ctl->pv_done[b]));
                 umma_commit(smem_u32(&ctl->v_empty[s]));
             }
         }
@@ -251,28 +263,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         const bool row_valid = row < n_rows;
         const int wlo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + hsel * 64;
-        float o[64];
-#pragma unroll
-        for (int i = 0; i < 64; ++i) o[i] = 0.0f;
-        float m = -INFINITY, l = 0.0f;     // m: maximum of the whole row; l: sum over this thread's keys only
-        float alpha_prev = 1.0f;           // the factor that goes with the P V result not yet added into O
+        float m_ref = -INFINITY;           // the maximum the probabilities (and O) are currently taken relative to
+        float l = 0.0f;                    // sum over this thread's keys only, relative to m_ref
         uint32_t it = 0;
         bool ok = true;
         uint32_t sreg[64];
-        // adds this thread's 64 columns of P V of tile `t` into O
-        auto add_pv = [&](uint32_t t, float alpha) -> bool {
-            const uint32_t b = t & 1, u = t >> 1;
-            if (!mbar_wait(smem_u32(&ctl->pv_full[b]), u & 1, abort_flag)) return false;
-            tc_fence_after();
-            tmem_ld32_nowait(lane_addr + 256 + b * 128, sreg);
-            tmem_ld32_nowait(lane_addr + 256 + b * 128 + 32, sreg + 32);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 64; ++i) o[i] = fmaf(o[i], alpha, __uint_as_float(sreg[i]));
-            tc_fence_before();
-            warp_arrive(smem_u32(&ctl->pv_free[b]), lane);
-            return true;
-        };
         for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
             const uint32_t b = it & 1, u = it >> 1;
             if (!mbar_wait(smem_u32(&ctl->s_full[b]), u & 1, abort_flag)) { ok = false; break; }
@@ -302,10 +297,32 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
             ctl->xchg[b][hsel][row] = mx;
             warp_arrive(smem_u32(&ctl->x_full[b]), lane);
             if (!mbar_wait(smem_u32(&ctl->x_full[b]), u & 1, abort_flag)) { ok = false; break; }
-            mx = fmaxf(fmaxf(mx, ctl->xchg[b][hsel ^ 1][row]), m);
-            const float use = (mx == -INFINITY) ? 0.0f : mx * scale_log2;
-            const float alpha = fast_exp2(m * scale_log2 - use);
-            m = mx;
+            mx = fmaxf(mx, ctl->xchg[b][hsel ^ 1][row]);
+            // Move the reference only when the maximum has outgrown it by RESCALE_STEP (or there was none): both
+            // threads of a row see the same numbers and decide alike.  O of a row without a reference is still zero.
+            const bool move = mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * scale_log2 > RESCALE_STEP);
+            const bool scale_o = move && m_ref != -INFINITY;
+            if (__any_sync(0xffffffffu, scale_o)) {
+                // O is at rest once P V of the previous tile is done (the next one waits for this tile's P)
+                if (it >= 1 && !mbar_wait(smem_u32(&ctl->pv_done[(it - 1) & 1]), ((it - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const float alpha = scale_o ? fast_exp2((m_ref - mx) * scale_log2) : 1.0f;
+                uint32_t oreg[32];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    tmem_ld32_nowait(lane_addr + 256 + c * 32, oreg);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+                    tmem_st32(lane_addr + 256 + c * 32, oreg);
+                }
+                tmem_st_wait();
+                l *= alpha;
+            }
+            if (move) m_ref = mx;
+            const float use = (m_ref == -INFINITY) ? 0.0f : m_ref * scale_log2;
+            // P buffer b was last read by P V of tile it - 2
+            if (it >= 2 && !mbar_wait(smem_u32(&ctl->pv_done[b]), ((it - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
             // probabilities, rounded to bf16 as the tensor core will read them; this thread's 64 keys are the
             // [128 x 64] half `hsel` of P: 8 chunks of 16 bytes in row `row`, chunk index xor-ed with row % 8
             float sum = 0.0f;
@@ -322,28 +339,38 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 }
                 *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
-            l = l * alpha + sum;
+            l += sum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P is read by the tensor core (async proxy)
+            tc_fence_before();                                                // ... and O, if it was rescaled, is in tensor memory
             warp_arrive(smem_u32(&ctl->p_full[b]), lane);
-            // while the tensor core multiplies this P with V, take in the previous tile's P V
-            if (it >= 1 && !add_pv(it - 1, alpha_prev)) { ok = false; break; }
-            alpha_prev = alpha;
         }
-        if (ok && it >= 1) ok = add_pv(it - 1, alpha_prev);
-        // the row sum is the sum of the two halves (both are scaled to the same final maximum)
+        // O is complete when the last P V is done
+        if (ok && it >= 1) ok = mbar_wait(smem_u32(&ctl->pv_done[(it - 1) & 1]), ((it - 1) >> 1) & 1, abort_flag);
+        tc_fence_after();
+        // the row sum is the sum of the two halves (both are relative to the same reference)
         // the buffer the last tile did not use: everyone finished reading it before arriving for the last tile's exchange
         const int lb = it & 1;
         ctl->xchg[lb][hsel][row] = l;
         warp_arrive(smem_u32(&ctl->l_full), lane);
         if (ok) ok = mbar_wait(smem_u32(&ctl->l_full), 0, abort_flag);
         l += ctl->xchg[lb][hsel ^ 1][row];
+        if (ok && it >= 1) {
+            tmem_ld32_nowait(lane_addr + 256, sreg);
+            tmem_ld32_nowait(lane_addr + 256 + 32, sreg + 32);
+            tmem_ld_wait();
+        } else {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) sreg[i] = 0u;
+        }
         if (ok && row_valid) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             __nv_bfloat16* orow = out + ((size_t)(row0 + row) * H + h) * HD + hsel * 64;
 #pragma unroll
             for (int i = 0; i < 64; i += 8) {
-                *reinterpret_cast<uint4*>(orow + i) = make_uint4(pack_bf16x2(o[i] * inv, o[i + 1] * inv), pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv),
-                                                                 pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv), pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv));
+                float o[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(sreg[i + j]) * inv;
+                *reinterpret_cast<uint4*>(orow + i) = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
             }
         }
     }
