@@ -234,9 +234,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 umma_commit(smem_u32(&ctl->k_empty[s]));        // the key tile is free once these products have read it
                 return true;
             };
+            // Two tiles ahead: S of tile it + 2 goes where S of tile it was as soon as the softmax threads have taken
+            // that into registers (early in their work on tile it), so S of the next tile is always there when they
+            // come for it.
             if (ok && n_tiles_k > 0) ok = issue_qk(0);
+            if (ok && n_tiles_k > 1) ok = issue_qk(1);
             for (uint32_t it = 0; (int)it < n_tiles_k && ok; ++it) {
-                if ((int)it + 1 < n_tiles_k && !issue_qk(it + 1)) { ok = false; break; }
+                if ((int)it + 2 < n_tiles_k && !issue_qk(it + 2)) { ok = false; break; }
                 const int s = it % KV_STAGES;
                 const uint32_t b = it & 1, u = it >> 1;
                 if (!mbar_wait(smem_u32(&ctl->p_full[b]), u & 1, abort_flag)) { ok = false; break; }      // P is there, O is rescaled
