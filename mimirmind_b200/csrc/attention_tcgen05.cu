@@ -5,20 +5,22 @@
 // from the page pool (in this cache layout one page of one KV head is one contiguous
 // [page_size, 128] block).  Per key tile:
 //     S  = Q K^T          tcgen05.mma 128x128x16 x 8, both operands K-major, S in tensor memory
-//     softmax             256 threads, two per query row (64 keys and 64 output columns each):
-//                         tcgen05.ld of the row, mask by position, running max/sum in fp32 (the two
-//                         halves of a row exchange their maxima through shared memory), P rounded
-//                         to bf16 into shared memory in the 128-byte-swizzled K-major layout the
-//                         tensor core reads
-//     O += P V            tcgen05.mma 128x128x16 x 8, V read MN-major (as stored: keys x head dim), accumulated
-//                         in tensor memory over all key tiles
+//     softmax             two groups of 128 threads, one thread per query row in each: group 0 takes the even
+//                         key tiles, group 1 the odd ones, each with a maximum, a sum and an O accumulator of
+//                         its own (merged at the end), so no thread ever waits for another thread's maximum
+//                         and one group's exponentials overlap the other group's loads, masks and stores:
+//                         tcgen05.ld of the row, mask by position, P rounded to bf16 into shared memory in
+//                         the 128-byte-swizzled K-major layout the tensor core reads
+//     O[g] += P V         tcgen05.mma 128x128x16 x 8, V read MN-major (as stored: keys x head dim), accumulated
+//                         in tensor memory over all key tiles of the group
 // O is rescaled lazily: probabilities are taken relative to a reference maximum that is only moved (and O, in
 // tensor memory, multiplied by the matching factor with tcgen05.ld / tcgen05.st) when the row's maximum has grown
 // by more than 2^8 since; until then P may exceed 1 by that factor, which bf16 and the fp32 sums hold easily.
 // After the first few tiles a row's maximum rarely grows that much, so the threads neither read nor scale O per
 // tile.  S and P are double-buffered: while the softmax threads work on tile t the tensor core already computes S
 // of tile t+1 and adds P V of tile t-1.
-// Warp 0 = TMA producer for keys (and Q), warp 10 = TMA producer for values: every lane fetches one half of one
+// Warp 1 issues Q K^T, warp 11 issues P V (a single issuing thread, waiting on the barriers of both products in
+// turn, was what bound the kernel); warp 0 = TMA producer for keys (and Q), warp 10 = TMA producer for values: every lane fetches one half of one
 // page, so the 16 to 32 small copies of a tile are issued at once (one thread issuing them in turn was the
 // bottleneck of the whole kernel); warp 1 = MMA issuer and tensor-memory owner; warps 2..9 = softmax and output.  Same formula as the other attention kernels (reference src/compute/Attention.cpp:43-94).
 // All mbarrier waits are bounded; on a time-out the kernel frees its tensor memory, sets `err`
@@ -35,11 +37,13 @@ constexpr int BN = 128;          // keys per tile
 constexpr int KV_STAGES = 2;
 constexpr int HALF_BYTES = 128 * 64 * 2;        // a [128 rows x 64 columns] bf16 sub-tile, 128 bytes per row
 constexpr int TILE_BYTES = 2 * HALF_BYTES;      // [128 x 128] as two column halves
-constexpr int ATT_TC_THREADS = 352;            // K producer warp, MMA warp, 8 softmax warps, V producer warp
+constexpr int ATT_TC_THREADS = 384;            // K producer warp, Q K^T issuer, 8 softmax warps, V producer warp, P V issuer
 constexpr int V_PRODUCER_WARP = 10;
-constexpr int SOFTMAX_WARPS = 8;               // barriers between the softmax warps and the tensor core count warps, not
+constexpr int PV_ISSUER_WARP = 11;             // the two products have issuers of their own: each waits on its own barriers
+constexpr int SOFTMAX_WARPS = 8;               // two groups of four
+constexpr int GROUP_WARPS = 4;                 // barriers between the softmax warps and the tensor core count warps, not
                                                // threads: one arrival per softmax warp on one mbarrier serialise and cost more than the math
-constexpr int TMEM_COLS_ATT = 512;              // S0, S1: columns 0..255; O: columns 256..383
+constexpr int TMEM_COLS_ATT = 512;              // S of the even / odd tiles: columns 0..255; O of the even / odd tiles: 256..511
 constexpr float RESCALE_STEP = 8.0f;            // log2 of how far a row's maximum may run ahead of its reference
 
 struct AttCtl {
@@ -55,9 +59,8 @@ struct AttCtl {
                              // the next P is published (tensor core -> softmax)
     uint32_t tmem_base;
     int abort_flag;
-    uint64_t x_full[2];      // both halves of every row have posted their maximum (one arrival per softmax warp)
-    uint64_t l_full;         // ... their sum, at the end
-    float xchg[2][2][128];   // [tile parity][half of the row][row]: row maxima; after the last tile [0][..][..] carries the row sums
+    uint64_t l_full;         // both groups have posted each row's reference maximum and sum (one arrival per softmax warp)
+    float xchg[2][2][128];   // [group][maximum, sum][row]
 };
 
 __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
@@ -71,15 +74,17 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
         : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+                   "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -144,10 +149,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&ctl->s_full[b]), 1);
-            mbar_init(smem_u32(&ctl->s_free[b]), SOFTMAX_WARPS);
-            mbar_init(smem_u32(&ctl->p_full[b]), SOFTMAX_WARPS);
+            mbar_init(smem_u32(&ctl->s_free[b]), GROUP_WARPS);
+            mbar_init(smem_u32(&ctl->p_full[b]), GROUP_WARPS);
             mbar_init(smem_u32(&ctl->pv_done[b]), 1);
-            mbar_init(smem_u32(&ctl->x_full[b]), SOFTMAX_WARPS);
         }
         mbar_init(smem_u32(&ctl->l_full), SOFTMAX_WARPS);
         ctl->abort_flag = 0;
@@ -213,7 +217,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         if (lane == 0) {
             // ---- MMA issuer ----
             constexpr uint32_t IDESC_QK = idesc_bf16(BM, BN, false);
-            constexpr uint32_t IDESC_PV = idesc_bf16(BM, HD, true);
             const int n_tiles_k = kt_end - kt_begin;
             const uint32_t q_addr = smem_u32(sQ);
             bool ok = mbar_wait(smem_u32(&ctl->q_full), 0, abort_flag);
@@ -234,147 +237,163 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 umma_commit(smem_u32(&ctl->k_empty[s]));        // the key tile is free once these products have read it
                 return true;
             };
-            // Two tiles ahead: S of tile it + 2 goes where S of tile it was as soon as the softmax threads have taken
-            // that into registers (early in their work on tile it), so S of the next tile is always there when they
-            // come for it.
-            if (ok && n_tiles_k > 0) ok = issue_qk(0);
-            if (ok && n_tiles_k > 1) ok = issue_qk(1);
-            for (uint32_t it = 0; (int)it < n_tiles_k && ok; ++it) {
-                if ((int)it + 2 < n_tiles_k && !issue_qk(it + 2)) { ok = false; break; }
+            // Two tiles ahead: S of tile it + 2 goes where S of tile it was as soon as its group has taken that into
+            // registers (early in its work on tile it), so S of a group's next tile is there when it comes for it.
+            for (uint32_t it = 0; (int)it < n_tiles_k && ok; ++it) ok = issue_qk(it);
+        }
+    } else if (warp == PV_ISSUER_WARP) {
+        if (lane == 0) {
+            // ---- P V issuer ----
+            constexpr uint32_t IDESC_PV = idesc_bf16(BM, HD, true);
+            const int n_tiles_k = kt_end - kt_begin;
+            for (uint32_t it = 0; (int)it < n_tiles_k; ++it) {
                 const int s = it % KV_STAGES;
                 const uint32_t b = it & 1, u = it >> 1;
-                if (!mbar_wait(smem_u32(&ctl->p_full[b]), u & 1, abort_flag)) { ok = false; break; }      // P is there, O is rescaled
-                if (!mbar_wait(smem_u32(&ctl->v_full[s]), (it / KV_STAGES) & 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&ctl->p_full[b]), u & 1, abort_flag)) break;       // P is there, O is rescaled
+                if (!mbar_wait(smem_u32(&ctl->v_full[s]), (it / KV_STAGES) & 1, abort_flag)) break;
                 tc_fence_after();
                 const uint32_t p_addr = smem_u32(sP + b * TILE_BYTES), v_addr = smem_u32(sV + s * TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k) {
                     const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;    // P: K-major over the keys
                     const uint32_t b_off = (uint32_t)k * 16 * 128;                  // V: 16 key rows of 128 bytes further
-                    umma_bf16(tmem_base + 256, smem_desc_sw128(p_addr + a_off, 16, 1024), smem_desc_sw128(v_addr + b_off, HALF_BYTES, 1024), IDESC_PV, (it | (uint32_t)k) ? 1u : 0u);
+                    umma_bf16(tmem_base + 256 + b * 128, smem_desc_sw128(p_addr + a_off, 16, 1024), smem_desc_sw128(v_addr + b_off, HALF_BYTES, 1024), IDESC_PV, (u | (uint32_t)k) ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&ctl->pv_done[b]));
                 umma_commit(smem_u32(&ctl->v_empty[s]));
             }
         }
     } else {
-        // ---- softmax and output: two threads per query row ----
-        // Warp w may read tensor-memory lanes 32*(w%4)..+31; warps 2..5 take keys/columns 0..63, warps 6..9 take 64..127.
+        // ---- softmax and output: group g (warps 2 + 4g .. 5 + 4g) takes the key tiles of parity g, one thread per row ----
+        // Warp w may read tensor-memory lanes 32*(w%4)..+31.
         const int q = warp & 3;
-        const int hsel = (warp - 2) >> 2;
+        const uint32_t g = (uint32_t)(warp - 2) >> 2;
         const int row = q * 32 + lane;
         const int pos = pos0 + row;
         const bool row_valid = row < n_rows;
         const int wlo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + hsel * 64;
-        float m_ref = -INFINITY;           // the maximum the probabilities (and O) are currently taken relative to
-        float l = 0.0f;                    // sum over this thread's keys only, relative to m_ref
-        uint32_t it = 0;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        const uint32_t s_addr = lane_addr + g * 128, o_addr = lane_addr + 256 + g * 128;
+        float m_ref = -INFINITY;           // the maximum the group's probabilities (and its O) are taken relative to
+        float l = 0.0f;                    // the group's sum for this row, relative to m_ref
+        const int n_tiles_k = kt_end - kt_begin;
+        uint32_t done = 0;                 // tiles of this group so far
         bool ok = true;
-        uint32_t sreg[64];
-        for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
-            const uint32_t b = it & 1, u = it >> 1;
-            if (!mbar_wait(smem_u32(&ctl->s_full[b]), u & 1, abort_flag)) { ok = false; break; }
+        uint32_t sreg[128];
+        for (uint32_t it = g; (int)it < n_tiles_k && ok; it += 2, ++done) {
+            const int kt = kt_begin + (int)it;
+            const uint32_t u = it >> 1;
+            if (!mbar_wait(smem_u32(&ctl->s_full[g]), u & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const int key0 = kt * BN + hsel * 64;          // first key of this thread's half
-            tmem_ld32_nowait(lane_addr + b * 128, sreg);
-            tmem_ld32_nowait(lane_addr + b * 128 + 32, sreg + 32);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32_nowait(s_addr + c * 32, sreg + c * 32);
             tmem_ld_wait();
             tc_fence_before();
-            warp_arrive(smem_u32(&ctl->s_free[b]), lane);  // S of this tile is in registers
-            // a half tile every key of which this row sees needs no mask
-            const bool interior = row_valid && key0 + 63 <= pos && key0 >= wlo;
+            warp_arrive(smem_u32(&ctl->s_free[g]), lane);  // S of this tile is in registers
+            const int key0 = kt * BN;
+            // a tile every key of which this row sees needs no mask
+            const bool interior = row_valid && key0 + BN - 1 <= pos && key0 >= wlo;
             float mx = -INFINITY;
             if (interior) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(sreg[i]));
+                for (int i = 0; i < BN; ++i) mx = fmaxf(mx, __uint_as_float(sreg[i]));
             } else {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
+                for (int i = 0; i < BN; ++i) {
                     const int key = key0 + i;
                     if (!(row_valid && key <= pos && key >= wlo)) sreg[i] = 0xff800000u;      // -inf
                     mx = fmaxf(mx, __uint_as_float(sreg[i]));
                 }
             }
-            // the row's maximum is over both halves
-            // (a bounded mbarrier wait, not bar.sync: a thread that gave up elsewhere must not leave the others hanging)
-            ctl->xchg[b][hsel][row] = mx;
-            warp_arrive(smem_u32(&ctl->x_full[b]), lane);
-            if (!mbar_wait(smem_u32(&ctl->x_full[b]), u & 1, abort_flag)) { ok = false; break; }
-            mx = fmaxf(mx, ctl->xchg[b][hsel ^ 1][row]);
-            // Move the reference only when the maximum has outgrown it by RESCALE_STEP (or there was none): both
-            // threads of a row see the same numbers and decide alike.  O of a row without a reference is still zero.
+            // P V of the group's previous tile is done: its P buffer is free and its O is at rest until this tile's P
+            // is published
+            if (done >= 1 && !mbar_wait(smem_u32(&ctl->pv_done[g]), (u - 1) & 1, abort_flag)) { ok = false; break; }
+            // Move the reference only when the maximum has outgrown it by RESCALE_STEP (or there was none).  O of a
+            // row without a reference is still zero.
             const bool move = mx > m_ref && (m_ref == -INFINITY || (mx - m_ref) * scale_log2 > RESCALE_STEP);
             const bool scale_o = move && m_ref != -INFINITY;
             if (__any_sync(0xffffffffu, scale_o)) {
-                // O is at rest once P V of the previous tile is done (the next one waits for this tile's P)
-                if (it >= 1 && !mbar_wait(smem_u32(&ctl->pv_done[(it - 1) & 1]), ((it - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const float alpha = scale_o ? fast_exp2((m_ref - mx) * scale_log2) : 1.0f;
-                uint32_t oreg[32];
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    tmem_ld32_nowait(lane_addr + 256 + c * 32, oreg);
+#pragma unroll 1
+                for (int c = 0; c < 8; ++c) {
+                    uint32_t oreg[16];
+                    tmem_ld16(o_addr + c * 16, oreg);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
-                    tmem_st32(lane_addr + 256 + c * 32, oreg);
+                    for (int i = 0; i < 16; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+                    tmem_st16(o_addr + c * 16, oreg);
                 }
                 tmem_st_wait();
                 l *= alpha;
             }
             if (move) m_ref = mx;
             const float use = (m_ref == -INFINITY) ? 0.0f : m_ref * scale_log2;
-            // P buffer b was last read by P V of tile it - 2
-            if (it >= 2 && !mbar_wait(smem_u32(&ctl->pv_done[b]), ((it - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
-            // probabilities, rounded to bf16 as the tensor core will read them; this thread's 64 keys are the
-            // [128 x 64] half `hsel` of P: 8 chunks of 16 bytes in row `row`, chunk index xor-ed with row % 8
+            // probabilities, rounded to bf16 as the tensor core will read them: the row of P is two halves of 64 keys,
+            // each 8 chunks of 16 bytes, chunk index xor-ed with row % 8
             float sum = 0.0f;
-            unsigned char* prow = sP + b * TILE_BYTES + hsel * HALF_BYTES + row * 128;
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-                uint32_t packed[4];
+            for (int hf = 0; hf < 2; ++hf) {
+                unsigned char* prow = sP + g * TILE_BYTES + hf * HALF_BYTES + row * 128;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sreg[ch * 8 + 2 * i]), scale_log2, -use));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sreg[ch * 8 + 2 * i + 1]), scale_log2, -use));
-                    sum += p0 + p1;
-                    packed[i] = pack_bf16x2(p0, p1);
+                for (int ch = 0; ch < 8; ++ch) {
+                    uint32_t packed[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(sreg[hf * 64 + ch * 8 + 2 * i]), scale_log2, -use));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(sreg[hf * 64 + ch * 8 + 2 * i + 1]), scale_log2, -use));
+                        sum += p0 + p1;
+                        packed[i] = pack_bf16x2(p0, p1);
+                    }
+                    *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 }
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
             l += sum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P is read by the tensor core (async proxy)
             tc_fence_before();                                                // ... and O, if it was rescaled, is in tensor memory
-            warp_arrive(smem_u32(&ctl->p_full[b]), lane);
+            warp_arrive(smem_u32(&ctl->p_full[g]), lane);
         }
-        // O is complete when the last P V is done
-        if (ok && it >= 1) ok = mbar_wait(smem_u32(&ctl->pv_done[(it - 1) & 1]), ((it - 1) >> 1) & 1, abort_flag);
-        tc_fence_after();
-        // the row sum is the sum of the two halves (both are relative to the same reference)
-        // the buffer the last tile did not use: everyone finished reading it before arriving for the last tile's exchange
-        const int lb = it & 1;
-        ctl->xchg[lb][hsel][row] = l;
+        // Merge the two groups: every thread posts its row's (reference, sum); the row's output is
+        // (O0 f0 + O1 f1) / (l0 f0 + l1 f1) with f = 2^((m_g - m) scale); group g writes output columns 64g .. 64g + 63.
+        ctl->xchg[g][0][row] = m_ref;
+        ctl->xchg[g][1][row] = l;
         warp_arrive(smem_u32(&ctl->l_full), lane);
         if (ok) ok = mbar_wait(smem_u32(&ctl->l_full), 0, abort_flag);
-        l += ctl->xchg[lb][hsel ^ 1][row];
-        if (ok && it >= 1) {
-            tmem_ld32_nowait(lane_addr + 256, sreg);
-            tmem_ld32_nowait(lane_addr + 256 + 32, sreg + 32);
-            tmem_ld_wait();
-        } else {
+        const float m0 = ctl->xchg[0][0][row], m1 = ctl->xchg[1][0][row];
+        const float l0 = ctl->xchg[0][1][row], l1 = ctl->xchg[1][1][row];
+        const float m = fmaxf(m0, m1);
+        const float f0 = (m0 == -INFINITY) ? 0.0f : fast_exp2((m0 - m) * scale_log2);
+        const float f1 = (m1 == -INFINITY) ? 0.0f : fast_exp2((m1 - m) * scale_log2);
+        const float total = l0 * f0 + l1 * f1;
+        // O of both groups is complete when their last P V is done (a group without tiles has no O)
+        const int tiles0 = (n_tiles_k + 1) / 2, tiles1 = n_tiles_k / 2;
+        if (ok && tiles0 > 0) ok = mbar_wait(smem_u32(&ctl->pv_done[0]), (uint32_t)(tiles0 - 1) & 1, abort_flag);
+        if (ok && tiles1 > 0) ok = mbar_wait(smem_u32(&ctl->pv_done[1]), (uint32_t)(tiles1 - 1) & 1, abort_flag);
+        tc_fence_after();
+        const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+        __nv_bfloat16* orow = out + ((size_t)(row0 + row) * H + h) * HD + g * 64;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {                              // 32 output columns at a time
+            float acc[32];
 #pragma unroll
-            for (int i = 0; i < 64; ++i) sreg[i] = 0u;
-        }
-        if (ok && row_valid) {
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            __nv_bfloat16* orow = out + ((size_t)(row0 + row) * H + h) * HD + hsel * 64;
+            for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
+            if (ok && tiles0 > 0) {                                // uniform over the CTA
+                tmem_ld32_nowait(lane_addr + 256 + g * 64 + c * 32, sreg);
+                tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 64; i += 8) {
-                float o[8];
+                for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(sreg[i]) * f0;
+            }
+            if (ok && tiles1 > 0) {
+                tmem_ld32_nowait(lane_addr + 384 + g * 64 + c * 32, sreg);
+                tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(sreg[i + j]) * inv;
-                *reinterpret_cast<uint4*>(orow + i) = make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]), pack_bf16x2(o[6], o[7]));
+                for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(sreg[i]), f1, acc[i]);
+            }
+            if (ok && row_valid) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8)
+                    *reinterpret_cast<uint4*>(orow + c * 32 + i) = make_uint4(pack_bf16x2(acc[i] * inv, acc[i + 1] * inv), pack_bf16x2(acc[i + 2] * inv, acc[i + 3] * inv),
+                                                                              pack_bf16x2(acc[i + 4] * inv, acc[i + 5] * inv), pack_bf16x2(acc[i + 6] * inv, acc[i + 7] * inv));
             }
         }
     }
