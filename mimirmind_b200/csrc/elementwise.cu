@@ -87,6 +87,24 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     }
 }
 
+// f[0..8) += p[0..8), p aligned to 8 elements: 16-byte loads instead of eight scalar ones (a warp whose threads are
+// 16 elements apart would otherwise touch 32 sectors with every scalar load).
+__device__ __forceinline__ void add8(const float* __restrict__ p, float* f) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
+    f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
+}
+__device__ __forceinline__ void add8(const __nv_bfloat16* __restrict__ p, float* f) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 x = __bfloat1622float2(p2[k]);
+        f[2 * k] += x.x;
+        f[2 * k + 1] += x.y;
+    }
+}
+
 // bfloat16 activations, width a multiple of 8 and at most 8192: every thread keeps 8 consecutive elements in
 // registers (two float4 of the residual, one 16-byte load of the branch output), so a row makes one trip.
 template <typename WT>
@@ -130,11 +148,12 @@ __global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ residual, const __
     }
     uint4 ov;
     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+    float w[8];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const float w0 = to_f32<WT>(weight[c + 2 * k]), w1 = to_f32<WT>(weight[c + 2 * k + 1]);
-        o2[k] = __floats2bfloat162_rn(v[2 * k] * w0 * inv_rms, v[2 * k + 1] * w1 * inv_rms);
-    }
+    for (int k = 0; k < 8; ++k) w[k] = 0.0f;
+    add8(weight + c, w);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o2[k] = __floats2bfloat162_rn(v[2 * k] * w[2 * k] * inv_rms, v[2 * k + 1] * w[2 * k + 1] * inv_rms);
     *reinterpret_cast<uint4*>(out + (size_t)i * d + c) = ov;
 }
 
@@ -420,10 +439,7 @@ __global__ void qkv_rope_kvwrite_bf16x8_kernel(const __nv_bfloat16* __restrict__
             f[2 * k] = x.x;
             f[2 * k + 1] = x.y;
         }
-        if (bias) {
-#pragma unroll
-            for (int k = 0; k < 8; ++k) f[k] += to_f32<WT>(bias[col + k]);
-        }
+        if (bias) add8(bias + col, f);
     };
     auto store8 = [&](__nv_bfloat16* dst, const float* f) {
         uint4 ov;
@@ -460,6 +476,115 @@ __global__ void qkv_rope_kvwrite_bf16x8_kernel(const __nv_bfloat16* __restrict__
             store8(vdst + (size_t)g * head_stride_in_page + i0, a);
         }
     }
+}
+
+// The same with the step's tables: rotation factors from rope_table [n, hd] (cos of the hd/2 angles, then sin) and
+// the cache place from slots [n] (page * page_size + place in the page, -1: not cached), both made once per step
+// for all layers.  No arithmetic on angles and no dependent look-ups here: every load of a thread is issued at once.
+template <typename WT>
+__global__ void qkv_rope_tables_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const WT* __restrict__ bias,
+                                              __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pages,
+                                              __nv_bfloat16* __restrict__ v_pages, const float* __restrict__ rope_table,
+                                              const int32_t* __restrict__ slots, int page_size, int H, int G, int hd,
+                                              int interleave) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int half = hd / 2;
+    const float* cosv = rope_table + (size_t)t * hd;
+    const float* sinv = cosv + half;
+    const int row_width = (H + 2 * G) * hd;
+    const __nv_bfloat16* src = qkv + (size_t)t * row_width;
+    __nv_bfloat16* kdst = nullptr;
+    __nv_bfloat16* vdst = nullptr;
+    if (k_pages != nullptr && slots != nullptr) {
+        const int slot = slots[t];
+        if (slot >= 0) {
+            const int page = slot / page_size;
+            const size_t base = ((size_t)page * G * page_size + (size_t)(slot - page * page_size)) * hd;
+            kdst = k_pages + base;
+            vdst = v_pages + base;
+        }
+    }
+    const size_t head_stride_in_page = (size_t)page_size * hd;
+    const int chunks = half / 8;
+    auto load8 = [&](int col, float* f) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + col);
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 x = __bfloat1622float2(p2[k]);
+            f[2 * k] = x.x;
+            f[2 * k + 1] = x.y;
+        }
+        if (bias) add8(bias + col, f);
+    };
+    auto store8 = [&](__nv_bfloat16* dst, const float* f) {
+        uint4 ov;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o2[k] = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+        *reinterpret_cast<uint4*>(dst) = ov;
+    };
+    const int rot_items = (H + G) * chunks;
+    const int v_items = vdst ? G * hd / 8 : 0;
+    for (int idx = threadIdx.x; idx < rot_items + v_items; idx += blockDim.x) {
+        if (idx < rot_items) {
+            const int h = idx / chunks, i0 = (idx - h * chunks) * 8;
+            __nv_bfloat16* dst = nullptr;
+            if (h < H) dst = q_out + (size_t)t * H * hd + (size_t)h * hd;
+            else if (kdst) dst = kdst + (size_t)(h - H) * head_stride_in_page;
+            if (!dst) continue;
+            float a[8], b[8], c[8], sn[8], ra[8], rb[8];
+            *reinterpret_cast<float4*>(c) = *reinterpret_cast<const float4*>(cosv + i0);
+            *reinterpret_cast<float4*>(c + 4) = *reinterpret_cast<const float4*>(cosv + i0 + 4);
+            *reinterpret_cast<float4*>(sn) = *reinterpret_cast<const float4*>(sinv + i0);
+            *reinterpret_cast<float4*>(sn + 4) = *reinterpret_cast<const float4*>(sinv + i0 + 4);
+            load8(interleave ? h * hd + 2 * i0 : h * hd + i0, a);
+            load8(interleave ? h * hd + 2 * i0 + 8 : h * hd + i0 + half, b);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                ra[k] = a[k] * c[k] - b[k] * sn[k];
+                rb[k] = a[k] * sn[k] + b[k] * c[k];
+            }
+            store8(dst + i0, ra);
+            store8(dst + i0 + half, rb);
+        } else {
+            const int j = idx - rot_items;
+            const int g = (j * 8) / hd, i0 = j * 8 - g * hd;
+            float a[8];
+            load8((H + G) * hd + j * 8, a);
+            store8(vdst + (size_t)g * head_stride_in_page + i0, a);
+        }
+    }
+}
+
+MM_EXPORT int mm_qkv_rope_tables(const void* qkv, const void* bias, int bias_dtype, void* q_out, void* k_pages,
+                                 void* v_pages, const void* rope_table, const void* slots, int page_size, int n_tokens,
+                                 int H, int G, int hd, int interleave, void* stream) {
+    typedef __nv_bfloat16 bf;
+    MM_REQUIRE(n_tokens >= 0 && H > 0 && G > 0 && hd > 0 && hd % 16 == 0,
+               "qkv_rope_tables: the head size must be a positive multiple of 16");
+    MM_REQUIRE(page_size > 0, "qkv_rope_tables: bad page geometry");
+    MM_REQUIRE((k_pages == nullptr) == (v_pages == nullptr), "qkv_rope_tables: k and v pools must both be given or both be null");
+    MM_REQUIRE(k_pages == nullptr || slots != nullptr, "qkv_rope_tables: a cache needs the slots of the tokens");
+    MM_REQUIRE(rope_table != nullptr, "qkv_rope_tables: no rotation table");
+    if (n_tokens == 0) return MM_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int items = (H + G) * (hd / 16) + G * hd / 8;
+    int threads = ((items + 31) / 32) * 32;
+    if (threads > 512) threads = 512;
+    if (bias == nullptr || bias_dtype == MM_F32)
+        mm_launch_pdl(qkv_rope_tables_bf16x8_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const bf*)qkv, (const float*)bias,
+                      (bf*)q_out, (bf*)k_pages, (bf*)v_pages, (const float*)rope_table, (const int32_t*)slots, page_size, H, G,
+                      hd, interleave);
+    else if (bias_dtype == MM_BF16)
+        mm_launch_pdl(qkv_rope_tables_bf16x8_kernel<bf>, dim3(n_tokens), dim3(threads), 0, s, (const bf*)qkv, (const bf*)bias,
+                      (bf*)q_out, (bf*)k_pages, (bf*)v_pages, (const float*)rope_table, (const int32_t*)slots, page_size, H, G,
+                      hd, interleave);
+    else MM_REQUIRE(false, "qkv_rope_tables: the bias must be float32 or bfloat16");
+    MM_CHECK_LAUNCH();
+    return MM_OK;
 }
 
 MM_EXPORT int mm_qkv_rope_kvwrite(const void* qkv, const void* bias, int bias_dtype, void* q_out, void* k_pages,

@@ -45,6 +45,7 @@ _PROTOTYPES = {
     "mm_rope_table": [P, P, I, I, F, P],
     "mm_slot_mapping": [P, P, P, I, I, I, P, P],
     "mm_qkv_rope_kvwrite": [P, P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P],
+    "mm_qkv_rope_tables": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, P],
     "mm_gather_rows": [P, P, P, I, I, I, P],
     "mm_attention_generic": [P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, P],
     "mm_gemm_simt": [P, I, P, I, P, I, P, I, I, I, I, I, I, P],

@@ -140,6 +140,45 @@ def qkv_rope_kvwrite(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_out: tor
         float(theta), int(interleave), _stream()), "qkv_rope_kvwrite")
 
 
+def qkv_rope_tables(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
+                    k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], table: torch.Tensor,
+                    slots: Optional[torch.Tensor], page_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                    interleave: bool = False) -> None:
+    """:func:`qkv_rope_kvwrite` for bfloat16 and a rotation of the whole head, with the step's tables: ``table``
+    from :func:`rope_table`, ``slots`` from :func:`slot_mapping` (needed when there are pages to write)."""
+    _need(qkv, "qkv", torch.bfloat16)
+    n = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape != (n, width):
+        raise KernelError(f"qkv: shape {tuple(qkv.shape)} is not [n, {width}]")
+    if head_dim % 16:
+        raise KernelError(f"qkv_rope_tables: head size {head_dim} is not a multiple of 16")
+    _need(q_out, "q_out", torch.bfloat16)
+    if q_out.shape != (n, num_heads * head_dim):
+        raise KernelError("q_out: wrong shape")
+    if bias is not None:
+        _need(bias, "qkv bias")
+        if bias.shape != (width,):
+            raise KernelError("qkv bias: wrong shape")
+    _need(table, "rope table", torch.float32)
+    if table.shape != (n, head_dim):
+        raise KernelError(f"rope table: shape {tuple(table.shape)} is not [{n}, {head_dim}]")
+    if k_pages is not None:
+        for name, pool in (("k_pages", k_pages), ("v_pages", v_pages)):
+            _need(pool, name, torch.bfloat16)
+            if pool.dim() != 4 or pool.shape[1:] != (num_kv_heads, page_size, head_dim):
+                raise KernelError(f"{name}: shape {tuple(pool.shape)} is not [pages, {num_kv_heads}, {page_size}, {head_dim}]")
+        if slots is None:
+            raise KernelError("qkv_rope_tables: pages without slots")
+        _need(slots, "slots", torch.int32)
+        if slots.shape != (n,):
+            raise KernelError("slots: wrong shape")
+    check(_lib.load().mm_qkv_rope_tables(
+        qkv.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, q_out.data_ptr(),
+        _ptr(k_pages), _ptr(v_pages), table.data_ptr(), _ptr(slots), page_size, n, num_heads, num_kv_heads, head_dim,
+        int(interleave), _stream()), "qkv_rope_tables")
+
+
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     _need(src, "gather src")
     _need(rows, "gather rows", torch.int32)

@@ -118,26 +118,32 @@ class GQAAttention(Mixer):
         fused = self.position.fused_rotary()
         fuses = self.fuses(n)
         q = torch.empty((n, H * hd), dtype=self.rt.dtype, device=x.xw.device if isinstance(x, FactoredRows) else x.device)
-        if fuses:
-            # a few tokens: projection, 1/rms of a factored input, bias, rotation and cache write in one launch
-            xin, scale = (x.xw, x.scale) if isinstance(x, FactoredRows) else (x, None)
-            # rotation angles and cache slots are the same in every layer that shares them: made once per step
+        # rotation factors and cache places are the same in every layer that shares them: made once per step
+        tables = fused is not None and fused[0] == hd and hd % 16 == 0 and self.rt.dtype == torch.bfloat16
+        table = slots = None
+        if tables:
             key = ("rope_table", hd, fused[1])
             if key not in ctx.derived:
                 ctx.derived[key] = ops.rope_table(ctx.positions, hd, fused[1])
-            slots = None
+            table = ctx.derived[key]
             if k_pages is not None:
                 skey = ("slots", cache.block_table.data_ptr(), cache.page_size)
                 if skey not in ctx.derived:
                     ctx.derived[skey] = ops.slot_mapping(ctx.positions, ctx.token_req, cache.block_table, cache.page_size)
                 slots = ctx.derived[skey]
-            ops.gemv_bf16_qkv_rope(xin, self.w_qkv, self.b_qkv, q, k_pages, v_pages, ctx.derived[key], slots,
+        if fuses:
+            # a few tokens: projection, 1/rms of a factored input, bias, rotation and cache write in one launch
+            xin, scale = (x.xw, x.scale) if isinstance(x, FactoredRows) else (x, None)
+            ops.gemv_bf16_qkv_rope(xin, self.w_qkv, self.b_qkv, q, k_pages, v_pages, table, slots,
                                    cache.page_size, H, G, hd, scale=scale, chain=ctx.chain)
             if ctx.chain is not None:
                 ctx.chain.flush()            # attention is not one of the chain's products: q, k and v must be there
         else:
             qkv = linear(x, self.w_qkv, None, self.rt)
-            if fused is not None:
+            if tables and qkv.dtype == torch.bfloat16:
+                ops.qkv_rope_tables(qkv, self.b_qkv, q, k_pages, v_pages, table, slots, cache.page_size, H, G, hd,
+                                    interleave=self.interleaved)
+            elif fused is not None:
                 rotary_dim, theta = fused
                 ops.qkv_rope_kvwrite(qkv, self.b_qkv, q, k_pages, v_pages, ctx.positions, ctx.token_req, cache.block_table,
                                      cache.page_size, H, G, hd, rotary_dim, theta, interleave=self.interleaved)

@@ -177,6 +177,65 @@ def test_qkv_rope_kvwrite(dtype, wdt, H, G, hd, rot, ps):
     assert (kp_h[untouched] == 768.0).all() and (vp_h[untouched] == 768.0).all()
 
 
+@pytest.mark.parametrize("wdt", [torch.float32, torch.bfloat16, None])
+@pytest.mark.parametrize("H,G,hd,ps,interleave", [(4, 2, 16, 16, False), (6, 3, 48, 8, True), (7, 1, 128, 16, True),
+                                                   (5, 5, 80, 32, False), (40, 8, 128, 16, True)])
+def test_qkv_rope_with_step_tables(wdt, H, G, hd, ps, interleave):
+    """The variant that reads rotation factors and cache places from the step's tables: against the plain rotation,
+    and bit-equal to the kernel that works them out itself."""
+    rng = np.random.RandomState(H * hd + ps)
+    theta = 1e4
+    lens_before, q_lens = [0, 37, 130], [21, 1, 67]
+    table, pages = paged_layout(rng, [a + b for a, b in zip(lens_before, q_lens)], ps)
+    n = sum(q_lens)
+    pos = np.concatenate([np.arange(a, a + b) for a, b in zip(lens_before, q_lens)]).astype(np.int32)
+    req = np.concatenate([np.full(b, r) for r, b in enumerate(q_lens)]).astype(np.int32)
+    width = (H + 2 * G) * hd
+    qkv = t(rng.randn(n, width), torch.bfloat16)
+    bias = t(rng.randn(width) * 0.5, wdt) if wdt is not None else None
+    d_pos, d_req, d_table = t(pos, torch.int32), t(req, torch.int32), t(table, torch.int32)
+    rope = ops().rope_table(d_pos, hd, theta)
+    slots = ops().slot_mapping(d_pos, d_req, d_table, ps)
+    outs = []
+    for which in ("tables", "positions"):
+        kp = torch.full((pages, G, ps, hd), 768.0, dtype=torch.bfloat16, device=DEV)
+        vp = torch.full((pages, G, ps, hd), 768.0, dtype=torch.bfloat16, device=DEV)
+        q_out = torch.empty((n, H * hd), dtype=torch.bfloat16, device=DEV)
+        src, b = qkv, bias
+        if interleave:
+            src = ops().interleave_halves(qkv.t().contiguous(), H + G, hd).t().contiguous()
+            b = ops().interleave_halves(bias, H + G, hd) if bias is not None else None
+        if which == "tables":
+            ops().qkv_rope_tables(src, b, q_out, kp, vp, rope, slots, ps, H, G, hd, interleave=interleave)
+        else:
+            ops().qkv_rope_kvwrite(src, b, q_out, kp, vp, d_pos, d_req, d_table, ps, H, G, hd, hd, theta, interleave=interleave)
+        outs.append((q_out, kp, vp))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    x = qkv.double().cpu().numpy() + (bias.double().cpu().numpy() if bias is not None else 0.0)
+    q_ref = plain.rope(x[:, :H * hd].reshape(n, H, hd), pos, theta)
+    k_ref = plain.rope(x[:, H * hd:(H + G) * hd].reshape(n, G, hd), pos, theta)
+    v_ref = x[:, (H + G) * hd:].reshape(n, G, hd)
+    q_out, kp, vp = outs[0]
+    tol = 2 ** -8
+    assert np.abs(q_out.float().cpu().numpy().reshape(n, H, hd) - q_ref).max() <= tol * np.abs(q_ref).max()
+    kp_h, vp_h = kp.float().cpu().numpy(), vp.float().cpu().numpy()
+    written = np.zeros((pages, ps), dtype=bool)
+    for i in range(n):
+        page, slot = table[req[i], pos[i] // ps], pos[i] % ps
+        written[page, slot] = True
+        assert np.abs(kp_h[page, :, slot] - k_ref[i]).max() <= tol * np.abs(k_ref).max()
+        assert np.abs(vp_h[page, :, slot] - v_ref[i]).max() <= tol * np.abs(v_ref).max()
+    untouched = ~written[:, None, :].repeat(G, axis=1)
+    assert (kp_h[untouched] == 768.0).all() and (vp_h[untouched] == 768.0).all()
+    # without pages only q is written
+    q2 = torch.empty_like(q_out)
+    src = ops().interleave_halves(qkv.t().contiguous(), H + G, hd).t().contiguous() if interleave else qkv
+    b = ops().interleave_halves(bias, H + G, hd) if (interleave and bias is not None) else bias
+    ops().qkv_rope_tables(src, b, q2, None, None, rope, None, ps, H, G, hd, interleave=interleave)
+    assert torch.equal(q2, q_out)
+
+
 # ---- attention -------------------------------------------------------------------------------------
 def make_attention_case(rng, H, G, hd, ps, ctx_lens, q_lens, dtype, spike=None):
     """Requests with ``ctx_lens[r]`` cached tokens of which the last ``q_lens[r]`` are this step's queries.
