@@ -32,6 +32,7 @@ _PROTOTYPES = {
     "mm_add_residual": [P, P, I, c_longlong, P],
     "mm_silu_mul": [P, P, I, I, I, I, P],
     "mm_gemm_tcgen05": [P, P, P, I, P, I, I, I, I, I, I, P, P],
+    "mm_gemm_tcgen05_pair": [P, P, P, I, P, I, I, I, I, I, I, P, P],
     "mm_gemv_bf16": [P, P, P, I, P, I, I, I, I, I, I, I, I, I, P, I, I, F, P],
     "mm_gemv_bf16_residual": [P, P, P, P, I, P, P, I, I, I, I, I, I, P, I, I, F, P],
     "mm_gemv_bf16_qkv_rope": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, I, F, P],

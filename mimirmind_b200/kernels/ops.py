@@ -536,10 +536,16 @@ def gemm_tcgen05_supported(m: int, n: int, k: int) -> bool:
     return m >= 1 and k % 8 == 0 and n % 8 == 0 and k >= 64
 
 
+# From this many rows on, the product runs on pairs of CTAs (cta_group::2, 256 x 256 tiles); below, the second
+# CTA's 128 rows would be padding.
+TCGEN05_PAIR_MIN_ROWS = 256
+
+
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-                 swiglu: bool = False) -> torch.Tensor:
+                 swiglu: bool = False, pair: Optional[bool] = None) -> torch.Tensor:
     """x[M, K] @ w[N, K]^T (+ bias) on the tcgen05 tensor cores (TMA operands, TMEM accumulators).
-    ``swiglu``: w interleaves gate and up rows in blocks of 8; returns silu(gate) * up, [M, N/2]."""
+    ``swiglu``: w interleaves gate and up rows in blocks of 8; returns silu(gate) * up, [M, N/2].
+    ``pair``: the kernel of CTA pairs or the single-CTA one; None chooses by the number of rows."""
     _need(x, "gemm x", torch.bfloat16)
     _need(w, "gemm w", torch.bfloat16)
     m, k = x.shape
@@ -556,9 +562,11 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
         epi = EPI_F32 if out_dtype == torch.float32 else EPI_BF16
     if bias is not None:
         _need(bias, "gemm bias")
-    check(_lib.load().mm_gemm_tcgen05(x.data_ptr(), w.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
-                                      out.data_ptr(), epi, m, n, k, k, out.shape[1], tcgen05_error_flag(x.device).data_ptr(),
-                                      _stream()), "gemm_tcgen05")
+    if pair is None:
+        pair = m >= TCGEN05_PAIR_MIN_ROWS
+    fn = _lib.load().mm_gemm_tcgen05_pair if pair else _lib.load().mm_gemm_tcgen05
+    check(fn(x.data_ptr(), w.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
+             out.data_ptr(), epi, m, n, k, k, out.shape[1], tcgen05_error_flag(x.device).data_ptr(), _stream()), "gemm_tcgen05")
     return out
 
 

@@ -723,20 +723,37 @@ def test_gemv_chain_equals_separate_launches():
 # ---- tcgen05 / TMA / TMEM matrix product -------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 8, 64), (200, 520, 192), (300, 264, 1000), (1100, 1048, 328)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
-def test_gemm_tcgen05(M, N, K, out_dtype):
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_tcgen05(M, N, K, out_dtype, pair):
+    """Both kernels: one CTA per 128 x 256 tile, and a pair of CTAs (cta_group::2) per 256 x 256 tile."""
     rng = np.random.RandomState(M + N + K)
     x, w, b = t(rng.randn(M, K), torch.bfloat16), t(rng.randn(N, K) * 0.05, torch.bfloat16), t(rng.randn(N), torch.float32)
     ref = x.double().cpu().numpy() @ w.double().cpu().numpy().T
     for bias in (None, b):
         want = ref + (b.double().cpu().numpy() if bias is not None else 0.0)
-        got = ops().gemm_tcgen05(x, w, bias, out_dtype).float().cpu().numpy()
+        got = ops().gemm_tcgen05(x, w, bias, out_dtype, pair=pair).float().cpu().numpy()
         ops().check_tcgen05_errors(x.device)
         tol = 3e-6 * np.sqrt(K) if out_dtype == torch.float32 else 2 ** -8
         assert np.abs(got - want).max() <= tol * np.abs(want).max() + 1e-5
 
 
+def test_gemm_tcgen05_pair_many_tiles_per_pair():
+    """More tiles than CTA pairs and more k-blocks than stages: both accumulators and every ring slot are reused,
+    and the result equals the single-CTA kernel's bit for bit (same products, same order along K)."""
+    rng = np.random.RandomState(5)
+    M, N, K = 1300, 20 * 256 + 72, 1544
+    x, w = t(rng.randn(M, K), torch.bfloat16), t(rng.randn(N, K) * 0.05, torch.bfloat16)
+    one = ops().gemm_tcgen05(x, w, None, torch.float32, pair=False)
+    two = ops().gemm_tcgen05(x, w, None, torch.float32, pair=True)
+    ops().check_tcgen05_errors(x.device)
+    assert torch.equal(one, two)
+    ref = x.double().cpu().numpy() @ w.double().cpu().numpy().T
+    assert np.abs(two.cpu().numpy() - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
+
+
 @pytest.mark.parametrize("M,F,K", [(130, 352, 256), (1030, 1000, 512), (64, 72, 64)])
-def test_gemm_tcgen05_swiglu_epilogue(M, F, K):
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_tcgen05_swiglu_epilogue(M, F, K, pair):
     rng = np.random.RandomState(F + M)
     x = t(rng.randn(M, K), torch.bfloat16)
     gate_t, up_t = t(rng.randn(F, K) * 0.05, torch.bfloat16), t(rng.randn(F, K) * 0.05, torch.bfloat16)
@@ -744,7 +761,7 @@ def test_gemm_tcgen05_swiglu_epilogue(M, F, K):
     g = x.double().cpu().numpy() @ gate_t.double().cpu().numpy().T
     u = x.double().cpu().numpy() @ up_t.double().cpu().numpy().T
     ref = g / (1 + np.exp(-g)) * u
-    got = ops().gemm_tcgen05(x, w, None, torch.bfloat16, swiglu=True).float().cpu().numpy()
+    got = ops().gemm_tcgen05(x, w, None, torch.bfloat16, swiglu=True, pair=pair).float().cpu().numpy()
     ops().check_tcgen05_errors(x.device)
     assert got.shape == (M, F)
     assert np.abs(got - ref).max() <= 2 ** -8 * np.abs(ref).max() + 1e-6
