@@ -22,6 +22,7 @@ import torch
 from ..kernels import ops
 from ..parts.base import StepContext
 from ..sampling.params import SamplingParams
+from .capture import capture
 from .runner import ModelRunner
 
 
@@ -167,7 +168,7 @@ class DecodeSession:
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):   # records the launches; nothing runs, buffers keep their contents
+            with capture(graph):            # records the launches; nothing runs, buffers keep their contents
                 self._launch()
             self.graph = graph
         else:

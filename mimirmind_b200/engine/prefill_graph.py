@@ -18,6 +18,7 @@ import numpy as np
 import torch
 
 from ..parts.base import StepContext
+from .capture import capture
 from .runner import ModelRunner
 
 
@@ -82,7 +83,7 @@ class PrefillSession:
                     base[:, 3] -= start
                     self.tile_base[id(plan)] = base
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):       # records the launches; nothing runs
+            with capture(graph):                # records the launches; nothing runs
                 self._launch()
             self.graph = graph
         else:

@@ -512,8 +512,10 @@ def gemv_bf16_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Te
 
 _TC_ERR = {}
 EPI_BF16, EPI_SWIGLU, EPI_F32 = 0, 1, 2
-# Measured on B200 (7B shapes): from about a thousand rows the fused product beats library product + activation kernel.
-TCGEN05_SWIGLU_MIN_ROWS = 1024
+# Measured on B200 (7B shapes, gate/up product): from 256 rows on the fused product is level with or ahead of the
+# library product + activation kernel (65 against 80 us at 256 rows, 197 against 217 at 1,024, 346 against 409 at 2,048);
+# below, a 128-row tile leaves the tensor cores short of work and the library's smaller tiles win (58 against 71 us at 96).
+TCGEN05_SWIGLU_MIN_ROWS = 256
 
 
 def tcgen05_error_flag(device) -> torch.Tensor:
@@ -536,9 +538,13 @@ def gemm_tcgen05_supported(m: int, n: int, k: int) -> bool:
     return m >= 1 and k % 8 == 0 and n % 8 == 0 and k >= 64
 
 
-# From this many rows on, the product runs on pairs of CTAs (cta_group::2, 256 x 256 tiles); below, the second
-# CTA's 128 rows would be padding.
+# From this many rows on, the product runs on pairs of CTAs (cta_group::2, 256 x 256 tiles), unless the last pair's
+# second CTA would have nothing but padding (384 rows cost as much as 512 there: 126 against 91 us).
 TCGEN05_PAIR_MIN_ROWS = 256
+
+
+def tcgen05_pair_suits(m: int) -> bool:
+    return m >= TCGEN05_PAIR_MIN_ROWS and (m - 1) % 256 >= 128
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
@@ -563,7 +569,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     if bias is not None:
         _need(bias, "gemm bias")
     if pair is None:
-        pair = m >= TCGEN05_PAIR_MIN_ROWS
+        pair = tcgen05_pair_suits(m)
     fn = _lib.load().mm_gemm_tcgen05_pair if pair else _lib.load().mm_gemm_tcgen05
     check(fn(x.data_ptr(), w.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
              out.data_ptr(), epi, m, n, k, k, out.shape[1], tcgen05_error_flag(x.device).data_ptr(), _stream()), "gemm_tcgen05")
