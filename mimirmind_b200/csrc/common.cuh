@@ -90,17 +90,27 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 
 // ---- programmatic dependent launch ------------------------------------------------------
-// The decode step is a chain of ~250 short kernels, each needing the previous one's output.
+// The decode step is a chain of ~150 short kernels, each needing the previous one's output.
 // Launched with the programmatic-serialization attribute, a kernel's blocks may be scheduled
 // while the previous kernel is still running; they do whatever does not depend on it (a
-// weight-streaming kernel already issues its first weight loads) and then block in
-// pdl_wait() until the previous grid has completed and its writes are visible.  Every kernel
-// launched this way calls pdl_wait() before its first read of activations and before any
-// write, and pdl_trigger() right after it: its own dependent may then be scheduled while it
-// runs, but never more than one kernel ahead (triggering before the wait let a whole chain of
-// future kernels pile up on the SMs and measured 2.5x slower).  Without the attribute both are
-// no-ops.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// weight-streaming kernel issues its first weight loads) and then block in pdl_wait() until
+// the previous grid has completed and its writes are visible.  Every kernel launched this way
+// calls pdl_wait() before its first read of activations and before any write, and
+// pdl_trigger() after it (the weight-streaming kernel: once its weights are through), so
+// never more than one kernel is ahead (triggering before the wait let a whole chain of future
+// kernels pile up on the SMs and measured 2.5x slower).  Without the attribute both are no-ops.
+// Off by default.  Measured on B200 at batch 8 (7B shapes): kernels do start 2.5-4 us before
+// their predecessor ends, but then take 2.5-4 us longer than after a plain launch: 3.36 ms
+// per step against 3.21 ms.  (Probable cause: their blocks land where the predecessor's blocks
+// happen to leave first instead of evenly over the SMs, and a streaming kernel with two or
+// three blocks per SM ends with its fullest SM.  In a probe with kernels that only spin, the
+// same launch pattern hides the part before the wait completely.)
+// One thread waits, the others stand at the CTA barrier: the blocks of a kernel that wait here share their SMs with
+// the running kernel, and 256 waiting threads per block slowed that kernel down measurably, one does not.
+__device__ __forceinline__ void pdl_wait() {
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+    __syncthreads();
+}
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 extern int g_mm_pdl;   // 1: use the attribute, 0: plain launches (default)

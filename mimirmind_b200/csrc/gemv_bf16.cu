@@ -292,6 +292,8 @@ __device__ __forceinline__ void gemv_item(const GemvArgs& a, int item, const Gem
     } else {
         stage();
     }
+    // the weights are through: the next kernel's blocks may move in beside this one's epilogue and request theirs
+    pdl_trigger();
     asm volatile("cp.async.wait_all;\n" ::: "memory");
     // sum the K splits of each row tile in a fixed order
     const bool need_sync = a.KS > 1 || a.in_ss != nullptr || kStaged;
@@ -422,7 +424,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
     GemvFirst<U> first;
     gemv_first_weights<U>(a, blockIdx.x, first);
     pdl_wait();
-    pdl_trigger();
     gemv_item<NT, U, EPI>(a, blockIdx.x, first, sm, ss_s);
 }
 
