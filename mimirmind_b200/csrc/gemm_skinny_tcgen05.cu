@@ -145,6 +145,17 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         ctl->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // the first round of the ring needs nobody else: its copies go out before this CTA's other warps have
+        // allocated tensor memory and met at the barrier
+        if (good) {
+            for (int i = 0; i < n_kb && i < STAGES; ++i) {
+                const uint32_t full = smem_u32(&ctl->full[i]);
+                mbar_expect_tx(full, STAGE_BYTES);
+                const uint32_t dst = smem_u32(ring + i * STAGE_BYTES);
+                tma_load_2d(dst, &tmW, (kb_begin + i) * SK_BK, n_tile0, full);
+                tma_load_2d(dst + SK_A_BYTES, &tmX, (kb_begin + i) * SK_BK, 0, full);
+            }
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(TMEM_COLS) : "memory");
@@ -157,8 +168,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
     if (warp == 0) {
         if (lane == 0 && good) {
-            // ---- TMA producer: this CTA's k blocks of the weight tile and of the batch ----
-            for (int i = 0; i < n_kb; ++i) {
+            // ---- TMA producer: this CTA's k blocks of the weight tile and of the batch (after the first round) ----
+            for (int i = STAGES; i < n_kb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t ph = (i / STAGES) & 1;
                 if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1, abort_flag)) break;
