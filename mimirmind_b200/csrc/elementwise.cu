@@ -34,6 +34,32 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __res
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32<T>(row[i]) * scale;
 }
 
+// bfloat16 table whose width is a multiple of 8: one 16-byte load and two 16-byte stores per thread and step, so a
+// row's loads are all in flight at once (a handful of decode tokens otherwise waits for one load after the other)
+__global__ void embedding_bf16x8_kernel(const int32_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                        float* __restrict__ out, int vocab, int d, float scale) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * d;
+    const bool known = id >= 0 && id < vocab;
+    const __nv_bfloat16* row = table + (size_t)(known ? id : 0) * d;
+    for (int c = threadIdx.x * 8; c < d; c += blockDim.x * 8) {
+        float4 lo = make_float4(0.0f, 0.0f, 0.0f, 0.0f), hi = lo;
+        if (known) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(row + c);
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const float2 a = __bfloat1622float2(p2[0]), b = __bfloat1622float2(p2[1]);
+            const float2 e = __bfloat1622float2(p2[2]), f = __bfloat1622float2(p2[3]);
+            lo = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+            hi = make_float4(e.x * scale, e.y * scale, f.x * scale, f.y * scale);
+        }
+        *reinterpret_cast<float4*>(o + c) = lo;
+        *reinterpret_cast<float4*>(o + c + 4) = hi;
+    }
+}
+
 MM_EXPORT int mm_embedding(const void* ids, const void* table, int table_dtype, void* out, int n_tokens,
                            int vocab, int d, float scale, void* stream) {
     MM_REQUIRE(n_tokens >= 0 && vocab > 0 && d > 0, "embedding: bad sizes");
@@ -42,6 +68,9 @@ MM_EXPORT int mm_embedding(const void* ids, const void* table, int table_dtype, 
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == MM_F32)
         mm_launch_pdl(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const int32_t*)ids, (const float*)table, (float*)out, vocab, d, scale);
+    else if (table_dtype == MM_BF16 && d % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0)
+        mm_launch_pdl(embedding_bf16x8_kernel, dim3(n_tokens), dim3(d >= 4096 ? 512 : (d >= 2048 ? 256 : 128)), 0, s,
+                      (const int32_t*)ids, (const __nv_bfloat16*)table, (float*)out, vocab, d, scale);
     else if (table_dtype == MM_BF16)
         mm_launch_pdl(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const int32_t*)ids, (const __nv_bfloat16*)table, (float*)out, vocab, d, scale);
     else

@@ -27,14 +27,16 @@ def bf16_round(a):
 
 # ---- embedding -------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_embedding(dtype):
-    rng = np.random.RandomState(0)
-    V, d = 1003, 136
+@pytest.mark.parametrize("d,scale", [(136, 1.0), (132, 1.0), (3584, 0.5), (8200, 1.0)])
+def test_embedding(dtype, d, scale):
+    """Widths that are and are not a multiple of 8 (the bfloat16 table has a 16-byte-load kernel for the former)."""
+    rng = np.random.RandomState(d)
+    V = 1003
     table = t(rng.randn(V, d), dtype)
     ids = torch.tensor([0, V - 1, 17, V, -3, 500], dtype=torch.int32, device=DEV)
-    out = torch.empty((6, d), dtype=torch.float32, device=DEV)
-    ops().embedding(ids, table, out, 1.0)
-    ref = plain.embedding(table.float().cpu().numpy().astype(np.float64), ids.cpu().tolist())
+    out = torch.full((6, d), 7.0, dtype=torch.float32, device=DEV)
+    ops().embedding(ids, table, out, scale)
+    ref = plain.embedding(table.float().cpu().numpy().astype(np.float64), ids.cpu().tolist()) * scale
     assert np.array_equal(out.cpu().numpy(), ref.astype(np.float32))
     assert not out[3].any() and not out[4].any()          # ids outside the table give zero rows
 
