@@ -484,6 +484,59 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
     const int first_split = sp.first, last_split = sp.last;
     if (first_split == last_split) return;   // written by the attention kernel itself
     const size_t base = ((size_t)item * H + h) * max_splits;
+    const int n = last_split - first_split + 1;
+    // Up to MERGE_SMEM splits: every thread fetches the (maximum, sum) of a few splits, the weights 2^(m_s - m) go to
+    // shared memory, and the sum over the splits then runs with sixteen loads in flight (in ascending order of the
+    // splits).  Longer lists take the plain loop below.
+    constexpr int MERGE_SMEM = 1024;
+    __shared__ float w_s[MERGE_SMEM];
+    __shared__ float l_s[MERGE_SMEM];
+    __shared__ float red_s[32];
+    __shared__ float inv_s;
+    if (n <= MERGE_SMEM) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+        float m = -INFINITY;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float2 ml = *reinterpret_cast<const float2*>(part_ml + (base + first_split + i) * 2);
+            w_s[i] = ml.x;
+            l_s[i] = ml.y;
+            m = fmaxf(m, ml.x);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) red_s[warp] = m;
+        __syncthreads();
+        m = red_s[0];
+        for (int i = 1; i < n_warps; ++i) m = fmaxf(m, red_s[i]);
+        const float mu = (m == -INFINITY) ? 0.0f : m;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) w_s[i] = exp2f(w_s[i] - mu);
+        __syncthreads();
+        if (warp == 0) {
+            // lane j adds the splits j, j + 32, ... in ascending order, then a fixed shuffle tree adds the lanes
+            float l = 0.0f;
+            for (int i = lane; i < n; i += 32) l += l_s[i] * w_s[i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+            if (lane == 0) inv_s = l > 0.0f ? 1.0f / l : 0.0f;
+        }
+        __syncthreads();
+        const float inv = inv_s;
+        for (int col = threadIdx.x; col < HD; col += blockDim.x) {
+            const float* po = part_o + (base + first_split) * HD + col;
+            float acc = 0.0f;
+            int i = 0;
+            for (; i + 16 <= n; i += 16) {
+                float v[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) v[u] = po[(size_t)(i + u) * HD];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) acc += v[u] * w_s[i + u];
+            }
+            for (; i < n; ++i) acc += po[(size_t)i * HD] * w_s[i];
+            out[((size_t)t * H + h) * HD + col] = __float2bfloat16_rn(acc * inv);
+        }
+        return;
+    }
     float m = -INFINITY;
     for (int s = first_split; s <= last_split; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
     const float mu = (m == -INFINITY) ? 0.0f : m;
