@@ -4,7 +4,7 @@ Option names, meanings and defaults are the reference's where it has them
 (src/mimirmind/CliParser.cpp:20-56, src/mimirmind/CliArgs.hpp:47-70): ``--config PATH``
 (default ./config.json, a hard error if the file is missing), ``--model PATH`` (overrides the
 default model's path), ``--prompt``, ``--max-new N`` (20), ``--temperature F`` (0 = greedy),
-``--top-k N`` (0 off), ``--top-p F`` (1.0 off), ``--seed N`` (0 = random), ``--log-level``.
+``--top-k N`` (0 off), ``--top-p F`` (1.0 off), ``--seed N`` (0 = random), ``--log-level``, ``--dump-dir``.
 This engine has no tokenizer (it takes token ids), so ``--prompt`` is a list of ids
 ("5 17 3" or "5,17,3"), as the reference's parity tool takes ``--tokens id,id,…``
 (tools/llama-parity-dump.cpp:111-124); ``--prompt-len N`` makes N seeded random ids instead.
@@ -35,6 +35,22 @@ def parse_prompt_ids(text: str) -> List[int]:
         raise SystemExit("--prompt must be token ids (\"5 17 3\" or \"5,17,3\"): this engine has no tokenizer") from None
 
 
+def print_kernel_shares(prof, top: int = 12) -> None:
+    """``diagnostics.profile``: where the GPU time of the run went, by kernel (the reference prints shares by category
+    of operation with ``diagnostics.traceOpTimes``, src/runtime/perf/OpProfiler.hpp)."""
+    import collections
+    import torch
+    agg = collections.defaultdict(lambda: [0.0, 0])
+    for e in prof.events():
+        if e.device_type == torch.autograd.DeviceType.CUDA:
+            agg[e.name][0] += e.time_range.elapsed_us()
+            agg[e.name][1] += 1
+    total = sum(v[0] for v in agg.values()) or 1.0
+    print(f"profile: {total / 1e3:.2f} ms of GPU time in {sum(v[1] for v in agg.values())} launches")
+    for name, (us, n) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:top]:
+        print(f"  {100 * us / total:5.1f} %  {us / 1e3:9.3f} ms  {n:6d} x  {name[:90]}")
+
+
 def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="mimirmind", description="B200-native inference engine (Qwen2.5 dense decoder)")
     ap.add_argument("mode", nargs="?", default="smoke", choices=USAGE_MODES)
@@ -49,6 +65,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--seed", type=int, default=0, help="RNG seed, 0 = random (default 0)")
     ap.add_argument("--dtype", default="", choices=["", "bfloat16", "float32"], help="overrides runtime.dtype")
     ap.add_argument("--log-level", default="info", choices=["trace", "debug", "info", "warn", "error", "off"])
+    ap.add_argument("--dump-dir", default="", help="directory for per-stage dumps of the prefill (sets diagnostics.parityDump to DIR/engine)")
     # replay mode
     ap.add_argument("--out", default="", help="(replay) folder for the logits files")
     ap.add_argument("--max-tokens", type=int, default=0, help="(replay) size of the cache pool in tokens")
@@ -93,6 +110,10 @@ def main(argv: Optional[List[str]] = None) -> int:
             cfg.defaultModel = "primary"
     if args.dtype:
         cfg.runtime.dtype = args.dtype
+    if args.dump_dir:
+        import os
+        os.makedirs(args.dump_dir, exist_ok=True)
+        cfg.diagnostics.parityDump = os.path.join(args.dump_dir, "engine")
     from .engine.engine import Engine
     from .sampling import SamplingParams
     import numpy as np
@@ -113,8 +134,21 @@ def main(argv: Optional[List[str]] = None) -> int:
         print(tok, end=" ", flush=True)
         return True
 
+    if cfg.diagnostics.parityDump:
+        log(f"diagnostics.parityDump={cfg.diagnostics.parityDump}: every layer writes its stages during the prefill "
+            f"({len(prompt)} tokens), synchronising at each")
+    prof = None
+    if cfg.diagnostics.profile:
+        from torch.profiler import ProfilerActivity, profile
+        prof = profile(activities=[ProfilerActivity.CUDA])
+        prof.__enter__()
     res = engine.generate([prompt], max_new_tokens=args.max_new, sampling=sp, on_token=on_token)[0]
     print()
+    if prof is not None:
+        import torch
+        torch.cuda.synchronize()
+        prof.__exit__(None, None, None)
+        print_kernel_shares(prof)
     st = res.stats
     n = st.generated_tokens
     if st.finish_reason.startswith("rejected") or st.finish_reason == "out_of_pages":

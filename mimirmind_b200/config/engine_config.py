@@ -47,8 +47,9 @@ class ServingSettings:
 
 @dataclass
 class DiagnosticsSettings:
-    profile: bool = False
-    traceDecodeFile: str = ""
+    parityDump: str = ""          # prefix of the per-stage dump files of a prefill (reference: diagnostics.parityDump)
+    traceDecodeFile: str = ""     # one JSON line per decode step (reference: diagnostics.traceDecodeFile)
+    profile: bool = False         # the command line prints where a prefill and a decode step spend their time
 
 
 @dataclass

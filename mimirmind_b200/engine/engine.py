@@ -63,6 +63,15 @@ class Engine:
         self.graph_steps = 0                # decode steps that were graph replays (statistics)
         self.h2d_bytes = 0                  # bytes copied host→device / device→host by generate()
         self.d2h_bytes = 0
+        self.decode_trace = None            # engine.diagnostics.DecodeTrace: a line per decode step
+
+    def set_diagnostics(self, parity_dump: str = "", trace_decode_file: str = "") -> None:
+        """Stage dumps of the steps that hold a prompt portion (file prefix) and a per-step decode trace (file)."""
+        from .diagnostics import DecodeTrace, StageDump
+        self.runner.stage_dump = StageDump(parity_dump) if parity_dump else None
+        if self.decode_trace is not None:
+            self.decode_trace.close()
+        self.decode_trace = DecodeTrace(trace_decode_file, self.model.rt.device.index or 0) if trace_decode_file else None
 
     # ---- construction ----------------------------------------------------------------
     @classmethod
@@ -81,9 +90,12 @@ class Engine:
             model = random_model(spec, int(entry.random.get("seed", 0)), cfg.runtime.dtype)
         else:
             model, _ = load_model(entry.path, cfg.runtime.dtype)
-        return cls(model, page_size=cfg.serving.blockSize, cache_tokens=cfg.runtime.cacheTokens,
-                   max_context=cfg.runtime.maxContextTokens, token_budget=cfg.serving.tokenBudget,
-                   max_active=cfg.serving.maxActiveRequests, prefill_chunk=cfg.serving.prefillChunk)
+        eng = cls(model, page_size=cfg.serving.blockSize, cache_tokens=cfg.runtime.cacheTokens,
+                  max_context=cfg.runtime.maxContextTokens, token_budget=cfg.serving.tokenBudget,
+                  max_active=cfg.serving.maxActiveRequests, prefill_chunk=cfg.serving.prefillChunk)
+        if cfg.diagnostics.parityDump or cfg.diagnostics.traceDecodeFile:
+            eng.set_diagnostics(cfg.diagnostics.parityDump, cfg.diagnostics.traceDecodeFile)
+        return eng
 
     # ---- generation --------------------------------------------------------------------
     def serve(self, max_graph_steps: int = 0) -> "ServingLoop":
@@ -175,12 +187,16 @@ class Engine:
             return stop
 
         cur = 0
+        t_prev = time.perf_counter()
         host_out[cur].copy_(sess.step(), non_blocking=True)
         stream.synchronize()
         while True:
             self.d2h_bytes += n * 4
             self.graph_steps += 1
             now = time.perf_counter()
+            if self.decode_trace is not None:
+                self.decode_trace.step(n, (now - t_prev) * 1e3)
+                t_prev = now
             toks = host_out[cur].tolist()
             more = sess.remaining() > 0
             if more:
@@ -196,8 +212,13 @@ class Engine:
             if stop:
                 self.d2h_bytes += n * 4
                 self.graph_steps += 1
-                account(host_out[cur].tolist(), time.perf_counter())
+                now = time.perf_counter()
+                if self.decode_trace is not None:
+                    self.decode_trace.step(n, (now - t_prev) * 1e3)
+                account(host_out[cur].tolist(), now)
                 break
+        if self.decode_trace is not None:
+            self.decode_trace.flush()
         return True
 
     def _run_plan(self, plan: Sequence[PlannedEntry]) -> Dict[Hashable, int]:
@@ -266,8 +287,12 @@ class ServingLoop:
             if sched.has_work():
                 raise RuntimeError("scheduler made no progress")   # cannot happen: a lone request fails instead
             return False
+        t_step = time.perf_counter()
         sampled = eng._run_plan(plan)
         now = time.perf_counter()
+        if eng.decode_trace is not None and all(p.count == 1 and p.samples for p in plan):
+            eng.decode_trace.step(len(plan), (now - t_step) * 1e3)
+            eng.decode_trace.flush()
         for p in plan:
             if p.samples:
                 self.first_at.setdefault(p.request.id, now)

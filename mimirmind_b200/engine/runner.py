@@ -65,6 +65,7 @@ class ModelRunner:
         self.steps_run = 0
         self._prefill_sessions: Dict[Tuple[int, bool], object] = {}
         self._prefill_seen: Dict[Tuple[int, bool], int] = {}
+        self.stage_dump = None       # engine.diagnostics.StageDump: steps with a prompt portion write their stages
 
     # ---- request life cycle ---------------------------------------------------
     def add_request(self, rid: Hashable) -> bool:
@@ -184,6 +185,10 @@ class ModelRunner:
         for e in entries:
             if mgr.mark_started(e.request):
                 self.storage.zero_slot(mgr.slot(e.request))
+        if self.stage_dump is not None and any(len(e.tokens) > 1 for e in entries):
+            ctx = self._build_context(entries)
+            ctx.plain_only = True
+            return self.forward(ctx, dump=self.stage_dump)
         session = self._prefill_session(entries)
         if session is not None:
             e = entries[0]
@@ -216,14 +221,18 @@ class ModelRunner:
             self._prefill_sessions[key] = sess
         return sess
 
-    def forward(self, ctx: StepContext) -> Optional[torch.Tensor]:
+    def forward(self, ctx: StepContext, dump=None) -> Optional[torch.Tensor]:
         m = self.model
         residual = m.embedding.forward(ctx.token_ids)
+        if dump is not None:
+            dump.write(0, "inp_scaled", residual)
         pending = None
         last = len(m.schedule) - 1
-        ctx.chain = ops.GemvChain() if (self.rt.dtype == torch.bfloat16 and USE_GEMV_CHAIN) else None
+        ctx.chain = ops.GemvChain() if (self.rt.dtype == torch.bfloat16 and USE_GEMV_CHAIN and dump is None) else None
         try:
             for i, e in enumerate(m.schedule):
+                if dump is not None:
+                    ctx.dump = lambda stage, rows, block=i: dump.write(block, stage, rows)
                 successor = m.layers[m.schedule[i + 1].layer] if i < last else None
                 pending = m.layers[e.layer].forward(residual, pending, ctx, self.storage.layer_cache(i, ctx), successor=successor)
             if ctx.chain is not None:

@@ -103,6 +103,20 @@ class GQAAttention(Mixer):
         self.position.apply(q.view(n, H, hd), k.view(n, G, hd), ctx.positions)
         return torch.cat([q, k.view(n, G * hd), v.view(n, G * hd)], dim=1)
 
+    def _dump_qkv(self, q: torch.Tensor, cache: LayerCache, ctx: StepContext) -> None:
+        """The reference's Qcur / Kcur / Vcur stages (src/runtime/arch/Qwen2Backend.cpp:390-392): q after bias and
+        rotation, and this step's keys and values as they stand in the cache (read back from their pages)."""
+        ctx.dump("Qcur", q)
+        if not cache.writes:
+            return
+        slots = ops.slot_mapping(ctx.positions, ctx.token_req, cache.block_table, cache.page_size).long()
+        ok = slots >= 0
+        page, place = (slots.clamp(min=0) // cache.page_size), (slots.clamp(min=0) % cache.page_size)
+        for stage, pool in (("Kcur", cache.k_pages), ("Vcur", cache.v_pages)):
+            rows = pool[page, :, place, :].reshape(q.shape[0], -1).clone()
+            rows[~ok] = 0
+            ctx.dump(stage, rows)
+
     def kv_cache_spec(self) -> Optional[KVCacheSpec]:
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
 
@@ -116,7 +130,7 @@ class GQAAttention(Mixer):
         H, G, hd = self.num_heads, self.num_kv_heads, self.head_dim
         k_pages, v_pages = (cache.k_pages, cache.v_pages) if cache.writes else (None, None)
         fused = self.position.fused_rotary()
-        fuses = self.fuses(n)
+        fuses = self.fuses(n) and not ctx.plain_only
         q = torch.empty((n, H * hd), dtype=self.rt.dtype, device=x.xw.device if isinstance(x, FactoredRows) else x.device)
         # rotation factors and cache places are the same in every layer that shares them: made once per step
         tables = fused is not None and fused[0] == hd and hd % 16 == 0 and self.rt.dtype == torch.bfloat16
@@ -151,6 +165,8 @@ class GQAAttention(Mixer):
                 qkv = self._encode_unfused(qkv, ctx)
                 ops.qkv_rope_kvwrite(qkv, None, q, k_pages, v_pages, ctx.positions, ctx.token_req, cache.block_table,
                                      cache.page_size, H, G, hd, 0, 1.0)
+        if ctx.dump is not None:
+            self._dump_qkv(q, cache, ctx)
         out = torch.empty_like(q)
         from ..kernels import attention as attn_kernels
         attn_kernels.paged_attention(q, cache, out, ctx, H, G, hd, self.window, self.scale)

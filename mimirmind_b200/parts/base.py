@@ -117,6 +117,10 @@ class StepContext:
     # kernels.ops.GemvChain or None: parts that fuse record their weight-streaming products here instead of launching
     # them; whoever launches anything else that reads their results flushes it first
     chain: Any = None
+    # diagnostics: ``dump(stage, tensor)`` writes a stage's rows for the layer that is running (None: off); with
+    # ``plain_only`` no part fuses its neighbours' work into its own kernels, so every stage exists as a tensor
+    dump: Any = None
+    plain_only: bool = False
 
 
 @dataclass

@@ -29,6 +29,8 @@ class PreNormBlock(Block):
         n = residual.shape[0]
         if ctx.chain is not None and not isinstance(pending, FactoredRows):
             ctx.chain.flush()                # the first norm is a kernel of its own
+        if ctx.plain_only:
+            return self._forward_plain(residual, pending, ctx, cache)
         mixer_fuses, ffn_fuses = self.mixer.fuses(n), self.feed_forward.fuses(n)
         h = pending if isinstance(pending, FactoredRows) else self.mixer_norm.forward(residual, pending)
         between = self.ffn_norm.factors() if (mixer_fuses and ffn_fuses) else None
@@ -43,3 +45,19 @@ class PreNormBlock(Block):
             return self.feed_forward.forward(h, ctx)       # the next block wants a plain pending sum
         sink = ResidualSink(residual, after[0], after[1]) if after is not None else ResidualSink(residual)
         return self.feed_forward.forward(h, ctx, sink=sink)
+
+    def _forward_plain(self, residual: torch.Tensor, pending, ctx: StepContext, cache: LayerCache):
+        """Every stage as a tensor of its own, with the stage dumps of the reference
+        (src/runtime/arch/Qwen2Backend.cpp:207, 431, 458, 462): the normalised input of the mixer, the two branch
+        outputs, and the layer's output (the residual stream with both branches added)."""
+        dump = ctx.dump or (lambda stage, t: None)
+        h = self.mixer_norm.forward(residual, pending)
+        dump("attn_norm", h)
+        branch = self.mixer.forward(h, ctx, cache)
+        dump("attn_out", branch)
+        h = self.ffn_norm.forward(residual, branch)
+        out = self.feed_forward.forward(h, ctx)
+        dump("ffn_mlp", out)
+        if ctx.dump is not None:
+            dump("l_out", residual + out.to(residual.dtype))
+        return out

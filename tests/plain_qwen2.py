@@ -165,6 +165,27 @@ def block(m: PlainModel, i: int, x: np.ndarray, positions: np.ndarray) -> np.nda
     return x + swiglu(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
 
 
+def block_stages(m: PlainModel, i: int, x: np.ndarray, positions: np.ndarray) -> Dict[str, np.ndarray]:
+    """The intermediate results of :func:`block` under the names of the reference's stage dumps
+    (src/runtime/arch/Qwen2Backend.cpp:207, 390-392, 431, 458, 462)."""
+    w, p = m.w, f"model.layers.{i}."
+    T = x.shape[0]
+    st = {}
+    st["attn_norm"] = n = rms_norm(x, w[p + "input_layernorm.weight"], m.eps)
+    q = linear(n, w[p + "self_attn.q_proj.weight"], w.get(p + "self_attn.q_proj.bias")).reshape(T, m.H, m.hd)
+    k = linear(n, w[p + "self_attn.k_proj.weight"], w.get(p + "self_attn.k_proj.bias")).reshape(T, m.G, m.hd)
+    v = linear(n, w[p + "self_attn.v_proj.weight"], w.get(p + "self_attn.v_proj.bias")).reshape(T, m.G, m.hd)
+    q, k = rope(q, positions, m.theta), rope(k, positions, m.theta)
+    st["Qcur"], st["Kcur"], st["Vcur"] = q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)
+    o = attention(q, k, v, m.windows[i]).reshape(T, m.H * m.hd)
+    st["attn_out"] = linear(o, w[p + "self_attn.o_proj.weight"])
+    x = x + st["attn_out"]
+    n = rms_norm(x, w[p + "post_attention_layernorm.weight"], m.eps)
+    st["ffn_mlp"] = swiglu(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    st["l_out"] = x + st["ffn_mlp"]
+    return st
+
+
 def forward(m: PlainModel, tokens: List[int], return_hidden: bool = False):
     """embedding -> L blocks -> final norm -> head; head = lm_head if present else the embedding table
     (src/runtime/InferenceEngine.cpp:1374-1377, 1685-1690)."""

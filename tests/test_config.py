@@ -103,6 +103,14 @@ def test_engine_config_defaults_and_ranges():
             parse_engine_config(bad)
 
 
+def test_engine_config_diagnostics():
+    cfg = parse_engine_config({"diagnostics": {"parityDump": "/tmp/p", "traceDecodeFile": "/tmp/t", "profile": True}})
+    assert cfg.diagnostics.parityDump == "/tmp/p" and cfg.diagnostics.traceDecodeFile == "/tmp/t" and cfg.diagnostics.profile
+    assert parse_engine_config({}).diagnostics.parityDump == ""
+    with pytest.raises(EngineConfigError, match="diagnostics.traceBlock0"):
+        parse_engine_config({"diagnostics": {"traceBlock0": True}})
+
+
 def test_engine_config_rejects_unknown_keys():
     with pytest.raises(EngineConfigError, match="unknown key 'server'"):
         parse_engine_config({"server": {"port": 8080}})

@@ -285,3 +285,52 @@ def test_requests_added_while_others_run_get_the_tokens_they_get_alone(model_fol
     assert eng.graph_steps > 0
     eng.runner.manager.check()
     assert not eng.runner.manager.live_requests()
+
+
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("D", "bfloat16")])
+def test_stage_dumps_of_a_prefill_and_the_decode_trace(name, dtype, model_folders, plain_models, tmp_path):
+    """diagnostics.parityDump: every layer's stages of the prefill in the reference's file format, against the
+    plain implementation's stages; diagnostics.traceDecodeFile: a line per decode step.  The tokens generated with the
+    diagnostics on are those generated without them."""
+    import plain_qwen2 as plain
+    from mimirmind_b200 import Engine
+    from mimirmind_b200.engine.diagnostics import read_stage_dump
+    pm = plain_models(name, dtype)
+    prompt = random_tokens(pm.V, 45, 3)
+    eng = Engine.from_folder(model_folders(name, dtype), dtype=dtype, cache_tokens=512,
+                             max_context=TINY[name]["max_position_embeddings"], token_budget=64, max_active=2)
+    want = eng.generate([prompt], max_new_tokens=12, use_eos=False)[0].tokens
+    prefix, trace = str(tmp_path / "dump"), str(tmp_path / "trace.ndjson")
+    eng.set_diagnostics(parity_dump=prefix, trace_decode_file=trace)
+    got = eng.generate([prompt], max_new_tokens=12, use_eos=False)[0].tokens
+    eng.set_diagnostics()
+    assert got == want
+    x = plain.embedding(pm.w["model.embed_tokens.weight"], prompt)
+    block, rows = read_stage_dump(prefix + "-blk0-inp_scaled.bin")
+    assert block == 0 and rows.shape == x.shape
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    assert np.abs(rows - x).max() <= tol * max(1.0, np.abs(x).max())
+    pos = np.arange(len(prompt))
+    for i in range(pm.L):
+        st = plain.block_stages(pm, i, x, pos)
+        for stage, ref in st.items():
+            block, rows = read_stage_dump(f"{prefix}-blk{i}-{stage}.bin")
+            assert block == i and rows.shape == ref.shape, (i, stage, rows.shape, ref.shape)
+            assert np.abs(rows - ref).max() <= tol * max(1.0, np.abs(ref).max()), (i, stage)
+        x = st["l_out"]
+    lines = [json.loads(l) for l in open(trace)]
+    assert len(lines) == 11 and [l["step"] for l in lines] == list(range(11))        # the first token comes from the prefill
+    assert all(l["tokens"] == 1 and l["wall_ms"] > 0 and {"sm_mhz", "gpu_c"} <= set(l) for l in lines)
+
+
+def test_command_line_dump_dir_and_profile(model_folders, tmp_path):
+    cfg = {"defaultModel": "m", "models": [{"id": "m", "path": model_folders("A", "float32")}],
+           "runtime": {"dtype": "float32", "maxContextTokens": 256, "cacheTokens": 512}, "diagnostics": {"profile": True}}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "mimirmind"), "smoke", "--config", str(tmp_path / "config.json"),
+           "--prompt", "5 17 3 200 9", "--max-new", "4", "--dump-dir", str(tmp_path / "dumps")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert "profile:" in out.stdout and "% " in out.stdout
+    names = sorted(os.listdir(tmp_path / "dumps"))
+    assert "engine-blk0-inp_scaled.bin" in names and "engine-blk1-l_out.bin" in names and len(names) == 1 + 2 * 7
