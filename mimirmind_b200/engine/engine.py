@@ -280,15 +280,26 @@ class ServingLoop:
         eng, sched = self.engine, self.sched
         if not sched.has_work():
             return False
-        if eng.use_graphs and sched.all_decoding() and eng._decode_run(self):
-            return sched.has_work()
+        if eng.use_graphs and sched.all_decoding():
+            running = list(sched.running)
+            try:
+                ran = eng._decode_run(self)
+            except Exception as e:
+                self._fail(running, e)
+                raise
+            if ran:
+                return sched.has_work()
         plan = sched.schedule()
         if not plan:
             if sched.has_work():
                 raise RuntimeError("scheduler made no progress")   # cannot happen: a lone request fails instead
             return False
         t_step = time.perf_counter()
-        sampled = eng._run_plan(plan)
+        try:
+            sampled = eng._run_plan(plan)
+        except Exception as e:
+            self._fail([p.request for p in plan], e)
+            raise
         now = time.perf_counter()
         if eng.decode_trace is not None and all(p.count == 1 and p.samples for p in plan):
             eng.decode_trace.step(len(plan), (now - t_step) * 1e3)
@@ -302,6 +313,14 @@ class ServingLoop:
             if p.samples and self.deliver(p.request, sampled[p.request.id]) is False and p.request.state != "finished":
                 sched.cancel(p.request.id)
         return sched.has_work()
+
+    def _fail(self, requests, error: Exception) -> None:
+        """A step that raised ends the requests it held (finish reason "error: ..."), as a failed batched step fails its
+        requests in the reference (src/runtime/serving/ContinuousBatcher.cpp:417-429); their pages and slots go back, the
+        requests that were not in the step and the loop itself stay usable, and the caller gets the exception."""
+        for r in requests:
+            if r.state != "finished":
+                self.sched.cancel(r.id, reason=f"error: {type(error).__name__}: {error}"[:200])
 
     def run_until_idle(self) -> None:
         while self.step():

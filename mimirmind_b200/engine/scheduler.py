@@ -242,13 +242,15 @@ class Scheduler:
         """Nothing waits and every running request has exactly its last token left to feed."""
         return bool(self._lib.mmh_sched_all_decoding(self._h))
 
-    def cancel(self, rid: Hashable) -> bool:
+    def cancel(self, rid: Hashable, reason: str = "cancelled") -> bool:
+        """Ends a waiting or running request and gives back what it holds.  ``reason`` becomes its finish reason
+        (a step that failed ends its requests with "error: ...")."""
         h = self._handle.get(rid)
         if h is None:
             return False
         rc = self._check(self._lib.mmh_sched_cancel(self._h, h))
         if rc == 1:
             req = self._by_handle[h]
-            req.state, req.finish_reason = FINISHED, "cancelled"
+            req.state, req.finish_reason = FINISHED, reason
             self.manager.forget(rid)
         return rc == 1

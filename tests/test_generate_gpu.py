@@ -334,3 +334,32 @@ def test_command_line_dump_dir_and_profile(model_folders, tmp_path):
     assert "profile:" in out.stdout and "% " in out.stdout
     names = sorted(os.listdir(tmp_path / "dumps"))
     assert "engine-blk0-inp_scaled.bin" in names and "engine-blk1-l_out.bin" in names and len(names) == 1 + 2 * 7
+
+
+def test_a_step_that_fails_ends_its_requests_and_nothing_else(model_folders):
+    """An exception out of a step: the requests in it finish with "error: ...", their pages go back, a request that was
+    still waiting runs afterwards, and so does the next call."""
+    from mimirmind_b200 import Engine
+    eng = Engine.from_folder(model_folders("A", "float32"), dtype="float32", cache_tokens=512, max_context=256,
+                             token_budget=64, max_active=2)
+    prompts = [random_tokens(256, n, n) for n in (20, 30, 10)]
+    alone = [eng.generate([p], max_new_tokens=8, use_eos=False)[0].tokens for p in prompts]
+    loop = eng.serve()
+    h = [loop.submit(p, 8, use_eos=False) for p in prompts]          # two run, the third waits (max_active=2)
+    real, calls = eng._run_plan, []
+
+    def failing(plan):
+        calls.append(len(plan))
+        if len(calls) == 1:
+            raise RuntimeError("injected")
+        return real(plan)
+    eng._run_plan = failing
+    with pytest.raises(RuntimeError, match="injected"):
+        loop.step()
+    assert loop.finished(h[0]) and loop.finished(h[1]) and not loop.finished(h[2])
+    assert loop.result(h[0]).stats.finish_reason.startswith("error: RuntimeError: injected")
+    loop.run_until_idle()
+    eng._run_plan = real
+    assert loop.result(h[2]).tokens == alone[2] and loop.result(h[2]).stats.finish_reason == "length"
+    assert eng.runner.manager.free_pages() == eng.runner.manager.total_pages()
+    assert eng.generate([prompts[0]], max_new_tokens=8, use_eos=False)[0].tokens == alone[0]
