@@ -1,9 +1,11 @@
 """bfloat16 matrix products y = x · Wᵀ (+ bias) on the tensor cores.
 
-Up to 16 rows go to this library's weight-streaming kernel (csrc/gemv_bf16.cu).  Beyond that the
-library route is cuBLAS through ``torch.mm`` (the reference's bf16 library route is
-cuBLASLt, src/compute/cuda/GpuMatmul.cpp:786-884); accumulation is fp32 inside the
-product and the result is rounded once to the requested dtype.
+The plain product of a part that does not fuse anything into it.  Up to ``ops.GEMV_MAX_ROWS`` rows go to this
+library's weight-streaming kernel (csrc/gemv_bf16.cu); beyond that the route is cuBLAS through ``torch.mm`` (the
+reference's bf16 library route is cuBLASLt, src/compute/cuda/GpuMatmul.cpp:786-884); accumulation is fp32 inside
+the product and the result is rounded once to the requested dtype.  The products with fused epilogues (the decode
+layer's, csrc/gemv_bf16.cu and csrc/gemm_skinny_tcgen05.cu; the prefill gate/up product, csrc/gemm_tcgen05.cu) are
+called by the parts directly.
 """
 from __future__ import annotations
 
