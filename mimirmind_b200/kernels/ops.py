@@ -230,7 +230,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     return out
 
 
-GEMV_MAX_ROWS = 12     # measured on B200 (7B shapes, whole decode step): fused streaming kernel vs library + separate norm/rotary/activation kernels: 9 rows 3.59 vs 3.66 ms, 12 rows 3.65 vs 3.70, 16 rows 3.77 vs 3.65
+GEMV_MAX_ROWS = 8      # measured on B200 (7B shapes, 8 layers, whole decode step): from 9 rows on the tcgen05 product is ahead of the register-streaming kernel's two-tile variant (9 rows 1.15 vs 1.25 ms, 12 rows 1.20 vs 1.30 ms)
 
 
 # Above the streaming kernel's rows and up to here the tcgen05 weight-streaming product (with the fused epilogues) is
