@@ -136,7 +136,8 @@ def run(q, cache, out, ctx, num_heads: int, num_kv_heads: int, head_dim: int, wi
         plan = make_plan(ctx, num_heads, num_kv_heads, head_dim)
         ctx.plans[key] = plan
     lib = _lib.load()
-    stream = torch.cuda.current_stream().cuda_stream
+    from . import ops
+    stream = ops._stream()
     table = cache.block_table
     if plan.n_tiles and plan.tile_rows == TILE_ROWS_TC:
         from . import ops

@@ -60,6 +60,8 @@ _PROTOTYPES = {
 
 def load(verbose: bool = True) -> ctypes.CDLL:
     global _lib
+    if _lib is not None:          # the usual case, without the lock: every launch comes through here
+        return _lib
     with _lock:
         if _lib is not None:
             return _lib
