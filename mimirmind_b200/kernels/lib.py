@@ -33,6 +33,7 @@ _PROTOTYPES = {
     "mm_silu_mul": [P, P, I, I, I, I, P],
     "mm_gemm_tcgen05": [P, P, P, I, P, I, I, I, I, I, I, P, P],
     "mm_gemm_tcgen05_pair": [P, P, P, I, P, I, I, I, I, I, I, P, P],
+    "mm_gemm_tcgen05_streamk": [P, P, P, I, P, I, I, I, I, I, I, P, P, I, P, P],
     "mm_gemv_bf16": [P, P, P, I, P, I, I, I, I, I, I, I, I, I, P, I, I, F, P],
     "mm_gemv_bf16_residual": [P, P, P, P, I, P, P, I, I, I, I, I, I, P, I, I, F, P],
     "mm_gemv_bf16_qkv_rope": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, I, F, P],

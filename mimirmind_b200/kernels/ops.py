@@ -578,6 +578,56 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     return out
 
 
+_STREAMK_SCRATCH = {}
+
+
+def _streamk_scratch(device):
+    """(pairs, partial sums fp32 [pairs, 2, 128, 256], flags int32 [(pairs + 1) * 2], zero) of a device, made once."""
+    key = str(device)
+    if key not in _STREAMK_SCRATCH:
+        pairs = torch.cuda.get_device_properties(device).multi_processor_count // 2
+        _STREAMK_SCRATCH[key] = (pairs, torch.empty((pairs, 2, 128, 256), dtype=torch.float32, device=device),
+                                 torch.zeros((pairs + 1) * 2, dtype=torch.int32, device=device))
+    return _STREAMK_SCRATCH[key]
+
+
+def gemm_tcgen05_streamk_supported(m: int, n: int, k: int, device) -> bool:
+    """The tiles left over after the whole rounds have at least one k block for every pair of CTAs."""
+    if not gemm_tcgen05_supported(m, n, k):
+        return False
+    pairs = torch.cuda.get_device_properties(device).multi_processor_count // 2
+    left = ((-(-m // 256)) * (-(-n // 256))) % pairs
+    return left == 0 or left * (-(-k // 64)) >= pairs
+
+
+def gemm_tcgen05_streamk(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
+                         swiglu: bool = False) -> torch.Tensor:
+    """:func:`gemm_tcgen05` on CTA pairs with the k blocks of all tiles shared out evenly over the pairs, for products
+    whose tiles do not fill a whole number of rounds.  Calls on one device share their scratch: one at a time."""
+    _need(x, "gemm x", torch.bfloat16)
+    _need(w, "gemm w", torch.bfloat16)
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape != (n, k) or not gemm_tcgen05_streamk_supported(m, n, k, x.device):
+        raise KernelError(f"gemm_tcgen05_streamk: shapes x{tuple(x.shape)} w{tuple(w.shape)} are not supported")
+    if swiglu:
+        if n % 16 or bias is not None or out_dtype != torch.bfloat16:
+            raise KernelError("gemm_tcgen05: the SwiGLU epilogue needs N a multiple of 16, no bias, bf16 output")
+        out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
+        epi = EPI_SWIGLU
+    else:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        epi = EPI_F32 if out_dtype == torch.float32 else EPI_BF16
+    if bias is not None:
+        _need(bias, "gemm bias")
+    pairs, ws, flags = _streamk_scratch(x.device)
+    check(_lib.load().mm_gemm_tcgen05_streamk(
+        x.data_ptr(), w.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, out.data_ptr(), epi,
+        m, n, k, k, out.shape[1], ws.data_ptr(), flags.data_ptr(), pairs, tcgen05_error_flag(x.device).data_ptr(), _stream()),
+        "gemm_tcgen05_streamk")
+    return out
+
+
 def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need(logits, "argmax logits", torch.float32)
     r, v = logits.shape

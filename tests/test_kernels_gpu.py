@@ -753,6 +753,38 @@ def test_gemm_tcgen05_pair_many_tiles_per_pair():
     assert np.abs(two.cpu().numpy() - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
 
 
+@pytest.mark.parametrize("M,N,K", [(2048, 2400, 1000), (1100, 4600, 1000), (2048, 3584, 448), (256, 512, 4096), (2048, 37888 // 4, 200)])
+def test_gemm_tcgen05_streamk(M, N, K):
+    """Whole rounds of tiles as in the pair kernel, the k blocks of the left-over tiles shared out over all CTA pairs:
+    a cut tile is summed through the scratch (two tiles among 74 pairs in one case: 36 sets of partial sums per tile).
+    Against the pair kernel (same products; only the cut tiles' sums are taken in parts), against float64 on some rows,
+    twice in a row (the flags are left clean), and the other epilogues."""
+    rng = np.random.RandomState(N)
+    x, w = t(rng.randn(M, K), torch.bfloat16), t(rng.randn(N, K) * 0.05, torch.bfloat16)
+    assert ops().gemm_tcgen05_streamk_supported(M, N, K, x.device)
+    whole = ops().gemm_tcgen05(x, w, None, torch.float32, pair=True)
+    for _ in range(2):
+        got = ops().gemm_tcgen05_streamk(x, w, None, torch.float32)
+        ops().check_tcgen05_errors(x.device)
+        assert (got - whole).abs().max().item() <= 2e-6 * np.sqrt(K) * whole.abs().max().item()
+    rows = [0, 127, 128, 255, M // 2, M - 1]
+    ref = x[rows].double().cpu().numpy() @ w.double().cpu().numpy().T
+    assert np.abs(got[rows].cpu().numpy() - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
+    bias = t(rng.randn(N), torch.float32)
+    gb = ops().gemm_tcgen05_streamk(x, w, bias, torch.bfloat16).float()
+    wb = ops().gemm_tcgen05(x, w, bias, torch.bfloat16, pair=True).float()
+    assert (gb - wb).abs().max().item() <= 2 ** -7 * wb.abs().max().item()
+    if N % 16 == 0:
+        ga = ops().gemm_tcgen05_streamk(x, w, None, torch.bfloat16, swiglu=True).float()
+        wa = ops().gemm_tcgen05(x, w, None, torch.bfloat16, swiglu=True, pair=True).float()
+        assert (ga - wa).abs().max().item() <= 2 ** -7 * max(wa.abs().max().item(), 1e-3)
+    ops().check_tcgen05_errors(x.device)
+    assert not ops().gemm_tcgen05_streamk_supported(256, 256, 64, x.device)        # one k block cannot feed every pair
+    from mimirmind_b200.kernels.lib import KernelError
+    with pytest.raises(KernelError):
+        ops().gemm_tcgen05_streamk(x[:256, :64].contiguous(), w[:256, :64].contiguous(), None, torch.float32)
+
+
 @pytest.mark.parametrize("M,F,K", [(130, 352, 256), (1030, 1000, 512), (64, 72, 64)])
 @pytest.mark.parametrize("pair", [False, True])
 def test_gemm_tcgen05_swiglu_epilogue(M, F, K, pair):
