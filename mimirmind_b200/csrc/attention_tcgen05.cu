@@ -139,23 +139,71 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         prefetch_tensormap(&tmK);
         prefetch_tensormap(&tmV);
     }
-    if (threadIdx.x == 0) {
-        mbar_init(smem_u32(&ctl->q_full), 1);
-        for (int s = 0; s < KV_STAGES; ++s) {
-            mbar_init(smem_u32(&ctl->k_full[s]), 1);
-            mbar_init(smem_u32(&ctl->k_empty[s]), 1);
-            mbar_init(smem_u32(&ctl->v_full[s]), 1);
-            mbar_init(smem_u32(&ctl->v_empty[s]), 1);
+    // ---- what the TMA producers need: warp 0 keys (and Q), warp 10 values; lane = (page of the tile, column half) ----
+    const int pages_per_tile = BN / page_size;
+    const uint32_t page_bytes = (uint32_t)page_size * 128u;           // one column half of a page
+    const int pj = lane >> 1, phf = lane & 1;                         // this lane's page and half
+    // pages of a tile that hold keys some row of the tile may see.  The ids are read a few tiles ahead: the load
+    // from the block table would otherwise sit, with its full latency, between every two tiles.
+    auto page_of = [&](int kt) -> int {
+        if (kt >= kt_end || pj >= pages_per_tile) return -1;
+        const int key_lo = kt * BN + pj * page_size;
+        return (key_lo < hi_all && key_lo + page_size > lo_all) ? table[kt * pages_per_tile + pj] : -1;
+    };
+    constexpr int AHEAD = 4;
+    int ahead[AHEAD];
+    // one tile of keys or values: waits for the stage (not for the very first round), announces the bytes, copies
+    auto produce = [&](bool for_k, int kt, uint32_t it, bool wait) -> bool {
+        const int s = it % KV_STAGES;
+        const uint32_t ph = (it / KV_STAGES) & 1;
+        const int pid = ahead[0];
+#pragma unroll
+        for (int i = 0; i + 1 < AHEAD; ++i) ahead[i] = ahead[i + 1];
+        ahead[AHEAD - 1] = page_of(kt + AHEAD);
+        const uint32_t have = __ballot_sync(0xffffffffu, pid >= 0);
+        const uint32_t full = smem_u32(for_k ? &ctl->k_full[s] : &ctl->v_full[s]);
+        bool ok = true;
+        if (lane == 0) {
+            if (wait) ok = mbar_wait(smem_u32(for_k ? &ctl->k_empty[s] : &ctl->v_empty[s]), ph ^ 1, abort_flag);
+            if (ok) mbar_expect_tx(full, (uint32_t)__popc(have) * page_bytes);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&ctl->s_full[b]), 1);
-            mbar_init(smem_u32(&ctl->s_free[b]), GROUP_WARPS);
-            mbar_init(smem_u32(&ctl->p_full[b]), GROUP_WARPS);
-            mbar_init(smem_u32(&ctl->pv_done[b]), 1);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok && pid >= 0)
+            tma_load_2d(smem_u32((for_k ? sK : sV) + s * TILE_BYTES) + phf * HALF_BYTES + (uint32_t)pj * page_bytes, for_k ? &tmK : &tmV,
+                        phf * 64, (pid * G + g) * page_size, full);
+        return ok;
+    };
+    if (warp == 0 || warp == V_PRODUCER_WARP) {
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i) ahead[i] = page_of(kt_begin + i);
+    }
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_init(smem_u32(&ctl->q_full), 1);
+            for (int s = 0; s < KV_STAGES; ++s) {
+                mbar_init(smem_u32(&ctl->k_full[s]), 1);
+                mbar_init(smem_u32(&ctl->k_empty[s]), 1);
+                mbar_init(smem_u32(&ctl->v_full[s]), 1);
+                mbar_init(smem_u32(&ctl->v_empty[s]), 1);
+            }
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(smem_u32(&ctl->s_full[b]), 1);
+                mbar_init(smem_u32(&ctl->s_free[b]), GROUP_WARPS);
+                mbar_init(smem_u32(&ctl->p_full[b]), GROUP_WARPS);
+                mbar_init(smem_u32(&ctl->pv_done[b]), 1);
+            }
+            mbar_init(smem_u32(&ctl->l_full), SOFTMAX_WARPS);
+            ctl->abort_flag = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // Q and the first tile of keys need nobody else: their copies go out before the CTA has set itself up
+            const uint32_t qbar = smem_u32(&ctl->q_full);
+            mbar_expect_tx(qbar, TILE_BYTES);
+            tma_load_2d(smem_u32(sQ), &tmQ, h * HD, row0, qbar);
+            tma_load_2d(smem_u32(sQ) + HALF_BYTES, &tmQ, h * HD + 64, row0, qbar);
         }
-        mbar_init(smem_u32(&ctl->l_full), SOFTMAX_WARPS);
-        ctl->abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        __syncwarp();
+        if (kt_begin < kt_end) produce(true, kt_begin, 0, false);
     }
     // Value tiles must never hold non-finite leftovers: rows of a page that was not fetched are multiplied by P = 0.
     for (int i = threadIdx.x; i < KV_STAGES * TILE_BYTES / 16; i += ATT_TC_THREADS) reinterpret_cast<uint4*>(sV)[i] = make_uint4(0, 0, 0, 0);
@@ -170,49 +218,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     const uint32_t tmem_base = ctl->tmem_base;
 
     if (warp == 0 || warp == V_PRODUCER_WARP) {
-        // ---- TMA producers: warp 0 keys (and Q), warp 10 values; lane = (page of the tile, column half) ----
+        // ---- TMA producers ----
         const bool for_k = warp == 0;
-        if (for_k && lane == 0) {
-            const uint32_t qbar = smem_u32(&ctl->q_full);
-            mbar_expect_tx(qbar, TILE_BYTES);
-            tma_load_2d(smem_u32(sQ), &tmQ, h * HD, row0, qbar);
-            tma_load_2d(smem_u32(sQ) + HALF_BYTES, &tmQ, h * HD + 64, row0, qbar);
-        }
-        const int pages_per_tile = BN / page_size;
-        const uint32_t page_bytes = (uint32_t)page_size * 128u;       // one column half of a page
-        const int j = lane >> 1, hf = lane & 1;                       // this lane's page and half
-        const CUtensorMap* map = for_k ? &tmK : &tmV;
-        unsigned char* ring = for_k ? sK : sV;
-        uint32_t it = 0;
         bool ok = true;
-        // pages of a tile that hold keys some row of the tile may see.  The ids are read a few tiles ahead: the load
-        // from the block table would otherwise sit, with its full latency, between every two tiles.
-        auto page_of = [&](int kt) -> int {
-            if (kt >= kt_end || j >= pages_per_tile) return -1;
-            const int key_lo = kt * BN + j * page_size;
-            return (key_lo < hi_all && key_lo + page_size > lo_all) ? table[kt * pages_per_tile + j] : -1;
-        };
-        constexpr int AHEAD = 4;
-        int ahead[AHEAD];
-#pragma unroll
-        for (int i = 0; i < AHEAD; ++i) ahead[i] = page_of(kt_begin + i);
-        for (int kt = kt_begin; kt < kt_end && ok; ++kt, ++it) {
-            const int s = it % KV_STAGES;
-            const uint32_t ph = (it / KV_STAGES) & 1;
-            const int pid = ahead[0];
-#pragma unroll
-            for (int i = 0; i + 1 < AHEAD; ++i) ahead[i] = ahead[i + 1];
-            ahead[AHEAD - 1] = page_of(kt + AHEAD);
-            const uint32_t have = __ballot_sync(0xffffffffu, pid >= 0);
-            const uint32_t full = smem_u32(for_k ? &ctl->k_full[s] : &ctl->v_full[s]);
-            if (lane == 0) {
-                ok = mbar_wait(smem_u32(for_k ? &ctl->k_empty[s] : &ctl->v_empty[s]), ph ^ 1, abort_flag);
-                if (ok) mbar_expect_tx(full, (uint32_t)__popc(have) * page_bytes);
-            }
-            ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (ok && pid >= 0)
-                tma_load_2d(smem_u32(ring + s * TILE_BYTES) + hf * HALF_BYTES + (uint32_t)j * page_bytes, map, hf * 64, (pid * G + g) * page_size, full);
-        }
+        uint32_t it = for_k ? 1u : 0u;                                 // the first key tile is on its way already
+        for (int kt = kt_begin + (int)it; kt < kt_end && ok; ++kt, ++it) ok = produce(for_k, kt, it, true);
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer ----
