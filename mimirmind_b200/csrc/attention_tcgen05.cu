@@ -23,6 +23,8 @@
 // turn, was what bound the kernel); warp 0 = TMA producer for keys (and Q), warp 10 = TMA producer for values: every lane fetches one half of one
 // page, so the 16 to 32 small copies of a tile are issued at once (one thread issuing them in turn was the
 // bottleneck of the whole kernel); warp 1 = MMA issuer and tensor-memory owner; warps 2..9 = softmax and output.  Same formula as the other attention kernels (reference src/compute/Attention.cpp:43-94).
+// Warp 0 requests Q and the first key tile before the CTA's set-up barrier (tensor-memory allocation, zeroing of the value
+// ring), which nothing of that needs.
 // All mbarrier waits are bounded; on a time-out the kernel frees its tensor memory, sets `err`
 // and returns.
 #include "tcgen05.cuh"
