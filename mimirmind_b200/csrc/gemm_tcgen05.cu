@@ -75,6 +75,24 @@ __device__ __forceinline__ void add_partial(uint32_t* r, const float* p_col0_row
     for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __ldcg(p_col0_row + (size_t)i * BM));
 }
 
+// The same for n blocks `stride` floats apart, two blocks' loads in flight at a time, added in the order of the blocks
+__device__ __forceinline__ void add_partials(uint32_t* r, const float* p, int n, size_t stride) {
+    int pi = 0;
+    for (; pi + 2 <= n; pi += 2) {
+        float a[32], b[32];
+        const float* pa = p + pi * stride;
+        const float* pb = pa + stride;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            a[i] = __ldcg(pa + (size_t)i * BM);
+            b[i] = __ldcg(pb + (size_t)i * BM);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint((__uint_as_float(r[i]) + a[i]) + b[i]);
+    }
+    if (pi < n) add_partial(r, p + pi * stride);
+}
+
 // One warp's 32 rows of a 128 x 256 accumulator, as they are, to `ws` (fp32 [256][128])
 __device__ __forceinline__ void dump_rows(uint32_t taddr, int q, int lane, float* __restrict__ ws) {
     float* wcol = ws + q * 32 + lane;
@@ -105,7 +123,7 @@ __device__ __forceinline__ void epilogue_rows(uint32_t taddr, int m0, int n0, in
             if (col0 >= N) break;                      // uniform over the warp
             uint32_t r[32];
             tmem_ld32(taddr + c * 32, r);
-            for (int pi = 0; pi < n_partial; ++pi) add_partial(r, prow + pi * partial_stride + (size_t)(c * 32) * BM);
+            add_partials(r, prow + (size_t)(c * 32) * BM, n_partial, partial_stride);
             if (row >= M) continue;
             float* o = (float*)out + (size_t)row * ldo + col0;
             for (int i = 0; i < 32 && col0 + i < N; ++i) {
@@ -130,7 +148,7 @@ __device__ __forceinline__ void epilogue_rows(uint32_t taddr, int m0, int n0, in
                 if (col0 >= N) break;                                 // uniform over the warp
                 uint32_t r[32];
                 tmem_ld32(taddr + c * 32, r);
-                for (int pi = 0; pi < n_partial; ++pi) add_partial(r, prow + pi * partial_stride + (size_t)(c * 32) * BM);
+                add_partials(r, prow + (size_t)(c * 32) * BM, n_partial, partial_stride);
                 float v[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
