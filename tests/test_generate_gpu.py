@@ -363,3 +363,49 @@ def test_a_step_that_fails_ends_its_requests_and_nothing_else(model_folders):
     assert loop.result(h[2]).tokens == alone[2] and loop.result(h[2]).stats.finish_reason == "length"
     assert eng.runner.manager.free_pages() == eng.runner.manager.total_pages()
     assert eng.generate([prompts[0]], max_new_tokens=8, use_eos=False)[0].tokens == alone[0]
+
+
+def test_random_settings_many_engines_in_one_process(model_folders):
+    """Engines come and go in one process, each with random batch, budget, pool, portion cap and sampling (greedy or
+    sampled, with and without top-k, top-p and penalties); captured decode runs, preemption and admission interleave.
+    In float32 every request's tokens equal those it gets alone without graphs."""
+    import gc
+    import random
+    from mimirmind_b200 import Engine, SamplingParams
+    rng = random.Random(5)
+    graph_steps = preempted = 0
+    for it in range(12):
+        name = rng.choice(["A", "B", "C"])
+        V, ctx = TINY[name]["vocab_size"], min(512, TINY[name]["max_position_embeddings"])
+        n, news, sampled = rng.randint(1, 9), rng.randint(2, 36), rng.random() < 0.5
+        prompts = [random_tokens(V, rng.randint(1, 110), rng.randint(0, 10 ** 6)) for _ in range(n)]
+
+        def params(i):
+            if not sampled:
+                return SamplingParams()
+            kw = dict(temperature=rng.choice([0.7, 1.0]), seed=100 + i)
+            if rng.random() < 0.4:
+                kw.update(top_k=rng.choice([5, 40]))
+            if rng.random() < 0.4:
+                kw.update(top_p=0.9)
+            if rng.random() < 0.3:
+                kw.update(repetition_penalty=1.2, penalty_window=rng.choice([8, 64]))
+            return SamplingParams(**kw)
+        sp = [params(i) for i in range(n)]
+        kw = dict(dtype="float32", max_context=ctx, token_budget=rng.choice([16, 48, 96, 512]), prefill_chunk=rng.choice([0, 0, 32]))
+        busy = Engine.from_folder(model_folders(name, "float32"), cache_tokens=rng.choice([256, 640, 4096]),
+                                  max_active=rng.choice([1, 2, 4, 8]), **kw)
+        got = busy.generate(prompts, max_new_tokens=news, sampling=sp, use_eos=False)
+        alone = Engine.from_folder(model_folders(name, "float32"), cache_tokens=4096, max_active=1, use_graphs=False, **kw)
+        for i, p in enumerate(prompts):
+            if got[i].stats.finish_reason.startswith("rejected") or got[i].stats.finish_reason == "out_of_pages":
+                continue
+            want = alone.generate([p], max_new_tokens=news, sampling=sp[i], use_eos=False)[0].tokens
+            assert got[i].tokens == want, (it, name, i, kw)
+        assert busy.runner.manager.free_pages() == busy.runner.manager.total_pages()
+        graph_steps += busy.graph_steps
+        preempted += busy.last_metrics.preempted
+        del busy, alone
+        if it % 3 == 0:
+            gc.collect()
+    assert graph_steps > 0
