@@ -59,6 +59,7 @@ class Engine:
         self.last_metrics = None
         self.use_graphs = use_graphs
         self.graph_min_steps = 8            # shorter decode runs are stepped eagerly
+        self.max_decode_graphs = 48         # captured decode steps kept at a time
         self._sessions: Dict[tuple, DecodeSession] = {}
         self.graph_steps = 0                # decode steps that were graph replays (statistics)
         self.h2d_bytes = 0                  # bytes copied host→device / device→host by generate()
@@ -145,10 +146,14 @@ class Engine:
             bound = self.runner.max_seq_len
         greedy = all(r.sampling.greedy for r in reqs)
         key = (len(reqs), bound, greedy, window)
-        sess = self._sessions.get(key)
+        sess = self._sessions.pop(key, None)
         if sess is None:
+            # every (batch size, bound, sampling kind) has a captured step of its own; the least recently used one goes
+            # when there are too many (a graph keeps its activations and logits)
+            while len(self._sessions) >= self.max_decode_graphs:
+                self._sessions.pop(next(iter(self._sessions)))
             sess = DecodeSession(self.runner, len(reqs), bound, greedy=greedy, feed_back=False, penalty_window=window)
-            self._sessions[key] = sess
+        self._sessions[key] = sess                # most recently used last
         ids = [r.id for r in reqs]
         firsts = [r.tokens[-1] for r in reqs]
         while True:

@@ -409,3 +409,17 @@ def test_random_settings_many_engines_in_one_process(model_folders):
         if it % 3 == 0:
             gc.collect()
     assert graph_steps > 0
+
+
+def test_captured_decode_steps_are_kept_up_to_a_limit(model_folders):
+    from mimirmind_b200 import Engine
+    eng = Engine.from_folder(model_folders("A", "float32"), dtype="float32", cache_tokens=2048, max_context=256,
+                             token_budget=256, max_active=8)
+    eng.max_decode_graphs = 2
+    outs = {}
+    for n in (1, 2, 3, 1, 3):
+        prompts = [random_tokens(256, 10 + i, i) for i in range(n)]
+        res = [r.tokens for r in eng.generate(prompts, max_new_tokens=12, use_eos=False)]
+        assert outs.setdefault(n, res) == res                   # a batch size that comes back (recaptured or kept) gives the same tokens
+        assert len(eng._sessions) <= 2
+    assert [k[0] for k in eng._sessions] == [1, 3]              # least recently used went first
