@@ -192,13 +192,19 @@ __device__ __forceinline__ void sample_cluster_sync() {
     asm volatile("barrier.cluster.arrive.release;\n" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire;\n" ::: "memory");
 }
-__device__ __forceinline__ unsigned long long ld_peer_u64(const unsigned long long* local, uint32_t rank) {
-    uint32_t remote;
+// The same word of every CTA of the cluster: the loads go out together (a loop that adds each value as it arrives would
+// wait for one remote load after the other).  v[r] for r >= n_ranks is 0.
+__device__ __forceinline__ void ld_all_peers_u64(const unsigned long long* local, uint32_t n_ranks, unsigned long long* v) {
     const uint32_t addr = (uint32_t)__cvta_generic_to_shared(local);
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(addr), "r"(rank));
-    unsigned long long v;
-    asm volatile("ld.shared::cluster.u64 %0, [%1];\n" : "=l"(v) : "r"(remote) : "memory");
-    return v;
+    uint32_t remote[SAMPLE_MAX_CLUSTER];
+#pragma unroll
+    for (uint32_t r = 0; r < SAMPLE_MAX_CLUSTER; ++r)
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote[r]) : "r"(addr), "r"(r < n_ranks ? r : 0u));
+#pragma unroll
+    for (uint32_t r = 0; r < SAMPLE_MAX_CLUSTER; ++r) {
+        v[r] = 0ull;
+        if (r < n_ranks) asm volatile("ld.shared::cluster.u64 %0, [%1];\n" : "=l"(v[r]) : "r"(remote[r]));
+    }
 }
 __device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v) {
 #pragma unroll
@@ -230,11 +236,10 @@ __device__ unsigned long long cluster_combine(ClusterCtx& c, unsigned long long 
     }
     __syncthreads();
     sample_cluster_sync();
-    unsigned long long all = 0ull;
-    for (uint32_t r = 0; r < c.n_ranks; ++r) {
-        const unsigned long long v = ld_peer_u64(&sh->pub[b][256], r);
-        all = take_max ? (v > all ? v : all) : all + v;
-    }
+    unsigned long long all = 0ull, v[SAMPLE_MAX_CLUSTER];
+    ld_all_peers_u64(&sh->pub[b][256], c.n_ranks, v);
+#pragma unroll
+    for (uint32_t r = 0; r < SAMPLE_MAX_CLUSTER; ++r) all = take_max ? (v[r] > all ? v[r] : all) : all + v[r];
     ++c.round;
     return all;
 }
@@ -289,8 +294,10 @@ __device__ SelectResult radix_select(ClusterCtx& c, const float* __restrict__ ro
         __syncthreads();
         sample_cluster_sync();
         if (threadIdx.x < 256) {
-            unsigned long long sum = 0ull;
-            for (uint32_t r = 0; r < c.n_ranks; ++r) sum += ld_peer_u64(&sh->pub[b][threadIdx.x], r);
+            unsigned long long sum = 0ull, v[SAMPLE_MAX_CLUSTER];
+            ld_all_peers_u64(&sh->pub[b][threadIdx.x], c.n_ranks, v);
+#pragma unroll
+            for (uint32_t r = 0; r < SAMPLE_MAX_CLUSTER; ++r) sum += v[r];
             sh->tot[threadIdx.x] = sum;
         }
         ++c.round;
@@ -380,11 +387,12 @@ __device__ void write_nth_with_key(ClusterCtx& c, const float* __restrict__ row,
     }
     __syncthreads();
     sample_cluster_sync();
-    unsigned long long before = 0ull, total = 0ull;
-    for (uint32_t r = 0; r < c.n_ranks; ++r) {
-        const unsigned long long v = ld_peer_u64(&sh->pub[b][256], r);
-        if (r < c.rank) before += v;
-        total += v;
+    unsigned long long before = 0ull, total = 0ull, v[SAMPLE_MAX_CLUSTER];
+    ld_all_peers_u64(&sh->pub[b][256], c.n_ranks, v);
+#pragma unroll
+    for (uint32_t r = 0; r < SAMPLE_MAX_CLUSTER; ++r) {
+        if (r < c.rank) before += v[r];
+        total += v[r];
     }
     ++c.round;
     if (total == 0ull) {
