@@ -101,10 +101,11 @@ static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) 
 // kernels pile up on the SMs and measured 2.5x slower).  Without the attribute both are no-ops.
 // Off by default.  Measured on B200 at batch 8 (7B shapes): kernels do start 2.5-4 us before
 // their predecessor ends, but then take 2.5-4 us longer than after a plain launch: 3.36 ms
-// per step against 3.21 ms.  (Probable cause: their blocks land where the predecessor's blocks
-// happen to leave first instead of evenly over the SMs, and a streaming kernel with two or
-// three blocks per SM ends with its fullest SM.  In a probe with kernels that only spin, the
-// same launch pattern hides the part before the wait completely.)
+// per step against 3.21 ms.  The cause, from recorded SM ids: after a dependent launch the blocks
+// land where the predecessor's blocks happen to leave first (the gate/up product's 296 blocks:
+// three on five SMs and one on five others instead of two everywhere), and a streaming kernel
+// with two or three blocks per SM ends with its fullest SM.  In a probe with kernels that only
+// spin, the same launch pattern hides the part before the wait completely.
 // One thread waits, the others stand at the CTA barrier: the blocks of a kernel that wait here share their SMs with
 // the running kernel, and 256 waiting threads per block slowed that kernel down measurably, one does not.
 __device__ __forceinline__ void pdl_wait() {
