@@ -107,7 +107,7 @@ static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) 
 // with two or three blocks per SM ends with its fullest SM.  In a probe with kernels that only
 // spin, the same launch pattern hides the part before the wait completely.
 // One thread waits, the others stand at the CTA barrier: the blocks of a kernel that wait here share their SMs with
-// the running kernel, and 256 waiting threads per block slowed that kernel down measurably, one does not.
+// the running kernel and should cost it as little as possible.
 __device__ __forceinline__ void pdl_wait() {
     if (threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
