@@ -511,7 +511,7 @@ __global__ void qkv_rope_kvwrite_bf16x8_kernel(const __nv_bfloat16* __restrict__
 // the cache place from slots [n] (page * page_size + place in the page, -1: not cached), both made once per step
 // for all layers.  No arithmetic on angles and no dependent look-ups here: every load of a thread is issued at once.
 template <typename WT>
-__global__ void qkv_rope_tables_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const WT* __restrict__ bias,
+__global__ void __launch_bounds__(384, 4) qkv_rope_tables_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const WT* __restrict__ bias,
                                               __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pages,
                                               __nv_bfloat16* __restrict__ v_pages, const float* __restrict__ rope_table,
                                               const int32_t* __restrict__ slots, int page_size, int H, int G, int hd,
@@ -602,7 +602,7 @@ MM_EXPORT int mm_qkv_rope_tables(const void* qkv, const void* bias, int bias_dty
     cudaStream_t s = (cudaStream_t)stream;
     const int items = (H + G) * (hd / 16) + G * hd / 8;
     int threads = ((items + 31) / 32) * 32;
-    if (threads > 512) threads = 512;
+    if (threads > 384) threads = 384;          // the kernel's launch bound (40 registers: five blocks of 320 threads per SM)
     if (bias == nullptr || bias_dtype == MM_F32)
         mm_launch_pdl(qkv_rope_tables_bf16x8_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const bf*)qkv, (const float*)bias,
                       (bf*)q_out, (bf*)k_pages, (bf*)v_pages, (const float*)rope_table, (const int32_t*)slots, page_size, H, G,
