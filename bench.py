@@ -161,6 +161,9 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    if PROMPT_LEN + warmup + steps > CONTEXT:           # the requests must fit their context
+        steps = CONTEXT - PROMPT_LEN - warmup
+        print(f"bench.py: --steps clamped to {steps} (prompts of {PROMPT_LEN} tokens in a context of {CONTEXT})", file=sys.stderr)
     if args.workload:
         return run_workload(args.workload, args.layers)
 
