@@ -28,7 +28,7 @@ from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 from . import host
-from .pages import INVALID_PAGE, PageAllocator
+from .pages import PageAllocator
 
 
 class CacheError(RuntimeError):

@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import json
 import struct
-from typing import Optional
 
 import torch
 

@@ -10,7 +10,7 @@ counts, prefill and decode time and whether a stop id was hit.
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Dict, Hashable, List, Optional, Sequence
 
 import torch

@@ -1,7 +1,7 @@
 """From a model folder (or a spec and a seed) to a Model on the device."""
 from __future__ import annotations
 
-from typing import Dict, Optional, Tuple
+from typing import Tuple
 
 import torch
 

@@ -8,7 +8,7 @@ keys of one head is contiguous.)  State arrays are ``[slots, *shape]`` per entry
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
 

@@ -13,7 +13,6 @@ from ctypes import c_float, c_int, c_void_p
 from dataclasses import dataclass
 from typing import Optional
 
-import numpy as np
 import torch
 
 from . import lib as _lib

@@ -13,7 +13,6 @@ bias + rotary + cache-write kernel.
 """
 from __future__ import annotations
 
-import math
 from typing import List, Optional
 
 import torch

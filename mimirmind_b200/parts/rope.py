@@ -9,7 +9,6 @@ from __future__ import annotations
 
 from typing import Optional, Tuple
 
-import torch
 
 from ..config.spec import PartSpec
 from ..registry import POSITION_ENCODINGS

@@ -7,7 +7,7 @@ not depend on what else is in the batch.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import Optional, Sequence
 
 import numpy as np
 import torch

@@ -15,13 +15,13 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Dict, Iterable, Optional, Tuple
 
 import torch
 
 from ..config.model_config import read_config_json
 from ..config.spec import ModelSpec, TensorSpec
-from ..registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, get_architecture)
+from ..registry import (EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, get_architecture)
 from .safetensors_io import SafetensorsFolder, write_safetensors
 
 
