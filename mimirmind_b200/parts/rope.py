@@ -9,7 +9,6 @@ from __future__ import annotations
 
 from typing import Optional, Tuple
 
-
 from ..config.spec import PartSpec
 from ..registry import POSITION_ENCODINGS
 from .base import PositionEncoding, Runtime, WeightView
