@@ -242,6 +242,10 @@ def parse_qwen2_config(obj: Dict[str, Any], where: str = "config.json") -> Qwen2
                 else:
                     raise ConfigError(f"{where}: layer_types[{i}] = {t!r} is not a kind this architecture has")
         else:
+            # no default: a guessed boundary would silently turn a windowed checkpoint into a full-attention one
+            if "max_window_layers" not in r.obj:
+                raise ConfigError(f"{where}: use_sliding_window is true but neither 'layer_types' nor "
+                                  "'max_window_layers' says which layers are windowed")
             first_windowed = r.opt_int("max_window_layers", layers, minimum=0)
             windows = [0 if i < first_windowed else window for i in range(layers)]
 

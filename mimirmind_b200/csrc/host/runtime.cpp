@@ -339,16 +339,20 @@ class Scheduler {
                 if (mgr_->release(vid) != 0) return -2;
                 running_.pop_back();
                 if (running_.empty()) {
+                    // it was alone and still did not fit: it fails, and nothing is left that its pages must serve
+                    // first, so waiting requests may be admitted in this same call (else the plan would be empty
+                    // with work left)
                     finish(victim, OUT_OF_PAGES);
                     ++m_finished_;
+                    preempted_now = false;
                 } else {
                     victim.state = WAITING;
                     ++victim.preemptions;
                     waiting_.push_front(vid);
                     ++m_preempted_;
                     events_.push_back({vid, EV_PREEMPTED, victim.preemptions});
+                    preempted_now = true;
                 }
-                preempted_now = true;
                 continue;
             }
             // admit waiting requests, first in first out (not in a step that had to preempt: the freed pages

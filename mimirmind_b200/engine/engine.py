@@ -129,6 +129,8 @@ class Engine:
         or the horizon ends.  Returns False (nothing done) when a graph run is not possible or not worth it."""
         sched, first_at, last_at = loop.sched, loop.first_at, loop.last_at
         reqs = list(sched.running)
+        if len(reqs) > self.sched_cfg.token_budget:
+            return False          # the scheduler would leave some of them out of a step: its plan decides, not this
         # soft-cap and penalties run inside the captured step, over rings of recent tokens kept on the device
         window = 0
         if any(r.sampling.penalties_active or r.sampling.final_logit_softcap > 0 for r in reqs):

@@ -32,7 +32,11 @@ class PrefillSession:
         # one int32 buffer: token ids, positions, then a block-table row per group
         total = 2 * n_tokens + self.width * len(self.groups)
         self.dev_buf = torch.zeros(total, dtype=torch.int32, device=dev)
-        self.host_buf = torch.empty(total, dtype=torch.int32, pin_memory=True)
+        # Two pinned staging buffers taken in turn, each with an event recorded after its copy: the host may be
+        # several runs ahead of the device (portions whose logits nobody reads are never waited for), and a buffer
+        # must not be rewritten before the copy that reads it has run.
+        self.host_bufs = [torch.empty(total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.copied = [None, None]
         self.token_ids = self.dev_buf[:n_tokens]
         self.positions = self.dev_buf[n_tokens:2 * n_tokens]
         self.tables = {g: self.dev_buf[2 * n_tokens + i * self.width:2 * n_tokens + (i + 1) * self.width].view(1, self.width)
@@ -58,12 +62,19 @@ class PrefillSession:
         """The step for ``tokens`` of request ``rid`` at positions [start, start + n); pages are reserved already.
         Returns fp32 logits [1, vocab] of the last token (a copy), or None if they were not wanted."""
         mgr, n = self.runner.manager, self.n
-        hv = self.host_buf.numpy()
+        turn = self.runs % 2
+        host_buf = self.host_bufs[turn]
+        if self.copied[turn] is not None:
+            self.copied[turn].synchronize()
+        hv = host_buf.numpy()
         hv[:n] = np.asarray(tokens, dtype=np.int32)
         hv[n:2 * n] = np.arange(start, start + n, dtype=np.int32)
         for i, g in enumerate(self.groups):
-            mgr.fill_tables(g, [rid], self.width, self.host_buf.data_ptr() + 4 * (2 * n + i * self.width))
-        self.dev_buf.copy_(self.host_buf, non_blocking=True)
+            mgr.fill_tables(g, [rid], self.width, host_buf.data_ptr() + 4 * (2 * n + i * self.width))
+        self.dev_buf.copy_(host_buf, non_blocking=True)
+        if self.copied[turn] is None:
+            self.copied[turn] = torch.cuda.Event()
+        self.copied[turn].record()
         self.slots.fill_(mgr.slot(rid))
         self.ctx.kv_len = [start + n]
         if self.graph is None:

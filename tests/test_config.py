@@ -49,6 +49,9 @@ def test_rejected_options():
         parse_qwen2_config(dict(TINY["A"], hidden_act="gelu"))
     with pytest.raises(ConfigError, match="sliding_window"):
         parse_qwen2_config(dict(TINY["A"], use_sliding_window=True))
+    with pytest.raises(ConfigError, match="max_window_layers"):
+        # windowed, but nothing says which layers: no boundary is guessed
+        parse_qwen2_config(dict(TINY["A"], use_sliding_window=True, sliding_window=64))
     with pytest.raises(ConfigError, match="integer"):
         parse_qwen2_config(dict(TINY["A"], hidden_size="64"))
 

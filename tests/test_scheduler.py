@@ -25,6 +25,7 @@ def run(sched, mgr, max_steps=10000, log=None):
     while sched.has_work():
         plan = sched.schedule()
         if not plan:
+            assert not sched.has_work(), "an empty plan while requests wait or run"
             break
         assert sum(p.count for p in plan) <= sched.cfg.token_budget
         ids = [p.request.id for p in plan]
@@ -153,6 +154,46 @@ def test_a_lone_request_that_cannot_fit_fails():
     run(s, m)
     assert r.finish_reason == "out_of_pages" and len(r.generated) >= 1
     assert m.free_pages() == m.total_pages() and not s.has_work()
+
+
+def test_a_failed_lone_request_does_not_hold_up_those_that_wait():
+    # A fills the pool while B waits; A's next token finds no page, A is alone and fails; B is admitted in the
+    # same call instead of the plan coming back empty with work left
+    s, m = make(pages=3, page_size=4, budget=64, max_active=4)
+    a, b = Request("a", [1] * 10, max_new=50), Request("b", [2] * 6, max_new=2)
+    s.add(a)
+    plan = s.schedule()
+    assert [(p.request.id, p.count) for p in plan] == [("a", 10)]
+    s.add(b)                                   # no page is free for b while a holds all three
+    log = []
+    while s.has_work():
+        s.commit(plan, {p.request.id: fake_token(p.request) for p in plan if p.samples})
+        m.check()
+        plan = s.schedule()
+        assert plan or not s.has_work(), "an empty plan while requests wait or run"
+        log.append([(p.request.id, p.count) for p in plan])
+    assert a.finish_reason == "out_of_pages" and b.finish_reason == "length" and len(b.generated) == 2
+    assert any(step and step[0][0] == "b" for step in log)
+    assert m.free_pages() == m.total_pages()
+
+
+def test_the_serving_loop_survives_a_lone_request_that_runs_out_of_pages():
+    # the same through ServingLoop, with a stand-in for the engine that "samples" the fake token
+    from types import SimpleNamespace
+
+    from mimirmind_b200.engine.engine import ServingLoop
+    s, m = make(pages=3, page_size=4, budget=64, max_active=4)
+    eng = SimpleNamespace(sched_cfg=s.cfg, runner=SimpleNamespace(manager=m), use_graphs=False, eos_ids=(),
+                          decode_trace=None,
+                          _run_plan=lambda plan: {p.request.id: fake_token(p.request) for p in plan if p.samples})
+    loop = ServingLoop(eng)
+    ha = loop.submit([1] * 10, max_new_tokens=50, use_eos=False)
+    loop.step()
+    hb = loop.submit([2] * 6, max_new_tokens=2, use_eos=False)
+    loop.run_until_idle()
+    assert loop.result(ha).stats.finish_reason == "out_of_pages"
+    assert loop.result(hb).stats.finish_reason == "length" and len(loop.result(hb).tokens) == 2
+    assert m.free_pages() == m.total_pages()
 
 
 def test_cancel():
