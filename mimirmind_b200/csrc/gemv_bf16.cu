@@ -27,13 +27,6 @@
 // Input row scale: with `in_ss` the accumulators of row m are multiplied by
 // 1 / sqrt(sum_j in_ss[j][m] / in_dim + eps) before the epilogue (the deferred 1/rms of RESID).
 //
-// Chain: up to GEMV_CHAIN_MAX products, each reading what the one before wrote, run as ONE cooperative launch of
-// a persistent grid (every CTA takes the work items of every phase in turn) with a grid-wide barrier between
-// phases.  Before a CTA enters the barrier it has already issued the first weight loads of its next item, so the
-// stream from HBM does not stop at the hand-over the way it does between two kernels.  The barrier is a counter in
-// global memory (release add, acquire poll) with a bounded number of polls; on a time-out the CTA sets the error
-// flag and goes on, so a launch always ends.
-//
 // The reference's counterparts are its bf16 GEMV and small-M GEMM
 // (kernels/cuda/common/matmul_bf16_vec.cu:53-99: warp per output row, M launches;
 // matmul_bf16_gemm.cu: scalar, M <= 16).
@@ -77,7 +70,7 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
-// activations may have been written earlier in the same (chained) launch by another SM: plain loads, never .nc
+// activations were written by the kernel before this one: plain loads, never .nc
 __device__ __forceinline__ uint4 ld_act(const void* p) {
     uint4 v;
     asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
@@ -91,16 +84,6 @@ __device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, ui
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
-#define GEMV_CHAIN_MAX 4
-
-struct GemvChainArgs {
-    int n;
-    int epi[GEMV_CHAIN_MAX];
-    GemvArgs phase[GEMV_CHAIN_MAX];
-    unsigned* sync;             // [2]: arrivals at the barriers, CTAs that have finished; both zero between launches
-    int* err;
-};
 
 // shared memory of a CTA, reused by every item and phase
 struct GemvSmem {
@@ -427,74 +410,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvAr
     gemv_item<NT, U, EPI>(a, blockIdx.x, first, sm, ss_s);
 }
 
-// Grid-wide barrier of a cooperative launch: every CTA adds one to the counter (release) and thread 0 polls it
-// (acquire) until `target` arrivals are in, at most GRID_SYNC_POLLS times.
-#define GRID_SYNC_POLLS (1u << 22)
-__device__ __forceinline__ void grid_sync(unsigned* count, unsigned target, int* err) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;\n" ::"l"(count) : "memory");
-        unsigned v = 0;
-        for (unsigned polls = 0; polls < GRID_SYNC_POLLS; ++polls) {
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(count) : "memory");
-            if (v >= target) break;
-            if (polls > 32) __nanosleep(64);
-        }
-        if (v < target && err != nullptr) atomicExch(err, 6);
-    }
-    __syncthreads();
-}
-
-template <int U>
-__device__ __forceinline__ void gemv_chain_item(const GemvChainArgs& c, int p, int item, const GemvFirst<U>& first, GemvSmem& sm, float* ss_s) {
-    switch (c.epi[p]) {
-        case EPI_SWIGLU: gemv_item<1, U, EPI_SWIGLU>(c.phase[p], item, first, sm, ss_s); break;
-        case EPI_RESID: gemv_item<1, U, EPI_RESID>(c.phase[p], item, first, sm, ss_s); break;
-        case EPI_ROPE: gemv_item<1, U, EPI_ROPE>(c.phase[p], item, first, sm, ss_s); break;
-        default: gemv_item<1, U, EPI_PLAIN>(c.phase[p], item, first, sm, ss_s); break;
-    }
-}
-
-// Persistent grid, at most 8 batch rows.  Phase p's items are dealt round-robin to the CTAs.
-__global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_chain_kernel(const __grid_constant__ GemvChainArgs c) {
-    constexpr int U = 4;
-    __shared__ GemvSmem sm;
-    extern __shared__ __align__(16) float ss_s[];
-    GemvFirst<U> first;
-    auto items_of = [&](int p) { return (c.phase[p].N / 16 + c.phase[p].RT - 1) / c.phase[p].RT; };
-    if ((int)blockIdx.x < items_of(0)) gemv_first_weights<U>(c.phase[0], blockIdx.x, first);
-    for (int p = 0; p < c.n; ++p) {
-        const int n_items = items_of(p);
-        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
-            gemv_chain_item<U>(c, p, item, first, sm, ss_s);
-            const int next = item + gridDim.x;
-            if (next < n_items) {
-                gemv_first_weights<U>(c.phase[p], next, first);
-                __syncthreads();                        // the shared buffers are free for the next item
-            }
-        }
-        if (p + 1 < c.n) {
-            // the next phase's first weights are requested before the barrier: HBM keeps streaming through it
-            if ((int)blockIdx.x < items_of(p + 1)) gemv_first_weights<U>(c.phase[p + 1], blockIdx.x, first);
-            grid_sync(c.sync, (unsigned)(p + 1) * gridDim.x, c.err);
-        }
-    }
-    // the last CTA to finish leaves both counters at zero for the next launch
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned done = atomicAdd(c.sync + 1, 1u);
-        if (done == gridDim.x - 1) {
-            c.sync[0] = 0;
-            c.sync[1] = 0;
-            __threadfence();
-        }
-    }
-}
-
-// An open chain collects the products of this thread's next calls instead of launching them.
-static thread_local bool t_chain_open = false;
-static thread_local GemvChainArgs t_chain;
-
 static size_t gemv_dynamic_smem(const GemvArgs& a) {
     return a.in_ss ? (size_t)a.in_tiles * ((a.M + 3) & ~3) * sizeof(float) : 0;   // the staged partial sums of the input rows
 }
@@ -510,93 +425,13 @@ static int launch_gemv_now(const GemvArgs& a, cudaStream_t s) {
     return MM_OK;
 }
 
-static int launch_gemv_by_code(int epi, const GemvArgs& a, cudaStream_t s) {
-    switch (epi) {
-        case EPI_SWIGLU: return launch_gemv_now<EPI_SWIGLU>(a, s);
-        case EPI_RESID: return launch_gemv_now<EPI_RESID>(a, s);
-        case EPI_ROPE: return launch_gemv_now<EPI_ROPE>(a, s);
-        default: return launch_gemv_now<EPI_PLAIN>(a, s);
-    }
-}
-
 template <int EPI>
 static int launch_gemv(const GemvArgs& a, cudaStream_t s) {
     if (gemv_dynamic_smem(a) > 16 * 1024) {
         mm_set_last_error("gemv: too many partial sums for the input scale (rows x producer tiles above 4096)");
         return MM_ERR_UNSUPPORTED;
     }
-    if (t_chain_open) {
-        MM_REQUIRE(a.M <= 8, "gemv chain: at most 8 rows");
-        MM_REQUIRE(t_chain.n < GEMV_CHAIN_MAX, "gemv chain: full (flush first)");
-        t_chain.phase[t_chain.n] = a;
-        t_chain.epi[t_chain.n] = EPI;
-        ++t_chain.n;
-        return MM_OK;
-    }
     return launch_gemv_now<EPI>(a, s);
-}
-
-// From now on this thread's mm_gemv_bf16* calls are collected (up to GEMV_CHAIN_MAX, each reading what the one before
-// wrote; at most 8 rows) until mm_gemv_chain_flush launches them together.  Nothing runs before the flush.
-MM_EXPORT int mm_gemv_chain_begin() {
-    MM_REQUIRE(!t_chain_open, "gemv chain: already open");
-    t_chain_open = true;
-    t_chain.n = 0;
-    return MM_OK;
-}
-
-MM_EXPORT int mm_gemv_chain_length() { return t_chain_open ? t_chain.n : -1; }
-
-// Forgets the collected products without running them (after an error between begin and flush).
-MM_EXPORT int mm_gemv_chain_discard() {
-    t_chain_open = false;
-    t_chain.n = 0;
-    return MM_OK;
-}
-
-// Launches the collected products: one as its ordinary kernel; several as one cooperative launch of a persistent grid
-// with grid-wide barriers between them.  sync: two zeroed uint32 in device memory that only these launches use
-// (they are left zero); err: device int set to 6 if a barrier gave up waiting.
-MM_EXPORT int mm_gemv_chain_flush(void* sync, void* err, void* stream) {
-    MM_REQUIRE(t_chain_open, "gemv chain: not open");
-    t_chain_open = false;
-    cudaStream_t s = (cudaStream_t)stream;
-    if (t_chain.n == 0) return MM_OK;
-    if (t_chain.n == 1) return launch_gemv_by_code(t_chain.epi[0], t_chain.phase[0], s);
-    MM_REQUIRE(sync != nullptr, "gemv chain: no barrier counters");
-    size_t smem = 0;
-    int items = 0;
-    for (int p = 0; p < t_chain.n; ++p) {
-        const GemvArgs& a = t_chain.phase[p];
-        smem = smem > gemv_dynamic_smem(a) ? smem : gemv_dynamic_smem(a);
-        const int n = (a.N / 16 + a.RT - 1) / a.RT;
-        items = items > n ? items : n;
-    }
-    int dev = 0, sms = 0, per_sm = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_chain_kernel, GEMV_THREADS, smem) != cudaSuccess || per_sm < 1) {
-        cudaGetLastError();
-        mm_set_last_error("gemv chain: the persistent kernel does not fit on an SM");
-        return MM_ERR_LAUNCH;
-    }
-    // every CTA must be resident at once (they wait for one another): a cooperative launch checks that
-    const int capacity = sms * (per_sm < 2 ? per_sm : 2);
-    t_chain.sync = (unsigned*)sync;
-    t_chain.err = (int*)err;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(items < capacity ? items : capacity);
-    cfg.blockDim = dim3(GEMV_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, gemv_chain_kernel, t_chain);
-    MM_CHECK_LAUNCH();
-    return MM_OK;
 }
 
 // Checks shared by the entry points; fills the common fields.

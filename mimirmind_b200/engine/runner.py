@@ -27,13 +27,6 @@ from ..parts.base import Runtime, StepContext
 from .model import Model
 from .storage import CacheStorage
 
-# Consecutive weight-streaming products of a small step (output projection, feed-forward, next q/k/v projection) can
-# run as one persistent launch with grid-wide barriers between them.  Off: measured on B200 at batch 8 (7B shapes) the
-# chained launch takes 96.6 us per layer against 89.6 us for the four separate launches inside a CUDA graph.  A
-# timeline of the chain shows why: a barrier costs 2.1-2.4 us after the slowest CTA arrives (write flush, atomic,
-# poll), as much as a kernel boundary in a graph, and CTAs of the cooperative launch start up to 2.3 us apart.
-USE_GEMV_CHAIN = False
-
 # A prompt portion of one request with at least this many tokens, of a size seen before, runs as a replayed CUDA
 # graph (engine/prefill_graph.py); at most PREFILL_GRAPHS sizes are kept.  0 turns it off.
 PREFILL_GRAPH_MIN_TOKENS = 512
@@ -228,19 +221,11 @@ class ModelRunner:
             dump.write(0, "inp_scaled", residual)
         pending = None
         last = len(m.schedule) - 1
-        ctx.chain = ops.GemvChain() if (self.rt.dtype == torch.bfloat16 and USE_GEMV_CHAIN and dump is None) else None
-        try:
-            for i, e in enumerate(m.schedule):
-                if dump is not None:
-                    ctx.dump = lambda stage, rows, block=i: dump.write(block, stage, rows)
-                successor = m.layers[m.schedule[i + 1].layer] if i < last else None
-                pending = m.layers[e.layer].forward(residual, pending, ctx, self.storage.layer_cache(i, ctx), successor=successor)
-            if ctx.chain is not None:
-                ctx.chain.flush()
-        except BaseException:
-            if ctx.chain is not None:
-                ctx.chain.discard()
-            raise
+        for i, e in enumerate(m.schedule):
+            if dump is not None:
+                ctx.dump = lambda stage, rows, block=i: dump.write(block, stage, rows)
+            successor = m.layers[m.schedule[i + 1].layer] if i < last else None
+            pending = m.layers[e.layer].forward(residual, pending, ctx, self.storage.layer_cache(i, ctx), successor=successor)
         if ctx.n_logit_rows == 0:
             return None
         normed = m.final_norm.forward(residual, pending, rows=ctx.logit_rows, n_rows=ctx.n_logit_rows)

@@ -33,17 +33,12 @@ _PROTOTYPES = {
     "mm_silu_mul": [P, P, I, I, I, I, P],
     "mm_gemm_tcgen05": [P, P, P, I, P, I, I, I, I, I, I, P, P],
     "mm_gemm_tcgen05_pair": [P, P, P, I, P, I, I, I, I, I, I, P, P],
-    "mm_gemm_tcgen05_streamk": [P, P, P, I, P, I, I, I, I, I, I, P, P, I, P, P],
     "mm_gemv_bf16": [P, P, P, I, P, I, I, I, I, I, I, I, I, I, P, I, I, F, P],
     "mm_gemv_bf16_residual": [P, P, P, P, I, P, P, I, I, I, I, I, I, P, I, I, F, P],
     "mm_gemv_bf16_qkv_rope": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, I, F, P],
     "mm_gemm_skinny": [P, P, P, I, P, I, I, I, I, I, I, I, I, P, I, I, I, F, P, P],
     "mm_gemm_skinny_residual": [P, P, P, P, I, P, P, I, I, I, I, I, I, P, I, I, I, F, P, P],
     "mm_gemm_skinny_qkv_rope": [P, P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P, I, I, I, F, P, P],
-    "mm_gemv_chain_begin": [],
-    "mm_gemv_chain_length": [],
-    "mm_gemv_chain_discard": [],
-    "mm_gemv_chain_flush": [P, P, P],
     "mm_rope_table": [P, P, I, I, F, P],
     "mm_slot_mapping": [P, P, P, I, I, I, P, P],
     "mm_qkv_rope_kvwrite": [P, P, I, P, P, P, I, P, P, P, I, I, I, I, I, I, I, F, I, P],

@@ -270,54 +270,6 @@ def _skinny_splits(n: int, k: int) -> int:
     return s
 
 
-GEMV_CHAIN_MAX = 4
-_CHAIN_SYNC = {}
-
-
-class GemvChain:
-    """Weight-streaming products of a few rows that read one another's results, launched together: calls of
-    gemv_bf16 / gemv_bf16_residual / gemv_bf16_qkv_rope with ``chain=`` are only recorded (their outputs are
-    allocated and returned, not yet written); ``flush`` runs them as one persistent cooperative kernel with a
-    grid-wide barrier between consecutive products, so the stream of weights from HBM does not stop between them.
-    Whoever reads an output with anything but another product of the same chain flushes first."""
-
-    def __init__(self):
-        self._open = False
-        self._keep = []
-
-    def __len__(self) -> int:
-        return _lib.load().mm_gemv_chain_length() if self._open else 0
-
-    def record(self, *tensors) -> None:
-        self._keep.extend(t for t in tensors if t is not None)     # operands stay alive until the launch
-
-    def begin(self) -> None:
-        if self._open and len(self) >= GEMV_CHAIN_MAX:
-            self.flush()
-        if not self._open:
-            check(_lib.load().mm_gemv_chain_begin(), "gemv_chain_begin")
-            self._open = True
-
-    def flush(self) -> None:
-        if not self._open:
-            return
-        self._open = False
-        dev = torch.cuda.current_device()
-        if dev not in _CHAIN_SYNC:
-            _CHAIN_SYNC[dev] = torch.zeros(2, dtype=torch.int32, device=f"cuda:{dev}")
-        err = tcgen05_error_flag(torch.device("cuda", dev))
-        try:
-            check(_lib.load().mm_gemv_chain_flush(_CHAIN_SYNC[dev].data_ptr(), err.data_ptr(), _stream()), "gemv_chain_flush")
-        finally:
-            self._keep.clear()
-
-    def discard(self) -> None:
-        if self._open:
-            _lib.load().mm_gemv_chain_discard()
-            self._open = False
-        self._keep.clear()
-
-
 @dataclass
 class RowScale:
     """The deferred 1/rms of rows that were written as ``residual * norm_weight``: per 16-column tile of the
@@ -363,7 +315,7 @@ def _skinny_scale_args(scale: Optional["RowScale"], m: int):
 
 
 def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-              swiglu: bool = False, scale: Optional[RowScale] = None, chain: Optional[GemvChain] = None) -> torch.Tensor:
+              swiglu: bool = False, scale: Optional[RowScale] = None) -> torch.Tensor:
     """x[M<=16, K] @ w[N, K]^T (+ bias) with the weight-streaming kernel.  ``swiglu``: w interleaves gate and
     up rows in blocks of 8 and the result is silu(gate) * up, [M, N/2].  ``scale``: rows of the product are
     multiplied by the deferred 1/rms before bias and activation."""
@@ -385,9 +337,6 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
                                          _stream()), "gemm_skinny")
         return out
     rt, ks = _gemv_layout(n, k)
-    if chain is not None:
-        chain.begin()
-        chain.record(x, w, bias, out, scale.ss if scale is not None else None)
     check(_lib.load().mm_gemv_bf16(w.data_ptr(), x.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
                                    out.data_ptr(), dtype_code(out_dtype), m, n, k, k, out.shape[1], rt, ks, int(swiglu),
                                    *_scale_args(scale, m), _stream()), "gemv_bf16")
@@ -395,7 +344,7 @@ def gemv_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
 
 
 def gemv_bf16_residual(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, norm_weight: Optional[torch.Tensor],
-                       eps: float = 0.0, scale: Optional[RowScale] = None, chain: Optional[GemvChain] = None):
+                       eps: float = 0.0, scale: Optional[RowScale] = None):
     """residual[M, N] (fp32, in place) += x @ w^T.  With ``norm_weight`` returns (xw, RowScale): the rows of
     ``residual * norm_weight`` in bfloat16 and the partial sums for their 1/rms; else returns None."""
     _need(x, "gemv x", torch.bfloat16)
@@ -421,9 +370,6 @@ def gemv_bf16_residual(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor,
             "gemm_skinny_residual")
         return None if norm_weight is None else (xw, RowScale(ss, n, float(eps)))
     rt, ks = _gemv_layout(n, k)
-    if chain is not None:
-        chain.begin()
-        chain.record(x, w, residual, norm_weight, xw, ss, scale.ss if scale is not None else None)
     check(_lib.load().mm_gemv_bf16_residual(w.data_ptr(), x.data_ptr(), residual.data_ptr(), _ptr(norm_weight),
                                             dtype_code(norm_weight.dtype) if norm_weight is not None else F32, _ptr(xw), _ptr(ss),
                                             m, n, k, k, rt, ks, *_scale_args(scale, m), _stream()), "gemv_bf16_residual")
@@ -467,7 +413,7 @@ def slot_mapping(positions: torch.Tensor, token_req: torch.Tensor, block_table: 
 def gemv_bf16_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], q_out: torch.Tensor,
                        k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], table: torch.Tensor,
                        slots: Optional[torch.Tensor], page_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                       scale: Optional[RowScale] = None, chain: Optional[GemvChain] = None) -> None:
+                       scale: Optional[RowScale] = None) -> None:
     """The q/k/v projection of up to 16 tokens with bias, rotary encoding and cache write in its epilogue.
     ``w`` and ``bias`` are in the order of :func:`interleave_halves`; q_out, k and v are in natural order.
     ``table``: :func:`rope_table` of the tokens for this head size; ``slots``: :func:`slot_mapping`."""
@@ -503,9 +449,6 @@ def gemv_bf16_qkv_rope(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Te
             tcgen05_error_flag(x.device).data_ptr(), _stream()), "gemm_skinny_qkv_rope")
         return
     rt, ks = _gemv_layout(n, k)
-    if chain is not None:
-        chain.begin()
-        chain.record(x, w, bias, q_out, k_pages, v_pages, table, slots, scale.ss if scale is not None else None)
     check(_lib.load().mm_gemv_bf16_qkv_rope(
         w.data_ptr(), x.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, q_out.data_ptr(),
         _ptr(k_pages), _ptr(v_pages), table.data_ptr(), _ptr(slots) if k_pages is not None else None, page_size,
@@ -575,56 +518,6 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     fn = _lib.load().mm_gemm_tcgen05_pair if pair else _lib.load().mm_gemm_tcgen05
     check(fn(x.data_ptr(), w.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
              out.data_ptr(), epi, m, n, k, k, out.shape[1], tcgen05_error_flag(x.device).data_ptr(), _stream()), "gemm_tcgen05")
-    return out
-
-
-_STREAMK_SCRATCH = {}
-
-
-def _streamk_scratch(device):
-    """(pairs, partial sums fp32 [pairs, 2, 128, 256], flags int32 [(pairs + 1) * 2], zero) of a device, made once."""
-    key = str(device)
-    if key not in _STREAMK_SCRATCH:
-        pairs = torch.cuda.get_device_properties(device).multi_processor_count // 2
-        _STREAMK_SCRATCH[key] = (pairs, torch.empty((pairs, 2, 128, 256), dtype=torch.float32, device=device),
-                                 torch.zeros((pairs + 1) * 2, dtype=torch.int32, device=device))
-    return _STREAMK_SCRATCH[key]
-
-
-def gemm_tcgen05_streamk_supported(m: int, n: int, k: int, device) -> bool:
-    """The tiles left over after the whole rounds have at least one k block for every pair of CTAs."""
-    if not gemm_tcgen05_supported(m, n, k):
-        return False
-    pairs = torch.cuda.get_device_properties(device).multi_processor_count // 2
-    left = ((-(-m // 256)) * (-(-n // 256))) % pairs
-    return left == 0 or left * (-(-k // 64)) >= pairs
-
-
-def gemm_tcgen05_streamk(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-                         swiglu: bool = False) -> torch.Tensor:
-    """:func:`gemm_tcgen05` on CTA pairs with the k blocks of all tiles shared out evenly over the pairs, for products
-    whose tiles do not fill a whole number of rounds.  Calls on one device share their scratch: one at a time."""
-    _need(x, "gemm x", torch.bfloat16)
-    _need(w, "gemm w", torch.bfloat16)
-    m, k = x.shape
-    n = w.shape[0]
-    if w.shape != (n, k) or not gemm_tcgen05_streamk_supported(m, n, k, x.device):
-        raise KernelError(f"gemm_tcgen05_streamk: shapes x{tuple(x.shape)} w{tuple(w.shape)} are not supported")
-    if swiglu:
-        if n % 16 or bias is not None or out_dtype != torch.bfloat16:
-            raise KernelError("gemm_tcgen05: the SwiGLU epilogue needs N a multiple of 16, no bias, bf16 output")
-        out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
-        epi = EPI_SWIGLU
-    else:
-        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
-        epi = EPI_F32 if out_dtype == torch.float32 else EPI_BF16
-    if bias is not None:
-        _need(bias, "gemm bias")
-    pairs, ws, flags = _streamk_scratch(x.device)
-    check(_lib.load().mm_gemm_tcgen05_streamk(
-        x.data_ptr(), w.data_ptr(), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, out.data_ptr(), epi,
-        m, n, k, k, out.shape[1], ws.data_ptr(), flags.data_ptr(), pairs, tcgen05_error_flag(x.device).data_ptr(), _stream()),
-        "gemm_tcgen05_streamk")
     return out
 
 

@@ -148,9 +148,7 @@ class GQAAttention(Mixer):
             # a few tokens: projection, 1/rms of a factored input, bias, rotation and cache write in one launch
             xin, scale = (x.xw, x.scale) if isinstance(x, FactoredRows) else (x, None)
             ops.gemv_bf16_qkv_rope(xin, self.w_qkv, self.b_qkv, q, k_pages, v_pages, table, slots,
-                                   cache.page_size, H, G, hd, scale=scale, chain=ctx.chain)
-            if ctx.chain is not None:
-                ctx.chain.flush()            # attention is not one of the chain's products: q, k and v must be there
+                                   cache.page_size, H, G, hd, scale=scale)
         else:
             qkv = linear(x, self.w_qkv, None, self.rt)
             if tables and qkv.dtype == torch.bfloat16:
@@ -171,5 +169,5 @@ class GQAAttention(Mixer):
         attn_kernels.paged_attention(q, cache, out, ctx, H, G, hd, self.window, self.scale)
         if sink is None:
             return linear(out, self.w_o, None, self.rt)
-        made = ops.gemv_bf16_residual(out, self.w_o, sink.residual, sink.norm_weight, sink.eps, chain=ctx.chain)
+        made = ops.gemv_bf16_residual(out, self.w_o, sink.residual, sink.norm_weight, sink.eps)
         return FactoredRows(*made) if made is not None else None

@@ -114,9 +114,6 @@ class StepContext:
     # device tensors derived from this step's inputs and shared between layers (rotation tables, cache slots);
     # whoever runs a context more than once (a captured decode step) clears this before every forward
     derived: Dict[Any, torch.Tensor] = field(default_factory=dict)
-    # kernels.ops.GemvChain or None: parts that fuse record their weight-streaming products here instead of launching
-    # them; whoever launches anything else that reads their results flushes it first
-    chain: Any = None
     # diagnostics: ``dump(stage, tensor)`` writes a stage's rows for the layer that is running (None: off); with
     # ``plain_only`` no part fuses its neighbours' work into its own kernels, so every stage exists as a tensor
     dump: Any = None

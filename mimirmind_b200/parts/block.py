@@ -27,8 +27,6 @@ class PreNormBlock(Block):
     def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: LayerCache,
                 successor: Optional[Block] = None):
         n = residual.shape[0]
-        if ctx.chain is not None and not isinstance(pending, FactoredRows):
-            ctx.chain.flush()                # the first norm is a kernel of its own
         if ctx.plain_only:
             return self._forward_plain(residual, pending, ctx, cache)
         mixer_fuses, ffn_fuses = self.mixer.fuses(n), self.feed_forward.fuses(n)

@@ -64,13 +64,10 @@ class SwiGLU(FeedForward):
             # a few tokens: two weight-streaming products; 1/rms and activation in the first one's epilogue,
             # residual add and the next norm in the second one's
             xin, scale = (x.xw, x.scale) if isinstance(x, FactoredRows) else (x, None)
-            act = ops.gemv_bf16(xin, self.w_gate_up, None, xin.dtype, swiglu=True, scale=scale, chain=ctx.chain)
+            act = ops.gemv_bf16(xin, self.w_gate_up, None, xin.dtype, swiglu=True, scale=scale)
             if sink is None:
-                out = ops.gemv_bf16(act, self.w_down, None, xin.dtype, chain=ctx.chain)
-                if ctx.chain is not None:
-                    ctx.chain.flush()        # the caller adds this to the residual with a kernel of its own
-                return out
-            made = ops.gemv_bf16_residual(act, self.w_down, sink.residual, sink.norm_weight, sink.eps, chain=ctx.chain)
+                return ops.gemv_bf16(act, self.w_down, None, xin.dtype)
+            made = ops.gemv_bf16_residual(act, self.w_down, sink.residual, sink.norm_weight, sink.eps)
             return FactoredRows(*made) if made is not None else None
         if self._tensor_cores() and m >= ops.TCGEN05_SWIGLU_MIN_ROWS and ops.gemm_tcgen05_supported(m, 2 * self.intermediate, self.hidden):
             # prefill-sized: tcgen05 product with the activation as its epilogue (the [m, 2F] intermediate never exists)

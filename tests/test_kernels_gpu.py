@@ -671,57 +671,6 @@ def test_gemv_qkv_rope_epilogue_and_interleaved_rope_kernel(H, G, hd, ps, K, M, 
             assert torch.equal(a_, b_)
 
 
-def test_gemv_chain_equals_separate_launches():
-    """Four dependent products (output projection into the residual, gated feed-forward, down projection into the
-    residual, q/k/v projection with rotation and cache write) as one persistent cooperative launch: bit-equal to the
-    same four launched one by one, twice in a row (the barrier counters are left at zero)."""
-    rng = np.random.RandomState(5)
-    M, d, F, H, G, hd, ps = 5, 512, 1024, 4, 2, 64, 16
-    width = (H + 2 * G) * hd
-    attn = t(rng.randn(M, H * hd), torch.bfloat16)
-    w_o, w_gu = t(rng.randn(d, H * hd) * 0.05, torch.bfloat16), t(rng.randn(2 * F, d) * 0.05, torch.bfloat16)
-    w_down, w_qkv = t(rng.randn(d, F) * 0.05, torch.bfloat16), t(rng.randn(width, d) * 0.05, torch.bfloat16)
-    nw1, nw2, bias = t(1 + 0.1 * rng.randn(d), torch.bfloat16), t(1 + 0.1 * rng.randn(d), torch.bfloat16), t(rng.randn(width), torch.bfloat16)
-    res0 = t(rng.randn(M, d))
-    pos = t(np.arange(M) * 7, torch.int32)
-    req = t(np.arange(M), torch.int32)
-    table = t(np.arange(M * 4).reshape(M, 4), torch.int32)
-    angles, slots = ops().rope_table(pos, hd, 1e4), ops().slot_mapping(pos, req, table, ps)
-
-    def run(chain):
-        residual = res0.clone()
-        kp = torch.zeros((M * 4, G, ps, hd), dtype=torch.bfloat16, device=DEV)
-        vp = torch.zeros_like(kp)
-        q = torch.zeros((M, H * hd), dtype=torch.bfloat16, device=DEV)
-        xw1, s1 = ops().gemv_bf16_residual(attn, w_o, residual, nw1, 1e-6, chain=chain)
-        act = ops().gemv_bf16(xw1, w_gu, None, torch.bfloat16, swiglu=True, scale=s1, chain=chain)
-        xw2, s2 = ops().gemv_bf16_residual(act, w_down, residual, nw2, 1e-6, chain=chain)
-        ops().gemv_bf16_qkv_rope(xw2, w_qkv, bias, q, kp, vp, angles, slots, ps, H, G, hd, scale=s2, chain=chain)
-        if chain is not None:
-            assert len(chain) == 4
-            chain.flush()
-            assert len(chain) == 0
-        return residual, xw1, act, xw2, q, kp, vp
-
-    ref = run(None)
-    for _ in range(2):
-        got = run(ops().GemvChain())
-        ops().check_tcgen05_errors(torch.device(DEV))
-        for a_, b_ in zip(ref, got):
-            assert torch.equal(a_, b_)
-    # a fifth product flushes the first four by itself; discard forgets what was recorded
-    chain = ops().GemvChain()
-    for _ in range(5):
-        out = ops().gemv_bf16(attn, w_o, None, torch.float32, chain=chain)
-    assert len(chain) == 1
-    chain.discard()
-    assert len(chain) == 0
-    # the thread's launches are direct again
-    direct = ops().gemv_bf16(attn, w_o, None, torch.float32).cpu().numpy()
-    ref_o = attn.double().cpu().numpy() @ w_o.double().cpu().numpy().T
-    assert np.abs(direct - ref_o).max() <= 3e-6 * np.sqrt(H * hd) * np.abs(ref_o).max() + 1e-5
-
-
 # ---- tcgen05 / TMA / TMEM matrix product -------------------------------------------------------------
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 8, 64), (200, 520, 192), (300, 264, 1000), (1100, 1048, 328)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
@@ -751,38 +700,6 @@ def test_gemm_tcgen05_pair_many_tiles_per_pair():
     assert torch.equal(one, two)
     ref = x.double().cpu().numpy() @ w.double().cpu().numpy().T
     assert np.abs(two.cpu().numpy() - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
-
-
-@pytest.mark.parametrize("M,N,K", [(2048, 2400, 1000), (1100, 4600, 1000), (2048, 3584, 448), (256, 512, 4096), (2048, 37888 // 4, 200)])
-def test_gemm_tcgen05_streamk(M, N, K):
-    """Whole rounds of tiles as in the pair kernel, the k blocks of the left-over tiles shared out over all CTA pairs:
-    a cut tile is summed through the scratch (two tiles among 74 pairs in one case: 36 sets of partial sums per tile).
-    Against the pair kernel (same products; only the cut tiles' sums are taken in parts), against float64 on some rows,
-    twice in a row (the flags are left clean), and the other epilogues."""
-    rng = np.random.RandomState(N)
-    x, w = t(rng.randn(M, K), torch.bfloat16), t(rng.randn(N, K) * 0.05, torch.bfloat16)
-    assert ops().gemm_tcgen05_streamk_supported(M, N, K, x.device)
-    whole = ops().gemm_tcgen05(x, w, None, torch.float32, pair=True)
-    for _ in range(2):
-        got = ops().gemm_tcgen05_streamk(x, w, None, torch.float32)
-        ops().check_tcgen05_errors(x.device)
-        assert (got - whole).abs().max().item() <= 2e-6 * np.sqrt(K) * whole.abs().max().item()
-    rows = [0, 127, 128, 255, M // 2, M - 1]
-    ref = x[rows].double().cpu().numpy() @ w.double().cpu().numpy().T
-    assert np.abs(got[rows].cpu().numpy() - ref).max() <= 3e-6 * np.sqrt(K) * np.abs(ref).max() + 1e-5
-    bias = t(rng.randn(N), torch.float32)
-    gb = ops().gemm_tcgen05_streamk(x, w, bias, torch.bfloat16).float()
-    wb = ops().gemm_tcgen05(x, w, bias, torch.bfloat16, pair=True).float()
-    assert (gb - wb).abs().max().item() <= 2 ** -7 * wb.abs().max().item()
-    if N % 16 == 0:
-        ga = ops().gemm_tcgen05_streamk(x, w, None, torch.bfloat16, swiglu=True).float()
-        wa = ops().gemm_tcgen05(x, w, None, torch.bfloat16, swiglu=True, pair=True).float()
-        assert (ga - wa).abs().max().item() <= 2 ** -7 * max(wa.abs().max().item(), 1e-3)
-    ops().check_tcgen05_errors(x.device)
-    assert not ops().gemm_tcgen05_streamk_supported(256, 256, 64, x.device)        # one k block cannot feed every pair
-    from mimirmind_b200.kernels.lib import KernelError
-    with pytest.raises(KernelError):
-        ops().gemm_tcgen05_streamk(x[:256, :64].contiguous(), w[:256, :64].contiguous(), None, torch.float32)
 
 
 @pytest.mark.parametrize("M,F,K", [(130, 352, 256), (1030, 1000, 512), (64, 72, 64)])
