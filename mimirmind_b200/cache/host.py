@@ -36,6 +36,7 @@ _PROTOTYPES = {
     "mmh_cache_table": (I, [P, L, I, PI, I]),
     "mmh_cache_tables": (I, [P, I, I, PL, I, c_void_p]),
     "mmh_cache_allocator": (P, [P, I]),
+    "mmh_cache_info": (I, [P, I, I]),
     "mmh_cache_live": (I, [P, PL, I]),
     "mmh_cache_check": (I, [P]),
     "mmh_sched_create": (P, [P, I, I, I, I]),

@@ -1,0 +1,462 @@
+// The native step: from (request, its next tokens) entries to logits at the wanted places, in one call.
+//
+// mmx_exec_run checks the entries against the cache manager (csrc/host/runtime.cpp), reserves their pages when asked
+// to, writes the step's integers (token ids, absolute positions, token -> request, wanted rows, one block-table row
+// per request and cache group, the attention work lists) into a pinned buffer, copies them to the device once, and
+// launches embedding, every schedule entry's block, the final norm on the wanted rows and the head.  mmx_exec_forward
+// runs the same launches on buffers the caller keeps on the device (a decode step captured in a CUDA graph).
+// The reference has a one-token-per-slot step and a per-request prefill as separate native calls
+// (src/runtime/engine/ServingSession.cpp:856-947, 949-1093); here any mix is one call.
+#include <algorithm>
+#include <cstring>
+#include <unordered_set>
+
+#include "../host/runtime_api.h"
+#include "exec.h"
+#include "kernels_api.h"
+
+#define MMX_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace mmx {
+
+struct ScheduleEntry {
+    int layer, cache_from;
+};
+
+struct Model {
+    std::unique_ptr<Embedding> embedding;
+    std::unique_ptr<Norm> final_norm;
+    std::unique_ptr<Head> head;
+    std::vector<std::unique_ptr<Block>> layers;
+    std::vector<ScheduleEntry> schedule;
+    int act_dtype = BF16;
+    bool simt = false;
+};
+
+struct EntryCache {
+    void* k_pages;
+    void* v_pages;
+    int group;       // -1: the entry keeps no keys and values
+    bool writes;
+};
+
+// what the caller of mmx_exec_forward describes: device arrays it keeps, host facts about the batch
+struct StepDesc {
+    int n_tokens, n_requests, n_logit_rows, max_kv_len, max_q_len, table_width;
+    const int* token_ids;
+    const int* positions;
+    const int* token_req;
+    const int* logit_rows;
+    const int* tables[MAX_GROUPS];
+    const int* q_start;      // host, [n_requests]
+    const int* q_len;
+    const int* kv_len;
+};
+
+constexpr int RUN_RESERVE = 1, RUN_COMMIT = 2;
+
+class Executor {
+  public:
+    Executor(Model* model, void* cache, int page_size, std::vector<int> group_pages, std::vector<EntryCache> entries, int vocab, int max_seq_len, void* err)
+        : model_(model), cache_(cache), page_size_(page_size), group_pages_(std::move(group_pages)), entries_(std::move(entries)), vocab_(vocab),
+          max_seq_len_(max_seq_len), err_(err), step_mem_(8u << 20), layer_mem_{Arena(16u << 20), Arena(16u << 20)} {
+        if (entries_.size() != model_->schedule.size()) throw ExecError("executor: one cache entry per schedule entry");
+        if ((int)group_pages_.size() > MAX_GROUPS) throw ExecError("executor: too many cache groups");
+        check_cuda(cudaMallocHost((void**)&err_host_, sizeof(int)), "pinned error flag");
+        *err_host_ = 0;
+    }
+    ~Executor() {
+        for (auto& s : ring_) {
+            if (s.host) cudaFreeHost(s.host);
+            if (s.copied) cudaEventDestroy(s.copied);
+        }
+        if (err_host_) cudaFreeHost(err_host_);
+    }
+
+    int n_groups() const { return (int)group_pages_.size(); }
+
+    // ---- the launches of a step whose integers are on the device -------------------------------------------------------
+    void forward(Step& st, float* logits) {
+        Model& m = *model_;
+        float* residual = m.embedding->forward(st, *st.step_mem);
+        Pending pending;
+        const int last = (int)m.schedule.size() - 1;
+        for (int i = 0; i <= last; ++i) {
+            Arena& mem = layer_mem_[i & 1];
+            mem.reset();
+            st.layer_mem = &mem;
+            LayerCache lc = layer_cache(i, st);
+            Block* successor = i < last ? m.layers[m.schedule[i + 1].layer].get() : nullptr;
+            pending = m.layers[m.schedule[i].layer]->forward(st, residual, pending, lc, successor);
+        }
+        if (st.n_logit_rows == 0) return;
+        if (pending.kind == Pending::FACTORED) throw ExecError("the last block left factored rows that no block takes");
+        Arena& mem = layer_mem_[(last + 1) & 1];
+        mem.reset();
+        Rows normed = m.final_norm->forward(st, mem, residual, pending.kind == Pending::DELTA ? &pending.delta : nullptr, st.logit_rows, st.n_logit_rows);
+        m.head->forward(st, mem, normed, logits);
+    }
+
+    LayerCache layer_cache(int entry, const Step& st) const {
+        const EntryCache& e = entries_[entry];
+        LayerCache lc;
+        lc.page_size = page_size_;
+        lc.writes = e.writes;
+        lc.group = e.group;
+        if (e.group >= 0) {
+            lc.k_pages = e.k_pages;
+            lc.v_pages = e.v_pages;
+            lc.table = st.tables[e.group];
+            lc.table_width = st.table_width;
+            lc.num_pages = std::max(group_pages_[e.group], 1);
+        }
+        return lc;
+    }
+
+    void init_step(Step& st, cudaStream_t stream) {
+        st.act_dtype = model_->act_dtype;
+        st.simt = model_->simt;
+        st.stream = stream;
+        st.err = err_;
+        st.page_size = page_size_;
+        step_mem_.reset();
+        st.step_mem = &step_mem_;
+        if (!blas_) blas_.reset(new Blas());
+        st.blas = blas_.get();
+    }
+
+    void prepare(Step& st) {
+        Model& m = *model_;
+        for (size_t i = 0; i < m.schedule.size(); ++i) {
+            LayerCache lc = layer_cache((int)i, st);
+            m.layers[m.schedule[i].layer]->prepare(st, &lc);
+        }
+    }
+
+    // ---- staging: a ring of pinned buffers, each reused only after its last copy has run -----------------------------------
+    struct Staging {
+        int* host = nullptr;
+        size_t cap = 0;
+        cudaEvent_t copied = nullptr;
+        bool in_flight = false;
+    };
+    Staging& next_staging(size_t ints) {
+        Staging& s = ring_[ring_next_];
+        ring_next_ = (ring_next_ + 1) % (int)(sizeof(ring_) / sizeof(ring_[0]));
+        if (s.in_flight) {
+            check_cuda(cudaEventSynchronize(s.copied), "waiting for a staging buffer");
+            s.in_flight = false;
+        }
+        if (s.cap < ints) {
+            if (s.host) cudaFreeHost(s.host);
+            s.host = nullptr;
+            s.cap = std::max(ints * 2, (size_t)16384);
+            check_cuda(cudaMallocHost((void**)&s.host, s.cap * sizeof(int)), "pinned staging buffer");
+        }
+        if (!s.copied) check_cuda(cudaEventCreateWithFlags(&s.copied, cudaEventDisableTiming), "staging event");
+        return s;
+    }
+
+    // copies `fixed` ints (already in s.host) and the step's uploads to the device in one copy; returns the device base
+    const int* copy_step(Step& st, Staging& s, size_t fixed) {
+        size_t total = fixed;
+        for (auto& u : st.uploads) total += (u.data.size() + 3) & ~(size_t)3;
+        if (total == 0) return nullptr;
+        if (total > s.cap) throw ExecError("executor: staging buffer too small");     // sized by the caller
+        size_t off = fixed;
+        std::vector<size_t> offs;
+        for (auto& u : st.uploads) {
+            std::memcpy(s.host + off, u.data.data(), u.data.size() * sizeof(int));
+            offs.push_back(off);
+            off += (u.data.size() + 3) & ~(size_t)3;
+        }
+        int* dev = st.step_mem->alloc_n<int>(total);
+        check_cuda(cudaMemcpyAsync(dev, s.host, total * sizeof(int), cudaMemcpyHostToDevice, st.stream), "copying the step's integers");
+        check_cuda(cudaEventRecord(s.copied, st.stream), "staging event");
+        s.in_flight = true;
+        for (size_t i = 0; i < st.uploads.size(); ++i) *st.uploads[i].where = dev + offs[i];
+        st.uploads.clear();
+        return dev;
+    }
+
+    size_t upload_ints(const Step& st) const {
+        size_t n = 0;
+        for (auto& u : st.uploads) n += (u.data.size() + 3) & ~(size_t)3;
+        return n;
+    }
+
+    // ---- one step from entries -------------------------------------------------------------------------------------------------
+    // Returns the number of logits rows written.
+    int run(int n_entries, const long long* rids, const int* counts, const int* tokens, const int* n_want, const int* want, int flags, float* logits,
+            long long logits_rows_cap, cudaStream_t stream) {
+        if (n_entries <= 0) return 0;
+        const int G = n_groups(), ps = page_size_;
+        // -- what the step refuses, before anything changes
+        std::unordered_set<long long> seen;
+        std::vector<int> start(n_entries);
+        int n_tok = 0, n_rows = 0;
+        for (int r = 0; r < n_entries; ++r) {
+            if (counts[r] < 1) throw StepRefused("request " + std::to_string(r) + " of the step: an entry needs at least one token");
+            if (!seen.insert(rids[r]).second) throw StepRefused("a request appears twice in one step");
+            if (!mmh_cache_has(cache_, rids[r])) throw StepRefused("unknown request");
+            start[r] = mmh_cache_request(cache_, rids[r], 0);
+            if (start[r] + counts[r] > max_seq_len_)
+                throw StepRefused(std::to_string(start[r] + counts[r]) + " tokens exceed the context of " + std::to_string(max_seq_len_));
+            for (int i = 0; i < counts[r]; ++i)
+                if (tokens[n_tok + i] < 0 || tokens[n_tok + i] >= vocab_) throw StepRefused("token id outside [0, " + std::to_string(vocab_) + ")");
+            for (int i = 0; i < n_want[r]; ++i)
+                if (want[n_rows + i] < 0 || want[n_rows + i] >= counts[r])
+                    throw StepRefused("wanted place " + std::to_string(want[n_rows + i]) + " is outside the entry's " + std::to_string(counts[r]) + " tokens");
+            n_tok += counts[r];
+            n_rows += n_want[r];
+        }
+        if (n_rows > logits_rows_cap) throw ExecError("executor: the logits buffer is too small for the wanted rows");
+        if (flags & RUN_RESERVE) {
+            // pages for every entry: the step runs fully or not at all
+            std::vector<int> need(G, 0), one(std::max(G, 1));
+            for (int r = 0; r < n_entries; ++r) {
+                if (mmh_cache_pages_needed(cache_, rids[r], start[r] + counts[r], one.data()) != 0) throw ExecError(mmh_last_error());
+                for (int g = 0; g < G; ++g) need[g] += one[g];
+            }
+            for (int g = 0; g < G; ++g) {
+                const int free_pages = mmh_cache_info(cache_, 3, g);
+                if (need[g] > free_pages)
+                    throw StepRefused("out of cache pages in group " + std::to_string(g) + ": the step needs " + std::to_string(need[g]) + ", " +
+                                      std::to_string(free_pages) + " of " + std::to_string(mmh_cache_info(cache_, 2, g)) + " are free");
+            }
+            for (int r = 0; r < n_entries; ++r)
+                if (mmh_cache_reserve(cache_, rids[r], start[r] + counts[r]) != 1) throw ExecError("executor: reserving checked pages failed");
+        }
+        for (int r = 0; r < n_entries; ++r) mmh_cache_request(cache_, rids[r], 3);      // the request has started (its state slot is in use)
+
+        // -- the batch
+        Step st;
+        init_step(st, stream);
+        st.n_tokens = n_tok;
+        st.n_requests = n_entries;
+        st.n_logit_rows = n_rows;
+        st.q_start.resize(n_entries);
+        st.q_len.assign(counts, counts + n_entries);
+        st.kv_len.resize(n_entries);
+        int at = 0;
+        for (int r = 0; r < n_entries; ++r) {
+            st.q_start[r] = at;
+            st.kv_len[r] = start[r] + counts[r];
+            st.max_kv_len = std::max(st.max_kv_len, st.kv_len[r]);
+            st.max_q_len = std::max(st.max_q_len, counts[r]);
+            at += counts[r];
+        }
+        st.table_width = std::max(1, (st.max_kv_len + ps - 1) / ps);
+        prepare(st);
+
+        // -- one pinned buffer, one copy: ids | positions | token -> request | wanted rows | a table per group | work lists
+        auto pad4 = [](size_t n) { return (n + 3) & ~(size_t)3; };
+        const size_t o_ids = 0, o_pos = o_ids + pad4(n_tok), o_req = o_pos + pad4(n_tok), o_rows = o_req + pad4(n_tok),
+                     o_tab = o_rows + pad4(std::max(n_rows, 1)), tab = pad4((size_t)n_entries * st.table_width), fixed = o_tab + tab * G;
+        Staging& sg = next_staging(fixed + upload_ints(st));
+        int* h = sg.host;
+        std::memcpy(h + o_ids, tokens, sizeof(int) * n_tok);
+        int row = 0, wi = 0;
+        for (int r = 0; r < n_entries; ++r) {
+            for (int i = 0; i < counts[r]; ++i) {
+                h[o_pos + st.q_start[r] + i] = start[r] + i;
+                h[o_req + st.q_start[r] + i] = r;
+            }
+            for (int i = 0; i < n_want[r]; ++i) h[o_rows + row++] = st.q_start[r] + want[wi++];
+        }
+        for (int g = 0; g < G; ++g)
+            if (mmh_cache_tables(cache_, g, n_entries, rids, st.table_width, h + o_tab + tab * g) != 0) throw ExecError(mmh_last_error());
+        const int* dev = copy_step(st, sg, fixed);
+        st.token_ids = dev + o_ids;
+        st.positions = dev + o_pos;
+        st.token_req = dev + o_req;
+        st.logit_rows = dev + o_rows;
+        for (int g = 0; g < G; ++g) st.tables[g] = dev + o_tab + tab * g;
+
+        forward(st, logits);
+        check_cuda(cudaMemcpyAsync(err_host_, err_, sizeof(int), cudaMemcpyDeviceToHost, stream), "reading the kernels' error flag");
+        if (flags & RUN_COMMIT)
+            for (int r = 0; r < n_entries; ++r)
+                if (mmh_cache_commit(cache_, rids[r], start[r] + counts[r]) != 0) throw ExecError(mmh_last_error());
+        ++steps_;
+        return n_rows;
+    }
+
+    // ---- the same launches over the caller's device buffers ------------------------------------------------------------------------
+    void forward_described(const StepDesc& d, float* logits, cudaStream_t stream) {
+        Step st;
+        init_step(st, stream);
+        st.n_tokens = d.n_tokens;
+        st.n_requests = d.n_requests;
+        st.n_logit_rows = d.n_logit_rows;
+        st.max_kv_len = d.max_kv_len;
+        st.max_q_len = d.max_q_len;
+        st.table_width = d.table_width;
+        st.token_ids = d.token_ids;
+        st.positions = d.positions;
+        st.token_req = d.token_req;
+        st.logit_rows = d.logit_rows;
+        for (int g = 0; g < n_groups(); ++g) st.tables[g] = d.tables[g];
+        st.q_start.assign(d.q_start, d.q_start + d.n_requests);
+        st.q_len.assign(d.q_len, d.q_len + d.n_requests);
+        st.kv_len.assign(d.kv_len, d.kv_len + d.n_requests);
+        prepare(st);
+        if (!st.uploads.empty()) {
+            cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+            cudaStreamIsCapturing(stream, &cs);
+            if (cs != cudaStreamCaptureStatusNone)
+                throw ExecError("this step needs work lists copied from the host (it holds a prompt portion); it cannot be captured");
+            Staging& sg = next_staging(upload_ints(st));
+            copy_step(st, sg, 0);
+        }
+        forward(st, logits);
+        ++steps_;
+    }
+
+    int take_error_flag() {
+        const int v = *err_host_;
+        *err_host_ = 0;
+        return v;
+    }
+    long long steps() const { return steps_; }
+    size_t memory() const { return step_mem_.capacity() + layer_mem_[0].capacity() + layer_mem_[1].capacity(); }
+
+  private:
+    Model* model_;
+    void* cache_;
+    int page_size_;
+    std::vector<int> group_pages_;
+    std::vector<EntryCache> entries_;
+    int vocab_, max_seq_len_;
+    void* err_;
+    int* err_host_ = nullptr;
+    Arena step_mem_;
+    Arena layer_mem_[2];
+    std::unique_ptr<Blas> blas_;
+    Staging ring_[4];
+    int ring_next_ = 0;
+    long long steps_ = 0;
+};
+
+}  // namespace mmx
+
+// ---- C interface -----------------------------------------------------------------------------------------------------------------
+using namespace mmx;
+
+static thread_local std::string g_mmx_error;
+static int set_error(int code, const std::exception& e) {
+    g_mmx_error = e.what();
+    return code;
+}
+#define MMX_GUARD(body)                                 \
+    try {                                               \
+        body                                            \
+    } catch (const StepRefused& e) {                    \
+        return set_error(-10, e);                       \
+    } catch (const std::exception& e) {                 \
+        return set_error(-1, e);                        \
+    }
+
+MMX_EXPORT const char* mmx_last_error() { return g_mmx_error.c_str(); }
+
+// descriptions: built by the loader, consumed by mmx_model_create
+MMX_EXPORT void* mmx_desc_new(const char* kind) {
+    auto* d = new PartDesc();
+    d->kind = kind;
+    return d;
+}
+MMX_EXPORT void mmx_desc_free(void* d) { delete static_cast<PartDesc*>(d); }
+MMX_EXPORT void mmx_desc_num(void* d, const char* key, double v) { static_cast<PartDesc*>(d)->num[key] = v; }
+MMX_EXPORT int mmx_desc_tensor(void* d, const char* key, void* ptr, int dtype, int ndim, const long long* shape) {
+    if (ndim < 0 || ndim > 4 || (dtype != F32 && dtype != BF16)) return -1;
+    Tensor t;
+    t.ptr = ptr;
+    t.dtype = dtype;
+    t.ndim = ndim;
+    for (int i = 0; i < ndim; ++i) t.shape[i] = shape[i];
+    static_cast<PartDesc*>(d)->tensors[key] = t;
+    return 0;
+}
+// the child belongs to the parent from here on
+MMX_EXPORT void mmx_desc_child(void* d, const char* key, void* child) {
+    static_cast<PartDesc*>(d)->children[key] = std::unique_ptr<PartDesc>(static_cast<PartDesc*>(child));
+}
+
+// A model from descriptions (which stay the caller's).  Null, with a message, when a part has no native class.
+MMX_EXPORT void* mmx_model_create(void* embedding, void* final_norm, void* head, int n_layers, void** blocks, int n_schedule, const int* sched_layer,
+                                  const int* sched_cache_from, int act_dtype, int simt) {
+    try {
+        std::unique_ptr<Model> m(new Model());
+        m->act_dtype = act_dtype;
+        m->simt = simt != 0;
+        m->embedding = build_as<Embedding>("embedding", *static_cast<PartDesc*>(embedding));
+        m->final_norm = build_as<Norm>("norm", *static_cast<PartDesc*>(final_norm));
+        m->head = build_as<Head>("head", *static_cast<PartDesc*>(head));
+        for (int i = 0; i < n_layers; ++i) m->layers.push_back(build_as<Block>("block", *static_cast<PartDesc*>(blocks[i])));
+        for (int i = 0; i < n_schedule; ++i) {
+            if (sched_layer[i] < 0 || sched_layer[i] >= n_layers) throw ExecError("schedule entry names a layer the model does not have");
+            m->schedule.push_back({sched_layer[i], sched_cache_from[i]});
+        }
+        return m.release();
+    } catch (const std::exception& e) {
+        g_mmx_error = e.what();
+        return nullptr;
+    }
+}
+MMX_EXPORT void mmx_model_destroy(void* m) { delete static_cast<Model*>(m); }
+
+// entry_group[i] < 0: schedule entry i keeps no keys and values; k_pages/v_pages: the pools of the entry whose cache it uses
+MMX_EXPORT void* mmx_exec_create(void* model, void* cache, int n_groups, int page_size, const int* group_pages, int n_entries, void** k_pages,
+                                 void** v_pages, const int* entry_group, const int* entry_writes, int vocab, int max_seq_len, void* err_flag) {
+    try {
+        std::vector<EntryCache> entries;
+        for (int i = 0; i < n_entries; ++i) entries.push_back({k_pages[i], v_pages[i], entry_group[i], entry_writes[i] != 0});
+        return new Executor(static_cast<Model*>(model), cache, page_size, std::vector<int>(group_pages, group_pages + n_groups), std::move(entries), vocab,
+                            max_seq_len, err_flag);
+    } catch (const std::exception& e) {
+        g_mmx_error = e.what();
+        return nullptr;
+    }
+}
+MMX_EXPORT void mmx_exec_destroy(void* ex) { delete static_cast<Executor*>(ex); }
+
+// One step.  rids, counts, n_want: per entry; tokens and want: the entries' tokens and wanted places, one after the other.
+// flags: 1 reserve the pages first (all or nothing), 2 commit the lengths after the launches.  Returns the number of
+// logits rows (fp32 [rows, vocab] at `logits`), -10 when the step is refused (nothing ran, nothing changed), -1 on
+// any other error; the text is mmx_last_error().
+MMX_EXPORT int mmx_exec_run(void* ex, int n_entries, const long long* rids, const int* counts, const int* tokens, const int* n_want, const int* want,
+                            int flags, void* logits, long long logits_rows_cap, void* stream) {
+    MMX_GUARD(return static_cast<Executor*>(ex)->run(n_entries, rids, counts, tokens, n_want, want, flags, (float*)logits, logits_rows_cap,
+                                                     (cudaStream_t)stream);)
+}
+
+MMX_EXPORT int mmx_exec_forward(void* ex, const StepDesc* d, void* logits, void* stream) {
+    MMX_GUARD(static_cast<Executor*>(ex)->forward_described(*d, (float*)logits, (cudaStream_t)stream); return 0;)
+}
+
+// The kernels' error flag as the last mmx_exec_run copied it back (valid once the stream has been synchronised); reading clears it.
+MMX_EXPORT int mmx_exec_take_error_flag(void* ex) { return static_cast<Executor*>(ex)->take_error_flag(); }
+MMX_EXPORT long long mmx_exec_stat(void* ex, int what) {
+    Executor* e = static_cast<Executor*>(ex);
+    return what == 0 ? e->steps() : (long long)e->memory();
+}
+
+// Tunables of the dispatch by name; returns the old value, or -1 for an unknown name.  value < 0 only reads.
+MMX_EXPORT int mmx_option(const char* name, int value) {
+    Options& o = options();
+    struct {
+        const char* n;
+        int* p;
+    } table[] = {{"prefill_min", &o.prefill_min}, {"use_tcgen05_prefill", &o.use_tcgen05_prefill}, {"use_tma_decode", &o.use_tma_decode},
+                 {"tma_decode_stages", &o.tma_decode_stages}, {"target_ctas", &o.target_ctas}, {"use_cluster_merge", &o.use_cluster_merge},
+                 {"cluster_max_wanted", &o.cluster_max_wanted}, {"fixed_split", &o.fixed_split}, {"gemv_max_rows", &o.gemv_max_rows},
+                 {"skinny_max_rows", &o.skinny_max_rows}, {"tcgen05_swiglu_min_rows", &o.tcgen05_swiglu_min_rows},
+                 {"tcgen05_pair_min_rows", &o.tcgen05_pair_min_rows}};
+    for (auto& t : table)
+        if (std::strcmp(t.n, name) == 0) {
+            const int old = *t.p;
+            if (value >= 0) *t.p = value;
+            return old;
+        }
+    return -1;
+}

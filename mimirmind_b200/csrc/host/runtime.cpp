@@ -530,6 +530,14 @@ MMH int mmh_cache_tables(void* h, int group, int n, const long long* rids, int w
     }
     return 0;
 }
+// what: 0 number of groups, 1 page size, 2 pages of a group, 3 free pages of a group
+MMH int mmh_cache_info(void* h, int what, int group) {
+    CacheManager* m = static_cast<CacheManager*>(h);
+    if (what == 0) return m->n_groups();
+    if (what == 1) return m->page_size();
+    if (group < 0 || group >= m->n_groups()) return fail("no such cache group");
+    return what == 2 ? m->allocator(group).num_pages() : m->allocator(group).num_free();
+}
 MMH void* mmh_cache_allocator(void* h, int group) {
     CacheManager* m = static_cast<CacheManager*>(h);
     if (group == -1) return &m->slots();

@@ -16,7 +16,7 @@ after the step was enqueued without error (src/runtime/KvCache.hpp:90-103).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -24,14 +24,9 @@ import torch
 from ..cache.manager import CacheManager
 from ..kernels import ops
 from ..parts.base import Runtime, StepContext
+from . import native
 from .model import Model
 from .storage import CacheStorage
-
-# A prompt portion of one request with at least this many tokens, of a size seen before, runs as a replayed CUDA
-# graph (engine/prefill_graph.py); at most PREFILL_GRAPHS sizes are kept.  0 turns it off.
-PREFILL_GRAPH_MIN_TOKENS = 512
-PREFILL_GRAPHS = 4
-
 
 class StepError(RuntimeError):
     pass
@@ -56,9 +51,10 @@ class ModelRunner:
         self.page_size = page_size
         self.vocab = model.spec.vocab_size
         self.steps_run = 0
-        self._prefill_sessions: Dict[Tuple[int, bool], object] = {}
-        self._prefill_seen: Dict[Tuple[int, bool], int] = {}
         self.stage_dump = None       # engine.diagnostics.StageDump: steps with a prompt portion write their stages
+        # The library's executor when every part of the model has a native class, else None: then steps are put
+        # together and launched here, part by part, through the Python classes.
+        self.native: Optional[native.NativeExecutor] = native.NativeExecutor.build(model, self.storage, self.manager, self.max_seq_len)
 
     # ---- request life cycle ---------------------------------------------------
     def add_request(self, rid: Hashable) -> bool:
@@ -143,6 +139,10 @@ class ModelRunner:
         if not entries:
             return None
         mgr = self.manager
+        if self.native is not None and self.stage_dump is None:
+            logits = self._run_native(entries, reserve=True, commit=True)       # checks, pages, launches, lengths: one call
+            self.steps_run += 1
+            return logits
         seen = set()
         for e in entries:
             if e.request in seen:
@@ -175,46 +175,33 @@ class ModelRunner:
         """Runs the model on entries whose pages are reserved (by ``step`` or by a scheduler); lengths are not
         committed here.  Returns fp32 logits [wanted, vocab] or None."""
         mgr = self.manager
+        if self.native is not None and not (self.stage_dump is not None and any(len(e.tokens) > 1 for e in entries)):
+            return self._run_native(entries, reserve=False, commit=False)
         for e in entries:
             if mgr.mark_started(e.request):
                 self.storage.zero_slot(mgr.slot(e.request))
+        ctx = self._build_context(entries)
         if self.stage_dump is not None and any(len(e.tokens) > 1 for e in entries):
-            ctx = self._build_context(entries)
             ctx.plain_only = True
             return self.forward(ctx, dump=self.stage_dump)
-        session = self._prefill_session(entries)
-        if session is not None:
-            e = entries[0]
-            return session.run(e.request, e.tokens, mgr.length(e.request))
-        return self.forward(self._build_context(entries))
+        return self.forward(ctx)
 
-    def _prefill_session(self, entries: Sequence[StepEntry]):
-        """The graph session for this step, or None: one request, bfloat16, a long portion whose size was seen
-        before, logits wanted at its last token or nowhere."""
-        if (PREFILL_GRAPH_MIN_TOKENS <= 0 or len(entries) != 1 or self.rt.dtype != torch.bfloat16
-                or len(entries[0].tokens) < PREFILL_GRAPH_MIN_TOKENS):
-            return None
-        e = entries[0]
-        n = len(e.tokens)
-        want = list(e.want)
-        if want not in ([], [n - 1]):
-            return None
-        if min(e.tokens) < 0 or max(e.tokens) >= self.vocab:
-            raise StepError(f"request {e.request!r}: token id outside [0, {self.vocab})")
-        key = (n, bool(want))
-        sess = self._prefill_sessions.get(key)
-        if sess is None:
-            self._prefill_seen[key] = self._prefill_seen.get(key, 0) + 1
-            if self._prefill_seen[key] < 2:
-                return None                      # a size seen once is not worth a capture
-            if len(self._prefill_sessions) >= PREFILL_GRAPHS:
-                self._prefill_sessions.pop(next(iter(self._prefill_sessions)))
-            from .prefill_graph import PrefillSession
-            sess = PrefillSession(self, n, bool(want))
-            self._prefill_sessions[key] = sess
-        return sess
+    def _run_native(self, entries: Sequence[StepEntry], reserve: bool, commit: bool) -> Optional[torch.Tensor]:
+        mgr = self.manager
+        try:
+            handles = [mgr.handle(e.request) for e in entries]
+        except Exception:
+            missing = next(e.request for e in entries if not mgr.has(e.request))
+            raise StepError(f"unknown request {missing!r}") from None
+        try:
+            return self.native.run(handles, [e.tokens for e in entries], [e.want for e in entries], reserve, commit)
+        except native.StepRefused as e:
+            raise StepError(str(e)) from None
 
     def forward(self, ctx: StepContext, dump=None) -> Optional[torch.Tensor]:
+        """The launches of a step whose context is on the device: by the library's executor, or part by part here."""
+        if self.native is not None and dump is None and not ctx.plain_only:
+            return self.native.forward(ctx)
         m = self.model
         residual = m.embedding.forward(ctx.token_ids)
         if dump is not None:

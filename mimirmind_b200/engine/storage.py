@@ -38,6 +38,10 @@ class CacheStorage:
         return sum(t.numel() * t.element_size() for t in self.pools.values()) + \
             sum(t.numel() * t.element_size() for t in self.states.values())
 
+    def entry_pool(self, entry: int):
+        """(group name, index in the group's pool) of a schedule entry that owns keys and values, else None."""
+        return self._entry_group.get(entry)
+
     def zero_slot(self, slot: int) -> None:
         for t in self.states.values():
             t[slot].zero_()

@@ -50,12 +50,21 @@ def find_nvcc() -> str:
     raise BuildError("nvcc not found (set CUDA_HOME or MIMIRMIND_NVCC); the CUDA kernels cannot be built")
 
 
+EXEC_DIR = os.path.join(CSRC_DIR, "exec")     # the native step executor: host code over the kernels' entry points
+
+
 def _sources() -> List[str]:
-    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
+    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith(".cu")) + \
+        sorted("exec/" + f for f in os.listdir(EXEC_DIR) if f.endswith(".cu"))
 
 
 def _headers() -> List[str]:
-    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h")))
+    return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith((".cuh", ".h"))) + \
+        sorted("exec/" + f for f in os.listdir(EXEC_DIR) if f.endswith(".h")) + ["host/runtime_api.h"]
+
+
+def _obj(build_dir: str, src: str) -> str:
+    return os.path.join(build_dir, src[:-3].replace("/", "_") + ".o")
 
 
 def _digest(paths: List[str], extra: str) -> str:
@@ -101,7 +110,7 @@ def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
     """Path of the built library; compiles what is missing or stale first."""
     srcs = _sources()
     hdrs = _headers()
-    flags = " ".join(NVCC_FLAGS + LINK_FLAGS)
+    flags = " ".join(NVCC_FLAGS + LINK_FLAGS + ["host-linked"])
     header_digest = _digest(hdrs, flags)
     build_dir = _writable_build_dir()
     manifest_path = os.path.join(build_dir, "manifest.json")
@@ -112,7 +121,7 @@ def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
     except (OSError, ValueError):
         manifest = {}
     want = {s: _digest([s], header_digest) for s in srcs}
-    stale = [s for s in srcs if manifest.get(s) != want[s] or not os.path.isfile(os.path.join(build_dir, s[:-3] + ".o"))]
+    stale = [s for s in srcs if manifest.get(s) != want[s] or not os.path.isfile(_obj(build_dir, s))]
     removed = [s for s in manifest if s not in want]
     if not stale and not removed and os.path.isfile(lib_path):
         return lib_path
@@ -125,15 +134,18 @@ def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
     done = 0
     workers = min(len(stale), max(1, min(8, (os.cpu_count() or 2)))) or 1
     with concurrent.futures.ThreadPoolExecutor(max_workers=workers) as pool:
-        futs = {pool.submit(_compile_one, nvcc, s, os.path.join(build_dir, s[:-3] + ".o")): s for s in stale}
+        futs = {pool.submit(_compile_one, nvcc, s, _obj(build_dir, s)): s for s in stale}
         for fut in concurrent.futures.as_completed(futs):
             secs = fut.result()
             done += 1
             if verbose:
                 _log(f"  [{done}/{len(stale)}] {futs[fut]} ({secs:.1f} s, {time.time() - t0:.0f} s elapsed)")
-    objs = [os.path.join(build_dir, s[:-3] + ".o") for s in srcs]
+    objs = [_obj(build_dir, s) for s in srcs]
     tmp_lib = lib_path + f".tmp{os.getpid()}"
-    proc = subprocess.run([nvcc] + LINK_FLAGS + ["-o", tmp_lib] + objs, capture_output=True, text=True)
+    # the executor calls the host runtime (cache manager, scheduler), which lives in a library of its own beside this one
+    host_dir = os.path.dirname(host_library_path(verbose=verbose))
+    link = LINK_FLAGS + ["-L", host_dir, "-lmimirmind_host", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-ldl"]
+    proc = subprocess.run([nvcc] + link + ["-o", tmp_lib] + objs, capture_output=True, text=True)
     if proc.returncode != 0:
         raise BuildError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
     os.replace(tmp_lib, lib_path)
@@ -146,7 +158,7 @@ def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
 
 HOST_DIR = os.path.join(CSRC_DIR, "host")
 HOST_LIB_NAME = "libmimirmind_host.so"
-HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wl,-soname," + HOST_LIB_NAME]
 
 
 def host_library_path(verbose: bool = True) -> str:

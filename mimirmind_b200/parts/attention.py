@@ -20,7 +20,7 @@ import torch
 from ..config.spec import PartSpec, TensorSpec
 from ..kernels import ops
 from ..registry import MIXERS, POSITION_ENCODINGS
-from .base import FactoredRows, KVCacheSpec, LayerCache, Mixer, ResidualSink, Runtime, StepContext, WeightView
+from .base import FactoredRows, KVCacheSpec, LayerCache, Mixer, NativeDesc, ResidualSink, Runtime, StepContext, WeightView
 from .linear import linear
 
 
@@ -118,6 +118,17 @@ class GQAAttention(Mixer):
 
     def kv_cache_spec(self) -> Optional[KVCacheSpec]:
         return KVCacheSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def native(self):
+        position = self.position.native()
+        if type(self) is not GQAAttention or position is None or self.position.fused_rotary() is None:
+            return None
+        tensors = {"w_qkv": self.w_qkv, "w_o": self.w_o}
+        if self.b_qkv is not None:
+            tensors["b_qkv"] = self.b_qkv
+        return NativeDesc("gqa_attention", {
+            "hidden": self.hidden, "num_heads": self.num_heads, "num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim,
+            "window": self.window, "scale": self.scale, "interleaved": int(self.interleaved)}, tensors, {"position": position})
 
     def fuses(self, n_tokens: int) -> bool:
         width = (self.num_heads + 2 * self.num_kv_heads) * self.head_dim

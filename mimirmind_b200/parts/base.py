@@ -146,6 +146,17 @@ class ResidualSink:
     eps: float = 0.0
 
 
+@dataclass
+class NativeDesc:
+    """What the native step executor (csrc/exec) needs to build its own object of a part: the kind under which a
+    C++ class is registered, numbers, tensors (as the part holds them after fusing) and the parts inside it."""
+
+    kind: str
+    numbers: Dict[str, float] = field(default_factory=dict)
+    tensors: Dict[str, torch.Tensor] = field(default_factory=dict)
+    children: Dict[str, "NativeDesc"] = field(default_factory=dict)
+
+
 class Part:
     """Base of every part: declares its tensors, builds from weights."""
 
@@ -156,6 +167,11 @@ class Part:
     def __init__(self, spec: PartSpec, weights: WeightView, rt: Runtime):
         self.spec = spec
         self.rt = rt
+
+    def native(self) -> Optional["NativeDesc"]:
+        """The part's description for the native step executor, or None: the part exists in Python only, and a model
+        that holds it runs its steps through the Python classes."""
+        return None
 
 
 class Norm(Part):

@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 
 from ..registry import BLOCKS
-from .base import Block, FactoredRows, LayerCache, ResidualSink, StepContext
+from .base import Block, FactoredRows, LayerCache, NativeDesc, ResidualSink, StepContext
 
 
 @BLOCKS.register("pre_norm")
@@ -23,6 +23,13 @@ class PreNormBlock(Block):
     def entry_norm(self, n_tokens: int):
         f = self.mixer_norm.factors()
         return f if f is not None and self.mixer.fuses(n_tokens) else None
+
+    def native(self):
+        parts = {"mixer_norm": self.mixer_norm.native(), "mixer": self.mixer.native(), "ffn_norm": self.ffn_norm.native(),
+                 "feed_forward": self.feed_forward.native()}
+        if type(self) is not PreNormBlock or any(p is None for p in parts.values()):
+            return None
+        return NativeDesc("pre_norm", {}, {}, parts)
 
     def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: LayerCache,
                 successor: Optional[Block] = None):

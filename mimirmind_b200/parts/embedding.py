@@ -15,7 +15,7 @@ import torch
 from ..config.spec import PartSpec, TensorSpec
 from ..kernels import ops
 from ..registry import EMBEDDINGS, HEADS
-from .base import Part, Runtime, WeightView
+from .base import NativeDesc, Part, Runtime, WeightView
 from .linear import linear
 
 
@@ -33,6 +33,11 @@ class TokenEmbedding(Part):
         self.width = int(spec["width"])
         self.scale = float(spec.get("scale", 1.0))
         self.table = weights.get(spec["weight"]).contiguous()
+
+    def native(self):
+        if type(self) is not TokenEmbedding:
+            return None
+        return NativeDesc("token_embedding", {"vocab": self.vocab, "width": self.width, "scale": self.scale}, {"table": self.table})
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = torch.empty((token_ids.numel(), self.width), dtype=torch.float32, device=token_ids.device)
@@ -57,6 +62,9 @@ class LMHead(Part):
             self.weight = weights.get(spec["tied_to"]).contiguous()
         else:
             raise KeyError(f"tensor '{spec['weight']}' not in model")
+
+    def native(self):
+        return NativeDesc("lm_head", {"vocab": self.vocab}, {"weight": self.weight}) if type(self) is LMHead else None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return linear(x, self.weight, None, self.rt, out_dtype=torch.float32)

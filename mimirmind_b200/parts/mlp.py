@@ -13,7 +13,7 @@ import torch
 from ..config.spec import PartSpec, TensorSpec
 from ..kernels import ops
 from ..registry import FEED_FORWARDS
-from .base import FactoredRows, FeedForward, ResidualSink, Runtime, StepContext, WeightView
+from .base import FactoredRows, FeedForward, NativeDesc, ResidualSink, Runtime, StepContext, WeightView
 from .linear import linear
 
 
@@ -49,6 +49,12 @@ class SwiGLU(FeedForward):
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()  # [2F, d]
         del gate, up
         self.w_down = weights.take(spec["down"]).contiguous()       # [d, F]
+
+    def native(self):
+        if type(self) is not SwiGLU:
+            return None
+        return NativeDesc("swiglu", {"hidden": self.hidden, "intermediate": self.intermediate, "interleave": self.interleave},
+                          {"w_gate_up": self.w_gate_up, "w_down": self.w_down})
 
     def _tensor_cores(self) -> bool:
         return bool(self.interleave) and self.rt.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 \

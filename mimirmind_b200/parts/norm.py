@@ -14,7 +14,7 @@ import torch
 from ..config.spec import PartSpec, TensorSpec
 from ..kernels import ops
 from ..registry import NORMS
-from .base import Norm, Runtime, WeightView
+from .base import NativeDesc, Norm, Runtime, WeightView
 
 
 @NORMS.register("rmsnorm")
@@ -33,6 +33,11 @@ class RMSNorm(Norm):
 
     def factors(self):
         return self.weight, self.eps
+
+    def native(self):
+        if type(self) is not RMSNorm:
+            return None
+        return NativeDesc("rmsnorm", {"width": self.width, "eps": self.eps}, {"weight": self.weight})
 
     def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
                 n_rows: Optional[int] = None) -> torch.Tensor:

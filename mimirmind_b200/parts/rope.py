@@ -11,7 +11,7 @@ from typing import Optional, Tuple
 
 from ..config.spec import PartSpec
 from ..registry import POSITION_ENCODINGS
-from .base import PositionEncoding, Runtime, WeightView
+from .base import NativeDesc, PositionEncoding, Runtime, WeightView
 
 
 @POSITION_ENCODINGS.register("rotary_half")
@@ -28,6 +28,11 @@ class RotaryHalf(PositionEncoding):
     def fused_rotary(self) -> Optional[Tuple[int, float]]:
         return self.rotary_dim, self.theta
 
+    def native(self):
+        if type(self) is not RotaryHalf:
+            return None
+        return NativeDesc("rotary_half", {"theta": self.theta, "rotary_dim": self.rotary_dim})
+
 
 @POSITION_ENCODINGS.register("none")
 class NoPositionEncoding(PositionEncoding):
@@ -35,3 +40,6 @@ class NoPositionEncoding(PositionEncoding):
 
     def fused_rotary(self) -> Optional[Tuple[int, float]]:
         return 0, 1.0
+
+    def native(self):
+        return NativeDesc("none") if type(self) is NoPositionEncoding else None

@@ -167,54 +167,90 @@ def test_many_requests_in_32_bit_are_identical_token_for_token(model_folders):
         assert alone.generate([p], max_new_tokens=30)[0].tokens == r.tokens, f"request {i}"
 
 
-def test_long_prompt_portions_replayed_as_graphs_equal_eager_steps(tmp_path):
-    """A portion of one request of a size seen before runs as a captured graph.  Three requests with the same
-    tokens in portions of 600 (logits wanted, not wanted, wanted): the first runs eagerly, the second captures, the
-    third only replays, at first positions 0, 600 and 1200; all logits equal the eager runner's bit for bit, and a
-    portion with other tokens through the same graphs differs."""
-    import torch
-    from mimirmind_b200.engine import runner as runner_mod
+def _wide_tiny_model(tmp_path, dtype, layers=2, hidden=256):
     from mimirmind_b200.engine.loader import load_model
+    from mimirmind_b200.weights import write_random_model
+    cfg = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=400, hidden_size=hidden, intermediate_size=352,
+               num_hidden_layers=layers, num_attention_heads=4, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
+               rope_theta=10000.0, max_position_embeddings=8192, tie_word_embeddings=False)
+    write_random_model(str(tmp_path), cfg, 21, dtype)
+    return load_model(str(tmp_path), dtype=dtype)[0]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_library_executor_equals_the_python_part_classes(tmp_path, dtype):
+    """A model whose parts all have native classes steps inside the library (one call per step); the same model with
+    the executor switched off steps through the Python part classes.  Both launch the same kernels of this library, so
+    mixed steps (a portion beside decoded tokens, portions of two requests, decoding alone) give equal logits: bit for
+    bit in float32 and for steps of at most 64 tokens in bfloat16 (own kernels only); where the plain products of
+    longer steps go to the library product (cuBLASLt here, through torch there) they agree to bfloat16 rounding."""
+    import torch
+    from mimirmind_b200.engine import native
     from mimirmind_b200.engine.runner import ModelRunner, StepEntry
     from mimirmind_b200.kernels import ops
-    from mimirmind_b200.weights import write_random_model
-    cfg = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=400, hidden_size=256, intermediate_size=352,
-               num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
-               rope_theta=10000.0, max_position_embeddings=4096, tie_word_embeddings=False)
-    write_random_model(str(tmp_path), cfg, 21, "bfloat16")
-    model, _ = load_model(str(tmp_path), dtype="bfloat16")
-    toks = random_tokens(400, 1800, 9)
-    other = random_tokens(400, 1800, 10)
+    model = _wide_tiny_model(tmp_path, dtype)
+    a, b, c = random_tokens(400, 700, 1), random_tokens(400, 300, 2), random_tokens(400, 90, 3)
+    steps = [
+        [("a", a[:600], [599])],                                   # a long portion alone
+        [("a", a[600:640], [0, 39]), ("b", b[:9], [8])],           # 49 tokens: the fused small-step kernels
+        [("a", a[640:641], [0]), ("b", b[9:10], [0]), ("c", c[:30], [29])],
+        [("b", b[10:300], [289]), ("c", c[30:90], []), ("a", a[641:642], [0])],   # two portions beside a decoded token
+        [("a", a[642:643], [0]), ("b", [7], [0]), ("c", [9], [0])],                # decoding only
+    ]
 
-    def run(runner, rid, tokens):
-        runner.add_request(rid)
-        a = runner.step([StepEntry(rid, tokens[:600], [599])])
-        b = runner.step([StepEntry(rid, tokens[600:1200], [])])
-        c = runner.step([StepEntry(rid, tokens[1200:], [599])])
-        runner.release(rid)
-        assert b is None
-        return a.cpu().numpy(), c.cpu().numpy()
+    def run(runner):
+        outs = []
+        for rid in "abc":
+            runner.add_request(rid)
+        for step in steps:
+            out = runner.step([StepEntry(r, t, w) for r, t, w in step])
+            outs.append(out.cpu().numpy())
+        runner.manager.check()
+        return outs
 
-    old = runner_mod.PREFILL_GRAPH_MIN_TOKENS
+    lib_runner = ModelRunner(model, 16, 256, 4, max_seq_len=4096)
+    assert lib_runner.native is not None
+    got = run(lib_runner)
+    assert lib_runner.native.steps() == len(steps)
+    old = native.ENABLED
     try:
-        runner_mod.PREFILL_GRAPH_MIN_TOKENS = 0
-        eager = ModelRunner(model, 16, 256, 4, max_seq_len=4096)
-        ref, ref_other = run(eager, "r", toks), run(eager, "o", other)
-        runner_mod.PREFILL_GRAPH_MIN_TOKENS = 512
-        graphs = ModelRunner(model, 16, 256, 4, max_seq_len=4096)
-        for i in range(3):
-            got = run(graphs, ("g", i), toks)
-            assert np.array_equal(got[0], ref[0]) and np.array_equal(got[1], ref[1]), i
-        sessions = graphs._prefill_sessions
-        assert set(sessions) == {(600, True), (600, False)}
-        assert all(s.graph is not None for s in sessions.values()) and sessions[(600, True)].runs == 5 and sessions[(600, False)].runs == 2
-        got = run(graphs, "x", other)
-        assert np.array_equal(got[0], ref_other[0]) and np.array_equal(got[1], ref_other[1])
-        assert not np.array_equal(got[1], ref[1])
-        graphs.manager.check()
-        ops.check_tcgen05_errors(torch.device("cuda"))
+        native.ENABLED = False
+        py_runner = ModelRunner(model, 16, 256, 4, max_seq_len=4096)
     finally:
-        runner_mod.PREFILL_GRAPH_MIN_TOKENS = old
+        native.ENABLED = old
+    assert py_runner.native is None
+    want = run(py_runner)
+    ops.check_tcgen05_errors(torch.device("cuda"))
+    for i, (g, w) in enumerate(zip(got, want)):
+        small = sum(len(t) for _, t, _ in steps[i]) <= 64
+        if dtype == "float32" or small:
+            assert np.array_equal(g, w), f"step {i}"
+        else:
+            assert np.abs(g - w).max() <= 2.0 ** -6 * np.abs(w).max(), f"step {i}"
+
+
+def test_portions_back_to_back_never_overtake_their_staging_buffers(tmp_path):
+    """Portions whose logits nobody reads are launched without the host ever waiting for the device, so the host runs
+    many steps ahead; every step's integers go through one of a few pinned buffers, which must not be rewritten before
+    the copy that reads it has run.  Twelve portions back to back and then the last one: its logits equal, bit for
+    bit, those of the same steps with a synchronisation after each."""
+    import torch
+    from mimirmind_b200.engine.runner import ModelRunner, StepEntry
+    model = _wide_tiny_model(tmp_path, "bfloat16", layers=8, hidden=1024)
+    toks = random_tokens(400, 13 * 256 + 40, 5)
+
+    def run(sync):
+        runner = ModelRunner(model, 16, 512, 2, max_seq_len=8192)
+        assert runner.native is not None
+        runner.add_request("r")
+        for i in range(13):
+            assert runner.step([StepEntry("r", toks[256 * i:256 * (i + 1)], [])]) is None
+            if sync:
+                torch.cuda.synchronize()
+        out = runner.step([StepEntry("r", toks[13 * 256:], [39])])
+        return out.cpu().numpy()
+
+    assert np.array_equal(run(False), run(True))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
