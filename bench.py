@@ -55,7 +55,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
         self.thread = threading.Thread(target=self._read, daemon=True)
@@ -141,7 +141,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed"],
                     help="run one phase only and print its timing (for profiling small cases)")
     ap.add_argument("--batch", type=int, default=BATCH, help="decode batch size of --only decode")
     ap.add_argument("--workload", default="", choices=["", "14b-serving", "32b-long"],
@@ -215,7 +215,7 @@ def main() -> int:
         runner.add_request(rid)
         return runner.step([StepEntry(rid, toks, [len(toks) - 1])])
 
-    for i in range(0 if args.only == "decode" else 3):
+    for i in range(0 if args.only in ("decode", "mixed") else 3):
         prefill_once(("warm", i), prompts[i])
         runner.release(("warm", i))
     torch.cuda.synchronize()
@@ -252,10 +252,11 @@ def main() -> int:
         before = kernel_lib.launch_count()
         sess.step()                                   # eager + capture: the step's kernels are launched twice
         per_step_calls = (kernel_lib.launch_count() - before) // 2
+        torch.cuda.synchronize()
+        mark = len(clocks.samples)                    # the clock record covers the warm-up replays too: the timed region may be shorter than a sample
         for _ in range(w_steps - 1):
             sess.step()
         torch.cuda.synchronize()
-        mark = len(clocks.samples)
         a, b = ev(), ev()
         a.record()
         for _ in range(k_steps):
@@ -268,6 +269,38 @@ def main() -> int:
             runner.release(r)
         return ms, per_step_calls, kv_tokens, mark
 
+    # ---- a mixed step, not captured: 8 decoded tokens beside a 192-token prompt portion ------------------
+    # The steady state of continuous batching.  "host_ms" is how long the call takes to return (the step is put
+    # together and every kernel launched); "ms" is the device time between events around it.
+    def mixed_run(k_steps):
+        ids = [("mix", i) for i in range(BATCH)]
+        for rid, toks in zip(ids, prompts[:BATCH]):
+            prefill_once(rid, toks)
+        runner.add_request("mix-long")
+        host, dev = [], []
+        for i in range(3 + k_steps):          # 192 * (3 + k_steps) tokens of the long prompt must exist
+            entries = [StepEntry(rid, [int(prompts[j][i])], [0]) for j, rid in enumerate(ids)]
+            entries.append(StepEntry("mix-long", prompts[BATCH][192 * i:192 * (i + 1)], []))
+            torch.cuda.synchronize()
+            a, b = ev(), ev()
+            t0 = time.perf_counter()
+            a.record()
+            runner.step(entries)
+            b.record()
+            t1 = time.perf_counter()
+            torch.cuda.synchronize()
+            if i >= 3:
+                host.append((t1 - t0) * 1e3)
+                dev.append(a.elapsed_time(b))
+        for rid in ids + ["mix-long"]:
+            runner.release(rid)
+        med = lambda v: sorted(v)[len(v) // 2]
+        return {"tokens": BATCH + 192, "decode_tokens": BATCH, "portion_tokens": 192, "ms": med(dev), "host_ms": med(host),
+                "steps": k_steps, "launched_by": "library executor" if runner.native is not None else "python parts"}
+    if args.only == "mixed":
+        clocks.stop()
+        print(json.dumps(dict(mixed_run(max(1, min(steps, 12))), only="mixed", layers=L)))
+        return 0
     if args.only == "prefill":
         clocks.stop()
         print(json.dumps({"only": "prefill", "ms": pf_ms, "tflops": prefill["tflops"], "layers": L}))
@@ -282,11 +315,16 @@ def main() -> int:
     value = BATCH / (ms8 * 1e-3)
     step_bytes = weight_bytes + kv_tokens * kv_bytes_per_token + BATCH * d * 2
     achieved = step_bytes / (ms8 * 1e-3) / 1e9
-    points = {}
+    points, point_rooflines = {}, {}
     if not args.no_points:
         for b, k in ((1, max(16, steps // 4)), (64, max(16, steps // 4))):
-            ms, _, _, _ = decode_run(b, k, warmup)
+            ms, _, kv_b, _ = decode_run(b, k, warmup)
             points[f"decode_b{b}"] = b / (ms * 1e-3)
+            nbytes = weight_bytes + kv_b * kv_bytes_per_token + b * d * 2
+            point_rooflines[f"decode_b{b}"] = {"ms_per_step": ms, "bytes_per_step": nbytes, "achieved": nbytes / (ms * 1e-3) / 1e9,
+                                               "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+
+    mixed = mixed_run(7)
 
     # ---- end to end: Engine.generate, host token lists in and out ------------------------------
     n_new = min(steps, 256) + 1
@@ -315,7 +353,7 @@ def main() -> int:
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / peaks["hbm_gbs"], "bytes_per_step": step_bytes, "peaks": peaks["source"]},
-        "points": points, "clocks": clock_summary,
+        "points": points, "point_rooflines": point_rooflines, "mixed": mixed, "clocks": clock_summary,
     }
     print(json.dumps(out))
     return 0

@@ -59,7 +59,11 @@ class DecodeSession:
             q_start=list(range(b)), q_len=[1] * b, kv_len=[self.kv_bound] * b, req_meta=None, state_slots=self.slots,
             block_tables=self.tables, logit_rows=ar, n_logit_rows=b, page_size=ps, runtime=runner.rt,
             max_kv_len=self.kv_bound, max_q_len=1)
-        self.out_tokens = torch.zeros(b, dtype=torch.int32, device=dev)
+        # the step's results in one buffer, so that one copy brings both to the host: the sampled tokens, then the flag
+        # that a kernel sets when it gave up a bounded wait (kernels.ops.tcgen05_error_flag)
+        self.out = torch.zeros(b + 1, dtype=torch.int32, device=dev)
+        self.out_tokens = self.out[:b]
+        self.error_flag = ops.tcgen05_error_flag(dev)
         self.logits: Optional[torch.Tensor] = None
         if not greedy:
             self.temperature = torch.zeros(b, dtype=torch.float32, device=dev)
@@ -151,8 +155,12 @@ class DecodeSession:
         if self.penalty_window > 0:
             ops.window_push(self.recent, self.widths, self.lengths, self.out_tokens)
         self.positions += 1
+        self.out[self.batch:].copy_(self.error_flag)
         if self.feed_back:
             self.token_ids.copy_(self.out_tokens)
+
+    def clear_error(self) -> None:
+        self.error_flag.zero_()
 
     def step(self) -> torch.Tensor:
         """One decode step for every bound request; returns the device tensor of sampled tokens (valid

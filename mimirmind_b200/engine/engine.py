@@ -15,6 +15,7 @@ from typing import Callable, Dict, Hashable, List, Optional, Sequence
 
 import torch
 
+from ..kernels.lib import KernelError
 from ..sampling import Sampler, SamplingParams
 from .decode_graph import DecodeSession, context_bound
 from .loader import load_model, random_model
@@ -173,7 +174,7 @@ class Engine:
         # still valid for the others; the stopped request's extra token is dropped.
         n = len(reqs)
         host_in = torch.empty(n, dtype=torch.int32, pin_memory=True)
-        host_out = [torch.empty(n, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        host_out = [torch.empty(n + 1, dtype=torch.int32, pin_memory=True) for _ in range(2)]    # the tokens and the kernels' error flag
         stream = torch.cuda.current_stream()
         alive = [True] * n
 
@@ -193,36 +194,45 @@ class Engine:
                     stop = True
             return stop
 
+        def tokens_of(buf) -> List[int]:
+            vals = buf.tolist()
+            if vals[n] != 0:                      # a kernel of that step gave up a bounded wait: its tokens are not valid
+                sess.clear_error()
+                raise KernelError("a kernel of the decode step gave up waiting on its pipeline; the step's output is not valid")
+            return vals[:n]
+
         cur = 0
         t_prev = time.perf_counter()
-        host_out[cur].copy_(sess.step(), non_blocking=True)
+        sess.step()
+        host_out[cur].copy_(sess.out, non_blocking=True)
         stream.synchronize()
         while True:
-            self.d2h_bytes += n * 4
+            self.d2h_bytes += (n + 1) * 4
             self.graph_steps += 1
             now = time.perf_counter()
             if self.decode_trace is not None:
                 self.decode_trace.step(n, (now - t_prev) * 1e3)
                 t_prev = now
-            toks = host_out[cur].tolist()
+            toks = tokens_of(host_out[cur])
             more = sess.remaining() > 0
             if more:
-                host_in.copy_(host_out[cur])
+                host_in.copy_(host_out[cur][:n])
                 sess.token_ids.copy_(host_in, non_blocking=True)      # next step's inputs, from pinned memory
                 self.h2d_bytes += n * 4
-                host_out[cur ^ 1].copy_(sess.step(), non_blocking=True)
+                sess.step()
+                host_out[cur ^ 1].copy_(sess.out, non_blocking=True)
             stop = account(toks, now)
             if not more:
                 break
             stream.synchronize()
             cur ^= 1
             if stop:
-                self.d2h_bytes += n * 4
+                self.d2h_bytes += (n + 1) * 4
                 self.graph_steps += 1
                 now = time.perf_counter()
                 if self.decode_trace is not None:
                     self.decode_trace.step(n, (now - t_prev) * 1e3)
-                account(host_out[cur].tolist(), now)
+                account(tokens_of(host_out[cur]), now)
                 break
         if self.decode_trace is not None:
             self.decode_trace.flush()
@@ -238,6 +248,7 @@ class Engine:
                                        [len(p.request.generated) for p in rows],
                                        [p.request.tokens for p in rows])
             host = toks.cpu().tolist()
+            self.runner.check_errors()        # the copy above waited for the step: a kernel that gave up fails the step
             self.d2h_bytes += 4 * len(host)
             for p, t in zip(rows, host):
                 sampled[p.request.id] = t

@@ -198,6 +198,17 @@ class ModelRunner:
         except native.StepRefused as e:
             raise StepError(str(e)) from None
 
+    def check_errors(self) -> None:
+        """To be called after the host has waited for a step's results (a copy of tokens or logits): raises if one of
+        the step's kernels gave up a bounded wait, since its output is then not valid.  With the library's executor
+        the flag came back with the step (no further synchronisation); otherwise it is read here."""
+        if self.native is not None:
+            if self.native.take_error_flag() == 0:
+                return
+            ops.tcgen05_error_flag(self.rt.device).zero_()
+            raise ops.KernelError("a kernel of the step gave up waiting on its pipeline; the step's output is not valid")
+        ops.check_tcgen05_errors(self.rt.device)
+
     def forward(self, ctx: StepContext, dump=None) -> Optional[torch.Tensor]:
         """The launches of a step whose context is on the device: by the library's executor, or part by part here."""
         if self.native is not None and dump is None and not ctx.plain_only:

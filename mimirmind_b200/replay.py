@@ -53,6 +53,7 @@ def main(argv=None) -> int:
         logits = runner.step(entries) if entries else None
         if logits is not None:
             host = logits.to(torch.float32).cpu().contiguous().numpy()
+            runner.check_errors()           # no file is written from the output of a kernel that gave up a wait
             tmp = os.path.join(args.out, f".{step}.f32.tmp")
             host.astype("<f4").tofile(tmp)
             os.replace(tmp, os.path.join(args.out, f"{step}.f32"))

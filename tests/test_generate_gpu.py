@@ -401,6 +401,57 @@ def test_a_step_that_fails_ends_its_requests_and_nothing_else(model_folders):
     assert eng.generate([prompts[0]], max_new_tokens=8, use_eos=False)[0].tokens == alone[0]
 
 
+@pytest.mark.parametrize("native_steps", [True, False])
+def test_a_kernel_that_gave_up_a_wait_fails_the_steps_requests(model_folders, native_steps):
+    """The kernels with bounded waits set a flag on the device when a wait runs out.  The flag comes back to the host with
+    every step's tokens; when it is set the step fails like any step that raised: its requests end with "error: ...",
+    their pages go back, the flag is cleared and the loop goes on.  No kernel is made to give up here: the test sets
+    the flag itself, before an eager step and before a captured decode step."""
+    import torch
+    from mimirmind_b200 import Engine
+    from mimirmind_b200.engine import native
+    from mimirmind_b200.kernels import ops
+    from mimirmind_b200.kernels.lib import KernelError
+    old = native.ENABLED
+    try:
+        native.ENABLED = native_steps
+        eng = Engine.from_folder(model_folders("D", "bfloat16"), dtype="bfloat16", cache_tokens=1024, max_context=256,
+                                 token_budget=64, max_active=2)
+    finally:
+        native.ENABLED = old
+    assert (eng.runner.native is not None) == native_steps
+    eng.graph_min_steps = 4
+    flag = ops.tcgen05_error_flag(torch.device("cuda", torch.cuda.current_device()))
+    prompts = [random_tokens(331, n, n) for n in (20, 30, 10)]
+    alone = [eng.generate([p], max_new_tokens=12, use_eos=False)[0].tokens for p in prompts]
+    # an eager step (two prompts in one step, the third waits)
+    loop = eng.serve()
+    h = [loop.submit(p, 12, use_eos=False) for p in prompts]
+    flag.fill_(1)
+    with pytest.raises(KernelError, match="gave up"):
+        loop.step()
+    assert int(flag.item()) == 0
+    assert loop.finished(h[0]) and loop.finished(h[1]) and not loop.finished(h[2])
+    assert loop.result(h[0]).stats.finish_reason.startswith("error: KernelError")
+    loop.run_until_idle()
+    assert loop.result(h[2]).tokens == alone[2]
+    assert eng.runner.manager.free_pages() == eng.runner.manager.total_pages()
+    # a captured decode step: the flag rides with the tokens of the step
+    loop = eng.serve()
+    h = [loop.submit(p, 12, use_eos=False) for p in prompts[:2]]
+    loop.step()                                   # both prompts, first tokens
+    assert loop.sched.all_decoding()
+    flag.fill_(1)
+    graph_steps = eng.graph_steps
+    with pytest.raises(KernelError, match="gave up"):
+        loop.step()
+    assert eng.graph_steps > graph_steps and int(flag.item()) == 0
+    assert all(loop.finished(x) and loop.result(x).stats.finish_reason.startswith("error: KernelError") for x in h)
+    assert eng.runner.manager.free_pages() == eng.runner.manager.total_pages()
+    again = eng.generate(prompts, max_new_tokens=12, use_eos=False)           # the engine is as usable as before
+    assert [r.stats.finish_reason for r in again] == ["length"] * 3 and again[0].tokens[:3] == alone[0][:3]
+
+
 def test_random_settings_many_engines_in_one_process(model_folders):
     """Engines come and go in one process, each with random batch, budget, pool, portion cap and sampling (greedy or
     sampled, with and without top-k, top-p and penalties); captured decode runs, preemption and admission interleave.
