@@ -7,7 +7,7 @@ In the reference's manner (src/core/config/Config.hpp:362-415, config.example.js
 ``diagnostics`` section; an unknown key is an error, not a warning.  Keys the reference has
 for servers, other backends, speculative decoding or host governors do not exist here.
 Ours, beside the reference's: ``runtime.dtype``, ``runtime.cacheTokens`` (size of the page
-pool in tokens), ``serving.prefillChunk``, and ``models[].random`` (a config.json object and
+pool in tokens; 0 sizes it from the free device memory, ``runtime.cacheMemoryFraction`` of it), ``serving.prefillChunk``, and ``models[].random`` (a config.json object and
 a seed instead of a path).
 """
 from __future__ import annotations
@@ -34,7 +34,9 @@ class ModelEntry:
 class RuntimeSettings:
     dtype: str = "bfloat16"
     maxContextTokens: int = 8192
-    cacheTokens: int = 0          # 0: maxContextTokens * serving.maxActiveRequests, capped by free memory
+    cacheTokens: int = 0          # size of the page pool in tokens; 0: what fits in cacheMemoryFraction of the free device
+                                  # memory once the weights are loaded, at most maxContextTokens * serving.maxActiveRequests
+    cacheMemoryFraction: float = 0.9
 
 
 @dataclass
@@ -87,6 +89,10 @@ def _fill(section: str, cls, obj: Any):
             raise EngineConfigError(f"'{section}.{k}' must be an integer")
         if want is str and not isinstance(v, str):
             raise EngineConfigError(f"'{section}.{k}' must be a string")
+        if want is float:
+            if isinstance(v, bool) or not isinstance(v, (int, float)):
+                raise EngineConfigError(f"'{section}.{k}' must be a number")
+            v = float(v)
         setattr(inst, k, v)
     return inst
 
@@ -133,6 +139,8 @@ def validate(cfg: EngineConfig) -> None:
         raise EngineConfigError("runtime.maxContextTokens must be positive")
     if r.cacheTokens < 0:
         raise EngineConfigError("runtime.cacheTokens must be >= 0")
+    if not (0.0 < r.cacheMemoryFraction <= 1.0):
+        raise EngineConfigError("runtime.cacheMemoryFraction must be in (0, 1]")
     ids = [m.id for m in cfg.models]
     if len(set(ids)) != len(ids):
         raise EngineConfigError("model ids must be unique")

@@ -45,11 +45,12 @@ class GenerateResult:
 
 class Engine:
     def __init__(self, model: Model, *, page_size: int = 16, cache_tokens: int = 0, max_context: int = 8192,
-                 token_budget: int = 512, max_active: int = 32, prefill_chunk: int = 0, use_graphs: bool = True):
+                 token_budget: int = 512, max_active: int = 32, prefill_chunk: int = 0, use_graphs: bool = True,
+                 cache_memory_fraction: float = 0.9):
         self.model = model
         max_context = min(max_context, model.spec.max_positions)
         if cache_tokens <= 0:
-            cache_tokens = max_context * min(max_active, 4)
+            cache_tokens = self.cache_tokens_that_fit(model, page_size, max_context, token_budget, max_active, cache_memory_fraction)
         num_pages = (cache_tokens + page_size - 1) // page_size
         self.runner = ModelRunner(model, page_size=page_size, num_pages=num_pages, max_requests=max_active,
                                   max_seq_len=max_context)
@@ -66,6 +67,20 @@ class Engine:
         self.h2d_bytes = 0                  # bytes copied host→device / device→host by generate()
         self.d2h_bytes = 0
         self.decode_trace = None            # engine.diagnostics.DecodeTrace: a line per decode step
+
+    @staticmethod
+    def cache_tokens_that_fit(model: Model, page_size: int, max_context: int, token_budget: int, max_active: int,
+                              fraction: float) -> int:
+        """The pool size when none is configured: what fits in ``fraction`` of the device memory that is free now
+        (the weights are loaded), less what a step of ``token_budget`` tokens needs, at most
+        ``max_context x max_active`` tokens."""
+        from ..cache import sizing
+        from ..weights.store import layer_tensor_shapes
+        esz = 4 if model.rt.dtype == torch.float32 else 2
+        shapes = layer_tensor_shapes(model.spec)
+        free, _total = torch.cuda.mem_get_info(model.rt.device)
+        return sizing.pool_tokens(free, fraction, sizing.step_reserve_bytes(model.spec, shapes, esz, token_budget, max_active),
+                                  sizing.cache_bytes_per_token(model.cache_groups(), esz), page_size, max_context, max_active)
 
     def set_diagnostics(self, parity_dump: str = "", trace_decode_file: str = "") -> None:
         """Stage dumps of the steps that hold a prompt portion (file prefix) and a per-step decode trace (file)."""
@@ -94,7 +109,8 @@ class Engine:
             model, _ = load_model(entry.path, cfg.runtime.dtype)
         eng = cls(model, page_size=cfg.serving.blockSize, cache_tokens=cfg.runtime.cacheTokens,
                   max_context=cfg.runtime.maxContextTokens, token_budget=cfg.serving.tokenBudget,
-                  max_active=cfg.serving.maxActiveRequests, prefill_chunk=cfg.serving.prefillChunk)
+                  max_active=cfg.serving.maxActiveRequests, prefill_chunk=cfg.serving.prefillChunk,
+                  cache_memory_fraction=cfg.runtime.cacheMemoryFraction)
         if cfg.diagnostics.parityDump or cfg.diagnostics.traceDecodeFile:
             eng.set_diagnostics(cfg.diagnostics.parityDump, cfg.diagnostics.traceDecodeFile)
         return eng

@@ -51,6 +51,17 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
     return out
 
 
+def layer_tensor_shapes(spec: ModelSpec):
+    """Per layer, the shapes of the tensors its parts declare (for estimates of a step's working memory)."""
+    out = []
+    for layer in spec.layers:
+        specs = []
+        for reg, part in ((NORMS, layer.mixer_norm), (MIXERS, layer.mixer), (NORMS, layer.ffn_norm), (FEED_FORWARDS, layer.feed_forward)):
+            specs += reg.get(part.kind).tensor_specs(part, layer.prefix)
+        out.append([tuple(ts.shape) for ts in specs])
+    return out
+
+
 def check_names_and_shapes(have: Dict[str, Tuple[int, ...]], want: Dict[str, TensorSpec], where: str) -> None:
     missing = [n for n, ts in want.items() if n not in have and not ts.optional]
     unexpected = [n for n in have if n not in want]

@@ -47,8 +47,12 @@ TINY = {
                num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6, rope_theta=10000.0,
                max_position_embeddings=2048, tie_word_embeddings=True, use_sliding_window=True, sliding_window=100,
                max_window_layers=0),
+    # the second tiny configuration of the baseline's list as it is written there: B without a window, context 256
+    "F": _base(vocab_size=384, hidden_size=192, intermediate_size=352, num_hidden_layers=3, num_attention_heads=6,
+               num_key_value_heads=1, head_dim=32, rms_norm_eps=1e-5, rope_theta=1000000.0,
+               max_position_embeddings=256, tie_word_embeddings=False, use_sliding_window=False),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 1}
 
 
 @pytest.fixture(scope="session")

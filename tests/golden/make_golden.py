@@ -9,7 +9,9 @@ logits and final hidden state as float32.  ``test_plain_vs_golden.py`` regenerat
 weights from the seed and compares the plain implementation with these files.
 
 The reference's block has no sliding window for this architecture
-(src/runtime/arch/Qwen2Backend.cpp:424), so the golden configurations have none.
+(src/runtime/arch/Qwen2Backend.cpp:424), so the golden configurations have none; its attention function has one
+(src/compute/Attention.cpp:46-50), and ``golden_attention.npz`` holds its outputs for direct calls with a window
+and a position offset.
 
     python tests/golden/make_golden.py --reference /path/to/mimirmind
 """
@@ -27,7 +29,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 sys.path.insert(0, os.path.dirname(HERE))
 
-from golden_configs import GOLDEN  # noqa: E402
+from golden_configs import GOLDEN, GOLDEN_ATTENTION, attention_inputs  # noqa: E402
 
 SOURCES = [
     "runtime/arch/Qwen2Backend.cpp", "runtime/KvCache.cpp", "runtime/BlockBuffers.cpp", "compute/cpu/GpuOps.cpp",
@@ -89,6 +91,20 @@ def main() -> None:
             np.savez_compressed(os.path.join(HERE, name + ".npz"), tokens=tokens, logits=logits, hidden=hidden)
             ours = plain.forward(m, tokens.tolist())
             print(name, "max|plain - reference| =", float(np.abs(ours - logits).max()), "max|logit| =", float(np.abs(logits).max()))
+        outs = {}
+        for i, case in enumerate(GOLDEN_ATTENTION):
+            q, k, v = attention_inputs(case)
+            inp, outp = os.path.join(tmp, f"att{i}.in"), os.path.join(tmp, f"att{i}.out")
+            with open(inp, "wb") as f:
+                f.write(struct.pack("<7I", case["Tq"], case["Tk"], case["H"], case["G"], case["hd"], case["offset"], case["window"]))
+                f.write(q.astype("<f4").tobytes() + k.astype("<f4").tobytes() + v.astype("<f4").tobytes())
+            subprocess.run([exe, "--attention", inp, outp], check=True)
+            outs[f"case{i}"] = np.fromfile(outp, dtype="<f4").reshape(case["Tq"], case["H"], case["hd"])
+            full = np.zeros((case["Tk"], case["H"], case["hd"]))
+            full[case["offset"]:case["offset"] + case["Tq"]] = q
+            ours = plain.attention(full, k.astype(np.float64), v.astype(np.float64), case["window"])[case["offset"]:case["offset"] + case["Tq"]]
+            print(f"attention case {i}: max|plain - reference| =", float(np.abs(ours - outs[f'case{i}']).max()))
+        np.savez_compressed(os.path.join(HERE, "golden_attention.npz"), **outs)
 
 
 if __name__ == "__main__":

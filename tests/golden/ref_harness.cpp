@@ -3,6 +3,11 @@
 // a flat binary file, and writes the logits of every position.  Built and run only by
 // make_golden.py; the tests read the committed outputs, never this program.
 //
+// A second mode, `ref_harness --attention IN OUT`, calls the reference's compute::multiHeadAttention
+// (src/compute/Attention.cpp:15-104) directly, with a sliding window and a position offset, which the block of this
+// architecture never passes: IN is u32 Tq,Tk,H,G,hd,offset,window; f32 q[Tq*H*hd], k[Tk*G*hd], v[Tk*G*hd]; OUT is
+// f32 out[Tq*H*hd].
+//
 // Input file:  u32 L,d,F,H,G,hd,V,T,tied; f32 eps,theta; i32 tokens[T];
 //              then f32 tensors in the order written by make_golden.py.
 // Output file: f32 logits[T*V], then f32 hidden[T*d] (the residual stream after the last block).
@@ -15,6 +20,7 @@
 #include "compute/Embedding.hpp"
 #include "compute/Norm.hpp"
 #include "compute/Matmul.hpp"
+#include "compute/Attention.hpp"
 #include "core/cpu/CpuContext.hpp"
 #include "core/gguf/WeightsMap.hpp"
 #include "model/LlmConfig.hpp"
@@ -29,7 +35,26 @@ using namespace mimirmind;
 // nullptr below, so this definition is never reached.
 const model::FusedQkvWeights::Block* model::FusedQkvWeights::find(std::size_t) const noexcept { return nullptr; }
 
+static int attention_mode(const char* in, const char* out) {
+    FILE* f = std::fopen(in, "rb");
+    if (!f) return 3;
+    std::uint32_t h[7];
+    if (std::fread(h, 4, 7, f) != 7) return 4;
+    const std::size_t Tq = h[0], Tk = h[1], H = h[2], G = h[3], hd = h[4], offset = h[5], window = h[6];
+    std::vector<float> q(Tq * H * hd), k(Tk * G * hd), v(Tk * G * hd), o(Tq * H * hd), scratch(Tk);
+    if (std::fread(q.data(), 4, q.size(), f) != q.size() || std::fread(k.data(), 4, k.size(), f) != k.size() ||
+        std::fread(v.data(), 4, v.size(), f) != v.size()) return 4;
+    std::fclose(f);
+    compute::multiHeadAttention(q.data(), k.data(), v.data(), Tq, Tk, H, G, hd, offset, scratch.data(), o.data(), window);
+    FILE* w = std::fopen(out, "wb");
+    std::fwrite(o.data(), 4, o.size(), w);
+    std::fclose(w);
+    std::printf("ok attention Tq=%zu Tk=%zu window=%zu offset=%zu\n", Tq, Tk, window, offset);
+    return 0;
+}
+
 int main(int argc, char** argv) {
+    if (argc == 4 && std::string(argv[1]) == "--attention") return attention_mode(argv[2], argv[3]);
     if (argc != 3) { std::fprintf(stderr, "usage: ref_harness IN OUT\n"); return 2; }
     FILE* f = std::fopen(argv[1], "rb");
     if (!f) return 3;

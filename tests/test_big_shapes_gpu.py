@@ -1,68 +1,86 @@
-"""The kernels that only large shapes reach (weight-streaming products with 8 row tiles per CTA, the tcgen05
-product with the SwiGLU epilogue, tcgen05 prefill attention, split-key decode attention over thousands of keys,
-decode as a replayed graph) inside the whole engine: one layer with the widths of the benchmark model, bfloat16
-against the engine's own 32-bit path on the same weights (that path is checked against the plain implementation
-on the tiny models)."""
+"""The widths of the benchmark models against the plain implementation.
+
+The tiny configurations never reach the kernels that only large shapes use: weight-streaming products with 8 row
+tiles per CTA, the tcgen05 products with many tiles per CTA pair, K splits over clusters, the head over a wide
+vocabulary.  Here one layer with the widths of the 7B-shaped model, one with those of the 14B-shaped one and one
+with the feed-forward width of the 32B-shaped one (40 query heads over 8 KV heads: 5 per group) run every way of
+cutting the replay test has (whole, last 32 tokens one by one, portions of changing size down to two tokens, mixed
+with up to four live requests in the smallest pool, pages used again), in float32 and bfloat16, every returned
+row against ``tests/plain_qwen2.py`` (numpy float64 on the same weights); float32 bit-equal between the cuttings.
+"""
 import numpy as np
 import pytest
 import torch
 
 from conftest import random_tokens
+from test_replay_gpu import every_way_of_cutting
 
 pytestmark = pytest.mark.gpu
 
-WIDE = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=2048, hidden_size=3584, intermediate_size=18944,
-            num_hidden_layers=1, num_attention_heads=28, num_key_value_heads=4, head_dim=128, rms_norm_eps=1e-6,
-            rope_theta=1000000.0, max_position_embeddings=4096, tie_word_embeddings=False)
+
+def _cfg(hidden, heads, kv_heads, intermediate, vocab, eps):
+    return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=vocab, hidden_size=hidden, intermediate_size=intermediate,
+                num_hidden_layers=1, num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=128, rms_norm_eps=eps,
+                rope_theta=1000000.0, max_position_embeddings=4096, tie_word_embeddings=False)
+
+
+SHAPES = {
+    "7b": (_cfg(3584, 28, 4, 18944, 8192, 1e-6), 5, [40, 300, 700]),
+    "14b": (_cfg(5120, 40, 8, 13824, 8200, 1e-5), 6, [33, 270, 520]),
+    "32b": (_cfg(5120, 40, 8, 27648, 8192, 1e-6), 7, [17, 290]),
+}
+_folders = {}
 
 
 @pytest.fixture(scope="module")
-def wide_folder(tmp_path_factory):
+def wide_folders(tmp_path_factory):
     from mimirmind_b200.weights import write_random_model
-    d = tmp_path_factory.mktemp("wide")
-    write_random_model(str(d), WIDE, 5, "bfloat16")
-    return str(d)
+
+    def get(name, dtype):
+        if (name, dtype) not in _folders:
+            d = tmp_path_factory.mktemp(f"wide_{name}_{dtype}")
+            write_random_model(str(d), SHAPES[name][0], SHAPES[name][1], dtype)
+            _folders[(name, dtype)] = str(d)
+        return _folders[(name, dtype)]
+    return get
 
 
-def run_steps(folder, dtype, cuts, toks):
-    from mimirmind_b200.engine.loader import load_model
-    from mimirmind_b200.engine.runner import ModelRunner, StepEntry
+@pytest.mark.parametrize("name,dtype", [("7b", "float32"), ("7b", "bfloat16"), ("14b", "float32"), ("14b", "bfloat16"), ("32b", "bfloat16")])
+def test_wide_layers_every_way_of_cutting_against_the_plain_implementation(name, dtype, wide_folders):
+    import plain_qwen2 as plain
     from mimirmind_b200.kernels import ops
-    model, _ = load_model(folder, dtype)
-    runner = ModelRunner(model, 16, 4096 // 16, 4)
-    runner.add_request("a")
-    outs, p = [], 0
-    for c in cuts:
-        want = [c - 1]
-        outs.append(runner.step([StepEntry("a", toks[p:p + c], want)]).float().cpu().numpy())
-        p += c
-    ops.check_tcgen05_errors(model.rt.device)
-    del runner, model
+    folder = wide_folders(name, dtype)
+    pm = plain.PlainModel(folder)
+    reqs = {f"{name}{i}": random_tokens(pm.V, n, 31 * i + n) for i, n in enumerate(SHAPES[name][2])}
+    ref = {rid: pm.logits(t) for rid, t in reqs.items()}
+    del pm
+    every_way_of_cutting(folder, dtype, reqs, ref, seed=11)
+    ops.check_tcgen05_errors(torch.device("cuda"))
     torch.cuda.empty_cache()
-    return np.concatenate(outs)
 
 
-def test_wide_layer_bf16_kernels_agree_with_the_32_bit_path(wide_folder):
-    toks = random_tokens(2048, 1500 + 40, 9)
-    # a 1,500-token portion (tcgen05 product and attention), a 24-token portion, then single tokens (streaming products)
-    cuts = [1500, 24] + [1] * 16
-    ref = run_steps(wide_folder, "float32", cuts, toks)
-    got = run_steps(wide_folder, "bfloat16", cuts, toks)
-    scale = np.abs(ref).max()
-    err = np.abs(got - ref)
-    assert err.max() <= 4e-2 * scale, f"max error {err.max():.4f} of scale {scale:.3f} at row {err.max(axis=1).argmax()}"
-    assert err.mean() <= 6e-3 * scale
-
-
-def test_wide_layer_graph_decode_equals_eager_decode(wide_folder):
+def test_wide_layer_graph_decode_equals_eager_decode(wide_folders):
     from mimirmind_b200 import Engine
-    prompts = [random_tokens(2048, n, n) for n in (700, 33, 1200)]
-    eager = Engine.from_folder(wide_folder, dtype="bfloat16", cache_tokens=8192, max_context=2048, token_budget=2048, max_active=4, use_graphs=False)
+    folder = wide_folders("7b", "bfloat16")
+    prompts = [random_tokens(8192, n, n) for n in (700, 33, 1200)]
+    eager = Engine.from_folder(folder, dtype="bfloat16", cache_tokens=8192, max_context=2048, token_budget=2048, max_active=4, use_graphs=False)
     a = eager.generate(prompts, max_new_tokens=24)
     del eager
     torch.cuda.empty_cache()
-    graphs = Engine.from_folder(wide_folder, dtype="bfloat16", cache_tokens=8192, max_context=2048, token_budget=2048, max_active=4, use_graphs=True)
+    graphs = Engine.from_folder(folder, dtype="bfloat16", cache_tokens=8192, max_context=2048, token_budget=2048, max_active=4, use_graphs=True)
     b = graphs.generate(prompts, max_new_tokens=24)
     assert graphs.graph_steps > 0
     # same kernels on the same inputs: the replayed graph gives the same tokens as stepping eagerly
     assert [r.tokens for r in a] == [r.tokens for r in b]
+
+
+def test_the_pool_is_sized_from_the_device_when_nothing_is_configured(wide_folders):
+    """With no cache size given the pool takes what the free memory allows, at most every active request at the full
+    context: on this GPU, with one layer of the 7B width, that cap (32 requests of 4,096 tokens) is reached, so a full
+    house never preempts."""
+    from mimirmind_b200 import Engine
+    eng = Engine.from_folder(wide_folders("7b", "bfloat16"), dtype="bfloat16", max_context=4096, token_budget=512, max_active=32)
+    mgr = eng.runner.manager
+    assert mgr.total_pages() * mgr.page_size == 32 * 4096
+    free, _ = torch.cuda.mem_get_info()
+    assert free > 0

@@ -68,6 +68,29 @@ def test_chunked_mixed_temperature_run_is_seeded_and_batch_independent(model_fol
         toks.append(tok)
 
 
+def test_the_baselines_second_tiny_workload_as_written(model_folders, plain_models):
+    """The baseline's second tiny configuration as it stands there (no window, context 256): six requests with prompts
+    of 1, 9, 40, 77, 128 and 200 tokens, prompt portions of 32 beside decoding, 24 tokens each at temperature 0.8 with
+    fixed seeds, in float32.  Every sampled token of every request is the one the plain sampler draws from the plain
+    implementation's logits for the same history."""
+    from mimirmind_b200 import Engine, SamplingParams
+    pm = plain_models("F", "float32")
+    prompts = [random_tokens(pm.V, n, 7 * n + 1) for n in (1, 9, 40, 77, 128, 200)]
+    sp = [SamplingParams(temperature=0.8, seed=4000 + i) for i in range(6)]
+    eng = Engine.from_folder(model_folders("F", "float32"), dtype="float32", page_size=16, max_context=256, cache_tokens=6 * 256,
+                             token_budget=64, max_active=6, prefill_chunk=32)
+    res = eng.generate(prompts, max_new_tokens=24, sampling=sp, use_eos=False)
+    assert eng.last_metrics.steps > 12                      # portions of 32 under a budget of 64: the prompts took many steps
+    for i, (p, r) in enumerate(zip(prompts, res)):
+        assert r.stats.finish_reason == "length" and len(r.tokens) == 24
+        toks = list(p)
+        for step, tok in enumerate(r.tokens):
+            row = pm.logits(toks)[-1]
+            assert tok == plain.sample(row, 0.8, 0, 1.0, plain.uniform_from(4000 + i, step)), f"request {i}, token {step}"
+            toks.append(tok)
+    assert eng.runner.manager.free_pages() == eng.runner.manager.total_pages()
+
+
 def test_running_out_of_pages_changes_no_output(model_folders):
     from mimirmind_b200 import Engine
     folder = model_folders("A", "float32")

@@ -328,7 +328,7 @@ def run_bf16_attention(case, H, G, hd, ps, window, prefill_min=None, split=None,
     return out, plan
 
 
-@pytest.mark.parametrize("H,G,hd,ps", [(7, 1, 128, 16), (8, 2, 64, 32), (28, 4, 128, 16), (16, 1, 64, 8), (3, 3, 128, 64)])
+@pytest.mark.parametrize("H,G,hd,ps", [(7, 1, 128, 16), (8, 2, 64, 32), (28, 4, 128, 16), (16, 1, 64, 8), (3, 3, 128, 64), (40, 8, 128, 16)])
 @pytest.mark.parametrize("window", [0, 100])
 def test_attention_tensor_core_kernels(H, G, hd, ps, window):
     rng = np.random.RandomState(H * 3 + hd + window)
@@ -348,7 +348,8 @@ def test_attention_tensor_core_kernels(H, G, hd, ps, window):
     assert plan.n_tiles > 0 and plan.n_items == 0                  # the last run was all tiles
 
 
-@pytest.mark.parametrize("H,G,hd,ps,n,size", [(28, 4, 128, 16, 8, 8), (28, 4, 128, 16, 16, 4), (28, 4, 128, 16, 30, 2), (8, 2, 64, 32, 16, 8), (6, 2, 64, 8, 32, 4)])
+@pytest.mark.parametrize("H,G,hd,ps,n,size", [(28, 4, 128, 16, 8, 8), (28, 4, 128, 16, 16, 4), (28, 4, 128, 16, 30, 2), (8, 2, 64, 32, 16, 8), (6, 2, 64, 8, 32, 4),
+                                              (40, 8, 128, 16, 8, 4)])
 @pytest.mark.parametrize("window", [0, 100])
 def test_attention_decode_cluster_merge(H, G, hd, ps, n, size, window):
     """Single tokens of n requests: the splits of a token are a thread-block cluster that merges its partial results
@@ -374,6 +375,42 @@ def test_attention_decode_cluster_merge(H, G, hd, ps, n, size, window):
         ab.USE_CLUSTER_MERGE = old
     assert not plan2.cluster and plan2.part_o is not None
     assert np.abs(out2.float().cpu().numpy() - out.float().cpu().numpy()).max() <= 2 ** -7 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("n_keys", [4096, 8192])
+@pytest.mark.parametrize("far", ["first tile", "page edge"])
+def test_attention_over_thousands_of_keys(n_keys, far):
+    """One KV head with five query heads (the group of the 14B- and 32B-shaped models), head size 128, thousands of
+    cached keys: the tcgen05 prefill kernel over 32 and 64 key tiles (every slot of its rings many times, both softmax
+    groups, the lazy rescale when the dominant key comes late in the loop) and the split-key decode kernel as a cluster
+    of 8 and as 32 and more splits with the merge kernel.  The dominant key sits in the first tile, or at the last slot
+    of a page in the middle of the context."""
+    H, G, hd, ps = 5, 1, 128, 16
+    rng = np.random.RandomState(n_keys // 1000 + len(far))
+    kpos = 5 if far == "first tile" else (n_keys // 2 // ps) * ps + ps - 1
+    # a portion of 300 queries at the end of the context (three tiles of the prefill kernel); the last query is spiked
+    case = make_attention_case(rng, H, G, hd, ps, [n_keys], [300], torch.bfloat16, spike=(0, 299, kpos, H - 1))
+    ref = attention_reference(case, 0)
+    assert abs(ref[299, H - 1, 0] - 50.0) < 1.0
+    out, plan = run_bf16_attention(case, H, G, hd, ps, 0, prefill_min=1)
+    assert plan.n_tiles == 3 and plan.tile_rows == 128
+    err = np.abs(out.float().cpu().numpy().reshape(ref.shape) - ref)
+    assert err.max() <= 2.5 * 2 ** -8 * np.abs(ref).max(), np.unravel_index(err.argmax(), err.shape)
+    # the last 16 of these queries token by token through the decode kernel: the splits of a token as a cluster of 8,
+    # and through scratch memory and the merge kernel with 32 splits and more
+    dec = dict(case, q=case["q"][-16:].contiguous(), pos=case["pos"][-16:].contiguous(), req=case["req"][-16:].contiguous(), q_lens=[16])
+    for kwargs, cluster in ((dict(prefill_min=10 ** 6, target=8 * 16), True), (dict(prefill_min=10 ** 6, target=64 * 16), False),
+                            (dict(prefill_min=10 ** 6, split=128), False)):
+        out, plan = run_bf16_attention(dec, H, G, hd, ps, 0, **kwargs)
+        assert plan.n_items == 16 and plan.cluster == cluster and (plan.max_splits == 8 if cluster else plan.max_splits >= 32)
+        err = np.abs(out.float().cpu().numpy().reshape(16, H, hd) - ref[-16:])
+        assert err.max() <= 2.5 * 2 ** -8 * np.abs(ref).max(), (kwargs, np.unravel_index(err.argmax(), err.shape))
+    # one token alone over the whole context: the schedule of a decode step at batch 1
+    single = make_attention_case(rng, H, G, hd, ps, [n_keys], [1], torch.bfloat16, spike=(0, 0, kpos, 2))
+    ref1 = attention_reference(single, 0)
+    out, plan = run_bf16_attention(single, H, G, hd, ps, 0)
+    assert plan.max_splits >= 64 and not plan.cluster
+    assert np.abs(out.float().cpu().numpy().reshape(ref1.shape) - ref1).max() <= 2.5 * 2 ** -8 * np.abs(ref1).max()
 
 
 def test_attention_window_edge_is_exact():

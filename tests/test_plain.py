@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 import plain_qwen2 as plain
-from golden.golden_configs import GOLDEN
+from golden.golden_configs import GOLDEN, GOLDEN_ATTENTION, attention_inputs
 
 GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
@@ -24,6 +24,21 @@ def test_plain_matches_reference_cpu_code(name, tmp_path):
     assert np.abs(logits - z["logits"]).max() < 2e-6 * max(scale, 1.0)
     assert np.abs(hidden[-1] - z["hidden"]).max() < 2e-6 * max(np.abs(z["hidden"]).max(), 1.0)
     assert [plain.greedy(r) for r in logits.astype(np.float32)] == [int(np.argmax(r)) for r in z["logits"]]
+
+
+@pytest.mark.parametrize("i", range(len(GOLDEN_ATTENTION)))
+def test_plain_attention_window_matches_the_reference_function(i):
+    """The sliding window and the position offset of the reference's own attention function
+    (src/compute/Attention.cpp:46-50), which its block for this architecture never passes: a query at absolute
+    position a sees keys [max(0, a + 1 - W), a].  Committed outputs of direct calls, four cases."""
+    case = GOLDEN_ATTENTION[i]
+    want = np.load(os.path.join(GOLDEN_DIR, "golden_attention.npz"))[f"case{i}"]
+    q, k, v = attention_inputs(case)
+    lo, hi = case["offset"], case["offset"] + case["Tq"]
+    full = np.zeros((case["Tk"], case["H"], case["hd"]))       # the plain function takes whole sequences: rows before the queries are unused
+    full[lo:hi] = q
+    got = plain.attention(full, k.astype(np.float64), v.astype(np.float64), case["window"])[lo:hi]
+    assert want.shape == got.shape and np.abs(got - want).max() < 5e-7
 
 
 def test_rms_norm_formula():

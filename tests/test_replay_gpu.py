@@ -13,7 +13,8 @@ pytestmark = pytest.mark.gpu
 # against float64; bfloat16 rounds activations to 8 bits of mantissa between the kernels.
 TOL = {"float32": dict(max_abs=3e-5, mean_abs=3e-6), "bfloat16": dict(max_abs=4e-2, mean_abs=6e-3)}
 
-LENGTHS = {"A": [5, 70, 133, 260], "B": [1, 9, 77, 300], "C": [33, 64, 150], "D": [40, 129, 257], "E": [17, 230, 301]}
+LENGTHS = {"A": [5, 70, 133, 260], "B": [1, 9, 77, 300], "C": [33, 64, 150], "D": [40, 129, 257], "E": [17, 230, 301],
+           "F": [1, 9, 40, 77, 128, 200]}
 
 
 def requests_for(name, plain_model):
@@ -36,39 +37,35 @@ def check(trace, outputs, reqs, ref, dtype, what):
     return got
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", sorted(TINY))
-def test_every_way_of_cutting_matches_the_plain_implementation(name, dtype, model_folders, plain_models):
-    folder = model_folders(name, dtype)
-    pm = plain_models(name, dtype)
-    reqs = requests_for(name, pm)
-    ref = {rid: pm.logits(t) for rid, t in reqs.items()}
-
+def every_way_of_cutting(folder, dtype, reqs, ref, page_size=16, seed=7):
+    """The same requests whole, with the last 32 tokens one by one, in portions of changing size and mixed with
+    each other (each request twice, up to four live, in the smallest pool that holds them), every returned row
+    against ``ref``; in float32 every cutting must give the whole run's rows bit for bit."""
     results = {}
     # each request alone and whole
     t = ru.Trace()
     for rid, toks in reqs.items():
         ru.whole(t, rid, toks)
-    out, _ = ru.run_in_process(folder, dtype, t, t.max_live_tokens())
+    out, _ = ru.run_in_process(folder, dtype, t, t.max_live_tokens(), page_size)
     results["whole"] = check(t, out, reqs, ref, dtype, "whole")
     # most of it in one step, the last 32 tokens one by one
     t = ru.Trace()
     for rid, toks in reqs.items():
         ru.tail_one_by_one(t, rid, toks, 32)
-    out, _ = ru.run_in_process(folder, dtype, t, t.max_live_tokens())
+    out, _ = ru.run_in_process(folder, dtype, t, t.max_live_tokens(), page_size)
     results["tail"] = check(t, out, reqs, ref, dtype, "tail one by one")
     # portions of changing size, down to two tokens
     t = ru.Trace()
     for i, (rid, toks) in enumerate(reqs.items()):
         ru.chunks(t, rid, toks, [[17, 7, 5, 3, 2], [2, 64, 3, 31], [33, 2, 2, 16]][i % 3])
-    out, _ = ru.run_in_process(folder, dtype, t, t.max_live_tokens())
+    out, _ = ru.run_in_process(folder, dtype, t, t.max_live_tokens(), page_size)
     results["chunks"] = check(t, out, reqs, ref, dtype, "portions")
     # mixed, up to four live, in the smallest pool that holds them: pages are used again
     t = ru.Trace()
     twice = dict(reqs)
     twice.update({rid + "x": toks for rid, toks in reqs.items()})       # the same requests a second time, later
-    ru.mixed(t, twice, seed=len(name) + 7)
-    out, runner = ru.run_in_process(folder, dtype, t, t.max_live_tokens())
+    ru.mixed(t, twice, seed=seed)
+    out, runner = ru.run_in_process(folder, dtype, t, t.max_live_tokens(), page_size)
     ref2 = dict(ref)
     ref2.update({rid + "x": ref[rid] for rid in reqs})
     results["mixed"] = check(t, out, twice, ref2, dtype, "mixed")
@@ -84,6 +81,27 @@ def test_every_way_of_cutting_matches_the_plain_implementation(name, dtype, mode
         for rid in reqs:
             for p in range(len(reqs[rid])):
                 assert np.array_equal(results["mixed"][(rid + "x", p)], results["whole"][(rid, p)])
+    return results
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_every_way_of_cutting_matches_the_plain_implementation(name, dtype, model_folders, plain_models):
+    pm = plain_models(name, dtype)
+    reqs = requests_for(name, pm)
+    ref = {rid: pm.logits(t) for rid, t in reqs.items()}
+    every_way_of_cutting(model_folders(name, dtype), dtype, reqs, ref, seed=len(name) + 7)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page_size", [("D", 8), ("B", 32), ("E", 64), ("A", 8)])
+def test_every_way_of_cutting_at_other_page_sizes(name, page_size, dtype, model_folders, plain_models):
+    """The engine's other page sizes (8, 32, 64): a window over pages of 32 and 64, head sizes 128 and 64 on the
+    tensor-core kernels, the generic kernel at 16 and 32."""
+    pm = plain_models(name, dtype)
+    reqs = requests_for(name, pm)
+    ref = {rid: pm.logits(t) for rid, t in reqs.items()}
+    every_way_of_cutting(model_folders(name, dtype), dtype, reqs, ref, page_size=page_size, seed=page_size)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
