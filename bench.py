@@ -113,8 +113,8 @@ def run_workload(name: str, layers: int) -> int:
     engine = Engine(model, page_size=PAGE_SIZE, cache_tokens=sum(lens) + len(lens) * (new + 64), max_context=ctx,
                     token_budget=2048, max_active=64)
     prompts = [rng.randint(0, mcfg.vocab_size, size=n).tolist() for n in lens]
-    # the first run also captures the CUDA graphs of the decode batches and of the repeated prompt portions (about a
-    # tenth of a second each); the second run is the steady state of a serving process
+    # the first run also captures the CUDA graphs of the decode batches (about a tenth of a second each); the second
+    # run is the steady state of a serving process
     times = []
     for _ in range(2):
         torch.cuda.synchronize()
@@ -125,12 +125,36 @@ def run_workload(name: str, layers: int) -> int:
     dt = times[1]
     ops.check_tcgen05_errors(torch.device("cuda"))
     gen = sum(r.stats.generated_tokens for r in res)
+    # What was timed is checked.  The shortest and the longest request are run again, alone and whole in one step
+    # (another batch, other kernels, other pages), with the tokens they generated in the batch appended, and the logits
+    # at every place where a token was chosen are read back: the token the batch chose must be that row's maximum, or
+    # within the rounding noise of bfloat16 of it (random weights give flat rows, where a near-tie may go either way
+    # between two batch shapes).  The noise between two bfloat16 paths of this engine on the same weights was measured
+    # at these widths as 0.010 of a row's largest magnitude after one layer, 0.019 after 4 and 0.032 after 16: it grows
+    # with the square root of the depth, so the bound is 0.01 * sqrt(layers).  Exact agreements are counted beside it.
+    bound = 0.01 * float(np.sqrt(mcfg.num_hidden_layers))
+    from mimirmind_b200.engine.runner import StepEntry
+    check = {}
+    verified = True
+    for which, i in (("shortest", int(np.argmin(lens))), ("longest", int(np.argmax(lens)))):
+        toks = list(prompts[i]) + list(res[i].tokens[:-1])
+        places = list(range(lens[i] - 1, len(toks)))
+        engine.runner.add_request(("check", i))
+        rows = engine.runner.step([StepEntry(("check", i), toks, places)]).float().cpu().numpy()
+        engine.runner.release(("check", i))
+        chosen = rows[np.arange(len(places)), res[i].tokens]
+        best = rows.max(axis=1)
+        worst = float(((best - chosen) / np.abs(rows).max(axis=1)).max())
+        check[which] = {"request": i, "prompt_tokens": lens[i], "tokens": len(places), "exactly_the_maximum": int((chosen == best).sum()),
+                        "worst_gap_over_row_scale": worst}
+        verified = verified and worst <= bound
+    ops.check_tcgen05_errors(torch.device("cuda"))
     print(json.dumps({"workload": name, "layers": mcfg.num_hidden_layers, "layers_of_config": full_layers, "requests": len(lens),
                       "prompt_tokens": sum(lens), "generated_tokens": gen, "first_run_seconds": times[0], "seconds": dt, "tokens_per_s": (sum(lens) + gen) / dt,
                       "generated_per_s": gen / dt, "graph_steps": engine.graph_steps,
-                      "finish": sorted({r.stats.finish_reason for r in res}),
+                      "finish": sorted({r.stats.finish_reason for r in res}), "verified": verified, "check_bound": bound, "check": check,
                       "device_gib": torch.cuda.max_memory_allocated() / 2 ** 30}))
-    return 0
+    return 0 if verified else 1
 
 
 def main() -> int:
