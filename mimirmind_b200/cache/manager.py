@@ -44,6 +44,12 @@ class GroupSpec:
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    # what an entry keeps per token: (name, shape per token, dtype name or None for the run's dtype); empty means
+    # keys and values of (num_kv_heads, head_dim)
+    arrays: Tuple[Tuple[str, Tuple[int, ...], Optional[str]], ...] = ()
+
+    def token_arrays(self) -> Tuple[Tuple[str, Tuple[int, ...], Optional[str]], ...]:
+        return self.arrays or (("k", (self.num_kv_heads, self.head_dim), None), ("v", (self.num_kv_heads, self.head_dim), None))
 
 
 class CacheManager:

@@ -20,8 +20,16 @@ class CacheSizingError(RuntimeError):
 
 
 def cache_bytes_per_token(groups: Iterable, element_bytes: int) -> int:
-    """Bytes one cached token takes over all groups (keys and values of every schedule entry of a group)."""
-    return sum(len(g.entries) * 2 * g.num_kv_heads * g.head_dim * element_bytes for g in groups)
+    """Bytes one cached token takes over all groups (every per-token array of every schedule entry of a group)."""
+    sizes = {None: element_bytes, "float32": 4, "bfloat16": 2, "float16": 2, "int32": 4, "int8": 1}
+    total = 0
+    for g in groups:
+        for _name, shape, dtype in g.token_arrays():
+            n = 1
+            for s in shape:
+                n *= int(s)
+            total += len(g.entries) * n * sizes[dtype]
+    return total
 
 
 def step_bytes_per_token(spec: ModelSpec, layer_tensor_shapes: Sequence[Sequence[Sequence[int]]], element_bytes: int) -> int:

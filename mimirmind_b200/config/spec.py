@@ -18,6 +18,7 @@ class PartSpec:
 
     kind: str
     params: Mapping[str, Any] = field(default_factory=dict)
+    category: str = ""      # which registry holds the kind ("norm", "mixer", ...); needed only for a layer's extra parts
 
     def __getitem__(self, key: str) -> Any:
         return self.params[key]
@@ -28,7 +29,7 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a block arrangement around a mixer and a feed-forward.
+    """One layer: a block arrangement around a mixer and a feed-forward, and whatever else the arrangement needs.
 
     ``prefix`` is the tensor-name prefix of the layer's weights (with trailing dot).
     """
@@ -39,6 +40,10 @@ class LayerSpec:
     feed_forward: PartSpec
     mixer_norm: PartSpec
     ffn_norm: PartSpec
+    # Further parts of the layer by name (a norm after each branch, a gate, a second feed-forward ...): each a
+    # PartSpec with its ``category``; they are built like the four above, declare their tensors like them, and are
+    # handed to the block arrangement, which alone knows what to do with them.
+    extras: Mapping[str, PartSpec] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -14,7 +14,7 @@ import torch
 from ..cache.manager import GroupSpec
 from ..config.spec import ModelSpec
 from ..parts.base import Block, KVCacheSpec, Runtime, StateSpec, WeightView
-from ..registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS
+from ..registry import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, part_class
 
 
 class Model:
@@ -32,7 +32,11 @@ class Model:
             mixer = MIXERS.get(ls.mixer.kind)(ls.mixer, w, rt)
             ffn_norm = NORMS.get(ls.ffn_norm.kind)(ls.ffn_norm, w, rt)
             ffn = FEED_FORWARDS.get(ls.feed_forward.kind)(ls.feed_forward, w, rt)
-            self.layers.append(BLOCKS.get(ls.block.kind)(ls.block, mixer_norm, mixer, ffn_norm, ffn, rt))
+            if ls.extras:
+                extras = {name: part_class(ps)(ps, w, rt) for name, ps in ls.extras.items()}
+                self.layers.append(BLOCKS.get(ls.block.kind)(ls.block, mixer_norm, mixer, ffn_norm, ffn, rt, extras=extras))
+            else:
+                self.layers.append(BLOCKS.get(ls.block.kind)(ls.block, mixer_norm, mixer, ffn_norm, ffn, rt))
         self.schedule = spec.schedule
         for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < len(self.layers)):
@@ -43,19 +47,26 @@ class Model:
 
     # ---- what the cache has to hold --------------------------------------------
     def cache_groups(self) -> List[GroupSpec]:
-        """Schedule entries that own a KV cache, grouped by (kv heads, head size, window)."""
-        by_key: Dict[Tuple[int, int, int], List[int]] = {}
+        """Schedule entries that own a paged cache, grouped by what they keep per token and how far back they look."""
+        by_key: Dict[tuple, List[int]] = {}
         for i, e in enumerate(self.schedule):
             if e.cache_from is not None:
                 continue
             ks: Optional[KVCacheSpec] = self.layers[e.layer].mixer.kv_cache_spec()
             if ks is None:
                 continue
-            by_key.setdefault((ks.num_kv_heads, ks.head_dim, ks.window), []).append(i)
+            arrays = tuple((a.name, tuple(int(x) for x in a.shape), None if a.dtype is None else str(a.dtype).replace("torch.", ""))
+                           for a in ks.token_arrays())
+            if any(len(shape) < 1 or min(shape) < 1 for _n, shape, _d in arrays) or len({n for n, _s, _d in arrays}) != len(arrays):
+                raise ValueError(f"schedule entry {i}: per-token cache arrays need distinct names and at least one axis of positive sizes")
+            by_key.setdefault((ks.num_kv_heads, ks.head_dim, ks.window, arrays if ks.arrays else ()), []).append(i)
         groups = []
-        for (g, hd, w), entries in by_key.items():
-            name = f"kv{g}x{hd}" + (f"_w{w}" if w else "_full")
-            groups.append(GroupSpec(name, tuple(entries), g, hd, w))
+        for (g, hd, w, arrays), entries in by_key.items():
+            if arrays:
+                name = "cache_" + "_".join(n + "x".join(str(x) for x in shape) for n, shape, _d in arrays)
+            else:
+                name = f"kv{g}x{hd}"
+            groups.append(GroupSpec(name + (f"_w{w}" if w else "_full"), tuple(entries), g, hd, w, arrays))
         return groups
 
     def state_specs(self) -> Dict[int, StateSpec]:

@@ -155,7 +155,7 @@ class NativeExecutor:
             else:
                 name, j = where
                 pool = storage.pools[name]
-                k_ptrs.append(pool[j, 0].data_ptr()), v_ptrs.append(pool[j, 1].data_ptr()), entry_group.append(group_names.index(name))
+                k_ptrs.append(pool["k"][j].data_ptr()), v_ptrs.append(pool["v"][j].data_ptr()), entry_group.append(group_names.index(name))
             entry_writes.append(int(e.cache_from is None))
         n = len(model.schedule)
         exec_h = lib.mmx_exec_create(model_h, manager._h, len(group_names), manager.page_size, pages, n,

@@ -57,12 +57,31 @@ class WeightView:
 
 
 @dataclass(frozen=True)
-class KVCacheSpec:
-    """A mixer that keeps keys and values per token: head geometry and how far back it looks."""
+class CacheArray:
+    """One array a mixer keeps per token in the paged cache: ``shape`` per token (at least one axis), ``dtype`` None
+    for the run's activation dtype.  Its pool is ``[pages, *shape[:-1], page_size, shape[-1]]``: the tokens of a page
+    stand before the last axis, so that for keys ``(kv_heads, head_dim)`` one head's page is one contiguous block."""
 
-    num_kv_heads: int
-    head_dim: int
+    name: str
+    shape: Tuple[int, ...]
+    dtype: Optional[torch.dtype] = None
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """What a mixer keeps per token and how far back it looks.  The usual case is keys and values of one head
+    geometry (``num_kv_heads``, ``head_dim``); a mixer that caches something else per token (one latent vector, keys
+    and values of different widths) lists its ``arrays`` instead."""
+
+    num_kv_heads: int = 0
+    head_dim: int = 0
     window: int = 0  # 0: every earlier token; W: the last W tokens (the current one included)
+    arrays: Tuple[CacheArray, ...] = ()
+
+    def token_arrays(self) -> Tuple[CacheArray, ...]:
+        if self.arrays:
+            return self.arrays
+        return (CacheArray("k", (self.num_kv_heads, self.head_dim)), CacheArray("v", (self.num_kv_heads, self.head_dim)))
 
 
 @dataclass(frozen=True)
@@ -77,8 +96,9 @@ class StateSpec:
 class LayerCache:
     """What one schedule entry sees of the cache during a step."""
 
-    k_pages: Optional[torch.Tensor] = None   # [pages, kv_heads, page_size, head_dim]
+    k_pages: Optional[torch.Tensor] = None   # [pages, kv_heads, page_size, head_dim]: the arrays "k" and "v", if the entry has them
     v_pages: Optional[torch.Tensor] = None
+    arrays: Dict[str, torch.Tensor] = field(default_factory=dict)   # every per-token array of the entry by name, [pages, ..., page_size, last]
     block_table: Optional[torch.Tensor] = None  # int32 [requests, width] of the entry's cache group
     page_size: int = 0
     writes: bool = True                      # False: the entry reads another entry's cache
@@ -228,13 +248,14 @@ class Block(Part):
     """Arrangement of norms, mixer and feed-forward around the residual stream."""
 
     def __init__(self, spec: PartSpec, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, feed_forward: FeedForward,
-                 rt: Runtime):
+                 rt: Runtime, extras: Optional[Dict[str, Part]] = None):
         self.spec = spec
         self.rt = rt
         self.mixer_norm = mixer_norm
         self.mixer = mixer
         self.ffn_norm = ffn_norm
         self.feed_forward = feed_forward
+        self.extras: Dict[str, Part] = dict(extras or {})     # the layer's further parts by name (LayerSpec.extras)
 
     def forward(self, residual: torch.Tensor, pending, ctx: StepContext, cache: LayerCache,
                 successor: Optional["Block"] = None):

@@ -60,6 +60,18 @@ POSITION_ENCODINGS = _Table("position encoding")
 BLOCKS = _Table("block arrangement")
 EMBEDDINGS = _Table("embedding")
 HEADS = _Table("output head")
+# the tables by the category a PartSpec may name (a layer's extra parts say which table holds their kind)
+CATEGORIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "position": POSITION_ENCODINGS, "block": BLOCKS,
+              "embedding": EMBEDDINGS, "head": HEADS}
+
+
+def part_class(spec) -> Any:
+    """The class of a PartSpec that names its category."""
+    try:
+        table = CATEGORIES[spec.category]
+    except KeyError:
+        raise RegistryError(f"part of kind '{spec.kind}' names the category '{spec.category}'; known: {', '.join(sorted(CATEGORIES))}") from None
+    return table.get(spec.kind)
 
 
 class ArchitectureEntry:

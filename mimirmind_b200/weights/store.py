@@ -21,7 +21,7 @@ import torch
 
 from ..config.model_config import read_config_json
 from ..config.spec import ModelSpec, TensorSpec
-from ..registry import (EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, get_architecture)
+from ..registry import (EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, get_architecture, part_class)
 from .safetensors_io import SafetensorsFolder, write_safetensors
 
 
@@ -46,6 +46,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorSpec]:
         add(MIXERS.get(layer.mixer.kind).tensor_specs(layer.mixer, layer.prefix))
         add(NORMS.get(layer.ffn_norm.kind).tensor_specs(layer.ffn_norm, layer.prefix))
         add(FEED_FORWARDS.get(layer.feed_forward.kind).tensor_specs(layer.feed_forward, layer.prefix))
+        for extra in layer.extras.values():
+            add(part_class(extra).tensor_specs(extra, layer.prefix))
     add(NORMS.get(spec.final_norm.kind).tensor_specs(spec.final_norm, ""))
     add(HEADS.get(spec.head.kind).tensor_specs(spec.head, ""))
     return out
@@ -58,6 +60,8 @@ def layer_tensor_shapes(spec: ModelSpec):
         specs = []
         for reg, part in ((NORMS, layer.mixer_norm), (MIXERS, layer.mixer), (NORMS, layer.ffn_norm), (FEED_FORWARDS, layer.feed_forward)):
             specs += reg.get(part.kind).tensor_specs(part, layer.prefix)
+        for extra in layer.extras.values():
+            specs += part_class(extra).tensor_specs(extra, layer.prefix)
         out.append([tuple(ts.shape) for ts in specs])
     return out
 

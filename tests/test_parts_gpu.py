@@ -210,6 +210,156 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
         registry.ARCHITECTURES.unregister("ToyForTest")
 
 
+# ---- a block with more than four parts, and a mixer that caches something else than keys and values ---------------
+
+def test_toy_block_with_post_norms_and_a_mixer_that_caches_one_latent_per_token():
+    """Two things an architecture may need that this one does not: a block arrangement with further parts (here a norm
+    after each branch, named in ``LayerSpec.extras``), and a mixer whose paged cache holds one latent vector per
+    token instead of keys and values (``KVCacheSpec.arrays``).  Both are registered from here, built from random
+    weights by name, stepped whole and in portions over a small pool, and compared with a numpy restatement of the
+    whole model; no file of the package changes."""
+    import plain_qwen2 as plain
+    from mimirmind_b200 import registry
+    from mimirmind_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec
+    from mimirmind_b200.engine.loader import make_runtime
+    from mimirmind_b200.engine.model import Model
+    from mimirmind_b200.engine.runner import ModelRunner, StepEntry
+    from mimirmind_b200.parts.base import Block, CacheArray, KVCacheSpec, Mixer
+    from mimirmind_b200.weights.store import expected_tensors, random_tensors
+    registry._ensure_builtin()
+    R = 12                                                     # width of the cached latent
+
+    @registry.MIXERS.register("toy_latent_attention", replace=True)
+    class LatentAttention(Mixer):
+        """c_t = x_t Wc^T is cached; out_t = Wo . sum_s softmax_s((x_t Wq^T) . c_s / sqrt(R)) c_s over s <= t."""
+
+        @classmethod
+        def tensor_specs(cls, spec, prefix):
+            d = spec["hidden"]
+            return [TensorSpec(prefix + "lat.c", (R, d)), TensorSpec(prefix + "lat.q", (R, d)), TensorSpec(prefix + "lat.o", (d, R))]
+
+        def __init__(self, spec, weights, rt):
+            super().__init__(spec, weights, rt)
+            self.wc, self.wq, self.wo = (weights.get(n).float() for n in ("lat.c", "lat.q", "lat.o"))
+
+        def kv_cache_spec(self):
+            return KVCacheSpec(window=0, arrays=(CacheArray("latent", (R,), torch.float32),))
+
+        def forward(self, x, ctx, cache):
+            pool, ps = cache.arrays["latent"], cache.page_size             # [pages, page_size, R]
+            assert pool.shape[1:] == (ps, R) and pool.dtype == torch.float32 and cache.k_pages is None
+            out = torch.empty_like(x)
+            for r in range(ctx.n_requests):
+                s, n, kv = ctx.q_start[r], ctx.q_len[r], ctx.kv_len[r]
+                xs = x[s:s + n].float()
+                pos = torch.arange(kv - n, kv, device=x.device)
+                table = cache.block_table[r].long()
+                pool[table[pos // ps], pos % ps] = xs @ self.wc.t()         # this step's latents into their pages
+                every = torch.arange(kv, device=x.device)
+                c = pool[table[every // ps], every % ps]                    # [kv, R], gathered page by page
+                score = (xs @ self.wq.t()) @ c.t() / np.sqrt(R)
+                score = score.masked_fill(every[None, :] > pos[:, None], float("-inf"))
+                out[s:s + n] = ((torch.softmax(score, dim=-1) @ c) @ self.wo.t()).to(x.dtype)
+            return out
+
+    @registry.BLOCKS.register("toy_sandwich", replace=True)
+    class Sandwich(Block):
+        """x += post1(mixer(pre1(x))); x += post2(ffn(pre2(x))): the two post-norms are the layer's extra parts."""
+
+        def forward(self, residual, pending, ctx, cache, successor=None):
+            h = self.mixer_norm.forward(residual, pending)
+            branch = self.mixer.forward(h, ctx, cache)
+            branch = self.extras["post_mixer_norm"].forward(branch.float().contiguous(), None)
+            h = self.ffn_norm.forward(residual, branch)
+            out = self.feed_forward.forward(h, ctx)
+            return self.extras["post_ffn_norm"].forward(out.float().contiguous(), None)
+
+    d, V = 32, 70
+
+    def toy_spec(cfg):
+        norm = lambda name: PartSpec("rmsnorm", {"width": d, "eps": 1e-5, "weight": name}, category="norm")
+        attn = PartSpec("gqa_attention", dict(hidden=d, num_heads=2, num_kv_heads=1, head_dim=16, window=0, scale=None, qkv_bias=False,
+                                              position=PartSpec("rotary_half", {"theta": 100.0, "rotary_dim": 16}),
+                                              q="q", k="k", v="v", o="o"))
+        ffn = PartSpec("swiglu", {"hidden": d, "intermediate": 40, "gate": "g.weight", "up": "u.weight", "down": "d.weight"})
+        layers = (
+            LayerSpec("l0.", PartSpec("toy_sandwich"), PartSpec("toy_latent_attention", {"hidden": d}), ffn, norm("n1"), norm("n2"),
+                      extras={"post_mixer_norm": norm("p1"), "post_ffn_norm": norm("p2")}),
+            LayerSpec("l1.", PartSpec("pre_norm"), attn, ffn, norm("n1"), norm("n2")),
+        )
+        return ModelSpec("ToySandwich", d, V, 512, PartSpec("token_embedding", {"vocab": V, "width": d, "scale": 1.0, "weight": "emb"}),
+                         layers, (ScheduleEntry(0), ScheduleEntry(1)), norm("nf"),
+                         PartSpec("lm_head", {"vocab": V, "width": d, "weight": "head", "tied_to": None}))
+
+    registry.register_architecture("ToySandwich", lambda obj, where="": obj, toy_spec, replace=True)
+    try:
+        entry = registry.get_architecture("ToySandwich")
+        spec = entry.build_spec(entry.parse_config({}))
+        names = expected_tensors(spec)
+        assert {"l0.p1", "l0.p2", "l0.lat.c", "l0.lat.q", "l0.lat.o"} <= set(names)       # the extras' and the mixer's tensors by name
+        rt_ = make_runtime("float32")
+        tensors = random_tensors(spec, 9, torch.float32, rt_.device)
+        w = {k: v.double().cpu().numpy() for k, v in tensors.items()}
+        model = Model(spec, tensors, rt_)
+        groups = {g.name: g for g in model.cache_groups()}
+        assert len(groups) == 2 and any(g.arrays == (("latent", (R,), "float32"),) for g in groups.values())
+        runner = ModelRunner(model, 8, 24, 4)                          # pages of 8 tokens, 24 of them per group
+        assert runner.native is None                                   # parts without native classes: the Python path
+        lat_pool = [p for p in runner.storage.pools.values() if "latent" in p][0]["latent"]
+        assert lat_pool.shape == (1, 24, 8, R) and lat_pool.dtype == torch.float32
+
+        def restated(toks):
+            T = len(toks)
+            x = w["emb"][toks]
+            # layer 0: the sandwich around the latent mixer
+            h = plain.rms_norm(x, w["l0.n1"], 1e-5)
+            c, q = h @ w["l0.lat.c"].T, h @ w["l0.lat.q"].T
+            sc = q @ c.T / np.sqrt(R)
+            sc = np.where(np.arange(T)[None, :] <= np.arange(T)[:, None], sc, -np.inf)
+            pr = np.exp(sc - sc.max(axis=-1, keepdims=True))
+            branch = ((pr / pr.sum(axis=-1, keepdims=True)) @ c) @ w["l0.lat.o"].T
+            x = x + plain.rms_norm(branch, w["l0.p1"], 1e-5)
+            f = plain.swiglu(plain.rms_norm(x, w["l0.n2"], 1e-5), w["l0.g.weight"], w["l0.u.weight"], w["l0.d.weight"])
+            x = x + plain.rms_norm(f, w["l0.p2"], 1e-5)
+            # layer 1: the ordinary pre-norm block
+            h = plain.rms_norm(x, w["l1.n1"], 1e-5)
+            pos = np.arange(T)
+            qh = plain.rope((h @ w["l1.q.weight"].T).reshape(T, 2, 16), pos, 100.0)
+            kh = plain.rope((h @ w["l1.k.weight"].T).reshape(T, 1, 16), pos, 100.0)
+            vh = (h @ w["l1.v.weight"].T).reshape(T, 1, 16)
+            x = x + plain.attention(qh, kh, vh, 0).reshape(T, 32) @ w["l1.o.weight"].T
+            x = x + plain.swiglu(plain.rms_norm(x, w["l1.n2"], 1e-5), w["l1.g.weight"], w["l1.u.weight"], w["l1.d.weight"])
+            return plain.rms_norm(x, w["nf"], 1e-5) @ w["head"].T
+
+        def run(cuts, rid, toks):
+            runner.add_request(rid)
+            outs, p = [], 0
+            for c in cuts:
+                outs.append(runner.step([StepEntry(rid, toks[p:p + c], list(range(c)))]).cpu().numpy())
+                p += c
+            return np.concatenate(outs)
+
+        a, b = random_tokens(V, 61, 1), random_tokens(V, 50, 2)
+        ref_a, ref_b = restated(a), restated(b)
+        whole = run([61], "a", a)
+        assert np.abs(whole - ref_a).max() <= 2e-5 * np.abs(ref_a).max()
+        parts = run([7, 1, 9, 2, 30, 12], "b", a)                       # portions that end inside pages, at their edges and beyond
+        assert np.abs(parts - ref_a).max() <= 2e-5 * np.abs(ref_a).max()
+        runner.release("a")
+        runner.release("b")
+        # two requests side by side in pages that were used before
+        runner.add_request("c"); runner.add_request("e")
+        both = runner.step([StepEntry("c", b, list(range(50))), StepEntry("e", a[:33], [32])]).cpu().numpy()
+        assert runner.manager.reuses() > 0
+        assert np.abs(both[:50] - ref_b).max() <= 2e-5 * np.abs(ref_b).max()
+        assert np.abs(both[50] - ref_a[32]).max() <= 2e-5 * np.abs(ref_a).max()
+        runner.manager.check()
+    finally:
+        registry.MIXERS.unregister("toy_latent_attention")
+        registry.BLOCKS.unregister("toy_sandwich")
+        registry.ARCHITECTURES.unregister("ToySandwich")
+
+
 def test_fused_handover_beside_a_mixer_that_does_not_fuse():
     """bfloat16, sizes the fused small-step path takes: a toy mixer that knows nothing of FactoredRows or sinks sits
     between layers whose attention and feed-forward fuse.  Its neighbours must fall back to the plain hand-over on
