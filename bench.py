@@ -176,9 +176,14 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
+        # The attempt is on record (baseline/reference_arm.py is what drove it): the reference's binary builds offline with
+        # its CUDA backend, loads a bfloat16 GGUF of this shape, and its process ends with SIGSEGV in generate() on this GPU,
+        # so it is not run again.
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a C++/CMake program without a Python package: pip cannot install it offline "
-                          "(no setup.py/pyproject), and its engine for this architecture reads 4-bit GGUF files only"}))
+                          "the reference builds offline (cmake -DMIMIRMIND_ENABLE_CUDA=ON) and loads a random bfloat16 GGUF, but its "
+                          "CUDA backend is written for an integrated GPU whose memory the host can read: on a B200 its 'smoke' "
+                          "mode dies with SIGSEGV in generate(), where the token embedding is looked up on the CPU from device memory; "
+                          "its code is not run again after that crash (pip cannot install it either: no setup.py/pyproject)"}))
         return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
