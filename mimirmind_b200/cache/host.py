@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from ctypes import POINTER, c_char_p, c_int, c_longlong, c_void_p
+from ctypes import POINTER, c_char_p, c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
 _lock = threading.Lock()
@@ -50,6 +50,7 @@ _PROTOTYPES = {
     "mmh_sched_events": (I, [P, PL, PI, PI, I]),
     "mmh_sched_commit": (I, [P, I, PL, PI, PI, PI, PI]),
     "mmh_sched_accept_token": (I, [P, L, I]),
+    "mmh_sched_set_sampling": (I, [P, L, c_float, I, c_float, L, c_float, c_float, c_float, I, c_float]),
     "mmh_sched_cancel": (I, [P, L]),
     "mmh_sched_request": (L, [P, L, I]),
     "mmh_sched_tokens": (I, [P, L, I, I, PI]),

@@ -210,7 +210,7 @@ class Executor {
             n_tok += counts[r];
             n_rows += n_want[r];
         }
-        if (n_rows > logits_rows_cap) throw ExecError("executor: the logits buffer is too small for the wanted rows");
+        if (logits != nullptr && n_rows > logits_rows_cap) throw ExecError("executor: the logits buffer is too small for the wanted rows");
         if (flags & RUN_RESERVE) {
             // pages for every entry: the step runs fully or not at all
             std::vector<int> need(G, 0), one(std::max(G, 1));
@@ -273,6 +273,8 @@ class Executor {
         st.logit_rows = dev + o_rows;
         for (int g = 0; g < G; ++g) st.tables[g] = dev + o_tab + tab * g;
 
+        if (logits == nullptr && n_rows > 0) logits = st.step_mem->alloc_n<float>((size_t)n_rows * vocab_);      // the caller samples from them itself
+        own_logits_ = logits;
         forward(st, logits);
         check_cuda(cudaMemcpyAsync(err_host_, err_, sizeof(int), cudaMemcpyDeviceToHost, stream), "reading the kernels' error flag");
         if (flags & RUN_COMMIT)
@@ -313,6 +315,166 @@ class Executor {
         ++steps_;
     }
 
+
+    // ---- one scheduler step, sampled and committed ------------------------------------------------------------------------------------
+    // Asks the scheduler (csrc/host/runtime.cpp) for the next step's plan, runs it, draws a token for every entry whose last
+    // token was fed (greedy, or temperature / top-k / top-p with the request's own seed and draw counter, after soft-cap and
+    // repetition / frequency / presence penalties over its recent tokens: src/compute/Sampling.cpp:119-264), waits for the tokens,
+    // and commits them: cache lengths advance, finished requests give back what they hold.  Returns the number of sampled tokens
+    // (out_rids / out_tokens); the plan it ran stays readable from the scheduler, what happened to requests from events().
+    int run_plan(void* sched, long long* out_rids, int* out_tokens, int cap, cudaStream_t stream) {
+        events_.clear();
+        planned_ = 0;
+        const int n = mmh_sched_schedule(sched);
+        if (n < 0) throw ExecError(mmh_last_error());
+        take_events(sched);
+        if (n == 0) return 0;
+        std::vector<long long> rids(n);
+        std::vector<int> starts(n), counts(n), samples(n), n_want(n), want, sampled(n, 0);
+        mmh_sched_plan(sched, rids.data(), starts.data(), counts.data(), samples.data(), n);
+        planned_ = n;
+        size_t total = 0;
+        for (int i = 0; i < n; ++i) total += counts[i];
+        std::vector<int> tokens(total);
+        size_t at = 0;
+        int rows = 0;
+        for (int i = 0; i < n; ++i) {
+            if (mmh_sched_tokens(sched, rids[i], starts[i], counts[i], tokens.data() + at) < 0) throw ExecError(mmh_last_error());
+            at += counts[i];
+            n_want[i] = samples[i] ? 1 : 0;
+            if (samples[i]) {
+                want.push_back(counts[i] - 1);
+                ++rows;
+            }
+        }
+        if (rows > cap) throw ExecError("executor: more sampled tokens than the caller has room for");
+        run(n, rids.data(), counts.data(), tokens.data(), n_want.data(), want.data(), 0, nullptr, 0, stream);
+        if (rows > 0) {
+            std::vector<long long> row_rids;
+            for (int i = 0; i < n; ++i)
+                if (samples[i]) row_rids.push_back(rids[i]);
+            int* dev_tokens = sample(sched, row_rids, own_logits_, stream);
+            Staging& sg = next_staging(rows);
+            check_cuda(cudaMemcpyAsync(sg.host, dev_tokens, rows * sizeof(int), cudaMemcpyDeviceToHost, stream), "reading the sampled tokens");
+            check_cuda(cudaStreamSynchronize(stream), "waiting for the step");
+            if (take_error_flag() != 0) {
+                cudaMemsetAsync(err_, 0, sizeof(int), stream);
+                throw ExecError("a kernel of the step gave up waiting on its pipeline; the step's output is not valid");
+            }
+            int r = 0;
+            for (int i = 0; i < n; ++i)
+                if (samples[i]) {
+                    if (sg.host[r] < 0 || sg.host[r] >= vocab_) throw ExecError("the sampler returned a token outside the vocabulary");
+                    sampled[i] = sg.host[r];
+                    out_rids[r] = rids[i];
+                    out_tokens[r] = sg.host[r];
+                    ++r;
+                }
+        }
+        if (mmh_sched_commit(sched, n, rids.data(), starts.data(), counts.data(), samples.data(), sampled.data()) != 0) throw ExecError(mmh_last_error());
+        take_events(sched);
+        return rows;
+    }
+
+    struct Event {
+        long long rid;
+        int kind, code;
+    };
+    const std::vector<Event>& events() const { return events_; }
+    int planned() const { return planned_; }
+
+  private:
+    void take_events(void* sched) {
+        long long r[256];
+        int k[256], c[256];
+        const int n = mmh_sched_events(sched, r, k, c, 256);
+        if (n > 256) throw ExecError("executor: more scheduler events in one call than it has room for");
+        for (int i = 0; i < n; ++i) events_.push_back({r[i], k[i], c[i]});
+    }
+
+    // Draws one token per row of logits [rows, vocab] for the requests `rids`; returns device int32 [rows].
+    int* sample(void* sched, const std::vector<long long>& rids, float* logits, cudaStream_t stream) {
+        const int R = (int)rids.size(), V = vocab_;
+        struct P {
+            float f[6];      // temperature, top_p, repetition, frequency, presence, softcap
+            int i[4];        // top_k, penalty window, generated, tokens
+            long long seed;
+        };
+        std::vector<P> p(R);
+        bool need_pen = false, need_cap = false, all_greedy = true;
+        int w = 0;
+        auto greedy = [](const P& x) { return x.f[0] <= 0.f || x.i[0] == 1; };
+        auto pen = [](const P& x) { return x.i[1] > 0 && (x.f[2] != 1.f || x.f[3] != 0.f || x.f[4] != 0.f); };
+        for (int r = 0; r < R; ++r) {
+            if (mmh_sched_get_sampling(sched, rids[r], p[r].f, p[r].i, &p[r].seed) != 0) throw ExecError(mmh_last_error());
+            if (pen(p[r]) && p[r].i[3] > 0) {
+                need_pen = true;
+                w = std::max(w, std::min(p[r].i[1], p[r].i[3]));
+            }
+            need_cap = need_cap || p[r].f[5] > 0.f;
+            all_greedy = all_greedy && greedy(p[r]);
+        }
+        Arena& mem = step_mem_;
+        int* out = mem.alloc_n<int>(R);
+        void* s = stream;
+        auto argmax = [&]() {
+            if (V > 16384) {          // wide rows: several blocks per row, then one to reduce them
+                const int parts = std::min(256, (V + 4095) / 4096);
+                float* pv = mem.alloc_n<float>((size_t)R * parts);
+                int* pi = mem.alloc_n<int>((size_t)R * parts);
+                check_kernel(mm_argmax_rows_split(logits, out, pv, pi, R, V, parts, s), "argmax_rows_split");
+            } else {
+                check_kernel(mm_argmax_rows(logits, out, R, V, s), "argmax_rows");
+            }
+            return out;
+        };
+        // greedy without penalties: the soft-cap is monotonic and leaves the maximum where it is
+        if (all_greedy && !need_pen) return argmax();
+        // the rows' parameters in one pinned block, one copy: 64-bit values first, then floats and integers
+        const int W = std::max(w, 1);
+        const size_t o_seed = 0, o_cnt = o_seed + 2 * (size_t)R, o_f = o_cnt + 2 * (size_t)R, o_k = o_f + 6 * (size_t)R, o_recent = o_k + R,
+                     total = o_recent + (size_t)R * W;
+        Staging& sg = next_staging(total);
+        long long* h_seed = reinterpret_cast<long long*>(sg.host + o_seed);
+        long long* h_cnt = reinterpret_cast<long long*>(sg.host + o_cnt);
+        float* h_f = reinterpret_cast<float*>(sg.host + o_f);      // rep | freq | pres | cap | temperature | top_p, R each
+        int* h_k = sg.host + o_k;
+        int* h_recent = sg.host + o_recent;
+        std::vector<int> hist;
+        for (int r = 0; r < R; ++r) {
+            const bool on = pen(p[r]);
+            h_seed[r] = p[r].seed & 0x7FFFFFFFFFFFFFFFLL;
+            h_cnt[r] = p[r].i[2];
+            h_f[0 * R + r] = on ? p[r].f[2] : 1.f;
+            h_f[1 * R + r] = on ? p[r].f[3] : 0.f;
+            h_f[2 * R + r] = on ? p[r].f[4] : 0.f;
+            h_f[3 * R + r] = p[r].f[5];
+            h_f[4 * R + r] = greedy(p[r]) ? 0.f : p[r].f[0];
+            h_f[5 * R + r] = p[r].f[1];
+            h_k[r] = p[r].i[0];
+            for (int j = 0; j < W; ++j) h_recent[(size_t)r * W + j] = -1;
+            const int k = on ? std::min(p[r].i[1], p[r].i[3]) : 0;
+            if (k > 0) {
+                hist.resize(k);
+                if (mmh_sched_tokens(sched, rids[r], p[r].i[3] - k, k, hist.data()) < 0) throw ExecError(mmh_last_error());
+                for (int j = 0; j < k; ++j) h_recent[(size_t)r * W + j] = hist[j];
+            }
+        }
+        int* dev = mem.alloc_n<int>(total);
+        check_cuda(cudaMemcpyAsync(dev, sg.host, total * sizeof(int), cudaMemcpyHostToDevice, stream), "copying the sampling parameters");
+        check_cuda(cudaEventRecord(sg.copied, stream), "staging event");
+        sg.in_flight = true;
+        const float* d_f = reinterpret_cast<const float*>(dev + o_f);
+        if (need_pen || need_cap) {
+            check_kernel(mm_apply_penalties(logits, R, V, w > 0 ? dev + o_recent : nullptr, w > 0 ? W : 0, d_f, d_f + R, d_f + 2 * R,
+                                            need_cap ? d_f + 3 * R : nullptr, s), "apply_penalties");
+            if (all_greedy) return argmax();
+        }
+        check_kernel(mm_sample_rows(logits, out, R, V, d_f + 4 * R, dev + o_k, d_f + 5 * R, dev + o_seed, dev + o_cnt, s), "sample_rows");
+        return out;
+    }
+
+  public:
     int take_error_flag() {
         const int v = *err_host_;
         *err_host_ = 0;
@@ -336,6 +498,9 @@ class Executor {
     Staging ring_[4];
     int ring_next_ = 0;
     long long steps_ = 0;
+    float* own_logits_ = nullptr;
+    std::vector<Event> events_;
+    int planned_ = 0;
 };
 
 }  // namespace mmx
@@ -432,6 +597,26 @@ MMX_EXPORT int mmx_exec_run(void* ex, int n_entries, const long long* rids, cons
 
 MMX_EXPORT int mmx_exec_forward(void* ex, const StepDesc* d, void* logits, void* stream) {
     MMX_GUARD(static_cast<Executor*>(ex)->forward_described(*d, (float*)logits, (cudaStream_t)stream); return 0;)
+}
+
+// One step of the scheduler `sched` (a handle of csrc/host/runtime.cpp made over the same cache manager): plan, launches,
+// sampling, the wait for the tokens, commit.  Returns the number of sampled tokens written to out_rids / out_tokens (at most
+// cap), -1 on an error (the plan it was running stays readable from the scheduler, so that the caller can fail its requests).
+MMX_EXPORT int mmx_exec_run_plan(void* ex, void* sched, long long* out_rids, int* out_tokens, int cap, void* stream) {
+    MMX_GUARD(return static_cast<Executor*>(ex)->run_plan(sched, out_rids, out_tokens, cap, (cudaStream_t)stream);)
+}
+// entries of the plan of the last mmx_exec_run_plan (0: the scheduler had nothing to run)
+MMX_EXPORT int mmx_exec_planned(void* ex) { return static_cast<Executor*>(ex)->planned(); }
+// what the last mmx_exec_run_plan did to requests (admitted, preempted, finished: the scheduler's event kinds and codes)
+MMX_EXPORT int mmx_exec_events(void* ex, long long* rids, int* kinds, int* codes, int cap) {
+    const auto& ev = static_cast<Executor*>(ex)->events();
+    const int n = (int)ev.size();
+    for (int i = 0; i < n && i < cap; ++i) {
+        rids[i] = ev[i].rid;
+        kinds[i] = ev[i].kind;
+        codes[i] = ev[i].code;
+    }
+    return n;
 }
 
 // The kernels' error flag as the last mmx_exec_run copied it back (valid once the stream has been synchronised); reading clears it.

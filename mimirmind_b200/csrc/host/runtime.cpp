@@ -232,6 +232,11 @@ struct SchedRequest {
     int state = WAITING, finish = NONE, preemptions = 0;
     long long admit_seq = -1;
     std::string reject_reason;
+    // how its tokens are drawn (names and meanings of the reference's sampler, src/compute/Sampling.hpp:40-87); kept here so
+    // that a step which samples inside the library needs nothing from the caller
+    float temperature = 0.f, top_p = 1.f, repetition = 1.f, frequency = 0.f, presence = 0.f, softcap = 0.f;
+    int top_k = 0, penalty_window = 0;
+    long long seed = 0;
 };
 
 struct PlanEntry {
@@ -596,6 +601,24 @@ MMH int mmh_sched_events(void* h, long long* rids, int* kinds, int* codes, int c
 }
 MMH int mmh_sched_commit(void* h, int n, const long long* rids, const int* starts, const int* counts, const int* samples, const int* sampled) {
     return static_cast<Scheduler*>(h)->commit(n, reinterpret_cast<const int64_t*>(rids), starts, counts, samples, sampled);
+}
+// how a request's tokens are drawn; values as the caller resolved them (seed != 0)
+MMH int mmh_sched_set_sampling(void* h, long long rid, float temperature, int top_k, float top_p, long long seed, float frequency,
+                               float presence, float repetition, int penalty_window, float softcap) {
+    SchedRequest* r = static_cast<Scheduler*>(h)->find(rid);
+    if (!r) return -2;
+    r->temperature = temperature; r->top_k = top_k; r->top_p = top_p; r->seed = seed;
+    r->frequency = frequency; r->presence = presence; r->repetition = repetition; r->penalty_window = penalty_window; r->softcap = softcap;
+    return 0;
+}
+// f: temperature, top_p, repetition, frequency, presence, softcap; i: top_k, penalty_window, tokens generated so far, tokens in all
+MMH int mmh_sched_get_sampling(void* h, long long rid, float* f, int* i, long long* seed) {
+    SchedRequest* r = static_cast<Scheduler*>(h)->find(rid);
+    if (!r) return -2;
+    f[0] = r->temperature; f[1] = r->top_p; f[2] = r->repetition; f[3] = r->frequency; f[4] = r->presence; f[5] = r->softcap;
+    i[0] = r->top_k; i[1] = r->penalty_window; i[2] = r->generated; i[3] = (int)r->tokens.size();
+    *seed = r->seed;
+    return 0;
 }
 MMH int mmh_sched_accept_token(void* h, long long rid, int tok) {
     Scheduler* s = static_cast<Scheduler*>(h);

@@ -20,6 +20,8 @@ int mmh_sched_schedule(void* sched);
 int mmh_sched_plan(void* sched, long long* rids, int* starts, int* counts, int* samples, int cap);
 int mmh_sched_tokens(void* sched, long long rid, int start, int count, int* out);
 long long mmh_sched_request(void* sched, long long rid, int what);
+int mmh_sched_events(void* sched, long long* rids, int* kinds, int* codes, int cap);
+int mmh_sched_get_sampling(void* sched, long long rid, float* f6, int* i4, long long* seed);
 int mmh_sched_commit(void* sched, int n, const long long* rids, const int* starts, const int* counts, const int* samples,
                      const int* sampled);
 }

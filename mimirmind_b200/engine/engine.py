@@ -323,6 +323,8 @@ class ServingLoop:
                 raise
             if ran:
                 return sched.has_work()
+        if eng.runner.native is not None and eng.runner.stage_dump is None:
+            return self._library_step()
         plan = sched.schedule()
         if not plan:
             if sched.has_work():
@@ -346,6 +348,41 @@ class ServingLoop:
         for p in plan:
             if p.samples and self.deliver(p.request, sampled[p.request.id]) is False and p.request.state != "finished":
                 sched.cancel(p.request.id)
+        return sched.has_work()
+
+    def _library_step(self) -> bool:
+        """A scheduler step inside the library: plan, step, sampling, the wait for the tokens and the commit are one call
+        (csrc/exec/executor.cu, run_plan); what is left here is to bring the Python requests up to date and to call back."""
+        eng, sched = self.engine, self.sched
+        native = eng.runner.native
+        t_step = time.perf_counter()
+        try:
+            handles, toks = native.run_plan(sched._h)
+        except Exception as e:
+            sched.apply_events(native.events())            # what the call did before it failed (admissions, preemptions)
+            self._fail([p.request for p in sched.last_plan(native.planned())], e)
+            raise
+        sched.apply_events(native.events())
+        planned = native.planned()
+        if planned == 0:
+            if sched.has_work():
+                raise RuntimeError("scheduler made no progress")   # cannot happen: a lone request fails instead
+            return False
+        now = time.perf_counter()
+        eng.d2h_bytes += 4 * len(toks)
+        if eng.decode_trace is not None and len(toks) == planned and all(p.count == 1 for p in sched.last_plan(planned)):
+            eng.decode_trace.step(planned, (now - t_step) * 1e3)
+            eng.decode_trace.flush()
+        for h, tok in zip(handles, toks):
+            req = sched.request_of(h)
+            req.tokens.append(tok)
+            req.generated.append(tok)
+            self.first_at.setdefault(req.id, now)
+            self.last_at[req.id] = now
+        for h, tok in zip(handles, toks):
+            req = sched.request_of(h)
+            if self.deliver(req, tok) is False and req.state != "finished":
+                sched.cancel(req.id)
         return sched.has_work()
 
     def _fail(self, requests, error: Exception) -> None:

@@ -59,6 +59,9 @@ def _declare():
         ("mmx_exec_destroy", None, [P]),
         ("mmx_exec_run", I, [P, I, P, P, P, P, P, I, P, L, P]),
         ("mmx_exec_forward", I, [P, POINTER(_StepDesc), P, P]),
+        ("mmx_exec_run_plan", I, [P, P, POINTER(L), POINTER(I), I, P]),
+        ("mmx_exec_planned", I, [P]),
+        ("mmx_exec_events", I, [P, POINTER(L), POINTER(I), POINTER(I), I]),
         ("mmx_exec_take_error_flag", I, [P]),
         ("mmx_exec_stat", L, [P, I]),
         ("mmx_option", I, [c_char_p, I]),
@@ -217,6 +220,31 @@ class NativeExecutor:
         if rc < 0:
             raise KernelError(last_error())
         return logits
+
+    def run_plan(self, scheduler_handle) -> "tuple[list, list]":
+        """One step of the library's scheduler: plan, launches, sampling, the wait for the tokens, commit, all in one
+        call.  Returns (request ids, sampled tokens) of the entries that sampled; ``planned()`` and ``events()`` tell
+        the rest.  Raises KernelError when the step failed (the plan stays readable from the scheduler)."""
+        cap = 1024
+        if not hasattr(self, "_plan_rids"):
+            self._plan_rids, self._plan_toks = (c_longlong * cap)(), (c_int * cap)()
+            self._ev = ((c_longlong * 512)(), (c_int * 512)(), (c_int * 512)())
+        n = self._lib.mmx_exec_run_plan(self._exec, scheduler_handle, self._plan_rids, self._plan_toks, cap, ops._stream())
+        if n < 0:
+            raise KernelError(last_error())
+        return list(self._plan_rids[:n]), list(self._plan_toks[:n])
+
+    def planned(self) -> int:
+        """Entries of the plan that the last ``run_plan`` ran (0: the scheduler had nothing to run)."""
+        return int(self._lib.mmx_exec_planned(self._exec))
+
+    def events(self):
+        """What the last ``run_plan`` did to requests: (request id, kind, code) in order."""
+        if not hasattr(self, "_ev"):
+            return []
+        r, k, c = self._ev
+        n = self._lib.mmx_exec_events(self._exec, r, k, c, 512)
+        return [(r[i], k[i], c[i]) for i in range(min(n, 512))]
 
     def take_error_flag(self) -> int:
         """The kernels' error flag as the last ``run`` copied it back (after a synchronisation); reading clears it."""

@@ -141,10 +141,13 @@ class Scheduler:
     def _apply_events(self) -> List[Request]:
         """Reads what the last call did to requests; returns those that finished."""
         n = self._lib.mmh_sched_events(self._h, self._rids, self._a, self._b, self._cap)
+        return self.apply_events([(self._rids[i], self._a[i], self._b[i]) for i in range(min(n, self._cap))])
+
+    def apply_events(self, events) -> List[Request]:
+        """Brings the Python face up to date from (request handle, kind, code) events; returns the requests that finished."""
         done: List[Request] = []
-        for i in range(min(n, self._cap)):
-            req = self._by_handle[self._rids[i]]
-            kind, code = self._a[i], self._b[i]
+        for handle, kind, code in events:
+            req = self._by_handle[handle]
             if kind == _EV_ADMITTED:
                 req.state, req.admit_seq = RUNNING, code
                 self.manager.adopt(req.id, self._handle[req.id])
@@ -190,6 +193,10 @@ class Scheduler:
         self._handle[req.id] = h
         self._by_handle[h] = req
         req.tokens = list(req.prompt)
+        sp = req.sampling
+        self._check(self._lib.mmh_sched_set_sampling(self._h, h, float(sp.temperature), int(sp.top_k), float(sp.top_p),
+                                                     int(sp.seed) & 0x7FFFFFFFFFFFFFFF, float(sp.frequency_penalty), float(sp.presence_penalty),
+                                                     float(sp.repetition_penalty), int(sp.penalty_window), float(sp.final_logit_softcap)))
         if rc == 0:
             req.state = FINISHED
             req.finish_reason = "rejected: " + self._lib.mmh_sched_reject_reason(self._h, h).decode()
@@ -209,6 +216,16 @@ class Scheduler:
             raise SchedulerError(f"a plan of {n} entries exceeds the buffer of {self._cap}")
         self._lib.mmh_sched_plan(self._h, self._rids, self._a, self._b, self._c, self._cap)
         return [PlannedEntry(self._by_handle[self._rids[i]], self._a[i], self._b[i], bool(self._c[i])) for i in range(n)]
+
+    def last_plan(self, n: int) -> List[PlannedEntry]:
+        """The plan of the last ``schedule`` (made here or inside the library's step), ``n`` entries."""
+        if n > self._cap:
+            raise SchedulerError(f"a plan of {n} entries exceeds the buffer of {self._cap}")
+        self._lib.mmh_sched_plan(self._h, self._rids, self._a, self._b, self._c, self._cap)
+        return [PlannedEntry(self._by_handle[self._rids[i]], self._a[i], self._b[i], bool(self._c[i])) for i in range(n)]
+
+    def request_of(self, handle: int) -> Request:
+        return self._by_handle[handle]
 
     # ---- after the step ------------------------------------------------------------------
     def commit(self, plan: Sequence[PlannedEntry], sampled: Dict[Hashable, int]) -> List[Request]:

@@ -399,8 +399,14 @@ def test_a_step_that_fails_ends_its_requests_and_nothing_else(model_folders):
     """An exception out of a step: the requests in it finish with "error: ...", their pages go back, a request that was
     still waiting runs afterwards, and so does the next call."""
     from mimirmind_b200 import Engine
-    eng = Engine.from_folder(model_folders("A", "float32"), dtype="float32", cache_tokens=512, max_context=256,
-                             token_budget=64, max_active=2)
+    from mimirmind_b200.engine import native
+    old = native.ENABLED
+    try:
+        native.ENABLED = False        # the failure is injected into the Python loop's step; the library's step is failed in the next test
+        eng = Engine.from_folder(model_folders("A", "float32"), dtype="float32", cache_tokens=512, max_context=256,
+                                 token_budget=64, max_active=2)
+    finally:
+        native.ENABLED = old
     prompts = [random_tokens(256, n, n) for n in (20, 30, 10)]
     alone = [eng.generate([p], max_new_tokens=8, use_eos=False)[0].tokens for p in prompts]
     loop = eng.serve()

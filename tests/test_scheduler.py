@@ -183,7 +183,7 @@ def test_the_serving_loop_survives_a_lone_request_that_runs_out_of_pages():
 
     from mimirmind_b200.engine.engine import ServingLoop
     s, m = make(pages=3, page_size=4, budget=64, max_active=4)
-    eng = SimpleNamespace(sched_cfg=s.cfg, runner=SimpleNamespace(manager=m), use_graphs=False, eos_ids=(),
+    eng = SimpleNamespace(sched_cfg=s.cfg, runner=SimpleNamespace(manager=m, native=None, stage_dump=None), use_graphs=False, eos_ids=(),
                           decode_trace=None,
                           _run_plan=lambda plan: {p.request.id: fake_token(p.request) for p in plan if p.samples})
     loop = ServingLoop(eng)
