@@ -172,6 +172,8 @@ def main() -> int:
                     help="instead of the default run: another workload of the baseline's list through Engine.generate "
                          "(14B-shaped, 64 requests of 128..2048 prompt tokens, 256 new tokens each, continuous batching; "
                          "32B-shaped, 8 requests of 8,192 prompt tokens, 128 new tokens each)")
+    ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
+                    help="set a tunable of the library's dispatch (csrc/exec/exec.h, Options) for this run, e.g. cluster_max_wanted=64")
     ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch for the decode kernels (measured slower; for comparison)")
     args = ap.parse_args()
 
@@ -217,6 +219,10 @@ def main() -> int:
     kernel_lib.load(verbose=True)
     if args.pdl:
         kernel_lib.load().mm_set_pdl(1)
+    for item in args.opt:
+        from mimirmind_b200.engine import native as native_exec
+        name, _, value = item.partition("=")
+        native_exec.option(name, int(value))
     model = random_model(spec, seed=0, dtype="bfloat16")
     L, d, F, V = mcfg.num_hidden_layers, mcfg.hidden_size, mcfg.intermediate_size, mcfg.vocab_size
     qs, kvs = mcfg.q_size, mcfg.kv_size
