@@ -172,6 +172,7 @@ def main() -> int:
                     help="instead of the default run: another workload of the baseline's list through Engine.generate "
                          "(14B-shaped, 64 requests of 128..2048 prompt tokens, 256 new tokens each, continuous batching; "
                          "32B-shaped, 8 requests of 8,192 prompt tokens, 128 new tokens each)")
+    ap.add_argument("--mixed-portion", type=int, default=192, help="tokens of the prompt portion in the mixed step")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="set a tunable of the library's dispatch (csrc/exec/exec.h, Options) for this run, e.g. cluster_max_wanted=64")
     ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch for the decode kernels (measured slower; for comparison)")
@@ -308,6 +309,7 @@ def main() -> int:
     # The steady state of continuous batching.  "host_ms" is how long the call takes to return (the step is put
     # together and every kernel launched); "ms" is the device time between events around it.
     def mixed_run(k_steps):
+        portion = args.mixed_portion
         ids = [("mix", i) for i in range(BATCH)]
         for rid, toks in zip(ids, prompts[:BATCH]):
             prefill_once(rid, toks)
@@ -315,7 +317,7 @@ def main() -> int:
         host, dev = [], []
         for i in range(3 + k_steps):          # 192 * (3 + k_steps) tokens of the long prompt must exist
             entries = [StepEntry(rid, [int(prompts[j][i])], [0]) for j, rid in enumerate(ids)]
-            entries.append(StepEntry("mix-long", prompts[BATCH][192 * i:192 * (i + 1)], []))
+            entries.append(StepEntry("mix-long", prompts[BATCH][portion * i:portion * (i + 1)], []))
             torch.cuda.synchronize()
             a, b = ev(), ev()
             t0 = time.perf_counter()
@@ -330,7 +332,7 @@ def main() -> int:
         for rid in ids + ["mix-long"]:
             runner.release(rid)
         med = lambda v: sorted(v)[len(v) // 2]
-        return {"tokens": BATCH + 192, "decode_tokens": BATCH, "portion_tokens": 192, "ms": med(dev), "host_ms": med(host),
+        return {"tokens": BATCH + portion, "decode_tokens": BATCH, "portion_tokens": portion, "ms": med(dev), "host_ms": med(host),
                 "steps": k_steps, "launched_by": "library executor" if runner.native is not None else "python parts"}
     if args.only == "mixed":
         clocks.stop()
