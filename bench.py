@@ -175,7 +175,6 @@ def main() -> int:
     ap.add_argument("--mixed-portion", type=int, default=192, help="tokens of the prompt portion in the mixed step")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="set a tunable of the library's dispatch (csrc/exec/exec.h, Options) for this run, e.g. cluster_max_wanted=64")
-    ap.add_argument("--pdl", action="store_true", help="programmatic dependent launch for the decode kernels (measured slower; for comparison)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -218,8 +217,6 @@ def main() -> int:
     mcfg = arch.parse_config(cfg_json, "bench")
     spec = arch.build_spec(mcfg)
     kernel_lib.load(verbose=True)
-    if args.pdl:
-        kernel_lib.load().mm_set_pdl(1)
     for item in args.opt:
         from mimirmind_b200.engine import native as native_exec
         name, _, value = item.partition("=")

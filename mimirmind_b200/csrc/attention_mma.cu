@@ -295,8 +295,6 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_decode_kernel(
     __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [DEC_STAGES][64][STRIDE]
     __nv_bfloat16* sV = sK + DEC_STAGES * KT * STRIDE;               // [DEC_STAGES][64][STRIDE]
 
-    pdl_wait();
-    pdl_trigger();
     const int item = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
     const int t = items ? items[item] : item;
     const int pos = positions[t];
@@ -474,8 +472,6 @@ __global__ void attention_merge_kernel(__nv_bfloat16* __restrict__ out, const fl
                                        const float* __restrict__ part_ml, const int32_t* __restrict__ items,
                                        const int32_t* __restrict__ positions, int H, int window, int split_len,
                                        int max_splits) {
-    pdl_wait();
-    pdl_trigger();
     const int item = blockIdx.x, h = blockIdx.y;
     const int t = items ? items[item] : item;
     const int hi = positions[t] + 1;
@@ -599,14 +595,14 @@ static int launch_decode(const void* q, const void* k, const void* v, void* out,
         configured = true;
     }
     dim3 grid(n_items, G, max_splits);
-    mm_launch_pdl(attention_decode_kernel<HD>, grid, dim3(ATT_THREADS), smem, s,
+    mm_launch(attention_decode_kernel<HD>, grid, dim3(ATT_THREADS), smem, s,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)out, (float*)part_o,
         (float*)part_ml, (const int32_t*)items, (const int32_t*)positions, (const int32_t*)token_req,
         (const int32_t*)table, table_width, page_size, H, G, window, scale * LOG2E, split_len, max_splits);
     MM_CHECK_LAUNCH();
     if (max_splits > 1) {
         dim3 mgrid(n_items, H);
-        mm_launch_pdl(attention_merge_kernel<HD>, mgrid, dim3(HD >= 128 ? 128 : 64), 0, s, (__nv_bfloat16*)out, (const float*)part_o,
+        mm_launch(attention_merge_kernel<HD>, mgrid, dim3(HD >= 128 ? 128 : 64), 0, s, (__nv_bfloat16*)out, (const float*)part_o,
                                                                          (const float*)part_ml, (const int32_t*)items,
                                                                          (const int32_t*)positions, H, window, split_len,
                                                                          max_splits);
@@ -648,10 +644,10 @@ MM_EXPORT int mm_attention_decode_merge_bf16(void* out, const void* part_o, cons
     cudaStream_t s = (cudaStream_t)stream;
     dim3 mgrid(n_items, H);
     if (hd == 128)
-        mm_launch_pdl(attention_merge_kernel<128>, mgrid, dim3(128), 0, s, (__nv_bfloat16*)out, (const float*)part_o, (const float*)part_ml,
+        mm_launch(attention_merge_kernel<128>, mgrid, dim3(128), 0, s, (__nv_bfloat16*)out, (const float*)part_o, (const float*)part_ml,
                       (const int32_t*)items, (const int32_t*)positions, H, window, split_len, max_splits);
     else
-        mm_launch_pdl(attention_merge_kernel<64>, mgrid, dim3(64), 0, s, (__nv_bfloat16*)out, (const float*)part_o, (const float*)part_ml,
+        mm_launch(attention_merge_kernel<64>, mgrid, dim3(64), 0, s, (__nv_bfloat16*)out, (const float*)part_o, (const float*)part_ml,
                       (const int32_t*)items, (const int32_t*)positions, H, window, split_len, max_splits);
     MM_CHECK_LAUNCH();
     return MM_OK;

@@ -89,44 +89,16 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 
-// ---- programmatic dependent launch ------------------------------------------------------
-// The decode step is a chain of ~150 short kernels, each needing the previous one's output.
-// Launched with the programmatic-serialization attribute, a kernel's blocks may be scheduled
-// while the previous kernel is still running; they do whatever does not depend on it (a
-// weight-streaming kernel issues its first weight loads) and then block in pdl_wait() until
-// the previous grid has completed and its writes are visible.  Every kernel launched this way
-// calls pdl_wait() before its first read of activations and before any write, and
-// pdl_trigger() after it (the weight-streaming kernel: once its weights are through), so
-// never more than one kernel is ahead (triggering before the wait let a whole chain of future
-// kernels pile up on the SMs and measured 2.5x slower).  Without the attribute both are no-ops.
-// Off by default.  Measured on B200 at batch 8 (7B shapes): kernels do start 2.5-4 us before
-// their predecessor ends, but then take 2.5-4 us longer than after a plain launch: 3.36 ms
-// per step against 3.21 ms.  The cause, from recorded SM ids: after a dependent launch the blocks
-// land where the predecessor's blocks happen to leave first (the gate/up product's 296 blocks:
-// three on five SMs and one on five others instead of two everywhere), and a streaming kernel
-// with two or three blocks per SM ends with its fullest SM.  In a probe with kernels that only
-// spin, the same launch pattern hides the part before the wait completely.
-// One thread waits, the others stand at the CTA barrier: the blocks of a kernel that wait here share their SMs with
-// the running kernel and should cost it as little as possible.
-__device__ __forceinline__ void pdl_wait() {
-    if (threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
-    __syncthreads();
-}
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-extern int g_mm_pdl;   // 1: use the attribute, 0: plain launches (default)
-
+// ---- launching ------------------------------------------------------------------------------------------------------
+// A plain stream-ordered launch with the kernel's parameter types enforced.  (Programmatic dependent launch was built
+// into these kernels twice and measured slower both times on B200: the blocks of the dependent kernel land where the
+// predecessor's blocks happen to leave first, and a weight-streaming kernel ends with its fullest SM.)
 template <typename... KArgs, typename... Args>
-static inline void mm_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+static inline void mm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = g_mm_pdl ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }

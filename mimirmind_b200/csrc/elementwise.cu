@@ -21,8 +21,6 @@
 template <typename T>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int vocab, int d, float scale) {
-    pdl_wait();
-    pdl_trigger();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * d;
@@ -38,8 +36,6 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const T* __res
 // row's loads are all in flight at once (a handful of decode tokens otherwise waits for one load after the other)
 __global__ void embedding_bf16x8_kernel(const int32_t* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                         float* __restrict__ out, int vocab, int d, float scale) {
-    pdl_wait();
-    pdl_trigger();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * d;
@@ -67,12 +63,12 @@ MM_EXPORT int mm_embedding(const void* ids, const void* table, int table_dtype, 
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == MM_F32)
-        mm_launch_pdl(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const int32_t*)ids, (const float*)table, (float*)out, vocab, d, scale);
+        mm_launch(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const int32_t*)ids, (const float*)table, (float*)out, vocab, d, scale);
     else if (table_dtype == MM_BF16 && d % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0)
-        mm_launch_pdl(embedding_bf16x8_kernel, dim3(n_tokens), dim3(d >= 4096 ? 512 : (d >= 2048 ? 256 : 128)), 0, s,
+        mm_launch(embedding_bf16x8_kernel, dim3(n_tokens), dim3(d >= 4096 ? 512 : (d >= 2048 ? 256 : 128)), 0, s,
                       (const int32_t*)ids, (const __nv_bfloat16*)table, (float*)out, vocab, d, scale);
     else if (table_dtype == MM_BF16)
-        mm_launch_pdl(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const int32_t*)ids, (const __nv_bfloat16*)table, (float*)out, vocab, d, scale);
+        mm_launch(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const int32_t*)ids, (const __nv_bfloat16*)table, (float*)out, vocab, d, scale);
     else
         MM_REQUIRE(false, "embedding: table dtype must be float32 or bfloat16");
     MM_CHECK_LAUNCH();
@@ -92,8 +88,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
                                    T* __restrict__ out, int d, float eps) {
     extern __shared__ float row_cache[];
     __shared__ float red[32];
-    pdl_wait();
-    pdl_trigger();
     const int i = blockIdx.x;
     const size_t r = rows ? (size_t)rows[i] : (size_t)i;
     float* res = residual + r * d;
@@ -141,8 +135,6 @@ __global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ residual, const __
                                           const int32_t* __restrict__ rows, const WT* __restrict__ weight,
                                           __nv_bfloat16* __restrict__ out, int d, float eps) {
     __shared__ float red[32];
-    pdl_wait();
-    pdl_trigger();
     const int i = blockIdx.x;
     const size_t r = rows ? (size_t)rows[i] : (size_t)i;
     const int c = threadIdx.x * 8;
@@ -192,7 +184,7 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const int32_t*
     if constexpr (sizeof(T) == 2) {
         if (d % 8 == 0 && d <= 8192) {
             const int threads = ((d / 8 + 31) / 32) * 32;
-            mm_launch_pdl(add_rmsnorm_bf16x8_kernel<WT>, dim3(n_rows), dim3(threads), 0, s, residual, (const __nv_bfloat16*)delta, rows,
+            mm_launch(add_rmsnorm_bf16x8_kernel<WT>, dim3(n_rows), dim3(threads), 0, s, residual, (const __nv_bfloat16*)delta, rows,
                           (const WT*)weight, (__nv_bfloat16*)out, d, eps);
             MM_CHECK_LAUNCH();
             return MM_OK;
@@ -207,7 +199,7 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const int32_t*
         cudaFuncSetAttribute(add_rmsnorm_kernel<T, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     }
     const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-    mm_launch_pdl(add_rmsnorm_kernel<T, WT>, dim3(n_rows), dim3(threads), smem, s, residual, (const T*)delta, rows, (const WT*)weight, (T*)out, d, eps);
+    mm_launch(add_rmsnorm_kernel<T, WT>, dim3(n_rows), dim3(threads), smem, s, residual, (const T*)delta, rows, (const WT*)weight, (T*)out, d, eps);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
@@ -253,8 +245,6 @@ MM_EXPORT int mm_add_residual(void* residual, const void* delta, int act_dtype, 
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n, int F, int interleave) {
-    pdl_wait();
-    pdl_trigger();
     const size_t total = (size_t)n * F;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -270,8 +260,6 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 
 // 8 bf16 values per thread when F is a multiple of 8
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int n, int F, int interleave) {
-    pdl_wait();
-    pdl_trigger();
     const int F8 = F / 8;
     const size_t total = (size_t)n * F8;
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -308,11 +296,11 @@ MM_EXPORT int mm_silu_mul(const void* gu, void* out, int act_dtype, int n, int F
     if (act_dtype == MM_BF16 && F % 8 == 0) {
         const size_t work = total / 8;
         const int blocks = (int)((work + 255) / 256 < 148 * 32 ? (work + 255) / 256 : 148 * 32);
-        mm_launch_pdl(silu_mul_bf16x8_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F, interleave);
+        mm_launch(silu_mul_bf16x8_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F, interleave);
     } else {
         const int blocks = (int)((total + 255) / 256 < 148 * 32 ? (total + 255) / 256 : 148 * 32);
-        if (act_dtype == MM_F32) mm_launch_pdl(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, (float*)out, n, F, interleave);
-        else if (act_dtype == MM_BF16) mm_launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F, interleave);
+        if (act_dtype == MM_F32) mm_launch(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)gu, (float*)out, n, F, interleave);
+        else if (act_dtype == MM_BF16) mm_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n, F, interleave);
         else MM_REQUIRE(false, "silu_mul: dtype must be float32 or bfloat16");
     }
     MM_CHECK_LAUNCH();
@@ -335,8 +323,6 @@ __global__ void qkv_rope_kvwrite_kernel(const T* __restrict__ qkv, const WT* __r
                                         const int32_t* __restrict__ block_table, int table_width, int page_size,
                                         int H, int G, int hd, int rotary_dim, float theta_base) {
     extern __shared__ float cs[];  // cos[half], sin[half]
-    pdl_wait();
-    pdl_trigger();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = rotary_dim / 2;
@@ -428,8 +414,6 @@ __global__ void qkv_rope_kvwrite_bf16x8_kernel(const __nv_bfloat16* __restrict__
                                                int table_width, int page_size, int H, int G, int hd, float theta_base,
                                                int interleave) {
     extern __shared__ float cs[];  // cos[half], sin[half]
-    pdl_wait();
-    pdl_trigger();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = hd / 2;
@@ -516,8 +500,6 @@ __global__ void __launch_bounds__(384, 4) qkv_rope_tables_bf16x8_kernel(const __
                                               __nv_bfloat16* __restrict__ v_pages, const float* __restrict__ rope_table,
                                               const int32_t* __restrict__ slots, int page_size, int H, int G, int hd,
                                               int interleave) {
-    pdl_wait();
-    pdl_trigger();
     const int t = blockIdx.x;
     const int half = hd / 2;
     const float* cosv = rope_table + (size_t)t * hd;
@@ -604,11 +586,11 @@ MM_EXPORT int mm_qkv_rope_tables(const void* qkv, const void* bias, int bias_dty
     int threads = ((items + 31) / 32) * 32;
     if (threads > 384) threads = 384;          // the kernel's launch bound (40 registers: five blocks of 320 threads per SM)
     if (bias == nullptr || bias_dtype == MM_F32)
-        mm_launch_pdl(qkv_rope_tables_bf16x8_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const bf*)qkv, (const float*)bias,
+        mm_launch(qkv_rope_tables_bf16x8_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const bf*)qkv, (const float*)bias,
                       (bf*)q_out, (bf*)k_pages, (bf*)v_pages, (const float*)rope_table, (const int32_t*)slots, page_size, H, G,
                       hd, interleave);
     else if (bias_dtype == MM_BF16)
-        mm_launch_pdl(qkv_rope_tables_bf16x8_kernel<bf>, dim3(n_tokens), dim3(threads), 0, s, (const bf*)qkv, (const bf*)bias,
+        mm_launch(qkv_rope_tables_bf16x8_kernel<bf>, dim3(n_tokens), dim3(threads), 0, s, (const bf*)qkv, (const bf*)bias,
                       (bf*)q_out, (bf*)k_pages, (bf*)v_pages, (const float*)rope_table, (const int32_t*)slots, page_size, H, G,
                       hd, interleave);
     else MM_REQUIRE(false, "qkv_rope_tables: the bias must be float32 or bfloat16");
@@ -631,7 +613,7 @@ MM_EXPORT int mm_qkv_rope_kvwrite(const void* qkv, const void* bias, int bias_dt
     const size_t smem = (size_t)rotary_dim * sizeof(float);
     const int threads = 256;
 #define MM_LAUNCH_QKV(T, WT)                                                                                       \
-    mm_launch_pdl(qkv_rope_kvwrite_kernel<T, WT>, dim3(n_tokens), dim3(threads), smem, s,                           \
+    mm_launch(qkv_rope_kvwrite_kernel<T, WT>, dim3(n_tokens), dim3(threads), smem, s,                           \
         (const T*)qkv, (const WT*)bias, (T*)q_out, (T*)k_pages, (T*)v_pages, (const int32_t*)positions,            \
         (const int32_t*)token_req, (const int32_t*)block_table, table_width, page_size, H, G, hd, rotary_dim,      \
         theta_base)
@@ -639,11 +621,11 @@ MM_EXPORT int mm_qkv_rope_kvwrite(const void* qkv, const void* bias, int bias_dt
     if (act_dtype == MM_BF16 && rotary_dim == hd && hd % 16 == 0) {
         typedef __nv_bfloat16 bf;
         if (bias_dtype == MM_F32)
-            mm_launch_pdl(qkv_rope_kvwrite_bf16x8_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, (const bf*)qkv, (const float*)bias,
+            mm_launch(qkv_rope_kvwrite_bf16x8_kernel<float>, dim3(n_tokens), dim3(threads), smem, s, (const bf*)qkv, (const float*)bias,
                           (bf*)q_out, (bf*)k_pages, (bf*)v_pages, (const int32_t*)positions, (const int32_t*)token_req,
                           (const int32_t*)block_table, table_width, page_size, H, G, hd, theta_base, interleave);
         else
-            mm_launch_pdl(qkv_rope_kvwrite_bf16x8_kernel<bf>, dim3(n_tokens), dim3(threads), smem, s, (const bf*)qkv, (const bf*)bias,
+            mm_launch(qkv_rope_kvwrite_bf16x8_kernel<bf>, dim3(n_tokens), dim3(threads), smem, s, (const bf*)qkv, (const bf*)bias,
                           (bf*)q_out, (bf*)k_pages, (bf*)v_pages, (const int32_t*)positions, (const int32_t*)token_req,
                           (const int32_t*)block_table, table_width, page_size, H, G, hd, theta_base, interleave);
         MM_CHECK_LAUNCH();

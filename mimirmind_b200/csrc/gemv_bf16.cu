@@ -275,8 +275,6 @@ __device__ __forceinline__ void gemv_item(const GemvArgs& a, int item, const Gem
     } else {
         stage();
     }
-    // the weights are through: the next kernel's blocks may move in beside this one's epilogue and request theirs
-    pdl_trigger();
     asm volatile("cp.async.wait_all;\n" ::: "memory");
     // sum the K splits of each row tile in a fixed order
     const bool need_sync = a.KS > 1 || a.in_ss != nullptr || kStaged;
@@ -402,11 +400,9 @@ template <int NT, int U, int EPI>
 __global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvArgs a) {
     __shared__ GemvSmem sm;
     extern __shared__ __align__(16) float ss_s[];
-    // The weights do not depend on the previous kernel: their first loads go out before this kernel waits for
-    // it, so the stream from HBM is already running when the activations become readable.
+    // The first weight loads go out before anything else of the item is set up.
     GemvFirst<U> first;
     gemv_first_weights<U>(a, blockIdx.x, first);
-    pdl_wait();
     gemv_item<NT, U, EPI>(a, blockIdx.x, first, sm, ss_s);
 }
 
@@ -419,8 +415,8 @@ static int launch_gemv_now(const GemvArgs& a, cudaStream_t s) {
     const int tiles = a.N / 16;
     const int blocks = (tiles + a.RT - 1) / a.RT;
     const size_t smem = gemv_dynamic_smem(a);
-    if (a.M <= 8) mm_launch_pdl(gemv_bf16_kernel<1, 4, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
-    else mm_launch_pdl(gemv_bf16_kernel<2, 2, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
+    if (a.M <= 8) mm_launch(gemv_bf16_kernel<1, 4, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
+    else mm_launch(gemv_bf16_kernel<2, 2, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }

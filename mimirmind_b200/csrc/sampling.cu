@@ -79,8 +79,6 @@ __device__ int block_argmax(const float* __restrict__ row, int V, float* max_out
 }
 
 __global__ void argmax_rows_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int V) {
-    pdl_wait();
-    pdl_trigger();
     const float* row = logits + (size_t)blockIdx.x * V;
     const int idx = block_argmax(row, V, nullptr);
     if (threadIdx.x == 0) out[blockIdx.x] = idx;
@@ -89,7 +87,7 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int32_t* __
 MM_EXPORT int mm_argmax_rows(const void* logits, void* out, int R, int V, void* stream) {
     MM_REQUIRE(R >= 0 && V > 0, "argmax: bad sizes");
     if (R == 0) return MM_OK;
-    mm_launch_pdl(argmax_rows_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, (const float*)logits, (int32_t*)out, V);
+    mm_launch(argmax_rows_kernel, dim3(R), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, (const float*)logits, (int32_t*)out, V);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }
@@ -98,8 +96,6 @@ MM_EXPORT int mm_argmax_rows(const void* logits, void* out, int R, int V, void* 
 // block per row reduces the P pairs.  `part` holds R*P pairs of (float value, int index).
 __global__ void argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ part_val,
                                       int32_t* __restrict__ part_idx, int V, int P) {
-    pdl_wait();
-    pdl_trigger();
     const int r = blockIdx.y, p = blockIdx.x;
     const int chunk = (V + P - 1) / P;
     const int begin = p * chunk, end = min(V, begin + chunk);
@@ -134,8 +130,6 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, float* _
 
 __global__ void argmax_final_kernel(const float* __restrict__ part_val, const int32_t* __restrict__ part_idx,
                                     int32_t* __restrict__ out, int P) {
-    pdl_wait();
-    pdl_trigger();
     const int r = blockIdx.x, lane = threadIdx.x;
     ArgmaxPair best{-INFINITY, 0x7fffffff};
     for (int p = lane; p < P; p += 32) best = better(best, ArgmaxPair{part_val[(size_t)r * P + p], part_idx[(size_t)r * P + p]});
@@ -152,9 +146,9 @@ MM_EXPORT int mm_argmax_rows_split(const void* logits, void* out, void* part_val
     MM_REQUIRE(R >= 0 && V > 0 && P >= 1 && P <= 1024 && R <= 65535, "argmax: bad sizes");
     if (R == 0) return MM_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    mm_launch_pdl(argmax_partial_kernel, dim3(P, R), dim3(256), 0, s, (const float*)logits, (float*)part_val, (int32_t*)part_idx, V, P);
+    mm_launch(argmax_partial_kernel, dim3(P, R), dim3(256), 0, s, (const float*)logits, (float*)part_val, (int32_t*)part_idx, V, P);
     MM_CHECK_LAUNCH();
-    mm_launch_pdl(argmax_final_kernel, dim3(R), dim3(32), 0, s, (const float*)part_val, (const int32_t*)part_idx, (int32_t*)out, P);
+    mm_launch(argmax_final_kernel, dim3(R), dim3(32), 0, s, (const float*)part_val, (const int32_t*)part_idx, (int32_t*)out, P);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }

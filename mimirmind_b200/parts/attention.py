@@ -82,11 +82,33 @@ class GQAAttention(Mixer):
         self.interleaved = bool(
             fused is not None and fused[0] == self.head_dim and self.head_dim % 16 == 0 and rt.dtype == torch.bfloat16
             and self.w_qkv.dtype == torch.bfloat16 and self.w_o.dtype == torch.bfloat16 and rt.matmul != "simt")
+        if rt.dtype == torch.bfloat16:
+            self._say_what_runs_slowly(fused)
         if self.interleaved:
             rot_heads = self.num_heads + self.num_kv_heads
             self.w_qkv = ops.interleave_halves(self.w_qkv, rot_heads, self.head_dim)
             if self.b_qkv is not None:
                 self.b_qkv = ops.interleave_halves(self.b_qkv, rot_heads, self.head_dim)
+
+    _told = set()
+
+    def _say_what_runs_slowly(self, fused) -> None:
+        """One warning per head geometry that the tensor-core attention kernels or the fused projection are not built for:
+        the model still runs, correctly, on the generic kernels, far from the speed of the built-for shapes."""
+        import warnings
+        from ..kernels import attention_bf16
+        H, G, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        reasons = []
+        if not attention_bf16.supports(hd, H, G):
+            reasons.append(f"attention with head size {hd} and {H // G} query heads per KV head runs the generic kernel "
+                           "(the tensor-core kernels take head sizes 64 and 128 and up to 16 query heads per KV head)")
+        if fused is None or fused[0] != hd or hd % 16:
+            reasons.append("the position encoding is not a rotation of the whole head in steps of 16, so small steps run the projection, "
+                           "the encoding and the cache write as separate kernels")
+        key = (H, G, hd, tuple(reasons))
+        if reasons and key not in GQAAttention._told:
+            GQAAttention._told.add(key)
+            warnings.warn("mimirmind_b200: " + "; ".join(reasons), RuntimeWarning, stacklevel=3)
 
     def _encode_unfused(self, qkv: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         """A position encoding the fused kernel cannot apply: add the bias with the same kernel into contiguous
