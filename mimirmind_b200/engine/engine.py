@@ -67,6 +67,7 @@ class Engine:
         self.h2d_bytes = 0                  # bytes copied host→device / device→host by generate()
         self.d2h_bytes = 0
         self.decode_trace = None            # engine.diagnostics.DecodeTrace: a line per decode step
+        self._pinned: Dict[int, tuple] = {}
 
     @staticmethod
     def cache_tokens_that_fit(model: Model, page_size: int, max_context: int, token_budget: int, max_active: int,
@@ -189,8 +190,11 @@ class Engine:
         # If the bookkeeping finds that a request stopped (a stop id, a callback), the step already in flight is
         # still valid for the others; the stopped request's extra token is dropped.
         n = len(reqs)
-        host_in = torch.empty(n, dtype=torch.int32, pin_memory=True)
-        host_out = [torch.empty(n + 1, dtype=torch.int32, pin_memory=True) for _ in range(2)]    # the tokens and the kernels' error flag
+        # pinned buffers are kept per batch size: allocating page-locked memory takes milliseconds and waits for the device
+        if n not in self._pinned:
+            self._pinned[n] = (torch.empty(n, dtype=torch.int32, pin_memory=True),
+                               [torch.empty(n + 1, dtype=torch.int32, pin_memory=True) for _ in range(2)])    # tokens + the kernels' error flag
+        host_in, host_out = self._pinned[n]
         stream = torch.cuda.current_stream()
         alive = [True] * n
 

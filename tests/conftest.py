@@ -51,8 +51,18 @@ TINY = {
     "F": _base(vocab_size=384, hidden_size=192, intermediate_size=352, num_hidden_layers=3, num_attention_heads=6,
                num_key_value_heads=1, head_dim=32, rms_norm_eps=1e-5, rope_theta=1000000.0,
                max_position_embeddings=256, tie_word_embeddings=False, use_sliding_window=False),
+    # sizes that fit no kernel's tile: a width of 50 (rows of bfloat16 that are not 16-byte aligned), a feed-forward width of 33,
+    # a vocabulary of 77, as many KV heads as query heads
+    "G": _base(vocab_size=77, hidden_size=50, intermediate_size=33, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5,
+               head_dim=32, rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=512, tie_word_embeddings=False),
+    # 17 query heads on one KV head of size 64 (more than the tensor-core attention kernels group), one layer
+    "H": _base(vocab_size=200, hidden_size=128, intermediate_size=256, num_hidden_layers=1, num_attention_heads=17, num_key_value_heads=1,
+               head_dim=64, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=512, tie_word_embeddings=False),
+    # a head size that is no multiple of 16 (18: the fused rotary kernels refuse it, the generic ones take it)
+    "I": _base(vocab_size=64, hidden_size=72, intermediate_size=80, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+               head_dim=18, rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=512, tie_word_embeddings=False),
 }
-SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 1}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 1, "G": 6, "H": 7, "I": 8}
 
 
 @pytest.fixture(scope="session")

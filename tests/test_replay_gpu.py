@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 TOL = {"float32": dict(max_abs=3e-5, mean_abs=3e-6), "bfloat16": dict(max_abs=4e-2, mean_abs=6e-3)}
 
 LENGTHS = {"A": [5, 70, 133, 260], "B": [1, 9, 77, 300], "C": [33, 64, 150], "D": [40, 129, 257], "E": [17, 230, 301],
-           "F": [1, 9, 40, 77, 128, 200]}
+           "F": [1, 9, 40, 77, 128, 200], "G": [9, 70, 150], "H": [9, 70, 150], "I": [9, 70, 150]}
 
 
 def requests_for(name, plain_model):
