@@ -1,9 +1,9 @@
-// Paged causal prefill attention on the tcgen05 tensor cores, head size 128, bfloat16.
+// Paged causal prefill attention on the tcgen05 tensor cores, head sizes 64 and 128, bfloat16.
 //
 // One CTA per (tile of up to 128 query tokens of one request, query head).  Q stays in shared
 // memory; keys and values stream in tiles of 128 keys, fetched page by page with TMA straight
 // from the page pool (in this cache layout one page of one KV head is one contiguous
-// [page_size, 128] block).  Per key tile:
+// [page_size, head size] block).  Per key tile (head size 128; with 64 the products have half the depth or width):
 //     S  = Q K^T          tcgen05.mma 128x128x16 x 8, both operands K-major, S in tensor memory
 //     softmax             two groups of 128 threads, one thread per query row in each: group 0 takes the even
 //                         key tiles, group 1 the odd ones, each with a maximum, a sum and an O accumulator of
@@ -33,19 +33,18 @@ namespace {
 
 using namespace tc;
 
-constexpr int HD = 128;          // head size
 constexpr int BM = 128;          // query rows per CTA (tensor-memory lanes)
 constexpr int BN = 128;          // keys per tile
 constexpr int KV_STAGES = 2;
 constexpr int HALF_BYTES = 128 * 64 * 2;        // a [128 rows x 64 columns] bf16 sub-tile, 128 bytes per row
-constexpr int TILE_BYTES = 2 * HALF_BYTES;      // [128 x 128] as two column halves
+constexpr int TILE_BYTES = 2 * HALF_BYTES;      // [128 x 128] as two column halves: a tile of P
 constexpr int ATT_TC_THREADS = 384;            // K producer warp, Q K^T issuer, 8 softmax warps, V producer warp, P V issuer
 constexpr int V_PRODUCER_WARP = 10;
 constexpr int PV_ISSUER_WARP = 11;             // the two products have issuers of their own: each waits on its own barriers
 constexpr int SOFTMAX_WARPS = 8;               // two groups of four
 constexpr int GROUP_WARPS = 4;                 // barriers between the softmax warps and the tensor core count warps, not
                                                // threads: one arrival per softmax warp on one mbarrier serialise and cost more than the math
-constexpr int TMEM_COLS_ATT = 512;              // S of the even / odd tiles: columns 0..255; O of the even / odd tiles: 256..511
+constexpr int TMEM_COLS_ATT = 512;              // S of the even / odd tiles: columns 0..255; O of the even / odd tiles: from 256, head-size columns each
 constexpr float RESCALE_STEP = 8.0f;            // log2 of how far a row's maximum may run ahead of its reference
 
 struct AttCtl {
@@ -109,6 +108,7 @@ __device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
 }
 
 // tiles: int32 [n_tiles, 4] = (request index, first token row, rows in the tile (<= 128), position of the first row)
+template <int HD>
 __global__ void __launch_bounds__(ATT_TC_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                             const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
@@ -119,11 +119,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         if (threadIdx.x == 0 && err != nullptr) atomicExch(err, 3);
         return;
     }
-    unsigned char* sQ = smem_raw;                               // TILE_BYTES
-    unsigned char* sP = sQ + TILE_BYTES;                        // 2 * TILE_BYTES
-    unsigned char* sK = sP + 2 * TILE_BYTES;                    // KV_STAGES * TILE_BYTES
-    unsigned char* sV = sK + KV_STAGES * TILE_BYTES;            // KV_STAGES * TILE_BYTES
-    AttCtl* ctl = reinterpret_cast<AttCtl*>(sV + KV_STAGES * TILE_BYTES);
+    constexpr int HALVES = HD / 64;                             // 64-column halves of a row of Q, K or V
+    constexpr int HEAD_TILE_BYTES = HALVES * HALF_BYTES;        // [128 rows x head size]: a tile of Q, of keys or of values
+    unsigned char* sQ = smem_raw;                               // HEAD_TILE_BYTES
+    unsigned char* sP = sQ + HEAD_TILE_BYTES;                   // 2 * TILE_BYTES
+    unsigned char* sK = sP + 2 * TILE_BYTES;                    // KV_STAGES * HEAD_TILE_BYTES
+    unsigned char* sV = sK + KV_STAGES * HEAD_TILE_BYTES;       // KV_STAGES * HEAD_TILE_BYTES
+    AttCtl* ctl = reinterpret_cast<AttCtl*>(sV + KV_STAGES * HEAD_TILE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile int* abort_flag = &ctl->abort_flag;
 
@@ -144,7 +146,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
     // ---- what the TMA producers need: warp 0 keys (and Q), warp 10 values; lane = (page of the tile, column half) ----
     const int pages_per_tile = BN / page_size;
     const uint32_t page_bytes = (uint32_t)page_size * 128u;           // one column half of a page
-    const int pj = lane >> 1, phf = lane & 1;                         // this lane's page and half
+    const int pj = lane / HALVES, phf = lane % HALVES;                // this lane's page and half
     // pages of a tile that hold keys some row of the tile may see.  The ids are read a few tiles ahead: the load
     // from the block table would otherwise sit, with its full latency, between every two tiles.
     auto page_of = [&](int kt) -> int {
@@ -171,7 +173,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (ok && pid >= 0)
-            tma_load_2d(smem_u32((for_k ? sK : sV) + s * TILE_BYTES) + phf * HALF_BYTES + (uint32_t)pj * page_bytes, for_k ? &tmK : &tmV,
+            tma_load_2d(smem_u32((for_k ? sK : sV) + s * HEAD_TILE_BYTES) + phf * HALF_BYTES + (uint32_t)pj * page_bytes, for_k ? &tmK : &tmV,
                         phf * 64, (pid * G + g) * page_size, full);
         return ok;
     };
@@ -200,15 +202,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             // Q and the first tile of keys need nobody else: their copies go out before the CTA has set itself up
             const uint32_t qbar = smem_u32(&ctl->q_full);
-            mbar_expect_tx(qbar, TILE_BYTES);
-            tma_load_2d(smem_u32(sQ), &tmQ, h * HD, row0, qbar);
-            tma_load_2d(smem_u32(sQ) + HALF_BYTES, &tmQ, h * HD + 64, row0, qbar);
+            mbar_expect_tx(qbar, HEAD_TILE_BYTES);
+#pragma unroll
+            for (int hf = 0; hf < HALVES; ++hf) tma_load_2d(smem_u32(sQ) + hf * HALF_BYTES, &tmQ, h * HD + hf * 64, row0, qbar);
         }
         __syncwarp();
         if (kt_begin < kt_end) produce(true, kt_begin, 0, false);
     }
     // Value tiles must never hold non-finite leftovers: rows of a page that was not fetched are multiplied by P = 0.
-    for (int i = threadIdx.x; i < KV_STAGES * TILE_BYTES / 16; i += ATT_TC_THREADS) reinterpret_cast<uint4*>(sV)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < KV_STAGES * HEAD_TILE_BYTES / 16; i += ATT_TC_THREADS) reinterpret_cast<uint4*>(sV)[i] = make_uint4(0, 0, 0, 0);
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ctl->tmem_base)), "r"(TMEM_COLS_ATT) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -239,7 +241,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 if (!mbar_wait(smem_u32(&ctl->s_free[b]), (u & 1) ^ 1, abort_flag)) return false;
                 if (!mbar_wait(smem_u32(&ctl->k_full[s]), (it / KV_STAGES) & 1, abort_flag)) return false;
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(sK + s * TILE_BYTES);
+                const uint32_t k_addr = smem_u32(sK + s * HEAD_TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;      // 16 columns = 32 bytes inside the swizzled row
@@ -264,12 +266,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 if (!mbar_wait(smem_u32(&ctl->p_full[b]), u & 1, abort_flag)) break;       // P is there, O is rescaled
                 if (!mbar_wait(smem_u32(&ctl->v_full[s]), (it / KV_STAGES) & 1, abort_flag)) break;
                 tc_fence_after();
-                const uint32_t p_addr = smem_u32(sP + b * TILE_BYTES), v_addr = smem_u32(sV + s * TILE_BYTES);
+                const uint32_t p_addr = smem_u32(sP + b * TILE_BYTES), v_addr = smem_u32(sV + s * HEAD_TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k) {
                     const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;    // P: K-major over the keys
                     const uint32_t b_off = (uint32_t)k * 16 * 128;                  // V: 16 key rows of 128 bytes further
-                    umma_bf16(tmem_base + 256 + b * 128, smem_desc_sw128(p_addr + a_off, 16, 1024), smem_desc_sw128(v_addr + b_off, HALF_BYTES, 1024), IDESC_PV, (u | (uint32_t)k) ? 1u : 0u);
+                    umma_bf16(tmem_base + 256 + b * HD, smem_desc_sw128(p_addr + a_off, 16, 1024), smem_desc_sw128(v_addr + b_off, HALF_BYTES, 1024), IDESC_PV, (u | (uint32_t)k) ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&ctl->pv_done[b]));
                 umma_commit(smem_u32(&ctl->v_empty[s]));
@@ -285,7 +287,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         const bool row_valid = row < n_rows;
         const int wlo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-        const uint32_t s_addr = lane_addr + g * 128, o_addr = lane_addr + 256 + g * 128;
+        const uint32_t s_addr = lane_addr + g * 128, o_addr = lane_addr + 256 + g * HD;
         float m_ref = -INFINITY;           // the maximum the group's probabilities (and its O) are taken relative to
         float l = 0.0f;                    // the group's sum for this row, relative to m_ref
         const int n_tiles_k = kt_end - kt_begin;
@@ -328,7 +330,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
                 tc_fence_after();
                 const float alpha = scale_o ? fast_exp2((m_ref - mx) * scale_log2) : 1.0f;
 #pragma unroll 1
-                for (int c = 0; c < 8; ++c) {
+                for (int c = 0; c < HD / 16; ++c) {
                     uint32_t oreg[16];
                     tmem_ld16(o_addr + c * 16, oreg);
                     tmem_ld_wait();
@@ -366,7 +368,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
             warp_arrive(smem_u32(&ctl->p_full[g]), lane);
         }
         // Merge the two groups: every thread posts its row's (reference, sum); the row's output is
-        // (O0 f0 + O1 f1) / (l0 f0 + l1 f1) with f = 2^((m_g - m) scale); group g writes output columns 64g .. 64g + 63.
+        // (O0 f0 + O1 f1) / (l0 f0 + l1 f1) with f = 2^((m_g - m) scale); group g writes its half of the output columns.
         ctl->xchg[g][0][row] = m_ref;
         ctl->xchg[g][1][row] = l;
         warp_arrive(smem_u32(&ctl->l_full), lane);
@@ -383,20 +385,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
         if (ok && tiles1 > 0) ok = mbar_wait(smem_u32(&ctl->pv_done[1]), (uint32_t)(tiles1 - 1) & 1, abort_flag);
         tc_fence_after();
         const float inv = total > 0.0f ? 1.0f / total : 0.0f;
-        __nv_bfloat16* orow = out + ((size_t)(row0 + row) * H + h) * HD + g * 64;
+        __nv_bfloat16* orow = out + ((size_t)(row0 + row) * H + h) * HD + g * (HD / 2);
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {                              // 32 output columns at a time
+        for (int c = 0; c < HD / 64; ++c) {                        // 32 output columns at a time
             float acc[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
             if (ok && tiles0 > 0) {                                // uniform over the CTA
-                tmem_ld32_nowait(lane_addr + 256 + g * 64 + c * 32, sreg);
+                tmem_ld32_nowait(lane_addr + 256 + g * (HD / 2) + c * 32, sreg);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(sreg[i]) * f0;
             }
             if (ok && tiles1 > 0) {
-                tmem_ld32_nowait(lane_addr + 384 + g * 64 + c * 32, sreg);
+                tmem_ld32_nowait(lane_addr + 256 + HD + g * (HD / 2) + c * 32, sreg);
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(sreg[i]), f1, acc[i]);
@@ -425,41 +427,49 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __gri
 
 }  // namespace
 
-// q, out: [n_tokens, H*128] bf16; k_pages, v_pages: [num_pages, G, page_size, 128] bf16 of one layer;
+// q, out: [n_tokens, H*hd] bf16; k_pages, v_pages: [num_pages, G, page_size, hd] bf16 of one layer (hd 64 or 128);
 // tiles: int32 [n_tiles, 4] (request, first row, rows <= 128, first position).  `err`: device int set to 2 when a
 // bounded wait ran out (may be null).
 MM_EXPORT int mm_attention_prefill_tcgen05(const void* q, const void* k_pages, const void* v_pages, void* out,
                                            const void* tiles, int n_tiles, const void* block_table, int table_width,
                                            int page_size, int num_pages, int n_tokens, int H, int G, int hd, int window,
                                            float scale, void* err, void* stream) {
-    MM_REQUIRE(hd == 128, "attention_prefill_tcgen05: built for head_dim 128");
+    MM_REQUIRE(hd == 128 || hd == 64, "attention_prefill_tcgen05: built for head sizes 64 and 128");
     MM_REQUIRE(n_tiles >= 0 && H > 0 && G > 0 && H % G == 0 && n_tokens > 0 && num_pages > 0, "attention_prefill_tcgen05: bad sizes");
     MM_REQUIRE(page_size >= 8 && page_size <= 128 && (128 % page_size) == 0, "attention_prefill_tcgen05: page_size must be 8, 16, 32, 64 or 128");
     MM_REQUIRE(table_width > 0 && window >= 0, "attention_prefill_tcgen05: bad table or window");
     if (n_tiles == 0) return MM_OK;
     CUtensorMap tq, tk, tv;
     const long long pool_rows = (long long)num_pages * G * page_size;
-    if (!tc::make_map_bf16(&tq, q, n_tokens, H * 128, (long long)H * 128, 128) ||
-        !tc::make_map_bf16(&tk, k_pages, pool_rows, 128, 128, page_size) ||
-        !tc::make_map_bf16(&tv, v_pages, pool_rows, 128, 128, page_size)) {
+    if (!tc::make_map_bf16(&tq, q, n_tokens, H * hd, (long long)H * hd, 128) ||
+        !tc::make_map_bf16(&tk, k_pages, pool_rows, hd, hd, page_size) ||
+        !tc::make_map_bf16(&tv, v_pages, pool_rows, hd, hd, page_size)) {
         mm_set_last_error("attention_prefill_tcgen05: cuTensorMapEncodeTiled failed or is not available");
         return MM_ERR_DRIVER;
     }
-    const size_t smem = (size_t)(3 + 2 * KV_STAGES) * TILE_BYTES + sizeof(AttCtl);
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    const int halves = hd / 64;
+    const size_t smem = (size_t)(halves + 4 + 2 * KV_STAGES * halves) * HALF_BYTES + sizeof(AttCtl);
+    static bool configured[2] = {false, false};
+    if (!configured[halves - 1]) {
+        const cudaError_t e = hd == 128 ? cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                        : cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
             mm_set_last_error("attention_prefill_tcgen05: cannot reserve shared memory");
             return MM_ERR_LAUNCH;
         }
-        configured = true;
+        configured[halves - 1] = true;
     }
     const float LOG2E = 1.4426950408889634f;
     MM_REQUIRE(n_tiles <= 65535, "attention_prefill_tcgen05: more than 65535 tiles in one launch");
     dim3 grid(H, n_tiles);
-    attention_prefill_tc_kernel<<<grid, ATT_TC_THREADS, smem, (cudaStream_t)stream>>>(
-        tq, tk, tv, (__nv_bfloat16*)out, (const int32_t*)tiles, (const int32_t*)block_table, table_width, page_size, H, G,
-        window, scale * LOG2E, (int*)err);
+    if (hd == 128)
+        attention_prefill_tc_kernel<128><<<grid, ATT_TC_THREADS, smem, (cudaStream_t)stream>>>(
+            tq, tk, tv, (__nv_bfloat16*)out, (const int32_t*)tiles, (const int32_t*)block_table, table_width, page_size, H, G,
+            window, scale * LOG2E, (int*)err);
+    else
+        attention_prefill_tc_kernel<64><<<grid, ATT_TC_THREADS, smem, (cudaStream_t)stream>>>(
+            tq, tk, tv, (__nv_bfloat16*)out, (const int32_t*)tiles, (const int32_t*)block_table, table_width, page_size, H, G,
+            window, scale * LOG2E, (int*)err);
     MM_CHECK_LAUNCH();
     return MM_OK;
 }

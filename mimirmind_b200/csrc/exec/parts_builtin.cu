@@ -159,7 +159,7 @@ struct GQAAttention : Mixer {
         if (!uses_plan(st) || !cache || st.plans.count(plan_key())) return;
         const Options& o = options();
         auto plan = std::make_shared<AttentionPlan>();
-        const bool tc = o.use_tcgen05_prefill && hd == 128 && (tma_page(st.page_size) || st.page_size == 128);
+        const bool tc = o.use_tcgen05_prefill && (hd == 128 || hd == 64) && (tma_page(st.page_size) || st.page_size == 128);
         plan->tile_rows = tc ? 128 : 64;
         struct Tile {
             int r, first, rows, pos;

@@ -20,7 +20,7 @@ from .lib import check
 
 PREFILL_MIN = 16       # shorter portions go token by token through the decode kernel
 TILE_ROWS = 64         # query rows per CTA of the mma.sync prefill kernel
-TILE_ROWS_TC = 128     # ... of the tcgen05 prefill kernel (head size 128)
+TILE_ROWS_TC = 128     # ... of the tcgen05 prefill kernel
 USE_TCGEN05_PREFILL = True
 USE_TMA_DECODE = True   # decode attention with a TMA producer warp (page sizes 8..64)
 TMA_DECODE_STAGES = 3
@@ -99,7 +99,7 @@ def choose_split(n_items: int, num_kv_heads: int, max_kv_len: int, head_dim: int
 
 
 def tcgen05_prefill_usable(head_dim: int, page_size: int) -> bool:
-    return USE_TCGEN05_PREFILL and head_dim == 128 and page_size in (8, 16, 32, 64, 128)
+    return USE_TCGEN05_PREFILL and head_dim in (64, 128) and page_size in (8, 16, 32, 64, 128)
 
 
 def make_plan(ctx, num_heads: int, num_kv_heads: int, head_dim: int) -> AttentionPlan:
