@@ -199,7 +199,7 @@ def main() -> int:
         return run_workload(args.workload, args.layers)
 
     import torch
-    from mimirmind_b200.engine.decode_graph import DecodeSession
+    from mimirmind_b200.engine.decode_graph import decode_session
     from mimirmind_b200.engine.engine import Engine
     from mimirmind_b200.engine.loader import random_model
     from mimirmind_b200.engine.runner import StepEntry
@@ -280,7 +280,7 @@ def main() -> int:
         for rid, toks in zip(ids, prompts[:batch]):
             lg = prefill_once(rid, toks)
             firsts.append(int(lg.argmax(-1).item()))
-        sess = DecodeSession(runner, batch, CONTEXT, greedy=True, feed_back=True)
+        sess = decode_session(runner, batch, CONTEXT, greedy=True, feed_back=True)
         sess.bind(ids, w_steps + k_steps, firsts)
         before = kernel_lib.launch_count()
         sess.step()                                   # eager + capture: the step's kernels are launched twice

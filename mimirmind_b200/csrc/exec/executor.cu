@@ -475,6 +475,12 @@ class Executor {
     }
 
   public:
+    void* error_flag_device() const { return err_; }
+    void* cache() const { return cache_; }
+    int page_size() const { return page_size_; }
+    int vocab() const { return vocab_; }
+    std::vector<Event>& events_buffer() { return events_; }
+
     int take_error_flag() {
         const int v = *err_host_;
         *err_host_ = 0;
@@ -501,6 +507,259 @@ class Executor {
     float* own_logits_ = nullptr;
     std::vector<Event> events_;
     int planned_ = 0;
+};
+
+
+// ---- steady-state decoding of a fixed set of requests as one replayed CUDA graph ---------------------------------------------------
+// When every running request is decoding, a step is the same launches with the same shapes each time: only token ids,
+// positions and block-table entries change, and they live in device buffers that the graph reads.  The step (forward,
+// penalties, sampling, position advance) is captured once and replayed; pages for a number of steps (the horizon) are
+// reserved at binding, so no host work is needed between replays except committing lengths.  The reference has graph
+// replay of its decode blocks as an opt-in (src/runtime/InferenceEngine.cpp:1826-1842, 1944-1998).
+class DecodeSession {
+  public:
+    DecodeSession(Executor* ex, void* cache, int n_groups, int page_size, int vocab, int batch, int kv_bound, bool greedy, bool feed_back, int window)
+        : ex_(ex), cache_(cache), G_(n_groups), ps_(page_size), V_(vocab), b_(batch), bound_(kv_bound), greedy_(greedy), feed_back_(feed_back), W_(window) {
+        width_ = std::max(1, (bound_ + ps_ - 1) / ps_);
+        parts_ = V_ > 16384 ? std::min(256, (V_ + 4095) / 4096) : 0;
+        auto pad = [](size_t n) { return (n + 63) & ~(size_t)63; };
+        // one block of device memory: 64-bit values first, then 32-bit ones
+        size_t off = 0;
+        auto take = [&](size_t bytes) { const size_t at = off; off += pad(bytes); return at; };
+        const size_t o_seeds = take(8 * b_), o_counters = take(8 * b_), o_lengths = take(8 * b_), o_ids = take(4 * b_), o_pos = take(4 * b_),
+                     o_req = take(4 * b_), o_out = take(4 * (b_ + 1)), o_topk = take(4 * b_), o_widths = take(4 * b_), o_temp = take(4 * b_),
+                     o_topp = take(4 * b_), o_pen = take(16 * b_), o_recent = take(4 * (size_t)b_ * std::max(W_, 1)),
+                     o_tables = take(4 * (size_t)G_ * b_ * width_), o_pv = take(4 * (size_t)b_ * std::max(parts_, 1)),
+                     o_pi = take(4 * (size_t)b_ * std::max(parts_, 1)), o_logits = take(4 * (size_t)b_ * V_);
+        check_cuda(cudaMalloc((void**)&mem_, off), "decode session memory");
+        check_cuda(cudaMemset(mem_, 0, off - pad(4 * (size_t)b_ * V_)), "decode session memory");
+        seeds_ = (long long*)(mem_ + o_seeds); counters_ = (long long*)(mem_ + o_counters); lengths_ = (long long*)(mem_ + o_lengths);
+        ids_ = (int*)(mem_ + o_ids); pos_ = (int*)(mem_ + o_pos); req_ = (int*)(mem_ + o_req); out_ = (int*)(mem_ + o_out);
+        topk_ = (int*)(mem_ + o_topk); widths_ = (int*)(mem_ + o_widths); temp_ = (float*)(mem_ + o_temp); topp_ = (float*)(mem_ + o_topp);
+        pen_ = (float*)(mem_ + o_pen); recent_ = (int*)(mem_ + o_recent); tables_ = (int*)(mem_ + o_tables);
+        part_val_ = (float*)(mem_ + o_pv); part_idx_ = (int*)(mem_ + o_pi); logits_ = (float*)(mem_ + o_logits);
+        std::vector<int> ar(b_);
+        for (int i = 0; i < b_; ++i) ar[i] = i;
+        check_cuda(cudaMemcpy(req_, ar.data(), 4 * b_, cudaMemcpyHostToDevice), "decode session set-up");
+        q_start_ = ar;
+        q_len_.assign(b_, 1);
+        kv_len_.assign(b_, bound_);
+        // pinned: the step's results (tokens, then the kernels' error flag) twice, the tokens fed back, and what a binding uploads
+        const size_t up = (size_t)G_ * b_ * width_ + (size_t)b_ * (std::max(W_, 1) + 24);
+        check_cuda(cudaMallocHost((void**)&pin_, 4 * (3 * (size_t)(b_ + 1) + up)), "decode session pinned memory");
+        pin_out_[0] = pin_;
+        pin_out_[1] = pin_ + (b_ + 1);
+        pin_in_ = pin_ + 2 * (b_ + 1);
+        pin_up_ = pin_ + 3 * (b_ + 1);
+        check_cuda(cudaStreamCreateWithFlags(&capture_stream_, cudaStreamNonBlocking), "decode session stream");
+    }
+    ~DecodeSession() {
+        if (graph_) cudaGraphExecDestroy(graph_);
+        if (capture_stream_) cudaStreamDestroy(capture_stream_);
+        if (pin_) cudaFreeHost(pin_);
+        if (mem_) cudaFree(mem_);
+    }
+
+    // Points the session at `rids` for `horizon` steps.  Returns 0; 1 when the pages for the horizon are not free (nothing
+    // changed); 2 when a request would outgrow the bound the session was made for.
+    int bind(const long long* rids, int horizon, const int* first_tokens, const float* temperature, const int* top_k, const float* top_p,
+             const long long* seeds, const long long* counters, const int* recent, const int* widths, const long long* lengths, const float* pen,
+             cudaStream_t s) {
+        std::vector<int> len(b_), need(std::max(G_, 1), 0), one(std::max(G_, 1));
+        for (int i = 0; i < b_; ++i) {
+            len[i] = mmh_cache_request(cache_, rids[i], 0);
+            if (len[i] < 0) throw ExecError(mmh_last_error());
+            if (len[i] + horizon > bound_) return 2;
+        }
+        for (int i = 0; i < b_; ++i) {
+            if (mmh_cache_pages_needed(cache_, rids[i], len[i] + horizon, one.data()) != 0) throw ExecError(mmh_last_error());
+            for (int g = 0; g < G_; ++g) need[g] += one[g];
+        }
+        for (int g = 0; g < G_; ++g)
+            if (need[g] > mmh_cache_info(cache_, 3, g)) return 1;
+        for (int i = 0; i < b_; ++i)
+            if (mmh_cache_reserve(cache_, rids[i], len[i] + horizon) != 1) throw ExecError("decode session: reserving checked pages failed");
+        rids_.assign(rids, rids + b_);
+        alive_.assign(b_, 1);
+        horizon_ = horizon;
+        done_ = 0;
+        // one pinned block, copied piece by piece (a binding is rare)
+        check_cuda(cudaStreamSynchronize(s), "decode session bind");       // the pinned block may still be read by an earlier copy
+        int* h = pin_up_;
+        auto up = [&](void* dst, const void* src, size_t bytes) {
+            std::memcpy(h, src, bytes);
+            check_cuda(cudaMemcpyAsync(dst, h, bytes, cudaMemcpyHostToDevice, s), "decode session bind");
+            h += (bytes + 7) / 8 * 2;
+        };
+        for (int g = 0; g < G_; ++g) {
+            if (mmh_cache_tables(cache_, g, b_, rids, width_, h) != 0) throw ExecError(mmh_last_error());
+            check_cuda(cudaMemcpyAsync(tables_ + (size_t)g * b_ * width_, h, 4 * (size_t)b_ * width_, cudaMemcpyHostToDevice, s), "decode session bind");
+            h += ((size_t)b_ * width_ + 1) / 2 * 2;
+        }
+        up(pos_, len.data(), 4 * b_);
+        up(ids_, first_tokens, 4 * b_);
+        if (!greedy_) {
+            if (!temperature || !top_k || !top_p || !seeds || !counters) throw ExecError("decode session: a sampling session needs the sampling parameters");
+            up(temp_, temperature, 4 * b_);
+            up(topk_, top_k, 4 * b_);
+            up(topp_, top_p, 4 * b_);
+            up(seeds_, seeds, 8 * b_);
+            up(counters_, counters, 8 * b_);
+        }
+        if (W_ > 0) {
+            if (!recent || !widths || !lengths || !pen) throw ExecError("decode session: a session with penalties needs the recent tokens");
+            check_cuda(cudaStreamSynchronize(s), "decode session bind");
+            h = pin_up_;
+            up(recent_, recent, 4 * (size_t)b_ * W_);
+            up(widths_, widths, 4 * b_);
+            up(lengths_, lengths, 8 * b_);
+            up(pen_, pen, 16 * b_);
+        }
+        check_cuda(cudaStreamSynchronize(s), "decode session bind");
+        return 0;
+    }
+
+    // one decode step for every bound request: launched eagerly the first time (and then captured), replayed afterwards
+    void step(cudaStream_t s) {
+        if (done_ >= horizon_) throw ExecError("decode session is past its horizon");
+        if (!graph_) {
+            launch(s);                               // a valid step of its own, and the warm-up of every kernel and workspace
+            check_cuda(cudaStreamSynchronize(s), "decode session warm-up");
+            check_cuda(cudaStreamBeginCapture(capture_stream_, cudaStreamCaptureModeThreadLocal), "decode session capture");
+            cudaGraph_t graph = nullptr;
+            try {
+                launch(capture_stream_);             // records the launches; nothing runs, the buffers keep their contents
+            } catch (...) {
+                cudaStreamEndCapture(capture_stream_, &graph);
+                if (graph) cudaGraphDestroy(graph);
+                throw;
+            }
+            check_cuda(cudaStreamEndCapture(capture_stream_, &graph), "decode session capture");
+            const cudaError_t e = cudaGraphInstantiate(&graph_, graph, 0);
+            cudaGraphDestroy(graph);
+            check_cuda(e, "decode session graph");
+        } else {
+            check_cuda(cudaGraphLaunch(graph_, s), "decode session replay");
+        }
+        for (long long rid : rids_)
+            if (mmh_cache_has(cache_, rid)) {        // a request may have been retired while this step was already in flight
+                const int n = mmh_cache_request(cache_, rid, 0);
+                if (mmh_cache_commit(cache_, rid, n + 1) != 0) throw ExecError(mmh_last_error());
+            }
+        ++done_;
+    }
+
+    // starts the copy of the step's results (tokens and error flag) into pinned buffer `which`
+    void read_out(int which, cudaStream_t s) {
+        check_cuda(cudaMemcpyAsync(pin_out_[which], out_, 4 * (b_ + 1), cudaMemcpyDeviceToHost, s), "reading the sampled tokens");
+    }
+
+    // The loop of a decode run, one call per step: waits for the step in flight, launches the next one with that step's
+    // tokens copied back from pinned memory as its inputs, and accounts for the finished step in the scheduler (tokens
+    // appended, finished requests retired).  out_tokens[b], out_done[b] (1: finished with this token, -1: not accounted,
+    // the request had left earlier).  Returns 1 if a request finished in this step, else 0.
+    int cycle(void* sched, bool launch_next, int* out_tokens, int* out_done, std::vector<Executor::Event>* events, cudaStream_t s) {
+        check_cuda(cudaStreamSynchronize(s), "waiting for the decode step");
+        const int* got = pin_out_[cur_];
+        if (got[b_] != 0) {
+            cudaMemsetAsync(ex_->error_flag_device(), 0, sizeof(int), s);
+            throw ExecError("a kernel of the decode step gave up waiting on its pipeline; the step's output is not valid");
+        }
+        for (int i = 0; i < b_; ++i)
+            if (got[i] < 0 || got[i] >= V_) throw ExecError("the sampler returned a token outside the vocabulary");
+        std::memcpy(out_tokens, got, 4 * b_);
+        if (launch_next && done_ < horizon_) {
+            if (!feed_back_) {
+                std::memcpy(pin_in_, got, 4 * b_);
+                check_cuda(cudaMemcpyAsync(ids_, pin_in_, 4 * b_, cudaMemcpyHostToDevice, s), "feeding the tokens back");      // next step's inputs, from pinned memory
+            }
+            step(s);
+            read_out(cur_ ^ 1, s);
+        }
+        cur_ ^= 1;
+        int stop = 0;
+        for (int i = 0; i < b_; ++i) {
+            out_done[i] = -1;
+            if (!alive_[i]) continue;
+            out_done[i] = 0;
+            if (sched != nullptr) {
+                const int rc = mmh_sched_accept_token(sched, rids_[i], out_tokens[i]);
+                if (rc < 0) throw ExecError(mmh_last_error());
+                long long r[8];
+                int k[8], c[8];
+                const int n = mmh_sched_events(sched, r, k, c, 8);
+                for (int j = 0; j < n && j < 8; ++j) events->push_back({r[j], k[j], c[j]});
+                if (rc == 1) {
+                    out_done[i] = 1;
+                    alive_[i] = 0;
+                    stop = 1;
+                }
+            }
+        }
+        return stop;
+    }
+
+    void begin(cudaStream_t s) {
+        cur_ = 0;
+        step(s);
+        read_out(0, s);
+    }
+    void drop(int i) {
+        if (i >= 0 && i < b_) alive_[i] = 0;
+    }
+    int remaining() const { return horizon_ - done_; }
+    int steps_done() const { return done_; }
+    bool captured() const { return graph_ != nullptr; }
+    int* device_tokens() { return out_; }
+    int* device_inputs() { return ids_; }
+
+  private:
+    void launch(cudaStream_t s) {
+        StepDesc d{};
+        d.n_tokens = d.n_requests = d.n_logit_rows = b_;
+        d.max_kv_len = bound_;
+        d.max_q_len = 1;
+        d.table_width = width_;
+        d.token_ids = ids_;
+        d.positions = pos_;
+        d.token_req = req_;
+        d.logit_rows = req_;
+        for (int g = 0; g < G_; ++g) d.tables[g] = tables_ + (size_t)g * b_ * width_;
+        d.q_start = q_start_.data();
+        d.q_len = q_len_.data();
+        d.kv_len = kv_len_.data();
+        ex_->forward_described(d, logits_, s);
+        if (W_ > 0) check_kernel(mm_apply_penalties(logits_, b_, V_, recent_, W_, pen_, pen_ + b_, pen_ + 2 * b_, pen_ + 3 * b_, s), "apply_penalties");
+        if (greedy_) {
+            if (parts_ > 0) check_kernel(mm_argmax_rows_split(logits_, out_, part_val_, part_idx_, b_, V_, parts_, s), "argmax_rows_split");
+            else check_kernel(mm_argmax_rows(logits_, out_, b_, V_, s), "argmax_rows");
+        } else {
+            check_kernel(mm_sample_rows(logits_, out_, b_, V_, temp_, topk_, topp_, seeds_, counters_, s), "sample_rows");
+        }
+        if (W_ > 0) check_kernel(mm_window_push(recent_, b_, W_, widths_, lengths_, out_, s), "window_push");
+        check_kernel(mm_advance_step(pos_, greedy_ ? nullptr : counters_, feed_back_ ? ids_ : nullptr, out_, b_, s), "advance_step");
+        check_cuda(cudaMemcpyAsync(out_ + b_, ex_->error_flag_device(), sizeof(int), cudaMemcpyDeviceToDevice, s), "copying the error flag");
+    }
+
+    Executor* ex_;
+    void* cache_;
+    int G_, ps_, V_, b_, bound_;
+    bool greedy_, feed_back_;
+    int W_, width_ = 1, parts_ = 0, horizon_ = 0, done_ = 0, cur_ = 0;
+    char* mem_ = nullptr;
+    long long *seeds_ = nullptr, *counters_ = nullptr, *lengths_ = nullptr;
+    int *ids_ = nullptr, *pos_ = nullptr, *req_ = nullptr, *out_ = nullptr, *topk_ = nullptr, *widths_ = nullptr, *recent_ = nullptr, *tables_ = nullptr,
+        *part_idx_ = nullptr;
+    float *temp_ = nullptr, *topp_ = nullptr, *pen_ = nullptr, *part_val_ = nullptr, *logits_ = nullptr;
+    int* pin_ = nullptr;
+    int* pin_out_[2] = {nullptr, nullptr};
+    int* pin_in_ = nullptr;
+    int* pin_up_ = nullptr;
+    std::vector<int> q_start_, q_len_, kv_len_;
+    std::vector<long long> rids_;
+    std::vector<char> alive_;
+    cudaStream_t capture_stream_ = nullptr;
+    cudaGraphExec_t graph_ = nullptr;
 };
 
 }  // namespace mmx
@@ -617,6 +876,50 @@ MMX_EXPORT int mmx_exec_events(void* ex, long long* rids, int* kinds, int* codes
         codes[i] = ev[i].code;
     }
     return n;
+}
+
+// ---- decode sessions: see DecodeSession above.  Codes: 0 ok, -1 error (mmx_last_error), bind: 1 no pages, 2 beyond the bound ----
+MMX_EXPORT void* mmx_decode_create(void* ex, int batch, int kv_bound, int greedy, int feed_back, int penalty_window) {
+    try {
+        Executor* e = static_cast<Executor*>(ex);
+        return new DecodeSession(e, e->cache(), e->n_groups(), e->page_size(), e->vocab(), batch, kv_bound, greedy != 0, feed_back != 0, penalty_window);
+    } catch (const std::exception& e) {
+        g_mmx_error = e.what();
+        return nullptr;
+    }
+}
+MMX_EXPORT void mmx_decode_destroy(void* sess) { delete static_cast<DecodeSession*>(sess); }
+MMX_EXPORT int mmx_decode_bind(void* sess, const long long* rids, int horizon, const int* first_tokens, const float* temperature, const int* top_k,
+                               const float* top_p, const long long* seeds, const long long* counters, const int* recent, const int* widths,
+                               const long long* lengths, const float* pen, void* stream) {
+    MMX_GUARD(return static_cast<DecodeSession*>(sess)->bind(rids, horizon, first_tokens, temperature, top_k, top_p, seeds, counters, recent, widths,
+                                                             lengths, pen, (cudaStream_t)stream);)
+}
+// one step (launch or replay, lengths committed); the tokens stay on the device
+MMX_EXPORT int mmx_decode_step(void* sess, void* stream) {
+    MMX_GUARD(static_cast<DecodeSession*>(sess)->step((cudaStream_t)stream); return 0;)
+}
+// the first step of a run whose results come back through mmx_decode_cycle
+MMX_EXPORT int mmx_decode_begin(void* sess, void* stream) {
+    MMX_GUARD(static_cast<DecodeSession*>(sess)->begin((cudaStream_t)stream); return 0;)
+}
+// One turn of the decode loop: waits for the step in flight, launches the next (launch_next != 0 and steps are left), accounts
+// for the finished one in `sched` (may be null).  Returns 1 if a request finished with this step, 0 if none, -1 on an error.
+// What happened to requests is read with mmx_exec_events of the executor the session belongs to.
+MMX_EXPORT int mmx_decode_cycle(void* ex, void* sess, void* sched, int launch_next, int* out_tokens, int* out_done, void* stream) {
+    MMX_GUARD(auto& ev = static_cast<Executor*>(ex)->events_buffer(); ev.clear();
+              return static_cast<DecodeSession*>(sess)->cycle(sched, launch_next != 0, out_tokens, out_done, &ev, (cudaStream_t)stream);)
+}
+MMX_EXPORT void mmx_decode_drop(void* sess, int index) { static_cast<DecodeSession*>(sess)->drop(index); }
+// what: 0 steps left of the horizon, 1 steps done since the binding, 2 whether the step has been captured
+MMX_EXPORT int mmx_decode_info(void* sess, int what) {
+    DecodeSession* d = static_cast<DecodeSession*>(sess);
+    return what == 0 ? d->remaining() : (what == 1 ? d->steps_done() : (d->captured() ? 1 : 0));
+}
+// device int32 arrays of the session: 0 the step's tokens [batch] (then the error flag), 1 the next step's input ids [batch]
+MMX_EXPORT void* mmx_decode_buffer(void* sess, int what) {
+    DecodeSession* d = static_cast<DecodeSession*>(sess);
+    return what == 0 ? (void*)d->device_tokens() : (void*)d->device_inputs();
 }
 
 // The kernels' error flag as the last mmx_exec_run copied it back (valid once the stream has been synchronised); reading clears it.

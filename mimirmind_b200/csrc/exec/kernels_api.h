@@ -83,6 +83,8 @@ int mm_argmax_rows(const void* logits, void* out, int R, int V, void* stream);
 int mm_argmax_rows_split(const void* logits, void* out, void* part_val, void* part_idx, int R, int V, int P, void* stream);
 int mm_sample_rows(const void* logits, void* out, int R, int V, const void* temperature, const void* top_k, const void* top_p,
                    const void* seeds, const void* counters, void* stream);
+int mm_window_push(void* recent, int R, int W, const void* widths, void* lengths, const void* tokens, void* stream);
+int mm_advance_step(void* positions, void* counters, void* next_ids, const void* tokens, int n, void* stream);
 int mm_apply_penalties(void* logits, int R, int V, const void* recent, int W, const void* rep, const void* freq,
                        const void* pres, const void* softcap, void* stream);
 }

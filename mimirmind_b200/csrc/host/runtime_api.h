@@ -22,6 +22,7 @@ int mmh_sched_tokens(void* sched, long long rid, int start, int count, int* out)
 long long mmh_sched_request(void* sched, long long rid, int what);
 int mmh_sched_events(void* sched, long long* rids, int* kinds, int* codes, int cap);
 int mmh_sched_get_sampling(void* sched, long long rid, float* f6, int* i4, long long* seed);
+int mmh_sched_accept_token(void* sched, long long rid, int token);    // 1: the request finished, 0: it goes on
 int mmh_sched_commit(void* sched, int n, const long long* rids, const int* starts, const int* counts, const int* samples,
                      const int* sampled);
 }

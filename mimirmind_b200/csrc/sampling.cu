@@ -641,6 +641,26 @@ MM_EXPORT int mm_window_push(void* recent, int R, int W, const void* widths, voi
     return MM_OK;
 }
 
+// After a decode step: every request's position moves on by one, its draw counter too (null: no counters), and the
+// sampled tokens become the next step's inputs (null: the caller feeds them).
+__global__ void advance_step_kernel(int32_t* __restrict__ positions, long long* __restrict__ counters, int32_t* __restrict__ next_ids,
+                                    const int32_t* __restrict__ tokens, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    positions[i] += 1;
+    if (counters != nullptr) counters[i] += 1;
+    if (next_ids != nullptr) next_ids[i] = tokens[i];
+}
+
+MM_EXPORT int mm_advance_step(void* positions, void* counters, void* next_ids, const void* tokens, int n, void* stream) {
+    MM_REQUIRE(n >= 0 && positions != nullptr && (next_ids == nullptr || tokens != nullptr), "advance_step: bad arguments");
+    if (n == 0) return MM_OK;
+    advance_step_kernel<<<(n + 127) / 128, 128, 0, (cudaStream_t)stream>>>((int32_t*)positions, (long long*)counters, (int32_t*)next_ids,
+                                                                          (const int32_t*)tokens, n);
+    MM_CHECK_LAUNCH();
+    return MM_OK;
+}
+
 // uniform number of (seed, counter), exported so the host-side plain sampler draws the same stream
 MM_EXPORT float mm_uniform_from(unsigned long long seed, unsigned long long counter) {
     return (float)(mix64(seed, counter) >> 40) * (1.0f / 16777216.0f);

@@ -26,6 +26,14 @@ from .capture import capture
 from .runner import ModelRunner
 
 
+def decode_session(runner: ModelRunner, batch: int, kv_bound: int, greedy: bool = True, feed_back: bool = True, penalty_window: int = 0):
+    """A decode session for ``runner``: the library's own (capture, replay and the loop's turn inside the library) when the
+    runner steps in the library, else the one of this module, which launches through the Python part classes."""
+    if runner.native is not None:
+        return LibraryDecodeSession(runner, batch, kv_bound, greedy, feed_back, penalty_window)
+    return DecodeSession(runner, batch, kv_bound, greedy, feed_back, penalty_window)
+
+
 def context_bound(n: int, floor: int = 256) -> int:
     """Smallest power of two >= n (at least ``floor``): the bucket a session's buffers are sized for."""
     b = floor
@@ -190,3 +198,117 @@ class DecodeSession:
 
     def remaining(self) -> int:
         return self.horizon - self.steps_done
+
+
+class LibraryDecodeSession:
+    """The same session inside the library (csrc/exec/executor.cu, DecodeSession): buffers, capture with the CUDA runtime's
+    stream capture, replay, commit of the lengths, and one call per turn of the decode loop (``cycle``: wait for the step in
+    flight, feed its tokens back, launch the next, account for the finished one in the scheduler)."""
+
+    def __init__(self, runner: ModelRunner, batch: int, kv_bound: int, greedy: bool = True, feed_back: bool = True,
+                 penalty_window: int = 0):
+        import ctypes
+
+        import numpy as np
+
+        from . import native as nat
+        self._np, self._ct = np, ctypes
+        self.runner, self.batch = runner, batch
+        self.kv_bound = min(kv_bound, runner.max_seq_len)
+        self.greedy, self.feed_back, self.penalty_window = greedy, feed_back, penalty_window
+        self._lib = nat._declare()
+        self._exec = runner.native._exec
+        self._h = self._lib.mmx_decode_create(self._exec, batch, self.kv_bound, int(greedy), int(feed_back), penalty_window)
+        if not self._h:
+            raise ops.KernelError(f"the decode session could not be created: {nat.last_error()}")
+        self._last_error = nat.last_error
+        self._toks = (ctypes.c_int * batch)()
+        self._done = (ctypes.c_int * batch)()
+        self.ids: List[Hashable] = []
+        self.horizon = 0
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.mmx_decode_destroy(self._h)
+            self._h = None
+
+    def bind(self, request_ids: Sequence[Hashable], horizon: int, first_tokens: Sequence[int],
+             sampling: Optional[Sequence[SamplingParams]] = None, draw_counters: Optional[Sequence[int]] = None,
+             histories: Optional[Sequence[Sequence[int]]] = None) -> None:
+        """As DecodeSession.bind: MemoryError when the pages for the horizon are not free, ValueError beyond the bound."""
+        np, mgr, b = self._np, self.runner.manager, self.batch
+        if len(request_ids) != b:
+            raise ValueError("wrong number of requests for this session")
+        rids = np.asarray([mgr.handle(r) for r in request_ids], dtype=np.int64)
+        firsts = np.asarray(list(first_tokens), dtype=np.int32)
+        keep = [rids, firsts]
+        ptr = lambda a: a.ctypes.data if a is not None else None
+        temp = topk = topp = seeds = counters = recent = widths = lengths = pen = None
+        if not self.greedy:
+            params = list(sampling)
+            temp = np.asarray([0.0 if p.greedy else p.temperature for p in params], dtype=np.float32)
+            topk = np.asarray([p.top_k for p in params], dtype=np.int32)
+            topp = np.asarray([p.top_p for p in params], dtype=np.float32)
+            seeds = np.asarray([p.seed & 0x7FFFFFFFFFFFFFFF for p in params], dtype=np.int64)
+            counters = np.asarray(list(draw_counters or [0] * b), dtype=np.int64)
+        if self.penalty_window > 0:
+            # every request's ring holds its last `width` tokens, token number n at place n % width
+            params, W = list(sampling), self.penalty_window
+            recent = np.full((b, W), -1, dtype=np.int32)
+            widths = np.zeros(b, dtype=np.int32)
+            pen = np.zeros((4, b), dtype=np.float32)
+            for i, p in enumerate(params):
+                w = min(p.penalty_window, W) if p.penalties_active else 0
+                widths[i] = w
+                hist = histories[i]
+                for n in range(max(0, len(hist) - w), len(hist)):
+                    recent[i, n % w] = hist[n]
+                pen[0, i] = p.repetition_penalty if p.penalties_active else 1.0
+                pen[1, i] = p.frequency_penalty if p.penalties_active else 0.0
+                pen[2, i] = p.presence_penalty if p.penalties_active else 0.0
+                pen[3, i] = p.final_logit_softcap
+            lengths = np.asarray([len(h) for h in histories], dtype=np.int64)
+        rc = self._lib.mmx_decode_bind(self._h, ptr(rids), int(horizon), ptr(firsts), ptr(temp), ptr(topk), ptr(topp), ptr(seeds), ptr(counters),
+                                       ptr(recent), ptr(widths), ptr(lengths), ptr(pen), ops._stream())
+        del keep
+        if rc == 1:
+            raise MemoryError("the decode session's pages for the horizon are not free")
+        if rc == 2:
+            raise ValueError(f"requests would grow beyond the {self.kv_bound} tokens the session is bound to")
+        if rc != 0:
+            raise ops.KernelError(self._last_error())
+        self.ids, self.horizon = list(request_ids), horizon
+
+    def step(self) -> None:
+        """One decode step for every bound request (launched eagerly and captured the first time, replayed afterwards);
+        the sampled tokens stay on the device (``tokens()`` copies them)."""
+        if self._lib.mmx_decode_step(self._h, ops._stream()) != 0:
+            raise ops.KernelError(self._last_error())
+
+    def begin(self) -> None:
+        """The first step of a run whose results come back through ``cycle``."""
+        if self._lib.mmx_decode_begin(self._h, ops._stream()) != 0:
+            raise ops.KernelError(self._last_error())
+
+    def cycle(self, scheduler_handle, launch_next: bool):
+        """One turn of the decode loop in one call.  Returns (tokens of the finished step, per request: 1 finished with this
+        token / 0 goes on / -1 had left before, whether any finished)."""
+        rc = self._lib.mmx_decode_cycle(self._exec, self._h, scheduler_handle, int(launch_next), self._toks, self._done, ops._stream())
+        if rc < 0:
+            raise ops.KernelError(self._last_error())
+        return list(self._toks), list(self._done), rc == 1
+
+    def drop(self, index: int) -> None:
+        """Request ``index`` of the binding has left (cancelled by its caller): its further tokens are not accounted for."""
+        self._lib.mmx_decode_drop(self._h, int(index))
+
+    def remaining(self) -> int:
+        return int(self._lib.mmx_decode_info(self._h, 0))
+
+    @property
+    def steps_done(self) -> int:
+        return int(self._lib.mmx_decode_info(self._h, 1))
+
+    @property
+    def graph(self):
+        return True if self._lib.mmx_decode_info(self._h, 2) else None

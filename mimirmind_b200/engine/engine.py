@@ -17,7 +17,7 @@ import torch
 
 from ..kernels.lib import KernelError
 from ..sampling import Sampler, SamplingParams
-from .decode_graph import DecodeSession, context_bound
+from .decode_graph import DecodeSession, LibraryDecodeSession, context_bound, decode_session
 from .loader import load_model, random_model
 from .model import Model
 from .runner import ModelRunner, StepEntry
@@ -172,7 +172,7 @@ class Engine:
             # when there are too many (a graph keeps its activations and logits)
             while len(self._sessions) >= self.max_decode_graphs:
                 self._sessions.pop(next(iter(self._sessions)))
-            sess = DecodeSession(self.runner, len(reqs), bound, greedy=greedy, feed_back=False, penalty_window=window)
+            sess = decode_session(self.runner, len(reqs), bound, greedy=greedy, feed_back=False, penalty_window=window)
         self._sessions[key] = sess                # most recently used last
         ids = [r.id for r in reqs]
         firsts = [r.tokens[-1] for r in reqs]
@@ -185,6 +185,8 @@ class Engine:
                 horizon //= 2          # fewer pages ahead; below the threshold the eager path (and preemption) decides
                 if horizon < self.graph_min_steps:
                     return False
+        if isinstance(sess, LibraryDecodeSession):
+            return self._decode_run_library(loop, sess, reqs)
         # One step of look-ahead: as soon as a step's tokens are on the host they are copied back as the next
         # step's inputs and that step is launched; the host's bookkeeping for the step runs while the GPU works.
         # If the bookkeeping finds that a request stopped (a stop id, a callback), the step already in flight is
@@ -253,6 +255,50 @@ class Engine:
                 if self.decode_trace is not None:
                     self.decode_trace.step(n, (now - t_prev) * 1e3)
                 account(tokens_of(host_out[cur]), now)
+                break
+        if self.decode_trace is not None:
+            self.decode_trace.flush()
+        return True
+
+    def _decode_run_library(self, loop: "ServingLoop", sess: LibraryDecodeSession, reqs) -> bool:
+        """The decode run with the library's session: one call per step (``cycle``) waits for the step in flight, copies its
+        tokens back as the next step's inputs (from pinned memory), launches that step and accounts for the finished one in
+        the library's scheduler; here the Python requests are brought up to date and the callbacks called.  A request that
+        stops is dropped one step late: the step already in flight is still valid for the others."""
+        sched, native = loop.sched, self.runner.native
+        n = len(reqs)
+        alive = [True] * n
+        t_prev = time.perf_counter()
+        sess.begin()
+        stop_seen = False
+        while True:
+            more = sess.remaining() > 0 and not stop_seen
+            self.graph_steps += 1                      # the step in flight, whose results this turn waits for
+            toks, done, _ = sess.cycle(sched._h, more)
+            sched.apply_events(native.events())
+            now = time.perf_counter()
+            self.d2h_bytes += (n + 1) * 4
+            if more:
+                self.h2d_bytes += n * 4
+            if self.decode_trace is not None:
+                self.decode_trace.step(n, (now - t_prev) * 1e3)
+                t_prev = now
+            for i, (r, tok, d) in enumerate(zip(reqs, toks, done)):
+                if d < 0 or not alive[i]:
+                    continue
+                r.tokens.append(tok)
+                r.generated.append(tok)
+                loop.first_at.setdefault(r.id, now)
+                loop.last_at[r.id] = now
+                if d == 1:
+                    alive[i] = False
+                    stop_seen = True
+                if loop.deliver(r, tok) is False and d == 0:
+                    sched.cancel(r.id)
+                    sess.drop(i)
+                    alive[i] = False
+                    stop_seen = True
+            if not more:
                 break
         if self.decode_trace is not None:
             self.decode_trace.flush()

@@ -62,6 +62,15 @@ def _declare():
         ("mmx_exec_run_plan", I, [P, P, POINTER(L), POINTER(I), I, P]),
         ("mmx_exec_planned", I, [P]),
         ("mmx_exec_events", I, [P, POINTER(L), POINTER(I), POINTER(I), I]),
+        ("mmx_decode_create", P, [P, I, I, I, I, I]),
+        ("mmx_decode_destroy", None, [P]),
+        ("mmx_decode_bind", I, [P, P, I, P, P, P, P, P, P, P, P, P, P, P]),
+        ("mmx_decode_step", I, [P, P]),
+        ("mmx_decode_begin", I, [P, P]),
+        ("mmx_decode_cycle", I, [P, P, P, I, P, P, P]),
+        ("mmx_decode_drop", None, [P, I]),
+        ("mmx_decode_info", I, [P, I]),
+        ("mmx_decode_buffer", P, [P, I]),
         ("mmx_exec_take_error_flag", I, [P]),
         ("mmx_exec_stat", L, [P, I]),
         ("mmx_option", I, [c_char_p, I]),
