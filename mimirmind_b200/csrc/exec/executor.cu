@@ -385,10 +385,15 @@ class Executor {
 
   private:
     void take_events(void* sched) {
-        long long r[256];
-        int k[256], c[256];
-        const int n = mmh_sched_events(sched, r, k, c, 256);
-        if (n > 256) throw ExecError("executor: more scheduler events in one call than it has room for");
+        std::vector<long long> r(256);
+        std::vector<int> k(256), c(256);
+        int n = mmh_sched_events(sched, r.data(), k.data(), c.data(), 256);
+        if (n > 256) {                      // more than fit the first time: the list stays until the scheduler's next call
+            r.resize(n);
+            k.resize(n);
+            c.resize(n);
+            n = mmh_sched_events(sched, r.data(), k.data(), c.data(), n);
+        }
         for (int i = 0; i < n; ++i) events_.push_back({r[i], k[i], c[i]});
     }
 

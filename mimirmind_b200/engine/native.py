@@ -252,8 +252,11 @@ class NativeExecutor:
         if not hasattr(self, "_ev"):
             return []
         r, k, c = self._ev
-        n = self._lib.mmx_exec_events(self._exec, r, k, c, 512)
-        return [(r[i], k[i], c[i]) for i in range(min(n, 512))]
+        n = self._lib.mmx_exec_events(self._exec, r, k, c, len(r))
+        if n > len(r):
+            self._ev = r, k, c = (c_longlong * n)(), (c_int * n)(), (c_int * n)()
+            n = self._lib.mmx_exec_events(self._exec, r, k, c, n)
+        return [(r[i], k[i], c[i]) for i in range(n)]
 
     def take_error_flag(self) -> int:
         """The kernels' error flag as the last ``run`` copied it back (after a synchronisation); reading clears it."""
