@@ -31,6 +31,7 @@ PROMPT_LEN = 2048
 CONTEXT = 4096
 PAGE_SIZE = 16
 BATCH = 8
+SETTLE_STEPS = 48       # decode replays after the prompts' prefill and before the warm-up steps (see decode_run)
 
 
 def load_peaks():
@@ -192,8 +193,8 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
-    if PROMPT_LEN + warmup + steps > CONTEXT:           # the requests must fit their context
-        steps = CONTEXT - PROMPT_LEN - warmup
+    if PROMPT_LEN + SETTLE_STEPS + warmup + steps > CONTEXT:           # the requests must fit their context
+        steps = CONTEXT - PROMPT_LEN - SETTLE_STEPS - warmup
         print(f"bench.py: --steps clamped to {steps} (prompts of {PROMPT_LEN} tokens in a context of {CONTEXT})", file=sys.stderr)
     if args.workload:
         return run_workload(args.workload, args.layers)
@@ -281,13 +282,20 @@ def main() -> int:
             lg = prefill_once(rid, toks)
             firsts.append(int(lg.argmax(-1).item()))
         sess = decode_session(runner, batch, CONTEXT, greedy=True, feed_back=True)
-        sess.bind(ids, w_steps + k_steps, firsts)
+        sess.bind(ids, SETTLE_STEPS + w_steps + k_steps, firsts)
         before = kernel_lib.launch_count()
         sess.step()                                   # eager + capture: the step's kernels are launched twice
         per_step_calls = (kernel_lib.launch_count() - before) // 2
         torch.cuda.synchronize()
+        # The prompts' prefill has just run the GPU into its power cap, and the SM clock stays low for some tens of
+        # milliseconds afterwards (the first dozen decode steps after a prefill take 3.7 ms instead of 3.4).  Decoding is
+        # measured in its steady state: SETTLE_STEPS steps of the same replays (about 150 ms) come first; they belong to
+        # the set-up like the prefill, and are counted neither as warm-up nor as timed steps.
+        for _ in range(SETTLE_STEPS - 1):
+            sess.step()
+        torch.cuda.synchronize()
         mark = len(clocks.samples)                    # the clock record covers the warm-up replays too: the timed region may be shorter than a sample
-        for _ in range(w_steps - 1):
+        for _ in range(w_steps):
             sess.step()
         torch.cuda.synchronize()
         a, b = ev(), ev()
@@ -361,7 +369,9 @@ def main() -> int:
     mixed = mixed_run(7)
 
     # ---- end to end: Engine.generate, host token lists in and out ------------------------------
-    n_new = min(steps, 256) + 1
+    # at least 128 decoded tokens per request: the first dozen steps after the prompts' prefill run at a clock that the
+    # prefill's power cap has pulled down, which a run of 20 tokens would measure instead of decoding
+    n_new = max(min(steps, 256), 128) + 1
     engine.generate(prompts[:BATCH], max_new_tokens=max(engine.graph_min_steps + 1, min(n_new, 12)), use_eos=False)   # warm-up: captures the graph
     h0, d0, g0 = engine.h2d_bytes, engine.d2h_bytes, engine.graph_steps
     res = engine.generate(prompts[:BATCH], max_new_tokens=n_new, use_eos=False)
@@ -382,7 +392,7 @@ def main() -> int:
                    "kv_heads": mcfg.num_key_value_heads, "head_dim": mcfg.head_dim, "intermediate": F, "vocab": V,
                    "global_batch": BATCH, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE_SIZE,
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (weights 15 GB per step)",
-                   "decode": "CUDA graph of the step, greedy sampling on device"},
+                   "decode": "CUDA graph of the step, greedy sampling on device", "settle_steps_before_warmup": SETTLE_STEPS},
         "e2e": e2e, "gpu_launches": calls * steps, "launches_per_step": calls,
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
