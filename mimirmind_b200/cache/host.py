@@ -39,6 +39,17 @@ _PROTOTYPES = {
     "mmh_cache_info": (I, [P, I, I]),
     "mmh_cache_live": (I, [P, PL, I]),
     "mmh_cache_check": (I, [P]),
+    "mmh_st_parse_header": (P, [c_void_p, L, L, c_char_p]),
+    "mmh_st_open_folder": (P, [c_char_p]),
+    "mmh_st_close": (None, [P]),
+    "mmh_st_count": (I, [P]),
+    "mmh_st_name": (c_char_p, [P, I]),
+    "mmh_st_dtype": (c_char_p, [P, I]),
+    "mmh_st_shard": (c_char_p, [P, I]),
+    "mmh_st_shape": (I, [P, I, PL, I]),
+    "mmh_st_offset": (L, [P, I, I]),
+    "mmh_st_read": (I, [P, I, c_void_p, L]),
+    "mmh_st_write": (I, [c_char_p, I, POINTER(c_char_p), POINTER(c_char_p), PI, PL, POINTER(c_void_p), PL, I, POINTER(c_char_p)]),
     "mmh_sched_create": (P, [P, I, I, I, I]),
     "mmh_sched_destroy": (None, [P]),
     "mmh_sched_add": (I, [P, L, PI, I, I, PI, I]),

@@ -29,6 +29,12 @@ int fail(const std::string& msg) {
     g_error = msg;
     return -2;
 }
+}  // namespace
+
+// the library's other source files report their errors through the same message
+void mmh_set_error(const std::string& msg) { g_error = msg; }
+
+namespace {
 
 constexpr int32_t INVALID_PAGE = -1;
 

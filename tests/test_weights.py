@@ -77,6 +77,35 @@ def test_sharded_folder(tmp_path):
         SafetensorsFolder(str(tmp_path))
 
 
+def test_names_with_escapes_and_metadata_round_trip(tmp_path):
+    # a name with a quote, a backslash, a control character and letters beyond ASCII (two and four bytes in UTF-8)
+    odd = 'w"\\\t\u00e9\U0001d11e.weight'
+    t = {odd: torch.arange(4, dtype=torch.int32), "empty": torch.zeros(0, 3), "scalar": torch.tensor(2.5)}
+    p = tmp_path / "model.safetensors"
+    write_safetensors(str(p), t, metadata={"format": "pt", 'k"ey': "v\nal"})
+    raw = p.read_bytes()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + hlen])                 # a standard reader agrees with what was written
+    assert header["__metadata__"] == {"format": "pt", 'k"ey': "v\nal"} and set(header) == set(t) | {"__metadata__"}
+    assert (8 + hlen) % 8 == 0                           # the data region starts on an 8-byte boundary
+    with SafetensorsFolder(str(tmp_path)) as f:
+        assert torch.equal(f.tensor(odd), t[odd]) and f.shape("empty") == (0, 3) and f.shape("scalar") == ()
+        assert f.tensor("empty").numel() == 0 and float(f.tensor("scalar")) == 2.5
+    # the same header written by a standard writer with \u escapes (surrogate pair included) reads back to the same name
+    blob = json.dumps({odd: {"dtype": "I32", "shape": [4], "data_offsets": [0, 16]}}, ensure_ascii=True).encode()
+    recs, _ = _parse(struct.pack("<Q", len(blob)) + blob + b"\0" * 16)
+    assert list(recs) == [odd]
+
+
+def test_a_file_that_shrank_after_opening_is_an_error(tmp_path):
+    p = tmp_path / "model.safetensors"
+    write_safetensors(str(p), {"a": torch.ones(1024)})
+    with SafetensorsFolder(str(tmp_path)) as f:
+        os.truncate(p, os.path.getsize(p) - 100)
+        with pytest.raises(SafetensorsError, match="read failed"):
+            f.tensor("a")
+
+
 def test_empty_folder(tmp_path):
     with pytest.raises(SafetensorsError, match="neither"):
         SafetensorsFolder(str(tmp_path))
