@@ -44,6 +44,18 @@ class Model:
             if e.cache_from is not None and not (0 <= e.cache_from < i and self.schedule[e.cache_from].cache_from is None):
                 raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_from}, which must be an "
                                  "earlier entry that owns a cache")
+            if e.cache_from is not None:
+                mine = self.layers[e.layer].mixer.kv_cache_spec()
+                theirs = self.layers[self.schedule[e.cache_from].layer].mixer.kv_cache_spec()
+                if mine is None or theirs is None:
+                    raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_from}: both mixers must keep a paged cache")
+                same = [(a.name, tuple(a.shape), a.dtype) for a in mine.token_arrays()] == \
+                       [(a.name, tuple(a.shape), a.dtype) for a in theirs.token_arrays()]
+                if not same:
+                    raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_from}, whose per-token arrays differ from its own")
+                if theirs.window and (not mine.window or mine.window > theirs.window):
+                    raise ValueError(f"schedule entry {i} looks back {mine.window or 'over all'} tokens, entry {e.cache_from} keeps only "
+                                     f"the last {theirs.window}")
 
     # ---- what the cache has to hold --------------------------------------------
     def cache_groups(self) -> List[GroupSpec]:

@@ -548,3 +548,98 @@ def test_toy_position_encoding_and_routed_feed_forward(tmp_path):
     finally:
         registry.POSITION_ENCODINGS.unregister("toy_position_scale")
         registry.FEED_FORWARDS.unregister("toy_two_experts")
+
+
+# ---- the order of layers is data: a layer named twice, an entry that reads another entry's cache ------------------
+
+def _plain_scheduled(w, cfg, schedule, windows, tokens):
+    """Whole-sequence forward of a model whose schedule names layers more than once and lets entries attend over the
+    keys and values that an earlier entry made (plain parts; one function per part from plain_qwen2)."""
+    T, H, G, hd = len(tokens), cfg["H"], cfg["G"], cfg["hd"]
+    pos = np.arange(T)
+    x = plain.embedding(w["emb"], tokens)
+    kept = {}
+    for idx, (layer, cache_from) in enumerate(schedule):
+        p = f"l{layer}."
+        n = plain.rms_norm(x, w[p + "n1"], cfg["eps"])
+        q = plain.rope(plain.linear(n, w[p + "q.weight"], w[p + "q.bias"]).reshape(T, H, hd), pos, cfg["theta"])
+        if cache_from is None:
+            k = plain.rope(plain.linear(n, w[p + "k.weight"], w[p + "k.bias"]).reshape(T, G, hd), pos, cfg["theta"])
+            v = plain.linear(n, w[p + "v.weight"], w[p + "v.bias"]).reshape(T, G, hd)
+            kept[idx] = (k, v)
+        else:
+            k, v = kept[cache_from]
+        o = plain.attention(q, k, v, windows[layer]).reshape(T, H * hd)
+        x = x + plain.linear(o, w[p + "o.weight"])
+        n = plain.rms_norm(x, w[p + "n2"], cfg["eps"])
+        x = x + plain.swiglu(n, w[p + "g.weight"], w[p + "u.weight"], w[p + "d.weight"])
+    return plain.linear(plain.rms_norm(x, w["nf"], cfg["eps"]), w["emb"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("use_native", [True, False])
+@pytest.mark.parametrize("sizes", [(176, 83, 5, 1, 48, 208), (256, 131, 4, 2, 64, 320)])   # generic kernels; tensor-core and fused ones
+def test_a_layer_named_twice_and_an_entry_that_reads_another_entrys_cache(sizes, dtype, use_native, monkeypatch):
+    """Three layers of the built-in parts, five schedule entries: layer 0, layer 1 (a window), layer 2 attending over
+    what entry 0 kept (with a window of its own), layer 0 a second time with a cache of its own, layer 2 over entry 0
+    again.  Whole, in portions and token by token, through the library's executor and through the Python parts,
+    against the plain composition; few pages, so that the window's group gives pages back."""
+    from mimirmind_b200 import registry
+    from mimirmind_b200.config.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from mimirmind_b200.engine import native
+    from mimirmind_b200.engine.loader import make_runtime
+    from mimirmind_b200.engine.model import Model
+    from mimirmind_b200.engine.runner import ModelRunner, StepEntry
+    from mimirmind_b200.weights.store import random_tensors
+    registry._ensure_builtin()
+    monkeypatch.setattr(native, "ENABLED", use_native)
+    d, V, H, G, hd, F = sizes
+    cfg = dict(H=H, G=G, hd=hd, eps=3e-6, theta=5000.0)
+    windows = [0, 20, 28]
+    schedule = [(0, None), (1, None), (2, 0), (0, None), (2, 0)]
+    norm = lambda name: PartSpec("rmsnorm", {"width": d, "eps": cfg["eps"], "weight": name})
+
+    def attn(window):
+        return PartSpec("gqa_attention", dict(hidden=d, num_heads=H, num_kv_heads=G, head_dim=hd, window=window, scale=None, qkv_bias=True,
+                                              position=PartSpec("rotary_half", {"theta": cfg["theta"], "rotary_dim": hd}),
+                                              q="q", k="k", v="v", o="o"))
+    ffn = PartSpec("swiglu", {"hidden": d, "intermediate": F, "gate": "g.weight", "up": "u.weight", "down": "d.weight"})
+    layers = tuple(LayerSpec(f"l{i}.", PartSpec("pre_norm"), attn(windows[i]), ffn, norm("n1"), norm("n2")) for i in range(3))
+    spec = ModelSpec("ScheduledForTest", d, V, 512, PartSpec("token_embedding", {"vocab": V, "width": d, "scale": 1.0, "weight": "emb"}),
+                     layers, tuple(ScheduleEntry(l, c) for l, c in schedule), norm("nf"),
+                     PartSpec("lm_head", {"vocab": V, "width": d, "weight": "head", "tied_to": "emb"}))
+    rt_ = make_runtime(dtype)
+    tensors = random_tensors(spec, 5, torch.bfloat16, rt_.device)
+    model = Model(spec, {k: (v.float() if dtype == "float32" and v.dtype == torch.bfloat16 else v.clone()) for k, v in tensors.items()}, rt_)
+    groups = {g.name: g for g in model.cache_groups()}
+    assert sorted(len(g.entries) for g in groups.values()) == [1, 2]      # entries 0 and 3 keep everything, entry 1 a window
+    w = {k: v.float().cpu().numpy().astype(np.float64) for k, v in tensors.items()}
+    toks = random_tokens(V, 90, 9)
+    want = _plain_scheduled(w, cfg, schedule, windows, toks)
+    scale = np.abs(want).max()
+    tol = 2e-4 if dtype == "float32" else 4e-2
+
+    def run(cuts, rid, runner):
+        runner.add_request(rid)
+        outs, p = [], 0
+        for c in cuts:
+            outs.append(runner.step([StepEntry(rid, toks[p:p + c], list(range(c)))]).float().cpu().numpy())
+            p += c
+        runner.release(rid)
+        return np.concatenate(outs)
+
+    runner = ModelRunner(model, 8, 16, 2)                               # 128 tokens of pages for 90: nothing to spare twice over
+    assert (runner.native is not None) == use_native
+    first = None
+    for n, cuts in enumerate(([90], [58] + [1] * 32, [2, 17, 3, 40, 2, 26], [33, 31, 2, 24])):
+        got = run(cuts, f"r{n}", runner)
+        assert np.abs(got - want).max() <= tol * scale, (cuts, np.abs(got - want).max() / scale)
+        if dtype == "float32":
+            first = got if first is None else first
+            assert np.array_equal(got, first), cuts                     # 32-bit: the same bits however the tokens are cut
+    runner.check_errors()
+
+    # an entry may not look further back than the entry whose cache it reads keeps
+    bad = ModelSpec("ScheduledBad", d, V, 512, spec.embedding, layers, (ScheduleEntry(1), ScheduleEntry(0, 0)), spec.final_norm, spec.head)
+    with pytest.raises(ValueError, match="keeps only"):
+        Model(bad, {k: v.clone() for k, v in tensors.items()}, rt_)
