@@ -174,6 +174,8 @@ def main() -> int:
                          "(14B-shaped, 64 requests of 128..2048 prompt tokens, 256 new tokens each, continuous batching; "
                          "32B-shaped, 8 requests of 8,192 prompt tokens, 128 new tokens each)")
     ap.add_argument("--mixed-portion", type=int, default=192, help="tokens of the prompt portion in the mixed step")
+    ap.add_argument("--prompt-len", type=int, default=0,
+                    help="with --only decode or prefill: prompts of this many tokens instead of 2,048 (the context grows with them)")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
                     help="set a tunable of the library's dispatch (csrc/exec/exec.h, Options) for this run, e.g. cluster_max_wanted=64")
     args = ap.parse_args()
@@ -193,6 +195,13 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    global PROMPT_LEN, CONTEXT
+    if args.prompt_len:
+        if args.only not in ("decode", "prefill"):
+            print("bench.py: --prompt-len goes with --only decode or --only prefill", file=sys.stderr)
+            return 2
+        PROMPT_LEN = args.prompt_len
+        CONTEXT = max(CONTEXT, -(-(PROMPT_LEN + SETTLE_STEPS + warmup + steps) // 1024) * 1024)
     if PROMPT_LEN + SETTLE_STEPS + warmup + steps > CONTEXT:           # the requests must fit their context
         steps = CONTEXT - PROMPT_LEN - SETTLE_STEPS - warmup
         print(f"bench.py: --steps clamped to {steps} (prompts of {PROMPT_LEN} tokens in a context of {CONTEXT})", file=sys.stderr)
@@ -210,7 +219,7 @@ def main() -> int:
 
     torch.cuda.set_device(0)
     peaks = load_peaks()
-    cfg_json = dict(MODEL_7B)
+    cfg_json = dict(MODEL_7B, max_position_embeddings=max(CONTEXT, MODEL_7B["max_position_embeddings"]))
     full_layers = cfg_json["num_hidden_layers"]
     if args.layers:
         cfg_json["num_hidden_layers"] = args.layers
@@ -229,14 +238,14 @@ def main() -> int:
     weight_bytes = 2 * (L * layer_params + d + V * d)               # every weight a decode step uses, once
     kv_bytes_per_token = 2 * L * kvs * 2
 
-    max_batch = 64
+    max_batch = max(args.batch, 1) if args.only == "decode" else (1 if args.only == "prefill" else 64)
     # token budget: all prompts of the batch are prefilled in one step, so that the end-to-end run is
     # pure decoding after the first token, like the device-timed run
-    engine = Engine(model, page_size=PAGE_SIZE, cache_tokens=max_batch * CONTEXT, max_context=CONTEXT,
-                    token_budget=BATCH * PROMPT_LEN, max_active=max_batch)
+    engine = Engine(model, page_size=PAGE_SIZE, cache_tokens=max(max_batch, 2) * CONTEXT, max_context=CONTEXT,
+                    token_budget=min(BATCH * PROMPT_LEN, 8192 * 16), max_active=max(max_batch, 2))
     runner = engine.runner
     rng = np.random.RandomState(0)
-    prompts = [rng.randint(0, V, size=PROMPT_LEN).tolist() for _ in range(max_batch)]
+    prompts = [rng.randint(0, V, size=PROMPT_LEN).tolist() for _ in range(max(max_batch, BATCH + 1 if args.only == "mixed" else 5))]
 
     def ev():
         return torch.cuda.Event(enable_timing=True)
@@ -345,12 +354,15 @@ def main() -> int:
         return 0
     if args.only == "prefill":
         clocks.stop()
-        print(json.dumps({"only": "prefill", "ms": pf_ms, "tflops": prefill["tflops"], "layers": L}))
+        print(json.dumps({"only": "prefill", "tokens": T, "ms": pf_ms, "tflops": prefill["tflops"], "frac": prefill["frac"], "layers": L}))
         return 0
     if args.only == "decode":
-        ms, calls, _, _ = decode_run(args.batch, steps, warmup)
+        ms, calls, kv_b, _ = decode_run(args.batch, steps, warmup)
         clocks.stop()
-        print(json.dumps({"only": "decode", "batch": args.batch, "ms_per_step": ms, "launches_per_step": calls, "layers": L}))
+        nbytes = weight_bytes + kv_b * kv_bytes_per_token + args.batch * d * 2
+        print(json.dumps({"only": "decode", "batch": args.batch, "prompt_len": PROMPT_LEN, "ms_per_step": ms, "launches_per_step": calls, "layers": L,
+                          "bytes_per_step": nbytes, "cache_bytes_per_step": kv_b * kv_bytes_per_token,
+                          "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}))
         return 0
     ms8, calls, kv_tokens, mark = decode_run(BATCH, steps, warmup)
     clock_summary = clocks.summary(mark)
