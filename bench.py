@@ -27,6 +27,14 @@ MODEL_7B = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidd
                 num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944, vocab_size=152064,
                 rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096,
                 use_sliding_window=False, torch_dtype="bfloat16")
+# Other shapes of the same architecture for --only runs (--shape): sizes of the published configurations of that name.
+SHAPES = {
+    "7b": {},
+    "0.5b": dict(num_hidden_layers=24, hidden_size=896, num_attention_heads=14, num_key_value_heads=2, head_dim=64, intermediate_size=4864,
+                 vocab_size=151936, tie_word_embeddings=True),
+    "14b": dict(num_hidden_layers=48, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, intermediate_size=13824, rms_norm_eps=1e-5),
+    "32b": dict(num_hidden_layers=64, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, intermediate_size=27648),
+}
 PROMPT_LEN = 2048
 CONTEXT = 4096
 PAGE_SIZE = 16
@@ -174,6 +182,7 @@ def main() -> int:
                          "(14B-shaped, 64 requests of 128..2048 prompt tokens, 256 new tokens each, continuous batching; "
                          "32B-shaped, 8 requests of 8,192 prompt tokens, 128 new tokens each)")
     ap.add_argument("--mixed-portion", type=int, default=192, help="tokens of the prompt portion in the mixed step")
+    ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="with --only: another size of the architecture (random weights)")
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="with --only decode or prefill: prompts of this many tokens instead of 2,048 (the context grows with them)")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
@@ -196,6 +205,9 @@ def main() -> int:
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
     global PROMPT_LEN, CONTEXT
+    if args.shape != "7b" and not args.only:
+        print("bench.py: --shape goes with --only", file=sys.stderr)
+        return 2
     if args.prompt_len:
         if args.only not in ("decode", "prefill"):
             print("bench.py: --prompt-len goes with --only decode or --only prefill", file=sys.stderr)
@@ -220,6 +232,7 @@ def main() -> int:
     torch.cuda.set_device(0)
     peaks = load_peaks()
     cfg_json = dict(MODEL_7B, max_position_embeddings=max(CONTEXT, MODEL_7B["max_position_embeddings"]))
+    cfg_json.update(SHAPES[args.shape])
     full_layers = cfg_json["num_hidden_layers"]
     if args.layers:
         cfg_json["num_hidden_layers"] = args.layers
@@ -354,13 +367,13 @@ def main() -> int:
         return 0
     if args.only == "prefill":
         clocks.stop()
-        print(json.dumps({"only": "prefill", "tokens": T, "ms": pf_ms, "tflops": prefill["tflops"], "frac": prefill["frac"], "layers": L}))
+        print(json.dumps({"only": "prefill", "shape": args.shape, "tokens": T, "ms": pf_ms, "tflops": prefill["tflops"], "frac": prefill["frac"], "layers": L}))
         return 0
     if args.only == "decode":
         ms, calls, kv_b, _ = decode_run(args.batch, steps, warmup)
         clocks.stop()
         nbytes = weight_bytes + kv_b * kv_bytes_per_token + args.batch * d * 2
-        print(json.dumps({"only": "decode", "batch": args.batch, "prompt_len": PROMPT_LEN, "ms_per_step": ms, "launches_per_step": calls, "layers": L,
+        print(json.dumps({"only": "decode", "shape": args.shape, "batch": args.batch, "prompt_len": PROMPT_LEN, "ms_per_step": ms, "launches_per_step": calls, "layers": L,
                           "bytes_per_step": nbytes, "cache_bytes_per_step": kv_b * kv_bytes_per_token,
                           "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}))
         return 0

@@ -231,11 +231,15 @@ static int skinny_splits(int n, int k) {
     return s;
 }
 
-// 8 warps per CTA of the register-streaming kernel as row tiles x K splits: 8 row tiles per CTA when that still
-// gives two CTAs per SM, else all warps of a CTA on one row tile.
+// 8 warps per CTA of the register-streaming kernel as row tiles x K splits: as many row tiles per CTA (8, 4, 2, 1) as
+// still leave one and a half CTAs per SM; fewer CTAs than that do not keep enough loads in flight, many more only add
+// CTAs that wait their turn.  Measured per product at 8 rows (us, best first): 1,728 tiles of 5,120: 4 tiles per CTA 45.9,
+// 2: 47.5, 8: 50.8, 1: 51.7; 2,368 tiles of 3,584: 8: 44.6, 2: 49.4; 608 of 896: 2: 6.4, 4: 7.3, 1: 8.3; 448 of 5,120:
+// 2: 15.3, 1: 18.7; 320 tiles and fewer: 1.
 static void gemv_layout(int n, int k, int* rt, int* ks) {
     const int tiles = n / 16;
-    int r = (tiles / 8 >= 2 * 148) ? 8 : 1;
+    int r = 8;
+    while (r > 1 && (tiles + r - 1) / r < 222) r /= 2;
     int s = 8 / r;
     while (s > k / 32) {
         s /= 2;

@@ -282,11 +282,14 @@ class RowScale:
 
 
 def _gemv_layout(n: int, k: int):
-    # 8 warps per CTA as row tiles x K splits: enough CTAs to fill the GPU, else split K inside the CTA
-    # Measured: with enough row tiles for two CTAs per SM, 8 row tiles per CTA stream best (6.0 TB/s on the
-    # gate/up product, 6.6 TB/s on the head); smaller products need all 8 warps of a CTA on one row tile.
+    # 8 warps per CTA as row tiles x K splits: as many row tiles per CTA (8, 4, 2, 1) as still leave one and a half
+    # CTAs per SM (measured: 1,728 tiles of 5,120 at 8 rows: 4 tiles per CTA 45.9 us, 2: 47.5, 8: 50.8, 1: 51.7;
+    # 2,368 tiles of 3,584: 8: 44.6, 2: 49.4; 608 of 896: 2: 6.4, 1: 8.3; 320 tiles and fewer: 1).  The same rule as
+    # the library's executor (csrc/exec/core.cu): the order of a sum depends on the split.
     tiles = n // 16
-    rt = 8 if tiles // 8 >= 2 * 148 else 1
+    rt = 8
+    while rt > 1 and -(-tiles // rt) < 222:
+        rt //= 2
     ks = 8 // rt
     while ks > k // 32:
         ks //= 2
