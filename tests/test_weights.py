@@ -97,6 +97,22 @@ def test_names_with_escapes_and_metadata_round_trip(tmp_path):
     assert list(recs) == [odd]
 
 
+def test_files_of_the_safetensors_package_both_ways(tmp_path):
+    """The container as the widely used writer makes it (header padded with spaces) reads here, and what is written here
+    reads there.  Skipped where that package is not installed."""
+    st = pytest.importorskip("safetensors.torch")
+    t = {"a.weight": torch.randn(5, 7).to(torch.bfloat16), "b": torch.arange(10, dtype=torch.int64), "c": torch.randn(3), "h": torch.randn(2, 2).half()}
+    st.save_file(t, str(tmp_path / "model.safetensors"), metadata={"format": "pt"})
+    with SafetensorsFolder(str(tmp_path)) as f:
+        assert set(f.names()) == set(t)
+        for k in t:
+            assert torch.equal(f.tensor(k), t[k]) and f.tensor(k).dtype == t[k].dtype
+    write_safetensors(str(tmp_path / "ours.safetensors"), t, metadata={"format": "pt"})
+    back = st.load_file(str(tmp_path / "ours.safetensors"))
+    for k in t:
+        assert torch.equal(back[k], t[k])
+
+
 def test_a_file_that_shrank_after_opening_is_an_error(tmp_path):
     p = tmp_path / "model.safetensors"
     write_safetensors(str(p), {"a": torch.ones(1024)})
