@@ -215,6 +215,15 @@ void Blas::gemm_nt(const void* x, const void* W, void* out, int out_dtype, int M
 }
 
 // ---- dispatch ---------------------------------------------------------------------------------------------------------
+void Step::fork() const {
+    check_cuda(cudaEventRecord(forked, stream), "forking the side stream");
+    check_cuda(cudaStreamWaitEvent(side, forked, 0), "forking the side stream");
+}
+void Step::join() const {
+    check_cuda(cudaEventRecord(joined, side), "joining the side stream");
+    check_cuda(cudaStreamWaitEvent(stream, joined, 0), "joining the side stream");
+}
+
 bool gemv_supported(int m, int n, int k) { return 1 <= m && m <= options().gemv_max_rows && n % 16 == 0 && k % 32 == 0 && k >= 256; }
 bool skinny_supported(int m, int n, int k) {
     return options().gemv_max_rows < m && m <= options().skinny_max_rows && n % 16 == 0 && k % 8 == 0 && k >= 64;

@@ -151,6 +151,12 @@ struct Step {
     bool simt = false;
     cudaStream_t stream = nullptr;
     void* err = nullptr;                  // device int the tcgen05 kernels set when a bounded wait ran out
+    // a second stream with two events (or null): independent kernels of a part may run there beside the step's own,
+    // between step.fork() and step.join()
+    cudaStream_t side = nullptr;
+    cudaEvent_t forked = nullptr, joined = nullptr;
+    void fork() const;                    // the side stream waits for what the step has launched so far
+    void join() const;                    // the step waits for what the side stream has been given
     Arena* step_mem = nullptr;            // lives until the step has been launched
     Arena* layer_mem = nullptr;           // the running layer's; the one before it keeps its memory one layer longer
     Blas* blas = nullptr;
@@ -267,6 +273,7 @@ struct Options {
     int skinny_max_rows = 64;
     int tcgen05_swiglu_min_rows = 256;
     int tcgen05_pair_min_rows = 256;
+    int use_side_stream = 1;          // a mixed step's decode attention runs beside its prefill attention
 };
 Options& options();
 

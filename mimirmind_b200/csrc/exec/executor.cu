@@ -64,6 +64,9 @@ class Executor {
         if ((int)group_pages_.size() > MAX_GROUPS) throw ExecError("executor: too many cache groups");
         check_cuda(cudaMallocHost((void**)&err_host_, sizeof(int)), "pinned error flag");
         *err_host_ = 0;
+        check_cuda(cudaStreamCreateWithFlags(&side_, cudaStreamNonBlocking), "the executor's side stream");
+        check_cuda(cudaEventCreateWithFlags(&forked_, cudaEventDisableTiming), "fork event");
+        check_cuda(cudaEventCreateWithFlags(&joined_, cudaEventDisableTiming), "join event");
     }
     ~Executor() {
         for (auto& s : ring_) {
@@ -71,6 +74,9 @@ class Executor {
             if (s.copied) cudaEventDestroy(s.copied);
         }
         if (err_host_) cudaFreeHost(err_host_);
+        if (forked_) cudaEventDestroy(forked_);
+        if (joined_) cudaEventDestroy(joined_);
+        if (side_) cudaStreamDestroy(side_);
     }
 
     int n_groups() const { return (int)group_pages_.size(); }
@@ -123,6 +129,9 @@ class Executor {
         st.step_mem = &step_mem_;
         if (!blas_) blas_.reset(new Blas());
         st.blas = blas_.get();
+        st.side = side_;
+        st.forked = forked_;
+        st.joined = joined_;
     }
 
     void prepare(Step& st) {
@@ -506,6 +515,8 @@ class Executor {
     Arena step_mem_;
     Arena layer_mem_[2];
     std::unique_ptr<Blas> blas_;
+    cudaStream_t side_ = nullptr;
+    cudaEvent_t forked_ = nullptr, joined_ = nullptr;
     Staging ring_[4];
     int ring_next_ = 0;
     long long steps_ = 0;
@@ -944,7 +955,7 @@ MMX_EXPORT int mmx_option(const char* name, int value) {
                  {"tma_decode_stages", &o.tma_decode_stages}, {"target_ctas", &o.target_ctas}, {"use_cluster_merge", &o.use_cluster_merge},
                  {"cluster_max_wanted", &o.cluster_max_wanted}, {"fixed_split", &o.fixed_split}, {"gemv_max_rows", &o.gemv_max_rows},
                  {"skinny_max_rows", &o.skinny_max_rows}, {"tcgen05_swiglu_min_rows", &o.tcgen05_swiglu_min_rows},
-                 {"tcgen05_pair_min_rows", &o.tcgen05_pair_min_rows}};
+                 {"tcgen05_pair_min_rows", &o.tcgen05_pair_min_rows}, {"use_side_stream", &o.use_side_stream}};
     for (auto& t : table)
         if (std::strcmp(t.n, name) == 0) {
             const int old = *t.p;

@@ -84,3 +84,55 @@ def test_the_pool_is_sized_from_the_device_when_nothing_is_configured(wide_folde
     assert mgr.total_pages() * mgr.page_size == 32 * 4096
     free, _ = torch.cuda.mem_get_info()
     assert free > 0
+
+
+def test_long_portions_beside_single_tokens(wide_folders):
+    """Steps that hold prompt portions of 128 tokens and more beside single decoded tokens of other requests: the two
+    attention kernels of such a step run side by side on two streams.  Every row against the plain implementation, and
+    the same bits with the second stream switched off."""
+    import plain_qwen2 as plain
+    import replay_util as ru
+    from mimirmind_b200.engine import native
+    from mimirmind_b200.kernels import ops
+    from test_replay_gpu import check
+    folder = wide_folders("7b", "bfloat16")
+    pm = plain.PlainModel(folder)
+    reqs = {"a": random_tokens(pm.V, 230, 1), "b": random_tokens(pm.V, 150, 2), "c": random_tokens(pm.V, 420, 3), "d": random_tokens(pm.V, 200, 4)}
+    ref = {rid: pm.logits(t) for rid, t in reqs.items()}
+    del pm
+    t = ru.Trace()
+    all_of = lambda n: list(range(n))
+    t.step([("a", reqs["a"][:200], all_of(200)), ("b", reqs["b"][:120], all_of(120))])
+    fed = {"a": 200, "b": 120, "c": 0, "d": 0}
+
+    def mixed_step(portions, end=()):
+        entries = []
+        for rid in ("a", "b"):
+            if fed[rid] < len(reqs[rid]):
+                entries.append((rid, reqs[rid][fed[rid]:fed[rid] + 1], [0]))
+                fed[rid] += 1
+        for rid, n in portions:
+            entries.append((rid, reqs[rid][fed[rid]:fed[rid] + n], all_of(n)))
+            fed[rid] += n
+        t.step(entries, end=end)
+
+    mixed_step([("c", 160)])                       # one portion of 160 beside two single tokens
+    mixed_step([("c", 129), ("d", 70)])            # two portions, 199 tokens together
+    mixed_step([("d", 130), ("c", 2)])
+    mixed_step([("c", 129)], end=["c", "d"])
+    while fed["a"] < len(reqs["a"]) or fed["b"] < len(reqs["b"]):
+        mixed_step([])
+    assert all(fed[r] == len(reqs[r]) for r in reqs)
+    outs = []
+    for side in (1, 0):
+        old = native.option("use_side_stream", side)
+        try:
+            out, _ = ru.run_in_process(folder, "bfloat16", t, t.max_live_tokens())
+        finally:
+            native.option("use_side_stream", old)
+        ops.check_tcgen05_errors(torch.device("cuda"))
+        check(t, out, reqs, ref, "bfloat16", f"long portions beside single tokens (side stream {side})")
+        outs.append(out)
+    for i in outs[0]:
+        assert np.array_equal(outs[0][i], outs[1][i]), f"step {i}"
+    torch.cuda.empty_cache()
