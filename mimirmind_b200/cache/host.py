@@ -39,6 +39,9 @@ _PROTOTYPES = {
     "mmh_cache_info": (I, [P, I, I]),
     "mmh_cache_live": (I, [P, PL, I]),
     "mmh_cache_check": (I, [P]),
+    "mmh_engine_config": (c_char_p, [c_char_p, L, c_char_p]),
+    "mmh_config_qwen2": (c_char_p, [c_char_p, L, c_char_p]),
+    "mmh_config_qwen2_folder": (c_char_p, [c_char_p]),
     "mmh_st_parse_header": (P, [c_void_p, L, L, c_char_p]),
     "mmh_st_open_folder": (P, [c_char_p]),
     "mmh_st_close": (None, [P]),

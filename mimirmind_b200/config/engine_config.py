@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import json
 import os
-from dataclasses import dataclass, field
+from dataclasses import asdict, dataclass, field
 from typing import Any, Dict, List, Optional
 
 
@@ -72,83 +72,32 @@ class EngineConfig:
         raise EngineConfigError(f"no model with id '{mid}' in the configuration")
 
 
-def _fill(section: str, cls, obj: Any):
-    if not isinstance(obj, dict):
-        raise EngineConfigError(f"'{section}' must be an object")
-    inst = cls()
-    known = inst.__dataclass_fields__
-    for k, v in obj.items():
-        if k not in known:
-            raise EngineConfigError(f"unknown key '{section}.{k}' (known: {', '.join(known)})")
-        want = type(getattr(inst, k)) if getattr(inst, k) is not None else None
-        if want is None and v is not None and not isinstance(v, dict):
-            raise EngineConfigError(f"'{section}.{k}' must be an object")
-        if want is bool and not isinstance(v, bool):
-            raise EngineConfigError(f"'{section}.{k}' must be true or false")
-        if want is int and (isinstance(v, bool) or not isinstance(v, int)):
-            raise EngineConfigError(f"'{section}.{k}' must be an integer")
-        if want is str and not isinstance(v, str):
-            raise EngineConfigError(f"'{section}.{k}' must be a string")
-        if want is float:
-            if isinstance(v, bool) or not isinstance(v, (int, float)):
-                raise EngineConfigError(f"'{section}.{k}' must be a number")
-            v = float(v)
-        setattr(inst, k, v)
-    return inst
+def _from_library(text: bytes, where: Optional[str]) -> EngineConfig:
+    """Reading, the strict key check, the defaults and the ranges are the host library's (``csrc/host/engine_config.cpp``)."""
+    from ..cache import host
+    lib = host.load()
+    answer = lib.mmh_engine_config(text, len(text), where.encode("utf-8") if where else None)
+    if not answer:
+        raise EngineConfigError(host.last_error())
+    f = json.loads(answer.decode("utf-8"))
+    f["runtime"]["cacheMemoryFraction"] = float(f["runtime"]["cacheMemoryFraction"])
+    return EngineConfig(defaultModel=f["defaultModel"], models=[ModelEntry(**m) for m in f["models"]], runtime=RuntimeSettings(**f["runtime"]),
+                        serving=ServingSettings(**f["serving"]), diagnostics=DiagnosticsSettings(**f["diagnostics"]))
 
 
 def parse_engine_config(obj: Dict[str, Any]) -> EngineConfig:
     if not isinstance(obj, dict):
         raise EngineConfigError("configuration must be a JSON object")
-    cfg = EngineConfig()
-    for k, v in obj.items():
-        if k == "defaultModel":
-            if not isinstance(v, str):
-                raise EngineConfigError("'defaultModel' must be a string")
-            cfg.defaultModel = v
-        elif k == "models":
-            if not isinstance(v, list):
-                raise EngineConfigError("'models' must be a list")
-            cfg.models = [_fill(f"models[{i}]", ModelEntry, m) for i, m in enumerate(v)]
-        elif k == "runtime":
-            cfg.runtime = _fill("runtime", RuntimeSettings, v)
-        elif k == "serving":
-            cfg.serving = _fill("serving", ServingSettings, v)
-        elif k == "diagnostics":
-            cfg.diagnostics = _fill("diagnostics", DiagnosticsSettings, v)
-        else:
-            raise EngineConfigError(f"unknown key '{k}' (known: defaultModel, models, runtime, serving, diagnostics)")
-    validate(cfg)
-    return cfg
+    try:
+        text = json.dumps(obj).encode("utf-8")
+    except (TypeError, ValueError) as e:
+        raise EngineConfigError(f"configuration is not JSON ({e})") from None
+    return _from_library(text, None)
 
 
 def validate(cfg: EngineConfig) -> None:
-    s, r = cfg.serving, cfg.runtime
-    # ranges of the reference (src/core/config/Config.hpp:285-351)
-    if not (1 <= s.tokenBudget <= 8192):
-        raise EngineConfigError("serving.tokenBudget must be in 1..8192")
-    if not (1 <= s.maxActiveRequests <= 256):
-        raise EngineConfigError("serving.maxActiveRequests must be in 1..256")
-    if s.blockSize not in (8, 16, 32, 64):
-        raise EngineConfigError("serving.blockSize must be 8, 16, 32 or 64")
-    if s.prefillChunk < 0:
-        raise EngineConfigError("serving.prefillChunk must be >= 0")
-    if r.dtype not in ("bfloat16", "float32"):
-        raise EngineConfigError("runtime.dtype must be bfloat16 or float32")
-    if r.maxContextTokens < 1:
-        raise EngineConfigError("runtime.maxContextTokens must be positive")
-    if r.cacheTokens < 0:
-        raise EngineConfigError("runtime.cacheTokens must be >= 0")
-    if not (0.0 < r.cacheMemoryFraction <= 1.0):
-        raise EngineConfigError("runtime.cacheMemoryFraction must be in (0, 1]")
-    ids = [m.id for m in cfg.models]
-    if len(set(ids)) != len(ids):
-        raise EngineConfigError("model ids must be unique")
-    for m in cfg.models:
-        if not m.id:
-            raise EngineConfigError("every model needs an 'id'")
-        if bool(m.path) == bool(m.random):
-            raise EngineConfigError(f"model '{m.id}' needs either 'path' or 'random'")
+    """The same checks on a configuration that was changed after it was read (command-line values override the file)."""
+    parse_engine_config(asdict(cfg))
 
 
 def load_engine_config(path: str) -> EngineConfig:
@@ -156,9 +105,5 @@ def load_engine_config(path: str) -> EngineConfig:
     (src/mimirmind/CliParser.cpp:34-36)."""
     if not os.path.isfile(path):
         raise EngineConfigError(f"config file '{path}' not found")
-    with open(path, "r", encoding="utf-8") as f:
-        try:
-            obj = json.load(f)
-        except json.JSONDecodeError as e:
-            raise EngineConfigError(f"{path}: not valid JSON ({e})") from None
-    return parse_engine_config(obj)
+    with open(path, "rb") as f:
+        return _from_library(f.read(), path)
