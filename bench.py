@@ -363,7 +363,11 @@ def main() -> int:
                 "steps": k_steps, "launched_by": "library executor" if runner.native is not None else "python parts"}
     if args.only == "mixed":
         clocks.stop()
-        print(json.dumps(dict(mixed_run(max(1, min(steps, 12))), only="mixed", layers=L)))
+        k = max(1, min(steps, 12, PROMPT_LEN // max(args.mixed_portion, 1) - 3))      # the long prompt must last for 3 + k portions
+        if args.mixed_portion < 1 or PROMPT_LEN // args.mixed_portion < 4:
+            print(f"bench.py: --mixed-portion must be in 1..{PROMPT_LEN // 4}", file=sys.stderr)
+            return 2
+        print(json.dumps(dict(mixed_run(k), only="mixed", layers=L)))
         return 0
     if args.only == "prefill":
         clocks.stop()
@@ -391,7 +395,7 @@ def main() -> int:
             point_rooflines[f"decode_b{b}"] = {"ms_per_step": ms, "bytes_per_step": nbytes, "achieved": nbytes / (ms * 1e-3) / 1e9,
                                                "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
 
-    mixed = mixed_run(7)
+    mixed = mixed_run(min(7, PROMPT_LEN // max(args.mixed_portion, 1) - 3))
 
     # ---- end to end: Engine.generate, host token lists in and out ------------------------------
     # at least 128 decoded tokens per request: the first dozen steps after the prompts' prefill run at a clock that the
