@@ -400,7 +400,7 @@ def main() -> int:
     # ---- end to end: Engine.generate, host token lists in and out ------------------------------
     # at least 128 decoded tokens per request: the first dozen steps after the prompts' prefill run at a clock that the
     # prefill's power cap has pulled down, which a run of 20 tokens would measure instead of decoding
-    n_new = max(min(steps, 256), 128) + 1
+    n_new = max(min(steps, 1024), 128) + 1       # as many decode steps as the device-timed run where the context allows
     engine.generate(prompts[:BATCH], max_new_tokens=max(engine.graph_min_steps + 1, min(n_new, 12)), use_eos=False)   # warm-up: captures the graph
     h0, d0, g0 = engine.h2d_bytes, engine.d2h_bytes, engine.graph_steps
     res = engine.generate(prompts[:BATCH], max_new_tokens=n_new, use_eos=False)
