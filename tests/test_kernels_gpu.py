@@ -512,7 +512,8 @@ def test_penalties_and_softcap():
 
 # ---- weight-streaming products for a handful of rows ----------------------------------------------
 @pytest.mark.parametrize("M", [1, 3, 8])
-@pytest.mark.parametrize("N,K", [(4608, 3584), (3584, 18944), (160, 256), (1008, 96 * 32), (152064 // 8, 3584)])
+# weight rows that give every arrangement of the dispatcher: 1, 1, 1, 1, 4, 2 and 8 row tiles per CTA
+@pytest.mark.parametrize("N,K", [(4608, 3584), (3584, 18944), (160, 256), (1008, 96 * 32), (152064 // 8, 3584), (7168, 512), (37888, 256)])
 def test_gemv_bf16(M, N, K):
     rng = np.random.RandomState(M + N + K)
     x, w, b = t(rng.randn(M, K), torch.bfloat16), t(rng.randn(N, K) * 0.05, torch.bfloat16), t(rng.randn(N), torch.bfloat16)
