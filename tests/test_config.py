@@ -121,3 +121,23 @@ def test_engine_config_rejects_unknown_keys():
         parse_engine_config({"serving": {"tokenBudgett": 5}})
     with pytest.raises(EngineConfigError, match="either 'path' or 'random'"):
         parse_engine_config({"models": [{"id": "m"}]})
+
+
+def test_any_json_object_survives_the_library_reader_unchanged():
+    """`models[].random` is an arbitrary JSON object that the C++ reader parses and hands back as text: what comes back
+    must be what went in, for strings with escapes and other alphabets, nested lists and objects, integers up to 18 digits,
+    fractions, exponents, true / false / null."""
+    hypothesis = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+    leaves = st.one_of(st.none(), st.booleans(), st.integers(min_value=-10 ** 17, max_value=10 ** 17),
+                       st.floats(allow_nan=False, allow_infinity=False, width=64), st.text(max_size=12))
+    values = st.recursive(leaves, lambda inner: st.one_of(st.lists(inner, max_size=4), st.dictionaries(st.text(max_size=6), inner, max_size=4)),
+                          max_leaves=20)
+
+    @settings(max_examples=150, deadline=None)
+    @given(st.dictionaries(st.text(min_size=1, max_size=6), values, min_size=1, max_size=4))
+    def check(obj):
+        cfg = parse_engine_config({"models": [{"id": "m", "random": obj}]})
+        assert cfg.models[0].random == obj
+
+    check()
