@@ -181,6 +181,7 @@ class Parser {
                         if (lo >= 0xDC00 && lo <= 0xDFFF) cp = 0x10000 + ((cp - 0xD800) << 10) + (lo - 0xDC00);
                         else fail("bad surrogate pair");
                     }
+                    if (cp >= 0xD800 && cp <= 0xDFFF) fail("half of a surrogate pair");      // not a character: it has no UTF-8 form
                     utf8(out, cp);
                     break;
                 }

@@ -141,3 +141,8 @@ def test_any_json_object_survives_the_library_reader_unchanged():
         assert cfg.models[0].random == obj
 
     check()
+
+
+def test_half_a_surrogate_pair_is_refused_not_passed_on():
+    with pytest.raises(EngineConfigError, match="surrogate"):
+        parse_engine_config({"models": [{"id": "m", "random": {"a": "\ud800"}}]})
