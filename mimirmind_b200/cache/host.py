@@ -52,6 +52,7 @@ _PROTOTYPES = {
     "mmh_st_shape": (I, [P, I, PL, I]),
     "mmh_st_offset": (L, [P, I, I]),
     "mmh_st_read": (I, [P, I, c_void_p, L]),
+    "mmh_st_check": (I, [P, c_char_p, I, POINTER(c_char_p), PI, PL, PI]),
     "mmh_st_write": (I, [c_char_p, I, POINTER(c_char_p), POINTER(c_char_p), PI, PL, POINTER(c_void_p), PL, I, POINTER(c_char_p)]),
     "mmh_sched_create": (P, [P, I, I, I, I]),
     "mmh_sched_destroy": (None, [P]),

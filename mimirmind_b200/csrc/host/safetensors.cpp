@@ -272,6 +272,51 @@ MMH int mmh_st_read(void* h, int i, void* dst, long long nbytes) {
     return 0;
 }
 
+// What a model needs against what the container offers: n tensors by name with their shapes (flat, one after the other)
+// and whether each may be absent.  0 when they match; else 1 with ONE message in mmh_last_error() that lists every missing
+// tensor, every unexpected one and every wrong shape (the reference finds a missing block tensor only at first use,
+// src/runtime/arch/Qwen2Backend.cpp:174-181; here the whole checkpoint is checked when it is opened).
+MMH int mmh_st_check(void* h, const char* where, int n, const char** names, const int* ndims, const long long* shapes, const int* optional) {
+    Container* c = static_cast<Container*>(h);
+    auto listed = [](const std::vector<long long>& shape) {
+        std::string out = "[";
+        for (size_t i = 0; i < shape.size(); ++i) out += (i ? ", " : "") + std::to_string(shape[i]);
+        return out + "]";
+    };
+    std::map<std::string, std::vector<long long>> want, have;
+    std::map<std::string, bool> may_miss;
+    size_t at = 0;
+    for (int i = 0; i < n; ++i) {
+        want[names[i]] = std::vector<long long>(shapes + at, shapes + at + ndims[i]);
+        may_miss[names[i]] = optional != nullptr && optional[i] != 0;
+        at += (size_t)ndims[i];
+    }
+    for (const Record& r : c->records) have[r.name] = r.shape;
+    std::vector<std::string> missing, unexpected, wrong;          // std::map walks its names in sorted order
+    for (auto& w : want) {
+        auto it = have.find(w.first);
+        if (it == have.end()) {
+            if (!may_miss[w.first]) missing.push_back("    " + w.first + "  " + listed(w.second));
+        } else if (it->second != w.second) {
+            wrong.push_back("    " + w.first + ": file has " + listed(it->second) + ", config needs " + listed(w.second));
+        }
+    }
+    for (auto& hv : have)
+        if (want.find(hv.first) == want.end()) unexpected.push_back("    " + hv.first + "  " + listed(hv.second));
+    if (missing.empty() && unexpected.empty() && wrong.empty()) return 0;
+    std::string msg = std::string(where ? where : "model") + ": the checkpoint does not match the model described by config.json";
+    auto section = [&](const char* title, const std::vector<std::string>& lines) {
+        if (lines.empty()) return;
+        msg += "\n  " + std::string(title) + " (" + std::to_string(lines.size()) + "):";
+        for (auto& l : lines) msg += "\n" + l;
+    };
+    section("missing tensors", missing);
+    section("unexpected tensors", unexpected);
+    section("wrong shapes", wrong);
+    mmh_set_error(msg);
+    return 1;
+}
+
 // Writes one file: names in the order given (the caller sorts), shapes flat one after the other, metadata as
 // alternating keys and values (may be null).  Written to a temporary name and renamed.
 MMH int mmh_st_write(const char* path, int n, const char* const* names, const char* const* dtypes, const int* ndims, const long long* shapes,

@@ -109,6 +109,20 @@ class SafetensorsFolder:
             raise SafetensorsError(host.last_error())
         return t
 
+    def mismatch(self, want: Mapping[str, Tuple[Tuple[int, ...], bool]], where: str) -> Optional[str]:
+        """``want``: name -> (shape, may be absent).  None when the folder holds exactly these tensors, else the one
+        message that lists every missing tensor, every unexpected one and every wrong shape."""
+        names = list(want)
+        n = len(names)
+        c_names = (ctypes.c_char_p * max(1, n))(*[s.encode("utf-8") for s in names])
+        ndims = (ctypes.c_int * max(1, n))(*[len(want[s][0]) for s in names])
+        flat = [int(d) for s in names for d in want[s][0]]
+        shapes = (ctypes.c_longlong * max(1, len(flat)))(*flat)
+        optional = (ctypes.c_int * max(1, n))(*[int(bool(want[s][1])) for s in names])
+        if self._lib.mmh_st_check(self._h, where.encode("utf-8"), n, c_names, ndims, shapes, optional) == 0:
+            return None
+        return host.last_error()
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             self._lib.mmh_st_close(self._h)

@@ -66,25 +66,6 @@ def layer_tensor_shapes(spec: ModelSpec):
     return out
 
 
-def check_names_and_shapes(have: Dict[str, Tuple[int, ...]], want: Dict[str, TensorSpec], where: str) -> None:
-    missing = [n for n, ts in want.items() if n not in have and not ts.optional]
-    unexpected = [n for n in have if n not in want]
-    wrong = [(n, have[n], ts.shape) for n, ts in want.items() if n in have and tuple(have[n]) != tuple(ts.shape)]
-    if not (missing or unexpected or wrong):
-        return
-    lines = [f"{where}: the checkpoint does not match the model described by config.json"]
-    if missing:
-        lines.append(f"  missing tensors ({len(missing)}):")
-        lines += [f"    {n}  {list(want[n].shape)}" for n in sorted(missing)]
-    if unexpected:
-        lines.append(f"  unexpected tensors ({len(unexpected)}):")
-        lines += [f"    {n}  {list(have[n])}" for n in sorted(unexpected)]
-    if wrong:
-        lines.append(f"  wrong shapes ({len(wrong)}):")
-        lines += [f"    {n}: file has {list(h)}, config needs {list(w)}" for n, h, w in sorted(wrong)]
-    raise WeightsError("\n".join(lines))
-
-
 def _storage_dtype(t: torch.Tensor, run_dtype: torch.dtype) -> torch.dtype:
     if not t.dtype.is_floating_point:
         return torch.int32
@@ -111,8 +92,10 @@ def load_tensors(model_dir: str, spec: ModelSpec, run_dtype: torch.dtype, device
     """All tensors of the folder, validated against the spec, converted and moved to ``device``."""
     want = expected_tensors(spec)
     with SafetensorsFolder(model_dir) as folder:
-        have = {n: folder.shape(n) for n in folder.names()}
-        check_names_and_shapes(have, want, model_dir)
+        # the comparison and its one message are the container library's (csrc/host/safetensors.cpp)
+        message = folder.mismatch({n: (tuple(ts.shape), ts.optional) for n, ts in want.items()}, model_dir)
+        if message is not None:
+            raise WeightsError(message)
         out: Dict[str, torch.Tensor] = {}
         for name in folder.names():
             t = folder.tensor(name)
