@@ -183,6 +183,8 @@ def main() -> int:
                          "32B-shaped, 8 requests of 8,192 prompt tokens, 128 new tokens each)")
     ap.add_argument("--mixed-portion", type=int, default=192, help="tokens of the prompt portion in the mixed step")
     ap.add_argument("--shape", default="7b", choices=sorted(SHAPES), help="with --only: another size of the architecture (random weights)")
+    ap.add_argument("--pdl", type=int, default=-1, help="for measurements: dependent launches of the weight-streaming kernels on (1) or off (0)")
+    ap.add_argument("--gemv-blocks", type=int, default=-1, help="for measurements: the build of the weight-streaming kernel, for 2 or 3 resident blocks per SM (0: by the grid)")
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="with --only decode or prefill: prompts of this many tokens instead of 2,048 (the context grows with them)")
     ap.add_argument("--opt", action="append", default=[], metavar="NAME=VALUE",
@@ -240,6 +242,10 @@ def main() -> int:
     mcfg = arch.parse_config(cfg_json, "bench")
     spec = arch.build_spec(mcfg)
     kernel_lib.load(verbose=True)
+    if args.pdl >= 0:
+        kernel_lib.load().mm_set_pdl(args.pdl)
+    if args.gemv_blocks >= 0:
+        kernel_lib.load().mm_set_gemv_blocks(args.gemv_blocks)
     for item in args.opt:
         from mimirmind_b200.engine import native as native_exec
         name, _, value = item.partition("=")

@@ -90,9 +90,7 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 
 // ---- launching ------------------------------------------------------------------------------------------------------
-// A plain stream-ordered launch with the kernel's parameter types enforced.  (Programmatic dependent launch was built
-// into these kernels twice and measured slower both times on B200: the blocks of the dependent kernel land where the
-// predecessor's blocks happen to leave first, and a weight-streaming kernel ends with its fullest SM.)
+// A plain stream-ordered launch with the kernel's parameter types enforced.
 template <typename... KArgs, typename... Args>
 static inline void mm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -100,5 +98,41 @@ static inline void mm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// ---- programmatic dependent launch --------------------------------------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may have its blocks scheduled while the kernel before
+// it in the stream still runs: they do what does not depend on it (a weight-streaming kernel issues its first weight
+// loads), then block in pdl_wait() until that kernel has completed and its writes are visible.  Such a kernel calls
+// pdl_wait() before its first read of activations and before any write, and pdl_trigger() once its own weights are
+// through, so never more than one kernel is ahead (triggering before the wait let a whole chain of future kernels pile
+// up on the SMs and measured 2.5 times slower).  Without the attribute both calls do nothing.
+// What decides whether this pays (B200, 7B shapes, batch 8): where the early blocks land.  With room for a third block
+// per SM they go wherever the running kernel's blocks leave first (the gate/up product's 296 blocks: three on five SMs and
+// one on five others instead of two everywhere), the kernel ends with its fullest SM, and the step is slower (3.35
+// against 3.17 ms).  Compiled for two blocks per SM (108 registers a thread, so a third block never fits) a block of the
+// next kernel can only take the place of one that left, every SM ends up with its two again, and the step is faster
+// (2.98 against 3.05 ms).  Reserving shared memory to the same end does not work: kernels whose shared-memory
+// carve-out differs from their neighbours' do not share an SM at all, and the change of carve-out costs more than the
+// boundary.  One thread waits, the others stand at the CTA barrier: waiting blocks share their SMs with the running kernel.
+__device__ __forceinline__ void pdl_wait() {
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.wait;" ::: "memory");
+    __syncthreads();
+}
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline void mm_launch_dependent(bool dependent, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependent ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }

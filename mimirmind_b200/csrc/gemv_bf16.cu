@@ -275,6 +275,8 @@ __device__ __forceinline__ void gemv_item(const GemvArgs& a, int item, const Gem
     } else {
         stage();
     }
+    // the weights are through: the next kernel's blocks may move in beside this one's epilogue and request theirs
+    pdl_trigger();
     asm volatile("cp.async.wait_all;\n" ::: "memory");
     // sum the K splits of each row tile in a fixed order
     const bool need_sync = a.KS > 1 || a.in_ss != nullptr || kStaged;
@@ -396,14 +398,26 @@ __device__ __forceinline__ void gemv_item(const GemvArgs& a, int item, const Gem
 }
 
 
-template <int NT, int U, int EPI>
-__global__ void __launch_bounds__(GEMV_THREADS, 3) gemv_bf16_kernel(const GemvArgs a) {
+template <int NT, int U, int EPI, int MINB>
+__global__ void __launch_bounds__(GEMV_THREADS, MINB) gemv_bf16_kernel(const GemvArgs a) {
     __shared__ GemvSmem sm;
     extern __shared__ __align__(16) float ss_s[];
-    // The first weight loads go out before anything else of the item is set up.
+    // The weights do not depend on the previous kernel: their first loads go out before this kernel waits for
+    // it, so the stream from HBM is already running when the activations become readable.
     GemvFirst<U> first;
     gemv_first_weights<U>(a, blockIdx.x, first);
+    pdl_wait();
     gemv_item<NT, U, EPI>(a, blockIdx.x, first, sm, ss_s);
+}
+
+extern int g_mm_pdl;            // host.cu: 1 = dependent launches where they pay
+static int g_gemv_blocks = 0;   // 0: by the grid's size; 2 or 3: that build always (for measurements)
+static long long g_gemv_last_count = -1;        // the library's launch count right after the last launch of the two-block build
+static cudaStream_t g_gemv_last_stream = nullptr;
+MM_EXPORT int mm_set_gemv_blocks(int n) {
+    const int old = g_gemv_blocks;
+    if (n == 0 || n == 2 || n == 3) g_gemv_blocks = n;
+    return old;
 }
 
 static size_t gemv_dynamic_smem(const GemvArgs& a) {
@@ -415,9 +429,33 @@ static int launch_gemv_now(const GemvArgs& a, cudaStream_t s) {
     const int tiles = a.N / 16;
     const int blocks = (tiles + a.RT - 1) / a.RT;
     const size_t smem = gemv_dynamic_smem(a);
-    if (a.M <= 8) mm_launch(gemv_bf16_kernel<1, 4, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
-    else mm_launch(gemv_bf16_kernel<2, 2, EPI>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
+    // Two builds of the kernel: for two resident blocks per SM (108 registers, nothing spilled, and a third block never
+    // fits, which is what lets a dependent launch land its blocks evenly) and for three (80 registers).  A grid of at most
+    // two blocks per SM takes the first, and with it the dependent launch; larger grids need the third slot.
+    int sms = 148;
+    {
+        static int cached = 0;
+        if (cached == 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+        }
+        sms = cached;
+    }
+    const bool two = g_gemv_blocks == 2 || (g_gemv_blocks == 0 && blocks <= 2 * sms);
+    if (two) {
+        // dependent only behind another launch of this build: its blocks then find every SM with exactly two places, one
+        // of which the kernel before it gives up as it ends (behind attention or a norm the early blocks land unevenly)
+        const bool dependent = g_mm_pdl != 0 && g_gemv_last_count == g_mm_launch_count && g_gemv_last_stream == s;
+        if (a.M <= 8) mm_launch_dependent(dependent, gemv_bf16_kernel<1, 4, EPI, 2>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
+        else mm_launch_dependent(dependent, gemv_bf16_kernel<2, 2, EPI, 2>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
+    } else {
+        if (a.M <= 8) mm_launch(gemv_bf16_kernel<1, 4, EPI, 3>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
+        else mm_launch(gemv_bf16_kernel<2, 2, EPI, 3>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
+    }
     MM_CHECK_LAUNCH();
+    g_gemv_last_count = two ? g_mm_launch_count : -1;
+    g_gemv_last_stream = s;
     return MM_OK;
 }
 

@@ -10,6 +10,11 @@ void mm_set_last_error(const char* msg) {
 
 extern "C" __attribute__((visibility("default"))) const char* mm_last_error() { return g_last_error; }
 
+// Dependent launches of the weight-streaming kernels that are built for two blocks per SM (common.cuh says when they pay).
+int g_mm_pdl = 1;
+extern "C" __attribute__((visibility("default"))) void mm_set_pdl(int on) { g_mm_pdl = on ? 1 : 0; }
+extern "C" __attribute__((visibility("default"))) int mm_get_pdl() { return g_mm_pdl; }
+
 // Every kernel launch of this library counts itself here (MM_CHECK_LAUNCH).
 long long g_mm_launch_count = 0;
 extern "C" __attribute__((visibility("default"))) long long mm_launch_count() { return g_mm_launch_count; }

@@ -65,6 +65,12 @@ def load(verbose: bool = True) -> ctypes.CDLL:
         lib = ctypes.CDLL(path)
         lib.mm_last_error.restype = ctypes.c_char_p
         lib.mm_last_error.argtypes = []
+        lib.mm_set_pdl.argtypes = [c_int]
+        lib.mm_set_pdl.restype = None
+        lib.mm_get_pdl.argtypes = []
+        lib.mm_get_pdl.restype = c_int
+        lib.mm_set_gemv_blocks.argtypes = [c_int]
+        lib.mm_set_gemv_blocks.restype = c_int
         lib.mm_launch_count.argtypes = []
         lib.mm_launch_count.restype = c_longlong
         lib.mm_uniform_from.restype = c_float

@@ -764,3 +764,70 @@ def test_gemm_tcgen05_refuses_unaligned_shapes():
         ops().gemm_tcgen05(z(4, 60), z(64, 60), None, torch.bfloat16)
     with pytest.raises(KernelError, match="SwiGLU"):
         ops().gemm_tcgen05(z(4, 64), z(24, 64), None, torch.bfloat16, swiglu=True)
+
+
+def test_gemv_builds_and_dependent_launches_give_the_same_bits():
+    """The weight-streaming kernel exists for two and for three resident blocks per SM, and launches of the first build
+    that follow each other are dependent launches: a kernel's blocks start while the one before it still runs, request
+    their first weights and wait for it to finish before they read what it wrote.  A layer's four products, each reading
+    the one before it, forty times over with nothing in between: the same bits from both builds, with and without
+    dependent launches, eager and as a replayed graph."""
+    from mimirmind_b200.kernels import lib
+    L = lib.load()
+    rng = np.random.RandomState(17)
+    M, d, F, H, G, hd, ps = 8, 1024, 2816, 8, 2, 64, 16
+    x = t(rng.randn(M, H * hd), torch.bfloat16)
+    wo, wd = t(rng.randn(d, H * hd) * 0.05, torch.bfloat16), t(rng.randn(d, F) * 0.03, torch.bfloat16)
+    wg, wu = t(rng.randn(F, d) * 0.05, torch.bfloat16), t(rng.randn(F, d) * 0.05, torch.bfloat16)
+    wgu = torch.stack([wg.view(F // 8, 8, d), wu.view(F // 8, 8, d)], dim=1).reshape(2 * F, d).contiguous()
+    wqkv = ops().interleave_halves(t(rng.randn((H + 2 * G) * hd, d) * 0.1, torch.bfloat16), H + G, hd)
+    bqkv = ops().interleave_halves(t(rng.randn((H + 2 * G) * hd) * 0.5, torch.bfloat16), H + G, hd)
+    nw = t(1.0 + 0.3 * rng.randn(d), torch.bfloat16)
+    res0 = t(rng.randn(M, d) * 3)
+    pos = t(np.arange(M) + 5, torch.int32)
+    table = ops().rope_table(pos, hd, 1e4)
+    slots = ops().slot_mapping(pos, t(np.arange(M), torch.int32), t(np.arange(M * 2).reshape(M, 2), torch.int32), ps)
+
+    def layer(res, kp, vp, q):
+        for _ in range(10):                                         # ten layers' worth of the same weights: every product reads the last
+            xw1, rs1 = ops().gemv_bf16_residual(x, wo, res, nw, 1e-6)
+            act = ops().gemv_bf16(xw1, wgu, None, torch.bfloat16, swiglu=True, scale=rs1)
+            xw2, rs2 = ops().gemv_bf16_residual(act, wd, res, nw, 1e-6)
+            ops().gemv_bf16_qkv_rope(xw2, wqkv, bqkv, q, kp, vp, table, slots, ps, H, G, hd, scale=rs2)
+        return xw2
+
+    def run(blocks, dependent, graph):
+        old_b, old_p = L.mm_set_gemv_blocks(blocks), L.mm_get_pdl()
+        L.mm_set_pdl(dependent)
+        try:
+            res = res0.clone()
+            kp = torch.zeros((M * 2, G, ps, hd), dtype=torch.bfloat16, device=DEV)
+            vp, q = torch.zeros_like(kp), torch.zeros((M, H * hd), dtype=torch.bfloat16, device=DEV)
+            if not graph:
+                for _ in range(4):
+                    xw2 = layer(res, kp, vp, q)
+            else:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    layer(res, kp, vp, q)                           # warm-up outside the capture
+                    g = torch.cuda.CUDAGraph()
+                    res.copy_(res0)
+                    with torch.cuda.graph(g, stream=side):
+                        xw2 = layer(res, kp, vp, q)
+                torch.cuda.current_stream().wait_stream(side)
+                res.copy_(res0)
+                for _ in range(4):
+                    g.replay()
+            torch.cuda.synchronize()
+            return res.clone(), q.clone(), kp.clone(), vp.clone(), xw2.clone()
+        finally:
+            L.mm_set_gemv_blocks(old_b)
+            L.mm_set_pdl(old_p)
+
+    want = run(3, 0, False)
+    assert torch.isfinite(want[0]).all()
+    for blocks, dependent, graph in ((2, 0, False), (2, 1, False), (0, 1, False), (2, 1, True), (0, 1, True), (3, 0, True)):
+        got = run(blocks, dependent, graph)
+        for a_, b_ in zip(got, want):
+            assert torch.equal(a_, b_), (blocks, dependent, graph)
