@@ -29,6 +29,8 @@
 // the library route above that (src/compute/cuda/GpuMatmul.cpp:786-884).
 #include "tcgen05.cuh"
 
+extern int g_mm_pdl;            // host.cu: 1 = dependent launches where they pay
+
 #include <map>
 #include <utility>
 
@@ -72,6 +74,9 @@ struct SkinnyArgs {
 };
 
 constexpr int SK_MAX_STAGES = 12;
+
+long long g_sk_last_count = -1;            // the library's launch count right after the last launch from this file
+cudaStream_t g_sk_last_stream = nullptr;
 
 struct SkinnyCtl {
     uint64_t full[SK_MAX_STAGES];
@@ -151,10 +156,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             for (int i = 0; i < n_kb && i < STAGES; ++i) {
                 const uint32_t full = smem_u32(&ctl->full[i]);
                 mbar_expect_tx(full, STAGE_BYTES);
-                const uint32_t dst = smem_u32(ring + i * STAGE_BYTES);
-                tma_load_2d(dst, &tmW, (kb_begin + i) * SK_BK, n_tile0, full);
-                tma_load_2d(dst + SK_A_BYTES, &tmX, (kb_begin + i) * SK_BK, 0, full);
+                tma_load_2d(smem_u32(ring + i * STAGE_BYTES), &tmW, (kb_begin + i) * SK_BK, n_tile0, full);
             }
+        }
+        // Launched dependently, this kernel may have started before the one ahead of it has finished: the weights above do
+        // not depend on that kernel, the batch does.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (good) {
+            for (int i = 0; i < n_kb && i < STAGES; ++i)
+                tma_load_2d(smem_u32(ring + i * STAGE_BYTES) + SK_A_BYTES, &tmX, (kb_begin + i) * SK_BK, 0, smem_u32(&ctl->full[i]));
         }
     }
     if (warp == 1) {
@@ -165,6 +175,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctl->tmem_base;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0 && good) {
@@ -180,6 +191,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                 tma_load_2d(dst + SK_A_BYTES, &tmX, (kb_begin + i) * SK_BK, 0, full);
             }
         }
+        // this CTA's weights have been asked for: a dependent kernel's blocks may move in and ask for theirs
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     } else if (warp == 1) {
         if (lane == 0 && good) {
             // ---- MMA issuer ----
@@ -439,15 +452,29 @@ int sk_launch(const CUtensorMap& tw, const CUtensorMap& tx, SkinnyArgs& a, cudaS
     cfg.blockDim = dim3(SK_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = a.S;          // the K splits of a tile are one cluster
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (a.S > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = a.S;          // the K splits of a tile are one cluster
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
+    // Directly behind another product of this file (a layer's products follow each other) the launch is a dependent one:
+    // the blocks start as that kernel's blocks leave (shared memory lets no third block onto an SM), ask for their first
+    // weights and wait for it to finish before they touch the batch.
+    if (g_mm_pdl != 0 && g_sk_last_count == g_mm_launch_count && g_sk_last_stream == s) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = a.S > 1 ? 1 : 0;
+    cfg.numAttrs = n_attr;
     cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<MP, EPI>, tw, tx, a);
     MM_CHECK_LAUNCH();
+    g_sk_last_count = g_mm_launch_count;
+    g_sk_last_stream = s;
     return MM_OK;
 }
 

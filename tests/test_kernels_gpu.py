@@ -766,16 +766,18 @@ def test_gemm_tcgen05_refuses_unaligned_shapes():
         ops().gemm_tcgen05(z(4, 64), z(24, 64), None, torch.bfloat16, swiglu=True)
 
 
-def test_gemv_builds_and_dependent_launches_give_the_same_bits():
+@pytest.mark.parametrize("M", [8, 24])
+def test_gemv_builds_and_dependent_launches_give_the_same_bits(M):
     """The weight-streaming kernel exists for two and for three resident blocks per SM, and launches of the first build
     that follow each other are dependent launches: a kernel's blocks start while the one before it still runs, request
     their first weights and wait for it to finish before they read what it wrote.  A layer's four products, each reading
     the one before it, forty times over with nothing in between: the same bits from both builds, with and without
-    dependent launches, eager and as a replayed graph."""
+    dependent launches, eager and as a replayed graph.  The tcgen05 product of 9..64 rows launches dependently behind
+    another of its kind in the same way (its residency is capped by shared memory)."""
     from mimirmind_b200.kernels import lib
     L = lib.load()
     rng = np.random.RandomState(17)
-    M, d, F, H, G, hd, ps = 8, 1024, 2816, 8, 2, 64, 16
+    d, F, H, G, hd, ps = 1024, 2816, 8, 2, 64, 16        # 8 rows: the register-streaming kernel; 24 rows: the tcgen05 one
     x = t(rng.randn(M, H * hd), torch.bfloat16)
     wo, wd = t(rng.randn(d, H * hd) * 0.05, torch.bfloat16), t(rng.randn(d, F) * 0.03, torch.bfloat16)
     wg, wu = t(rng.randn(F, d) * 0.05, torch.bfloat16), t(rng.randn(F, d) * 0.05, torch.bfloat16)
