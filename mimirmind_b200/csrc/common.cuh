@@ -35,6 +35,9 @@
     } while (0)
 
 extern long long g_mm_launch_count;   // kernels of this library launched (or captured) so far
+extern int g_mm_pdl;                  // host.cu: dependent launches where they pay (0 off, 1 on)
+extern long long g_mm_dep_count;      // the launch count right after the last launch that a dependent launch may follow
+extern void* g_mm_dep_stream;
 
 #define MM_REQUIRE(cond, msg)          \
     do {                               \

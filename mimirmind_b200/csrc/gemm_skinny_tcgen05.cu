@@ -29,7 +29,6 @@
 // the library route above that (src/compute/cuda/GpuMatmul.cpp:786-884).
 #include "tcgen05.cuh"
 
-extern int g_mm_pdl;            // host.cu: 1 = dependent launches where they pay
 
 #include <map>
 #include <utility>

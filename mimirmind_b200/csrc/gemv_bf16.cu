@@ -410,10 +410,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, MINB) gemv_bf16_kernel(const Gem
     gemv_item<NT, U, EPI>(a, blockIdx.x, first, sm, ss_s);
 }
 
-extern int g_mm_pdl;            // host.cu: 1 = dependent launches where they pay
 static int g_gemv_blocks = 0;   // 0: by the grid's size; 2 or 3: that build always (for measurements)
-static long long g_gemv_last_count = -1;        // the library's launch count right after the last launch of the two-block build
-static cudaStream_t g_gemv_last_stream = nullptr;
 MM_EXPORT int mm_set_gemv_blocks(int n) {
     const int old = g_gemv_blocks;
     if (n == 0 || n == 2 || n == 3) g_gemv_blocks = n;
@@ -446,7 +443,7 @@ static int launch_gemv_now(const GemvArgs& a, cudaStream_t s) {
     if (two) {
         // dependent only behind another launch of this build: its blocks then find every SM with exactly two places, one
         // of which the kernel before it gives up as it ends (behind attention or a norm the early blocks land unevenly)
-        const bool dependent = g_mm_pdl != 0 && g_gemv_last_count == g_mm_launch_count && g_gemv_last_stream == s;
+        const bool dependent = g_mm_pdl != 0 && g_mm_dep_count == g_mm_launch_count && g_mm_dep_stream == (void*)s;
         if (a.M <= 8) mm_launch_dependent(dependent, gemv_bf16_kernel<1, 4, EPI, 2>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
         else mm_launch_dependent(dependent, gemv_bf16_kernel<2, 2, EPI, 2>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
     } else {
@@ -454,8 +451,8 @@ static int launch_gemv_now(const GemvArgs& a, cudaStream_t s) {
         else mm_launch(gemv_bf16_kernel<2, 2, EPI, 3>, dim3(blocks), dim3(GEMV_THREADS), smem, s, a);
     }
     MM_CHECK_LAUNCH();
-    g_gemv_last_count = two ? g_mm_launch_count : -1;
-    g_gemv_last_stream = s;
+    g_mm_dep_count = two ? g_mm_launch_count : -1;
+    g_mm_dep_stream = (void*)s;
     return MM_OK;
 }
 

@@ -12,6 +12,8 @@ extern "C" __attribute__((visibility("default"))) const char* mm_last_error() { 
 
 // Dependent launches of the weight-streaming kernels that are built for two blocks per SM (common.cuh says when they pay).
 int g_mm_pdl = 1;
+long long g_mm_dep_count = -1;     // the launch count right after the last launch that a dependent launch may follow
+void* g_mm_dep_stream = nullptr;
 extern "C" __attribute__((visibility("default"))) void mm_set_pdl(int on) { g_mm_pdl = on ? 1 : 0; }
 extern "C" __attribute__((visibility("default"))) int mm_get_pdl() { return g_mm_pdl; }
 
