@@ -24,6 +24,9 @@
 //   ROPE    q/k/v projection: bias, rotary position encoding of q and k (split-half pairs; the
 //           weight rows of each q and k head interleave the two halves in blocks of 8, so a thread
 //           holds a pair), q written as [M, H * hd], k and v written into their cache pages.
+// Two builds (MINB = resident blocks per SM the compiler is asked for): 3 with 80 registers a thread, 2 with more and
+// nothing spilled; the launch code takes the second when the grid has at most two blocks per SM.  Launched directly behind
+// another launch of this kernel, a launch is a dependent one (common.cuh): the first weight loads go out before the wait.
 // Input row scale: with `in_ss` the accumulators of row m are multiplied by
 // 1 / sqrt(sum_j in_ss[j][m] / in_dim + eps) before the epilogue (the deferred 1/rms of RESID).
 //
