@@ -1,4 +1,5 @@
 // Host-side state of the kernel library: the last error message.
+#include <stdlib.h>
 #include <string.h>
 
 static thread_local char g_last_error[512] = "";
@@ -10,8 +11,13 @@ void mm_set_last_error(const char* msg) {
 
 extern "C" __attribute__((visibility("default"))) const char* mm_last_error() { return g_last_error; }
 
-// Dependent launches of the weight-streaming kernels that are built for two blocks per SM (common.cuh says when they pay).
-int g_mm_pdl = 1;
+// Dependent launches of the weight-streaming kernels (common.cuh says when they pay).  On unless the environment says
+// MIMIRMIND_B200_DEPENDENT_LAUNCH=0 (or mm_set_pdl(0) is called): a way out on a driver where they misbehave.
+static int dependent_launch_default() {
+    const char* v = getenv("MIMIRMIND_B200_DEPENDENT_LAUNCH");
+    return (v != nullptr && v[0] == '0') ? 0 : 1;
+}
+int g_mm_pdl = dependent_launch_default();
 long long g_mm_dep_count = -1;     // the launch count right after the last launch that a dependent launch may follow
 void* g_mm_dep_stream = nullptr;
 extern "C" __attribute__((visibility("default"))) void mm_set_pdl(int on) { g_mm_pdl = on ? 1 : 0; }
