@@ -114,7 +114,7 @@ static inline void mm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 // What decides whether this pays (B200, 7B shapes, batch 8): where the early blocks land.  With room for a third block
 // per SM they go wherever the running kernel's blocks leave first (the gate/up product's 296 blocks: three on five SMs and
 // one on five others instead of two everywhere), the kernel ends with its fullest SM, and the step is slower (3.35
-// against 3.17 ms).  Compiled for two blocks per SM (108 registers a thread, so a third block never fits) a block of the
+// against 3.17 ms).  Compiled for two blocks per SM (128 registers a thread, so a third block never fits) a block of the
 // next kernel can only take the place of one that left, every SM ends up with its two again, and the step is faster
 // (2.98 against 3.05 ms).  Reserving shared memory to the same end does not work: kernels whose shared-memory
 // carve-out differs from their neighbours' do not share an SM at all, and the change of carve-out costs more than the
